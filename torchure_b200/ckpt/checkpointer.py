@@ -1,0 +1,101 @@
+"""Step-directory checkpoints with a completion marker.
+
+Layout (reference ``torchure/checkpoint/checkpointer.py:18-102`` and ``trainer.py:298-327``)::
+
+    <root>/<completed_steps>/model.pt            model.state_dict() (fp32 master weights)
+                             optimizer.pt        AdamW state_dict
+                             scheduler.pt        LR scheduler state_dict
+                             trainer.pt          {"step", "cpu_rng", "cuda_rng", "config", "wandb_id"}
+                             dataloader_dp{r}.pt loader position of dp coordinate r
+                             .complete           written last; a step without it does not exist
+
+Files are written to a temporary name and renamed, so a crash leaves either the old file
+or the new one.  ``latest()`` / ``valid_step()`` only see completed steps.  Sharded
+strategies store per-shard files (``model_shard{r}.pt``, ``optimizer_shard{r}.pt``) in the
+same directory.
+"""
+
+from __future__ import annotations
+
+import os
+from pathlib import Path
+
+import torch
+
+MARKER = ".complete"
+
+
+class Checkpointer:
+    def __init__(self, root: str):
+        self.root = Path(root)
+        self.root.mkdir(parents=True, exist_ok=True)
+
+    # -- discovery -------------------------------------------------------------------------
+    def _steps(self) -> list[int]:
+        found = []
+        for child in self.root.iterdir():
+            if child.name.isdigit() and (child / MARKER).exists():
+                found.append(int(child.name))
+        return found
+
+    def latest(self) -> int | None:
+        steps = self._steps()
+        return max(steps) if steps else None
+
+    def valid_step(self, step: int) -> int | None:
+        return step if step in self._steps() else None
+
+    def step_dir(self, step: int, create: bool = False) -> Path:
+        d = self.root / str(step)
+        if create:
+            d.mkdir(parents=True, exist_ok=True)
+        return d
+
+    def mark_complete(self, step: int) -> None:
+        (self.step_dir(step, create=True) / MARKER).touch()
+
+    def is_complete(self, step: int) -> bool:
+        return (self.step_dir(step) / MARKER).exists()
+
+    # -- raw io ----------------------------------------------------------------------------
+    def _write(self, payload, step: int, name: str) -> None:
+        final = self.step_dir(step, create=True) / name
+        tmp = final.with_name(final.name + ".tmp")
+        torch.save(payload, tmp)
+        os.replace(tmp, final)
+
+    def _read(self, step: int, name: str, weights_only: bool = True):
+        return torch.load(self.step_dir(step) / name, map_location="cpu", weights_only=weights_only)
+
+    # -- components ------------------------------------------------------------------------
+    def save_model(self, model, step: int, shard: int | None = None) -> None:
+        self._write(model.state_dict(), step, "model.pt" if shard is None else f"model_shard{shard}.pt")
+
+    def load_model(self, model, step: int, shard: int | None = None) -> None:
+        model.load_state_dict(self._read(step, "model.pt" if shard is None else f"model_shard{shard}.pt"))
+
+    def save_optimizer(self, optimizer, step: int, shard: int | None = None) -> None:
+        self._write(optimizer.state_dict(), step, "optimizer.pt" if shard is None else f"optimizer_shard{shard}.pt")
+
+    def load_optimizer(self, optimizer, step: int, shard: int | None = None) -> None:
+        optimizer.load_state_dict(
+            self._read(step, "optimizer.pt" if shard is None else f"optimizer_shard{shard}.pt"))
+
+    def save_scheduler(self, scheduler, step: int) -> None:
+        self._write(scheduler.state_dict(), step, "scheduler.pt")
+
+    def load_scheduler(self, scheduler, step: int) -> None:
+        scheduler.load_state_dict(self._read(step, "scheduler.pt"))
+
+    def save_dataloader(self, dataloader, step: int, dp_rank: int = 0) -> None:
+        """`dataloader` is anything with ``state_dict()`` (a loader or the prefetcher that wraps it)."""
+        self._write(dataloader.state_dict(), step, f"dataloader_dp{dp_rank}.pt")
+
+    def load_dataloader(self, dataloader, step: int, dp_rank: int = 0) -> None:
+        dataloader.load_state_dict(self._read(step, f"dataloader_dp{dp_rank}.pt", weights_only=False))
+
+    def save_trainer(self, state: dict, step: int) -> None:
+        self._write(state, step, "trainer.pt")
+
+    def load_trainer(self, step: int) -> dict:
+        return self._read(step, "trainer.pt")

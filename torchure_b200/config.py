@@ -1,0 +1,74 @@
+"""JSON run configuration: loading, defaults and validation.
+
+Schema (superset of the reference's seven ``configs/*.json``; reference readers:
+``torchure/train/trainer.py:73-133``)::
+
+    model         {name, config{num_layers, num_heads, num_kv_heads, emb_dim, head_dim, vocab_size,
+                   [ffn_dim], [norm_eps], [rope_theta], [impl]}}
+    mesh          {axis: size, ...}   product == WORLD_SIZE, must contain "dp"
+    optimizer     {name, config{lr, weight_decay, betas, fused}, [max_norm],
+                   scheduler{type, warmup_ratio, decay_ratio, total_steps}}
+    objective     {name, config{ignore_index, fused_linear_ce, ce_chunk_size}}
+    data          {name | synthetic, tokenizer, eos_token, pad_token, text_field, shuffle_buffer, seed,
+                   num_workers, global_batch_size, micro_batch_size, seq_len, [pack_batch], [packer],
+                   synthetic extras: vocab_size, eos_id, mean_doc_len}
+    [ddp]         {bucket_mb, [fused], [merge_small]}
+    [comm]        {backend: "sm100" | "torch", [max_bytes]}
+    checkpointing {save_steps, resume: null|"auto"|int, [resume_scheduler]}
+    run_name      str
+    [wandb]       {enabled, project, entity}
+    [compile]     bool   per-block fused execution (hand-written kernels) on/off
+    [log_every]   int
+"""
+
+from __future__ import annotations
+
+import json
+import math
+
+REQUIRED = ("model", "mesh", "optimizer", "objective", "data", "checkpointing", "run_name")
+
+
+class ConfigError(ValueError):
+    pass
+
+
+def load_config(path: str) -> dict:
+    with open(path) as f:
+        cfg = json.load(f)
+    return validate_config(cfg)
+
+
+def validate_config(cfg: dict, world_size: int | None = None) -> dict:
+    for key in REQUIRED:
+        if key not in cfg:
+            raise ConfigError(f"config is missing the {key!r} section")
+    mesh = cfg["mesh"]
+    if "dp" not in mesh:
+        raise ConfigError('mesh must define a "dp" axis')
+    if world_size is not None and math.prod(mesh.values()) != world_size:
+        raise ConfigError(f"mesh {mesh} does not cover world size {world_size}")
+    opt = cfg["optimizer"]
+    for key in ("name", "config", "scheduler"):
+        if key not in opt:
+            raise ConfigError(f"optimizer.{key} is required")
+    sched = opt["scheduler"]
+    for key in ("type", "total_steps"):
+        if key not in sched:
+            raise ConfigError(f"optimizer.scheduler.{key} is required")
+    data = cfg["data"]
+    for key in ("global_batch_size", "micro_batch_size", "seq_len"):
+        if key not in data:
+            raise ConfigError(f"data.{key} is required")
+    dp = mesh["dp"]
+    per_backward = data["micro_batch_size"] * dp
+    if data["global_batch_size"] % per_backward != 0:
+        raise ConfigError(
+            f"global_batch_size {data['global_batch_size']} must be divisible by micro_batch_size "
+            f"{data['micro_batch_size']} x dp {dp} = {per_backward}")
+    ck = cfg["checkpointing"]
+    if "save_steps" not in ck or "resume" not in ck:
+        raise ConfigError("checkpointing needs save_steps and resume")
+    if not (ck["resume"] is None or ck["resume"] == "auto" or isinstance(ck["resume"], int)):
+        raise ConfigError('checkpointing.resume must be null, "auto" or a step number')
+    return cfg

@@ -1,0 +1,80 @@
+"""Chunked fused linear + cross-entropy: never holds the (N, V) logits of the whole batch.
+
+Semantics are ``F.cross_entropy(hidden @ weight.T, labels, ignore_index, reduction="mean")``
+with the divisor clamped to at least 1 (reference ``torchure/loss/fused_linear_ce.py:63-136``).
+Gradients w.r.t. ``hidden`` and ``weight`` are produced during the forward pass, one row
+chunk at a time, and only rescaled by ``grad_out / n_valid`` in backward, so a chunk's
+logits die before the next chunk starts.
+
+On CUDA with the sm_100a extension the three GEMMs per chunk are tcgen05 kernels and the
+softmax / target-gather / loss / dlogits step is one fused kernel that rewrites the bf16
+logits in place with the bf16 gradient (``torchure_b200/ops/linear_ce.py``).  The code
+below is the plain PyTorch statement of the same algorithm (CPU path and test oracle).
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def _chunk_torch(h: torch.Tensor, w: torch.Tensor, y: torch.Tensor, ignore_index: int):
+    logits = (h @ w.t()).float()
+    keep = y != ignore_index
+    tgt = torch.where(keep, y, torch.zeros_like(y))
+    lse = torch.logsumexp(logits, dim=-1)
+    picked = logits.gather(1, tgt[:, None]).squeeze(1)
+    loss_sum = torch.where(keep, lse - picked, torch.zeros_like(lse)).sum()
+    dlogits = torch.exp(logits - lse[:, None])
+    dlogits[torch.arange(h.shape[0], device=h.device), tgt] -= 1.0
+    dlogits = (dlogits * keep[:, None]).to(h.dtype)
+    return loss_sum, dlogits @ w, dlogits.t() @ h
+
+
+class _LinearCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, chunk_size):
+        n = hidden.shape[0]
+        w = weight.to(hidden.dtype)
+        loss_sum = torch.zeros((), dtype=torch.float32, device=hidden.device)
+        d_hidden = torch.empty_like(hidden)
+        d_weight = torch.zeros_like(weight, dtype=torch.float32) if weight.requires_grad else None
+        for lo in range(0, n, chunk_size):
+            hi = min(n, lo + chunk_size)
+            ls, dh, dw = _chunk_torch(hidden[lo:hi], w, labels[lo:hi], ignore_index)
+            loss_sum += ls
+            d_hidden[lo:hi] = dh
+            if d_weight is not None:
+                d_weight += dw
+        n_valid = (labels != ignore_index).sum().clamp_min(1)
+        ctx.stash = (d_hidden, d_weight, n_valid)
+        ctx.weight_dtype = weight.dtype
+        return loss_sum / n_valid
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        if ctx.stash is None:
+            raise RuntimeError("fused_linear_cross_entropy: backward ran twice; its grads are consumed in place")
+        d_hidden, d_weight, n_valid = ctx.stash
+        ctx.stash = None
+        scale = grad_out / n_valid
+        d_hidden.mul_(scale.to(d_hidden.dtype))
+        if d_weight is not None:
+            d_weight.mul_(scale)
+            d_weight = d_weight.to(ctx.weight_dtype)
+        return d_hidden, d_weight, None, None, None
+
+
+def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                               ignore_index: int = -100, chunk_size: int = 1024) -> torch.Tensor:
+    """hidden (B,S,D) or (N,D); weight (V,D); labels already shifted, (B,S) or (N,)."""
+    if hidden.dim() == 3:
+        hidden = hidden.reshape(-1, hidden.shape[-1])
+        labels = labels.reshape(-1)
+    if hidden.is_cuda:
+        from torchure_b200 import ops
+
+        if ops.available():
+            from torchure_b200.ops.linear_ce import linear_ce_sm100
+
+            return linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size)
+    return _LinearCE.apply(hidden, weight, labels, ignore_index, chunk_size)

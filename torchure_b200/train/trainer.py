@@ -1,0 +1,281 @@
+"""Training orchestration.
+
+Lifecycle (reference ``torchure/train/trainer.py:61-146``): mesh -> model -> init ->
+parallelize (DDP) -> objective -> optimizer -> scheduler -> data -> resume -> prefetcher.
+One optimizer step (reference ``trainer.py:371-402``): K micro-batches of forward+backward
+with ``requires_sync`` only on the last, ``ddp.sync()``, global grad-norm clip, optimizer,
+``zero_grad``, scheduler, loss averaged over dp.
+
+GPU specifics: gradient buckets are reduced by the fused NVLink kernel, the clip
+coefficient stays on the device and is applied inside the AdamW kernel, and nothing in a
+step reads a device value on the host; only the logging cadence synchronises.
+"""
+
+from __future__ import annotations
+
+import os
+from datetime import datetime
+
+import torch
+
+from torchure_b200.ckpt import Checkpointer
+from torchure_b200.config import load_config, validate_config
+from torchure_b200.core.collective import all_reduce, barrier, enable_sm100
+from torchure_b200.core.grad_helper import clip_grad_norm, grad_norm_and_coef
+from torchure_b200.core.mesh import Mesh
+from torchure_b200.data import CUDAPrefetcher, build_dataloader, is_synthetic
+from torchure_b200.models import build_model
+from torchure_b200.objectives import build_objective
+from torchure_b200.optim import build_optimizer, build_scheduler
+from torchure_b200.parallel.ddp import DDP
+from torchure_b200.utils import debug_time, get_project_dir, record_time
+
+try:
+    import wandb  # type: ignore
+
+    HAS_WANDB = True
+except Exception:  # pragma: no cover - optional dependency
+    wandb = None
+    HAS_WANDB = False
+
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+
+class Trainer:
+    def __init__(self, config: str | dict, rank: int, local_rank: int, world_size: int, benchmark: bool = False,
+                 device: str | None = None):
+        self.config = load_config(config) if isinstance(config, str) else validate_config(config)
+        validate_config(self.config, world_size)
+        self.rank, self.world_size, self.benchmark = rank, world_size, benchmark
+        if device is None:
+            device = f"cuda:{local_rank}" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        self.on_gpu = self.device.type == "cuda"
+        if self.on_gpu:
+            torch.cuda.set_device(self.device)
+            torch.backends.cuda.matmul.allow_tf32 = True
+            torch.backends.cudnn.allow_tf32 = True
+        self.mesh = Mesh(self.config["mesh"])
+        self.dp_size = self.mesh.size("dp")
+        comm_cfg = self.config.get("comm", {})
+        if self.on_gpu and comm_cfg.get("backend", "sm100") == "sm100":
+            from torchure_b200 import ops
+
+            if ops.available():
+                enable_sm100(self.mesh, "dp", comm_cfg.get("max_bytes", 64 << 20))
+
+        self.ignore_index = self.config["objective"]["config"]["ignore_index"]
+        self.tokenizer = None
+        if not is_synthetic(self.config["data"]):
+            from tokenizers import Tokenizer
+
+            self.tokenizer = Tokenizer.from_pretrained(self.config["data"]["tokenizer"])
+
+        self.model = self._build_model()
+        self._init_weights(self.model)
+        self.model = self._parallelize(self.model)
+        self.objective = build_objective(self.config["objective"]["name"], self.config["objective"]["config"])
+        opt_cfg = self.config["optimizer"]
+        self.optimizer = build_optimizer(self.model, opt_cfg["name"], opt_cfg["config"])
+        self.scheduler = build_scheduler(self.optimizer, opt_cfg["scheduler"])
+        self.num_train_steps = opt_cfg["scheduler"]["total_steps"]
+        self.max_norm = opt_cfg.get("max_norm")
+        self._wire_engine()
+
+        self.dataloader = self._build_dataloader()
+        data_cfg = self.config["data"]
+        self.global_batch_size = data_cfg["global_batch_size"]
+        self.micro_batch_size = data_cfg["micro_batch_size"]
+        self.microbatches_per_step = self.global_batch_size // (self.micro_batch_size * self.dp_size)
+        self.log_every = int(self.config.get("log_every", 1))
+
+        stamp = datetime.now().strftime("%Y-%m-%d_%H-%M-%S")
+        self.run_name = f"{self.config['run_name']}_{stamp}"
+        # keyed on the config's run_name alone so a relaunch finds its own checkpoints
+        self.checkpointer_path = os.path.join(get_project_dir(), "checkpoints", self.config["run_name"])
+        self.checkpointer = Checkpointer(self.checkpointer_path)
+        ck = self.config["checkpointing"]
+        self.resume, self.save_steps = ck["resume"], ck["save_steps"]
+        self.resume_scheduler = ck.get("resume_scheduler", True)
+        self.resume_wandb_id: str | None = None
+        self.start_step = self._resume()
+        self._setup_wandb()
+        self.prefetcher = CUDAPrefetcher(self.dataloader, self.device)
+
+    # -- construction --------------------------------------------------------------------------
+    def _build_model(self):
+        mc = dict(self.config["model"]["config"])
+        if not self.config.get("compile", True):
+            mc["impl"] = "torch"
+        return build_model(self.config["model"]["name"], mc)
+
+    def _init_weights(self, model) -> None:
+        model.to(self.device)
+        seed = self.config.get("seed")
+        if seed is not None:
+            torch.manual_seed(int(seed))
+        model.init_weights()
+
+    def _parallelize(self, model):
+        ddp_cfg = self.config.get("ddp", {})
+        self.ddp = DDP(model, self.mesh, dim="dp", bucket_mb=ddp_cfg.get("bucket_mb", 25),
+                       fused=ddp_cfg.get("fused"), merge_small=ddp_cfg.get("merge_small", True))
+        return model
+
+    def _wire_engine(self) -> None:
+        """Let the AdamW kernel refresh the bf16 shadow weights the sm_100a engine computes with."""
+        if not self.on_gpu or getattr(self.model, "impl", "torch") == "torch":
+            return
+        from torchure_b200 import ops
+
+        if ops.available() and hasattr(self.optimizer, "attach_shadow"):
+            for p, shadow in self.model.engine().shadow_pairs():
+                self.optimizer.attach_shadow(p, shadow)
+
+    @debug_time
+    def _build_dataloader(self):
+        data_cfg = dict(self.config["data"])
+        data_cfg.setdefault("vocab_size", self.config["model"]["config"]["vocab_size"])
+        return build_dataloader(data_cfg, self.tokenizer, self.ignore_index,
+                                self.mesh.coordinate("dp"), self.mesh.size("dp"))
+
+    def _setup_wandb(self) -> None:
+        self.wandb_run = None
+        wcfg = self.config.get("wandb", {})
+        if not wcfg.get("enabled", False) or self.rank != 0 or self.benchmark:
+            return
+        assert HAS_WANDB, "wandb.enabled is true but the wandb package is not installed"
+        self.wandb_run = wandb.init(project=wcfg.get("project", "torchure_b200"), entity=wcfg.get("entity"),
+                                    name=self.run_name, id=self.resume_wandb_id,
+                                    resume="must" if self.resume_wandb_id else None, config=self.config)
+
+    # -- checkpoint / resume -------------------------------------------------------------------
+    @debug_time
+    def checkpoint(self, step: int) -> None:
+        """Write the state after `step` completed steps; rank 0 writes replicas, every dp rank its loader."""
+        if self.rank == 0:
+            self.checkpointer.save_model(self.model, step)
+            self.checkpointer.save_optimizer(self.optimizer, step)
+            self.checkpointer.save_scheduler(self.scheduler, step)
+            self.checkpointer.save_trainer({
+                "step": step,
+                "cpu_rng": torch.get_rng_state(),
+                "cuda_rng": torch.cuda.get_rng_state(self.device) if self.on_gpu else None,
+                "config": self.config,
+                "wandb_id": self.wandb_run.id if self.wandb_run else None,
+            }, step)
+        # the prefetcher knows the position of the first batch that was NOT consumed
+        self.checkpointer.save_dataloader(self.prefetcher, step, self.mesh.coordinate("dp"))
+        barrier()
+        if self.rank == 0:
+            self.checkpointer.mark_complete(step)
+
+    def _resume(self) -> int:
+        if self.resume is None:
+            return 0
+        if self.resume == "auto":
+            step = self.checkpointer.latest()
+            if step is None:
+                return 0
+        elif isinstance(self.resume, int):
+            step = self.checkpointer.valid_step(self.resume)
+            assert step is not None, f"checkpoint step {self.resume} does not exist or is incomplete"
+        else:
+            raise ValueError('resume must be null, "auto" or a step number')
+        state = self.checkpointer.load_trainer(step)
+        assert state["config"]["mesh"] == self.config["mesh"], (
+            f"cannot resume across a mesh change: checkpoint {state['config']['mesh']}, config {self.config['mesh']}")
+        self.checkpointer.load_model(self.model, step)
+        self.checkpointer.load_optimizer(self.optimizer, step)
+        if self.resume_scheduler:
+            self.checkpointer.load_scheduler(self.scheduler, step)
+        else:
+            self.scheduler.last_epoch = step
+        self.checkpointer.load_dataloader(self.dataloader, step, self.mesh.coordinate("dp"))
+        torch.set_rng_state(state["cpu_rng"])
+        if self.on_gpu and state.get("cuda_rng") is not None:
+            torch.cuda.set_rng_state(state["cuda_rng"], self.device)
+        self.resume_wandb_id = state.get("wandb_id")
+        return state["step"]
+
+    # -- the step ------------------------------------------------------------------------------
+    def micro_train_step(self) -> torch.Tensor:
+        batch = next(self.prefetcher)
+        if self.on_gpu:
+            with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+                loss = self.objective.compute_loss(self.model, batch) / self.microbatches_per_step
+        else:
+            loss = self.objective.compute_loss(self.model, batch) / self.microbatches_per_step
+        loss.backward()
+        return loss.detach()
+
+    def train_step_untimed(self) -> dict[str, torch.Tensor]:
+        loss = torch.zeros((), device=self.device)
+        self.ddp.requires_sync = False
+        for _ in range(self.microbatches_per_step - 1):
+            loss += self.micro_train_step()
+        self.ddp.requires_sync = True
+        loss += self.micro_train_step()
+        self.ddp.sync()
+        sq = self.ddp.sq_norm()
+        params = [p for p in self.model.parameters() if p.requires_grad]
+        if sq is not None and hasattr(self.optimizer, "set_grad_scale"):
+            grad_norm, coef = grad_norm_and_coef(params, self.mesh, self.max_norm, shard_dims=(), presummed_sq=sq)
+            if self.max_norm is not None:
+                self.optimizer.set_grad_scale(coef)
+        else:
+            grad_norm = clip_grad_norm(params, self.mesh, self.max_norm, shard_dims=())
+        self.optimizer.step()
+        self.optimizer.zero_grad()
+        self.scheduler.step()
+        if self.dp_size > 1:
+            all_reduce(loss, self.mesh, "dp", "avg")
+        return {"loss": loss, "grad_norm": grad_norm}
+
+    train_step = record_time(train_step_untimed)
+
+    def _line(self, step: int, metrics: dict, seconds: float, tokens_per_step: int) -> str:
+        return (f"{step=} || loss={metrics['loss'].item():.4f} || gnorm={metrics['grad_norm'].item():.3f} "
+                f"|| lr={self.scheduler.get_last_lr()[0]:.2e} || tps={tokens_per_step / seconds:.0f}")
+
+    @debug_time
+    def train_n_step_test(self, n_steps: int) -> list[dict]:
+        tokens_per_step = self.config["data"]["seq_len"] * self.global_batch_size
+        history = []
+        for step in range(n_steps):
+            metrics, seconds = self.train_step()
+            history.append({"loss": float(metrics["loss"]), "grad_norm": float(metrics["grad_norm"]),
+                            "seconds": seconds})
+            if self.rank == 0:
+                print(self._line(step, metrics, seconds, tokens_per_step), flush=True)
+        if self.rank == 0 and self.on_gpu:
+            print(f"peak cuda mem: {torch.cuda.max_memory_allocated() / 2**30:.2f} GiB")
+        return history
+
+    def _log_metrics(self, metrics: dict, step: int, tokens_per_step: int, seconds: float) -> None:
+        if self.wandb_run is None:
+            return
+        self.wandb_run.log({
+            "train/loss": metrics["loss"].item(), "train/grad_norm": metrics["grad_norm"].item(),
+            "train/lr": self.scheduler.get_last_lr()[0], "train/tokens": step * tokens_per_step,
+            "perf/tps": tokens_per_step / seconds, "perf/step_time": seconds,
+            "perf/peak_mem_gib": torch.cuda.max_memory_allocated() / 2**30 if self.on_gpu else 0.0,
+        }, step=step)
+
+    def train(self) -> None:
+        tokens_per_step = self.config["data"]["seq_len"] * self.global_batch_size
+        try:
+            for step in range(self.start_step, self.num_train_steps):
+                metrics, seconds = self.train_step()
+                done = step + 1
+                if (done % self.save_steps == 0 and step != 0) or done == self.num_train_steps:
+                    self.checkpoint(done)
+                if self.rank == 0:
+                    self._log_metrics(metrics, done, tokens_per_step, seconds)
+                    if done % self.log_every == 0 or done == self.num_train_steps:
+                        print(self._line(step, metrics, seconds, tokens_per_step), flush=True)
+            if self.rank == 0 and self.on_gpu:
+                print(f"peak cuda mem: {torch.cuda.max_memory_allocated() / 2**30:.2f} GiB")
+        finally:
+            if self.wandb_run is not None:
+                self.wandb_run.finish()
