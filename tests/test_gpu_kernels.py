@@ -1,0 +1,233 @@
+"""GPU numerics: each sm_100a kernel against a plain PyTorch fp32 statement of the same op."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def relerr(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _check_kernel_errors():
+    yield
+    from torchure_b200.ops import kernels
+
+    kernels.check_error()
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 1024), (8192, 1024, 2048), (1000, 520, 192),
+               (77, 136, 64), (4096, 6144, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_bf16(M, N, K, a_mn, b_mn):
+    from torchure_b200.ops import kernels
+
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("a transposed operand needs a 16-byte aligned row stride")
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    out = kernels.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn)
+    assert out.dtype == torch.bfloat16 and out.shape == (M, N)
+    assert relerr(out, ref) < 5e-3
+    # elementwise: bf16 rounding of an fp32-accumulated result
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 128), (1000, 520, 192), (4096, 1024, 8192)])
+def test_gemm_fp32_out_and_accumulate(M, N, K):
+    from torchure_b200.ops import kernels
+
+    torch.manual_seed(1)
+    a = torch.randn(K, M, device="cuda").bfloat16()  # stored transposed: the wgrad layout
+    b = torch.randn(K, N, device="cuda").bfloat16()
+    ref = a.float().t() @ b.float()
+    out = kernels.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    assert relerr(out, ref) < 1e-4
+    base = torch.randn(M, N, device="cuda")
+    acc = base.clone()
+    kernels.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    assert relerr(acc, base + ref) < 1e-4
+
+
+def test_gemm_strided_views():
+    from torchure_b200.ops import kernels
+
+    torch.manual_seed(2)
+    big_a = torch.randn(512, 1024, device="cuda").bfloat16()
+    big_b = torch.randn(768, 1024, device="cuda").bfloat16()
+    big_o = torch.zeros(512, 1536, device="cuda", dtype=torch.bfloat16)
+    a, b = big_a[:, 256:768], big_b[:, 256:768]
+    out = big_o[:, 512:1280]
+    kernels.gemm(a, b, out=out)
+    ref = a.float() @ b.float().t()
+    assert relerr(out, ref) < 5e-3
+    assert big_o[:, :512].abs().sum() == 0 and big_o[:, 1280:].abs().sum() == 0
+
+
+@pytest.mark.parametrize("M,D", [(64, 512), (1000, 1024), (8192, 1024), (333, 2560)])
+def test_add_rmsnorm_fwd_bwd(M, D):
+    from torchure_b200.ops import kernels, oracle
+
+    torch.manual_seed(0)
+    x = torch.randn(M, D, device="cuda")
+    y = (torch.randn(M, D, device="cuda") * 0.5).bfloat16()
+    w = torch.rand(D, device="cuda") + 0.5
+    x_new, h, rstd = kernels.add_rmsnorm(x, y, w, 1e-6)
+    xr = x + y.float()
+    torch.testing.assert_close(x_new, xr)
+    assert relerr(h, oracle.rmsnorm(xr, w, 1e-6)) < 5e-3
+    torch.testing.assert_close(rstd, torch.rsqrt(xr.pow(2).mean(-1) + 1e-6), rtol=1e-5, atol=1e-6)
+    # no residual: x passes through
+    x2, h2, _ = kernels.add_rmsnorm(x, None, w, 1e-6)
+    assert x2 is x and relerr(h2, oracle.rmsnorm(x, w, 1e-6)) < 5e-3
+    # backward
+    dh = torch.randn(M, D, device="cuda").bfloat16()
+    dx_in = torch.randn(M, D, device="cuda")
+    dw = torch.zeros(D, device="cuda")
+    dx, dxb = kernels.rmsnorm_bwd(dh, xr, w, rstd, dx_in, dw)
+    xa = xr.clone().requires_grad_()
+    wa = w.clone().requires_grad_()
+    oracle.rmsnorm(xa, wa, 1e-6).backward(dh.float())
+    assert relerr(dx, xa.grad + dx_in) < 1e-5
+    assert relerr(dxb, dx) < 5e-3
+    assert relerr(dw, wa.grad) < 1e-4
+
+
+def test_embedding_gather_norm_and_scatter():
+    from torchure_b200.ops import kernels, oracle
+
+    torch.manual_seed(0)
+    V, D, M = 1000, 512, 777
+    table = torch.randn(V, D, device="cuda")
+    ids = torch.randint(0, V, (M,), device="cuda")
+    w = torch.rand(D, device="cuda") + 0.5
+    x, h, _ = kernels.add_rmsnorm(None, None, w, 1e-6, ids=ids, table=table)
+    torch.testing.assert_close(x, table[ids])
+    assert relerr(h, oracle.rmsnorm(table[ids], w, 1e-6)) < 5e-3
+    dx = torch.randn(M, D, device="cuda")
+    dt = torch.zeros(V, D, device="cuda")
+    kernels.embedding_bwd_(dx, ids, dt)
+    ref = torch.zeros(V, D, device="cuda").index_add_(0, ids, dx)
+    torch.testing.assert_close(dt, ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("use_norm", [True, False])
+def test_qknorm_rope_fwd_bwd(use_norm):
+    from torchure_b200.models.qwen3 import RotaryEmbedding
+    from torchure_b200.ops import kernels, oracle
+
+    torch.manual_seed(0)
+    B, S, Hq, Hkv, hd = 2, 256, 4, 2, 128
+    qkv = torch.randn(B * S, (Hq + 2 * Hkv) * hd, device="cuda").bfloat16()
+    qw, kw = torch.rand(hd, device="cuda") + 0.5, torch.rand(hd, device="cuda") + 0.5
+    cos, sin = RotaryEmbedding(hd).tables(S, "cuda")
+    out = kernels.qknorm_rope(qkv, qw, kw, cos, sin, S, Hq, Hkv, 1e-6, use_norm)
+    qa = qkv.float().requires_grad_()
+    qwa, kwa = qw.clone().requires_grad_(), kw.clone().requires_grad_()
+    ref = oracle.qknorm_rope(qa, qwa, kwa, cos, sin, B, S, Hq, Hkv, hd, 1e-6, use_norm)
+    assert relerr(out, ref) < 8e-3
+    g = torch.randn(B * S, (Hq + 2 * Hkv) * hd, device="cuda").bfloat16()
+    ref.backward(g[:, :(Hq + Hkv) * hd].float())
+    dqw, dkw = torch.zeros(hd, device="cuda"), torch.zeros(hd, device="cuda")
+    d = g.clone()
+    kernels.qknorm_rope_bwd_(d, qkv, qw, kw, cos, sin, dqw, dkw, S, Hq, Hkv, 1e-6, use_norm)
+    assert relerr(d[:, :(Hq + Hkv) * hd], qa.grad[:, :(Hq + Hkv) * hd]) < 8e-3
+    assert torch.equal(d[:, (Hq + Hkv) * hd:], g[:, (Hq + Hkv) * hd:]), "the v columns must pass through"
+    if use_norm:
+        assert relerr(dqw, qwa.grad) < 5e-3 and relerr(dkw, kwa.grad) < 5e-3
+
+
+def test_swiglu_fwd_bwd():
+    from torchure_b200.ops import kernels, oracle
+
+    torch.manual_seed(0)
+    M, F_ = 1000, 3072
+    gu = torch.randn(M, 2 * F_, device="cuda").bfloat16()
+    act = kernels.swiglu(gu)
+    ga = gu.float().requires_grad_()
+    ref = oracle.swiglu(ga)
+    assert relerr(act, ref) < 5e-3
+    d = torch.randn(M, F_, device="cuda").bfloat16()
+    ref.backward(d.float())
+    assert relerr(kernels.swiglu_bwd(d, gu), ga.grad) < 5e-3
+
+
+@pytest.mark.parametrize("C,V", [(64, 1000), (300, 5000), (512, 151936)])
+def test_ce_softmax_grad(C, V):
+    from torchure_b200.ops import kernels
+
+    torch.manual_seed(0)
+    logits = (torch.randn(C, V, device="cuda") * 2).bfloat16()
+    labels = torch.randint(0, V, (C,), device="cuda")
+    labels[torch.rand(C, device="cuda") < 0.1] = -100
+    n_valid = (labels != -100).sum().clamp_min(1)
+    inv = (1.0 / n_valid).float().reshape(1)
+    la = logits.float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(la, labels, ignore_index=-100, reduction="sum")
+    ref.backward()
+    work = logits.clone()
+    row_loss = torch.empty(C, device="cuda")
+    kernels.ce_softmax_grad_(work, labels, row_loss, inv, -100)
+    torch.testing.assert_close(row_loss.sum(), ref.detach(), rtol=1e-4, atol=1e-3)
+    assert relerr(work, la.grad / n_valid) < 8e-3
+    assert work[labels == -100].abs().sum() == 0
+
+
+def test_multi_tensor_adamw_norm_scale():
+    from torchure_b200.ops import multi_tensor, oracle
+
+    torch.manual_seed(0)
+    shapes = [(1024, 1024), (128,), (3, 5, 7), (40000,), (1,)]
+    ps = [torch.randn(s, device="cuda") for s in shapes]
+    gs = [torch.randn(s, device="cuda") for s in shapes]
+    gs[1] = gs[1].bfloat16()
+    ms = [torch.randn(s, device="cuda") * 0.1 for s in shapes]
+    vs = [torch.rand(s, device="cuda") * 0.1 for s in shapes]
+    sh = [torch.empty(s, device="cuda", dtype=torch.bfloat16) if i != 2 else None for i, s in enumerate(shapes)]
+    want_sq = sum(g.float().pow(2).sum() for g in gs)
+    torch.testing.assert_close(multi_tensor.sq_norm(gs), want_sq, rtol=1e-4, atol=1e-3)
+    coef = torch.tensor(0.37, device="cuda")
+    refs = [oracle.adamw(p.clone(), g.float() * 0.37, m.clone(), v.clone(), 1e-2, 0.9, 0.95, 1e-8, 0.1, 3)
+            for p, g, m, v in zip(ps, gs, ms, vs)]
+    multi_tensor.adamw_step(ps, gs, ms, vs, sh, 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, grad_scale=coef)
+    for p, m, v, s, (rp, rm, rv) in zip(ps, ms, vs, sh, refs):
+        torch.testing.assert_close(p, rp, rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(m, rm, rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(v, rv, rtol=1e-5, atol=1e-6)
+        if s is not None:
+            torch.testing.assert_close(s.float(), rp, rtol=1e-2, atol=1e-2)
+    xs = [torch.randn(s, device="cuda") for s in shapes]
+    want = [x * 0.5 for x in xs]
+    multi_tensor.scale_(xs, torch.tensor(0.5, device="cuda"))
+    for x, wv in zip(xs, want):
+        torch.testing.assert_close(x, wv)
+
+
+def test_bucket_pack():
+    from torchure_b200.ops import multi_tensor
+
+    torch.manual_seed(0)
+    shapes = [(512, 512), (128,), (30000,)]
+    grads = [torch.randn(s, device="cuda") for s in shapes]
+    grads[0] = grads[0].bfloat16()
+    flat = torch.full((sum(g.numel() for g in grads),), 7.0, device="cuda")
+    views, at = [], 0
+    for g in grads:
+        views.append(flat[at:at + g.numel()].view(g.shape))
+        at += g.numel()
+    sq = torch.zeros((), device="cuda")
+    multi_tensor.bucket_pack(grads, views, False, 1.0, sq)
+    want = torch.cat([g.float().flatten() for g in grads])
+    torch.testing.assert_close(flat, want)
+    torch.testing.assert_close(sq, want.pow(2).sum(), rtol=1e-4, atol=1e-3)
+    multi_tensor.bucket_pack(grads, views, True, 0.5, None)
+    torch.testing.assert_close(flat, want)  # (x + x) * 0.5

@@ -1,0 +1,76 @@
+// Host-callable launchers of the sm_100a kernels.  Plain C++ signatures (raw device pointers, sizes, a
+// stream) so the kernels compile without the PyTorch headers; bindings.cpp adapts tensors to them.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tb {
+
+// ---- tcgen05 GEMM --------------------------------------------------------------------------
+// C[M,N] = A * B^T over bf16 operands with fp32 accumulation in TMEM.
+//   a_mn == false: A is stored [M, K] (K contiguous), lda = row stride in elements
+//   a_mn == true : A is stored [K, M] (M contiguous), lda = row stride in elements
+//   b_mn == false: B is stored [N, K] (K contiguous)
+//   b_mn == true : B is stored [K, N] (N contiguous)
+// out_mode 0: C bf16 store, 1: C fp32 store, 2: C fp32 += (TMA reduce-add)
+// Returns 0 or a negative code for an argument error.  `err` is a device int that a kernel sets when
+// one of its bounded waits expires.
+int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+              bool a_mn, bool b_mn, int out_mode, int* err, int num_sms, cudaStream_t stream);
+
+// ---- elementwise / normalisation -------------------------------------------------------------
+// h = rmsnorm(x_new) * w with x_new = x (+ y); optional gather x = table[ids].  Writes x_new when y or ids
+// is given.  x/x_out fp32 [M,D], y bf16 [M,D], h bf16 [M,D], rstd fp32 [M].
+void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids, const float* table, const float* w,
+                     float* x_out, __nv_bfloat16* h, float* rstd, int M, int D, float eps, cudaStream_t stream);
+// dx = dx_in + d rmsnorm; dw += sum_rows(dh * xhat).  dx_bf16 (optional) receives a bf16 copy of dx.
+void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const float* rstd, const float* dx_in,
+                 float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, cudaStream_t stream);
+// per-head RMSNorm + RoPE on the q and k column ranges of qkv [M, (Hq+2Hkv)*hd]; out [M, (Hq+Hkv)*hd]
+void qknorm_rope_fwd(const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos, const float* sin,
+                     __nv_bfloat16* out, int M, int S, int Hq, int Hkv, int hd, float eps, int use_norm,
+                     cudaStream_t stream);
+// in place on the q/k column ranges of dqkv [M, (Hq+2Hkv)*hd]; dqw/dkw fp32 [hd] accumulate
+void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
+                     const float* sin, float* dqw, float* dkw, int M, int S, int Hq, int Hkv, int hd, float eps,
+                     int use_norm, int num_sms, cudaStream_t stream);
+void swiglu_fwd(const __nv_bfloat16* gu, __nv_bfloat16* act, int M, int F, cudaStream_t stream);
+void swiglu_bwd(const __nv_bfloat16* dact, const __nv_bfloat16* gu, __nv_bfloat16* dgu, int M, int F,
+                cudaStream_t stream);
+// dtable[ids[r]] += dx[r]
+void embedding_bwd(const float* dx, const int64_t* ids, float* dtable, int M, int D, cudaStream_t stream);
+// logits [C, V] bf16 (row stride ldl) -> per-row loss (0 for ignored rows) and, in place, dlogits scaled by
+// *inv_n_valid.
+void ce_softmax_grad(__nv_bfloat16* logits, int64_t ldl, const int64_t* labels, float* row_loss,
+                     const float* inv_n_valid, int C, int V, int ignore_index, cudaStream_t stream);
+void cast_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t stream);
+// x *= *scale unless *scale == 1
+void scale_inplace_f32(float* x, const float* scale, int64_t n, cudaStream_t stream);
+void scale_inplace_bf16(__nv_bfloat16* x, const float* scale, int64_t n, cudaStream_t stream);
+
+// ---- multi-tensor ------------------------------------------------------------------------------
+struct TensorList {           // device-resident table (built once per parameter set)
+  const int64_t* ptrs_a;      // meaning depends on the op
+  const int64_t* ptrs_b;
+  const int64_t* ptrs_c;
+  const int64_t* ptrs_d;
+  const int64_t* ptrs_e;
+  const int64_t* numel;       // elements per tensor
+  const int32_t* flags;       // per-tensor flags
+  const int32_t* block_tensor;   // per thread block: tensor index
+  const int32_t* block_chunk;    // per thread block: chunk index inside the tensor
+  int n_blocks;
+};
+constexpr int kChunkElems = 16384;
+// fp32 master p, fp32/bf16 grad g (flag bit0 = grad is bf16), m, v fp32, optional bf16 shadow (ptr 0 = none)
+void adamw_multi(const TensorList& t, float lr, float beta1, float beta2, float eps, float weight_decay,
+                 float bias1, float bias2, const float* grad_scale, int maximize, cudaStream_t stream);
+// out[0] += sum over all tensors of x^2 (flag bit0 = bf16)
+void sqnorm_multi(const TensorList& t, float* out, cudaStream_t stream);
+void scale_multi(const TensorList& t, const float* scale, cudaStream_t stream);
+// bucket[off_i ...] (=|+=) cast(grad_i); sq (optional) receives the sum of squares of the result
+void bucket_pack_multi(const TensorList& t, int accumulate, float post_scale, float* sq, cudaStream_t stream);
+
+}  // namespace tb

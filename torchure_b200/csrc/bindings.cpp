@@ -1,0 +1,180 @@
+// Python bindings: adapt torch tensors to the raw-pointer launchers of api.h.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "api.h"
+#include "comm_api.h"
+#include "attn_api.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+// one error word per process (one process drives one GPU)
+torch::Tensor& err_word() {
+  static torch::Tensor t;
+  if (!t.defined()) t = torch::zeros({4}, torch::dtype(torch::kInt32).device(torch::kCUDA));
+  return t;
+}
+
+const __nv_bfloat16* bf(const torch::Tensor& t) { return reinterpret_cast<const __nv_bfloat16*>(t.data_ptr()); }
+__nv_bfloat16* bfm(torch::Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); }
+template <class T>
+const T* opt_ptr(const c10::optional<torch::Tensor>& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<const T*>(t->data_ptr()) : nullptr;
+}
+template <class T>
+T* opt_mptr(c10::optional<torch::Tensor>& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+void gemm(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, bool a_mn, bool b_mn, int64_t out_mode) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm: CUDA tensors required");
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "gemm: bf16 operands");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "gemm: innermost stride must be 1");
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm: reduction sizes differ: ", K, " vs ", Kb);
+  TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemm: output shape");
+  TORCH_CHECK(out_mode == 0 ? out.scalar_type() == torch::kBFloat16 : out.scalar_type() == torch::kFloat32,
+              "gemm: output dtype does not match out_mode");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int rc = tb::gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0),
+                               b.stride(0), out.stride(0), a_mn, b_mn, (int)out_mode, err_word().data_ptr<int>(),
+                               num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16 failed with code ", rc);
+}
+
+void add_rmsnorm_fwd(c10::optional<torch::Tensor> x, c10::optional<torch::Tensor> y, c10::optional<torch::Tensor> ids,
+                     c10::optional<torch::Tensor> table, const torch::Tensor& w, c10::optional<torch::Tensor> x_out,
+                     torch::Tensor& h, torch::Tensor& rstd, double eps) {
+  const int M = (int)h.size(0), D = (int)h.size(1);
+  TORCH_CHECK(D % 4 == 0, "rmsnorm: D must be a multiple of 4");
+  tb::add_rmsnorm_fwd(opt_ptr<float>(x), opt_ptr<__nv_bfloat16>(y), opt_ptr<int64_t>(ids), opt_ptr<float>(table),
+                      w.data_ptr<float>(), opt_mptr<float>(x_out), bfm(h), rstd.data_ptr<float>(), M, D, (float)eps,
+                      cur_stream());
+}
+
+void rmsnorm_bwd(const torch::Tensor& dh, const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& rstd,
+                 c10::optional<torch::Tensor> dx_in, torch::Tensor& dx, c10::optional<torch::Tensor> dx_bf16,
+                 torch::Tensor& dw) {
+  const int M = (int)x.size(0), D = (int)x.size(1);
+  tb::rmsnorm_bwd(bf(dh), x.data_ptr<float>(), w.data_ptr<float>(), rstd.data_ptr<float>(), opt_ptr<float>(dx_in),
+                  dx.data_ptr<float>(), opt_mptr<__nv_bfloat16>(dx_bf16), dw.data_ptr<float>(), M, D, num_sms(),
+                  cur_stream());
+}
+
+void qknorm_rope_fwd(const torch::Tensor& qkv, const torch::Tensor& qw, const torch::Tensor& kw,
+                     const torch::Tensor& cos, const torch::Tensor& sin, torch::Tensor& out, int64_t S, int64_t Hq,
+                     int64_t Hkv, double eps, bool use_norm) {
+  TORCH_CHECK(qkv.size(1) == (Hq + 2 * Hkv) * 128, "qknorm_rope: head_dim must be 128");
+  tb::qknorm_rope_fwd(bf(qkv), qw.data_ptr<float>(), kw.data_ptr<float>(), cos.data_ptr<float>(),
+                      sin.data_ptr<float>(), bfm(out), (int)qkv.size(0), (int)S, (int)Hq, (int)Hkv, 128, (float)eps,
+                      use_norm ? 1 : 0, cur_stream());
+}
+
+void qknorm_rope_bwd(torch::Tensor& dqkv, const torch::Tensor& qkv, const torch::Tensor& qw, const torch::Tensor& kw,
+                     const torch::Tensor& cos, const torch::Tensor& sin, torch::Tensor& dqw, torch::Tensor& dkw,
+                     int64_t S, int64_t Hq, int64_t Hkv, double eps, bool use_norm) {
+  TORCH_CHECK(qkv.size(1) == (Hq + 2 * Hkv) * 128, "qknorm_rope: head_dim must be 128");
+  tb::qknorm_rope_bwd(bfm(dqkv), bf(qkv), qw.data_ptr<float>(), kw.data_ptr<float>(), cos.data_ptr<float>(),
+                      sin.data_ptr<float>(), dqw.data_ptr<float>(), dkw.data_ptr<float>(), (int)qkv.size(0), (int)S,
+                      (int)Hq, (int)Hkv, 128, (float)eps, use_norm ? 1 : 0, num_sms(), cur_stream());
+}
+
+void swiglu_fwd(const torch::Tensor& gu, torch::Tensor& act) {
+  TORCH_CHECK(act.size(1) % 8 == 0, "swiglu: F must be a multiple of 8");
+  tb::swiglu_fwd(bf(gu), bfm(act), (int)act.size(0), (int)act.size(1), cur_stream());
+}
+void swiglu_bwd(const torch::Tensor& dact, const torch::Tensor& gu, torch::Tensor& dgu) {
+  tb::swiglu_bwd(bf(dact), bf(gu), bfm(dgu), (int)dact.size(0), (int)dact.size(1), cur_stream());
+}
+void embedding_bwd(const torch::Tensor& dx, const torch::Tensor& ids, torch::Tensor& dtable) {
+  tb::embedding_bwd(dx.data_ptr<float>(), ids.data_ptr<int64_t>(), dtable.data_ptr<float>(), (int)dx.size(0),
+                    (int)dx.size(1), cur_stream());
+}
+void ce_softmax_grad(torch::Tensor& logits, const torch::Tensor& labels, torch::Tensor& row_loss,
+                     const torch::Tensor& inv_n_valid, int64_t ignore_index) {
+  TORCH_CHECK(logits.stride(1) == 1 && logits.stride(0) % 8 == 0, "ce: logits rows must be 16-byte aligned");
+  tb::ce_softmax_grad(bfm(logits), logits.stride(0), labels.data_ptr<int64_t>(), row_loss.data_ptr<float>(),
+                      inv_n_valid.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)ignore_index,
+                      cur_stream());
+}
+void cast_to_bf16(const torch::Tensor& src, torch::Tensor& dst) {
+  tb::cast_f32_to_bf16(src.data_ptr<float>(), bfm(dst), src.numel(), cur_stream());
+}
+void scale_inplace(torch::Tensor& x, const torch::Tensor& scale) {
+  if (x.scalar_type() == torch::kFloat32) tb::scale_inplace_f32(x.data_ptr<float>(), scale.data_ptr<float>(), x.numel(), cur_stream());
+  else tb::scale_inplace_bf16(bfm(x), scale.data_ptr<float>(), x.numel(), cur_stream());
+}
+
+tb::TensorList as_list(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
+                       const torch::Tensor& block_tensor, const torch::Tensor& block_chunk) {
+  tb::TensorList t;
+  const int64_t n = numel.numel();
+  const int64_t* base = ptrs.data_ptr<int64_t>();
+  t.ptrs_a = base; t.ptrs_b = base + n; t.ptrs_c = base + 2 * n; t.ptrs_d = base + 3 * n; t.ptrs_e = base + 4 * n;
+  t.numel = numel.data_ptr<int64_t>();
+  t.flags = flags.data_ptr<int32_t>();
+  t.block_tensor = block_tensor.data_ptr<int32_t>();
+  t.block_chunk = block_chunk.data_ptr<int32_t>();
+  t.n_blocks = (int)block_tensor.numel();
+  return t;
+}
+
+void adamw_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
+                 const torch::Tensor& bt, const torch::Tensor& bc, double lr, double b1, double b2, double eps,
+                 double wd, double bias1, double bias2, c10::optional<torch::Tensor> grad_scale, bool maximize) {
+  tb::adamw_multi(as_list(ptrs, numel, flags, bt, bc), (float)lr, (float)b1, (float)b2, (float)eps, (float)wd,
+                  (float)bias1, (float)bias2, opt_ptr<float>(grad_scale), maximize ? 1 : 0, cur_stream());
+}
+void sqnorm_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
+                  const torch::Tensor& bt, const torch::Tensor& bc, torch::Tensor& out) {
+  tb::sqnorm_multi(as_list(ptrs, numel, flags, bt, bc), out.data_ptr<float>(), cur_stream());
+}
+void scale_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
+                 const torch::Tensor& bt, const torch::Tensor& bc, const torch::Tensor& scale) {
+  tb::scale_multi(as_list(ptrs, numel, flags, bt, bc), scale.data_ptr<float>(), cur_stream());
+}
+void bucket_pack_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
+                       const torch::Tensor& bt, const torch::Tensor& bc, bool accumulate, double post_scale,
+                       c10::optional<torch::Tensor> sq) {
+  tb::bucket_pack_multi(as_list(ptrs, numel, flags, bt, bc), accumulate ? 1 : 0, (float)post_scale,
+                        opt_mptr<float>(sq), cur_stream());
+}
+
+torch::Tensor error_word() { return err_word(); }
+
+}  // namespace
+
+void register_comm(pybind11::module_& m);
+void register_attn(pybind11::module_& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, "bf16 tcgen05 GEMM: out = A * B^T (operand majors selectable)");
+  m.def("error_word", &error_word, "device int32[4]; [0] is set when a bounded wait of a kernel expired");
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("qknorm_rope_fwd", &qknorm_rope_fwd);
+  m.def("qknorm_rope_bwd", &qknorm_rope_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("ce_softmax_grad", &ce_softmax_grad);
+  m.def("cast_to_bf16", &cast_to_bf16);
+  m.def("scale_inplace", &scale_inplace);
+  m.def("adamw_multi", &adamw_multi);
+  m.def("sqnorm_multi", &sqnorm_multi);
+  m.def("scale_multi", &scale_multi);
+  m.def("bucket_pack_multi", &bucket_pack_multi);
+  register_comm(m);
+  register_attn(m);
+}

@@ -1,0 +1,303 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: TMA -> shared-memory ring -> tcgen05.mma into
+// TMEM -> tcgen05.ld epilogue -> TMA store.
+//
+//   CTA tile 128 x 256 x 64, 4 pipeline stages (48 KB each), 192 threads:
+//     warp 0      TMA producer (one elected lane)
+//     warp 1      TMEM allocator + MMA issuer (one elected lane issues tcgen05.mma / tcgen05.commit)
+//     warps 2..5  epilogue: each owns the 32 TMEM lanes its warp id maps to (warp_id % 4), converts
+//                 64-column slabs to bf16 (or 32-column slabs to fp32), stages them in shared memory in
+//                 the 128-byte swizzle and writes them with its own TMA store (or TMA reduce-add)
+//   Two 256-column accumulators fill the 512 TMEM columns, so the epilogue of tile i overlaps the
+//   main loop of tile i+1.  One CTA per SM, tiles assigned round-robin, M fastest so that concurrently
+//   running CTAs share the same weight tile in L2.
+//
+// Operands may be K-major or MN-major (transposed in memory); that covers forward (x W^T), dgrad
+// (dy W) and wgrad (dy^T x) without any transpose kernel.  Edges are handled by TMA (zero fill on
+// loads, clipping on stores); every coordinate passed to TMA is a multiple of 32 elements.
+#include "api.h"
+#include "common.cuh"
+
+#include <mutex>
+
+namespace tb {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;            // 16 KB
+constexpr int B_BYTES = BN * BK * 2;            // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
+constexpr int EPI_BUF = 4096;                   // 32 rows x 128 B
+constexpr int EPI_BYTES = 4 * 2 * EPI_BUF;
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+
+template <bool A_MN, bool B_MN, int OUT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + EPI_BYTES);
+  uint64_t* full = bars;                  // [STAGES]
+  uint64_t* empty = bars + STAGES;        // [STAGES]
+  uint64_t* tfull = bars + 2 * STAGES;    // [2]
+  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 128);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % num_m) * BM;
+        const int n0 = (tile / num_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, err, kErrProducerEmptyWait)) { ok = false; break; }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sA, &tmA, &full[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * 8192, &tmA, &full[stage], m0 + j * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sB, &tmB, &full[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, &full[stage], n0 + j * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
+      constexpr uint32_t a_step = A_MN ? (2048u >> 4) : (32u >> 4);  // descriptor advance per k=16
+      constexpr uint32_t b_step = B_MN ? (2048u >> 4) : (32u >> 4);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, err, kErrMmaTmemEmptyWait)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, err, kErrMmaFullWait)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t da = make_desc_sw128(a_addr, a_lbo, 1024);
+          const uint64_t db = make_desc_sw128(a_addr + A_BYTES, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_f16_ss(d_tmem, da + static_cast<uint64_t>(k * a_step), db + static_cast<uint64_t>(k * b_step), idesc,
+                        (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* buf0 = epi + q * 2 * EPI_BUF;
+    constexpr int COLS = (OUT == 0) ? 64 : 32;  // columns per staged slab (128 B per row)
+    int it = 0;
+    int slab = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int m0 = (tile % num_m) * BM;
+      const int n0 = (tile / num_m) * BN;
+      const int acc = it & 1;
+      if (!mbar_wait(&tfull[acc], (it >> 1) & 1, err, kErrEpilogueTmemFullWait)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const bool rows_live = (m0 + q * 32) < M;
+#pragma unroll 1
+      for (int c = 0; c < BN / COLS; ++c) {
+        uint32_t v[64];
+        if (OUT == 0) {
+          tmem_ld_32x32b_x32(t_row + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+          tmem_ld_32x32b_x32(t_row + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+        } else {
+          tmem_ld_32x32b_x32(t_row + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        }
+        tmem_ld_wait();
+        if (c == BN / COLS - 1) {
+          // the accumulator is in registers: hand it back to the MMA warp
+          tc_fence_before();
+          mbar_arrive(&tempty[acc]);
+        }
+        const bool live = rows_live && (n0 + c * COLS) < N;
+        if (live) {
+          uint8_t* buf = buf0 + (slab & 1) * EPI_BUF;
+          ++slab;
+          if (lane == 0) tma_wait_group_read<1>();  // the store that last used this buffer has read it
+          __syncwarp();
+          uint8_t* row = buf + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 pk;
+            if (OUT == 0) {
+              pk.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+              pk.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+              pk.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+              pk.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            } else {
+              pk.x = v[4 * j + 0]; pk.y = v[4 * j + 1]; pk.z = v[4 * j + 2]; pk.w = v[4 * j + 3];
+            }
+            *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (OUT == 2) tma_reduce_add_2d(&tmC, buf, n0 + c * COLS, m0 + q * 32);
+            else tma_store_2d(&tmC, buf, n0 + c * COLS, m0 + q * 32);
+            tma_commit_group();
+          }
+        }
+      }
+    }
+    if (lane == 0) tma_wait_group<0>();
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  if (*reinterpret_cast<volatile int*>(err) != 0) {
+    // a wait expired somewhere: give copies and MMAs in flight time to land before TMEM is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+}  // namespace
+
+// 2-D row-major tensor [rows, cols] with row stride `ld` elements, box [box_rows, box_cols], 128B swizzle
+int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows, uint32_t box_cols) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return -10;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return -11;
+  if ((ld * elem_bytes) % 16 != 0) return -12;
+  if (box_cols * elem_bytes != 128) return -13;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -14;
+}
+
+template <bool A_MN, bool B_MN, int OUT>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc, int M, int N, int K, int* err,
+                  int grid, cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
+    configured = true;
+  }
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb_, tc, M, N, K, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+              bool a_mn, bool b_mn, int out_mode, int* err, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  CUtensorMap ta, tb_, tc;
+  int r;
+  // K-major operand [R, K]: box 64 (k) x tile rows.  MN-major operand stored [K, R]: box 64 (r) x 64 (k rows).
+  r = a_mn ? make_tmap_2d(&ta, A, 2, K, M, lda, 64, 64) : make_tmap_2d(&ta, A, 2, M, K, lda, BM, 64);
+  if (r) return r;
+  r = b_mn ? make_tmap_2d(&tb_, B, 2, K, N, ldb, 64, 64) : make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
+  if (r) return r - 100;
+  r = out_mode == 0 ? make_tmap_2d(&tc, C, 2, M, N, ldc, 32, 64) : make_tmap_2d(&tc, C, 4, M, N, ldc, 32, 32);
+  if (r) return r - 200;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+#define TB_GEMM_CASE(AM, BMN, O) \
+  if (a_mn == AM && b_mn == BMN && out_mode == O) return launch<AM, BMN, O>(ta, tb_, tc, M, N, K, err, grid, stream);
+  TB_GEMM_CASE(false, false, 0)
+  TB_GEMM_CASE(false, false, 1)
+  TB_GEMM_CASE(false, false, 2)
+  TB_GEMM_CASE(false, true, 0)
+  TB_GEMM_CASE(false, true, 1)
+  TB_GEMM_CASE(true, true, 0)
+  TB_GEMM_CASE(true, true, 1)
+  TB_GEMM_CASE(true, true, 2)
+  TB_GEMM_CASE(true, false, 0)
+#undef TB_GEMM_CASE
+  return -2;
+}
+
+}  // namespace tb

@@ -1,0 +1,95 @@
+"""Multi-tensor kernels (AdamW, grad norm, scaling, DDP bucket fill) driven by device-resident tables.
+
+A ``TensorTable`` records, for a fixed list of tensors, up to five pointer columns, the element counts,
+per-tensor flags and the (tensor, chunk) assignment of every thread block.  It is uploaded once; while the
+underlying storages stay where they are (parameters, optimizer state, bucket views), every later launch
+reuses it.  Tables are rebuilt only when a pointer changes (fresh autograd grads).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from torchure_b200 import ops
+
+CHUNK = 16384
+
+
+def available() -> bool:
+    return ops.available()
+
+
+class TensorTable:
+    def __init__(self, columns: list[list[torch.Tensor | None]], flags: list[int] | None = None):
+        """columns: up to 5 equally long tensor lists (None entries become null pointers)."""
+        n = len(columns[0])
+        assert n > 0 and all(len(c) == n for c in columns)
+        dev = next(t for t in columns[0] if t is not None).device
+        ptrs = [[(t.data_ptr() if t is not None else 0) for t in col] for col in columns]
+        while len(ptrs) < 5:
+            ptrs.append([0] * n)
+        numel = [t.numel() for t in columns[0]]
+        bt, bc = [], []
+        for i, ne in enumerate(numel):
+            for c in range((ne + CHUNK - 1) // CHUNK):
+                bt.append(i)
+                bc.append(c)
+        self.key = tuple(tuple(p) for p in ptrs)
+        self.ptrs = torch.tensor(ptrs, dtype=torch.int64).to(dev, non_blocking=True)
+        self.numel = torch.tensor(numel, dtype=torch.int64).to(dev, non_blocking=True)
+        self.flags = torch.tensor(flags if flags is not None else [0] * n, dtype=torch.int32).to(dev, non_blocking=True)
+        self.bt = torch.tensor(bt, dtype=torch.int32).to(dev, non_blocking=True)
+        self.bc = torch.tensor(bc, dtype=torch.int32).to(dev, non_blocking=True)
+        self.keepalive = columns
+
+    def args(self):
+        return self.ptrs, self.numel, self.flags, self.bt, self.bc
+
+
+_CACHE: dict[tuple, TensorTable] = {}
+
+
+def _table(tag: str, columns, flags=None) -> TensorTable:
+    key = (tag,) + tuple(tuple((t.data_ptr() if t is not None else 0) for t in col) for col in columns)
+    tab = _CACHE.get(key)
+    if tab is None:
+        if len(_CACHE) > 256:
+            _CACHE.clear()
+        tab = TensorTable(columns, flags)
+        _CACHE[key] = tab
+    return tab
+
+
+def _bf16_flags(ts) -> list[int]:
+    return [1 if t.dtype == torch.bfloat16 else 0 for t in ts]
+
+
+def sq_norm(tensors: list[torch.Tensor]) -> torch.Tensor:
+    """0-d fp32 tensor: sum of squares over all `tensors` (fp32 or bf16)."""
+    out = torch.zeros((), dtype=torch.float32, device=tensors[0].device)
+    tab = _table("sq", [tensors], _bf16_flags(tensors))
+    ops.ext().sqnorm_multi(*tab.args(), out)
+    ops.count_launch()
+    return out
+
+
+def scale_(tensors: list[torch.Tensor], scale: torch.Tensor) -> None:
+    tab = _table("scale", [tensors], _bf16_flags(tensors))
+    ops.ext().scale_multi(*tab.args(), scale.to(torch.float32))
+    ops.count_launch()
+
+
+def adamw_step(params, grads, exp_avgs, exp_avg_sqs, shadows, lr, beta1, beta2, eps, weight_decay, step,
+               grad_scale=None, maximize=False) -> None:
+    tab = _table("adamw", [params, grads, exp_avgs, exp_avg_sqs, shadows], _bf16_flags(grads))
+    bias1 = 1.0 - beta1 ** step
+    bias2 = 1.0 - beta2 ** step
+    gs = grad_scale.to(torch.float32) if grad_scale is not None else None
+    ops.ext().adamw_multi(*tab.args(), lr, beta1, beta2, eps, weight_decay, bias1, bias2, gs, maximize)
+    ops.count_launch()
+
+
+def bucket_pack(grads, dst_views, accumulate: bool, post_scale: float, sq_out: torch.Tensor | None) -> None:
+    tab = _table("pack", [grads, dst_views], _bf16_flags(grads))
+    ops.ext().bucket_pack_multi(*tab.args(), accumulate, post_scale, sq_out)
+    ops.count_launch()
