@@ -74,7 +74,7 @@ def run_reference(args, cfg: dict, timed_steps, max_over_ranks, ClockSampler) ->
         metrics, _seconds = trainer.train_step()  # the reference's own sync-bracketed step
         return metrics
 
-    for _ in range(max(3, args.warmup)):
+    for _ in range(max(5, args.warmup)):
         step()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -91,7 +91,7 @@ def run_reference(args, cfg: dict, timed_steps, max_over_ranks, ClockSampler) ->
             "metric": "Qwen3-0.6B bf16 global tokens/sec @seq4096 bs2/GPU" if args.model == "0.6b"
                       else "Qwen3-4B bf16 global tokens/sec @seq4096 bs1/GPU",
             "impl": "reference", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": dev_ms / args.steps,
+            "steps": args.steps, "warmup": max(5, args.warmup), "ms_per_step": dev_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic packed uniform tokens, random-init weights",
             "config": {"model": f"qwen3-{args.model}", "ffn_dim": cfg["model"]["config"]["ffn_dim"],

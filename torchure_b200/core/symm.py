@@ -1,0 +1,196 @@
+"""Symmetric memory communicator: the transport under the sm_100a collectives.
+
+One ``SymmComm`` per mesh axis group.  It owns a symmetric allocation (every rank of the group maps
+every other rank's copy, plus an NVSwitch multicast mapping when the fabric offers one), laid out as::
+
+    [ flags 64 KiB | sum-of-squares partials 512 KiB | persistent region (DDP buckets) | staging area ]
+
+The bootstrap (allocation, handle exchange, peer and multicast mapping) uses
+``torch.distributed._symmetric_memory``; every byte moved afterwards is moved by the kernels of
+``csrc/comm.cu`` (plain peer loads/stores or ``multimem`` instructions), never by NCCL.
+
+Generic collectives on ordinary tensors stage through the staging area (one local copy in, one out).
+Tensors allocated with ``alloc()`` live inside the symmetric region and are reduced in place.
+Variant choice per call: one-shot reads for small all-reduces (<= 256 KiB), two-shot
+(reduce-scatter + broadcast) above; ``multimem`` when a multicast mapping exists and the op is a sum/avg.
+
+Set ``TORCHURE_B200_NVLS=0`` to keep every kernel on plain peer loads/stores.
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from torchure_b200 import ops
+
+_OPS = {"sum": 0, "avg": 1, "max": 2, "min": 3}
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+ONESHOT_BYTES = 256 * 1024
+
+
+def _align(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+class SymmComm:
+    def __init__(self, group, rank: int, world: int, staging_bytes: int = 64 << 20, persistent_bytes: int = 0,
+                 wait_limit_s: float = 30.0, blocks: int = 32):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        ext = ops.ext()
+        self.ext = ext
+        self.group, self.rank, self.world = group, rank, world
+        self.blocks = min(blocks, ext.COMM_MAX_BLOCKS)
+        self.header = ext.COMM_FLAG_BYTES + ext.COMM_PARTIAL_BYTES
+        self.persistent_bytes = _align(persistent_bytes, 4096)
+        self.staging_bytes = _align(staging_bytes, 4096)
+        total = self.header + self.persistent_bytes + self.staging_bytes
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        self.peers = [int(p) for p in self.handle.buffer_ptrs]
+        assert self.peers[rank] == self.buf.data_ptr(), "symmetric allocation does not start at the tensor"
+        mc = int(self.handle.multicast_ptr) if self.handle.has_multicast_support(dev.type, dev.index) else 0
+        if os.environ.get("TORCHURE_B200_NVLS", "1") == "0":
+            mc = 0
+        self.mc = mc
+        self.limit_ns = int(wait_limit_s * 1e9)
+        self._persist_at = 0
+        self.staging_off = self.header + self.persistent_bytes
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # every rank's flags are zero before the first kernel touches them
+
+    # -- helpers ---------------------------------------------------------------------------------
+    def _ctx(self):
+        return self.peers, self.mc, self.rank, self.world, self.limit_ns
+
+    def supports(self, t: torch.Tensor) -> bool:
+        return t.is_cuda and t.dtype in _DT and t.is_contiguous() and t.numel() > 0
+
+    def _staging(self, nbytes: int, dtype, at: int = 0) -> torch.Tensor:
+        lo = self.staging_off + at
+        assert at + nbytes <= self.staging_bytes, (
+            f"message of {nbytes} bytes exceeds the {self.staging_bytes}-byte staging area of this communicator")
+        return self.buf[lo:lo + nbytes].view(dtype)
+
+    def offset_of(self, t: torch.Tensor) -> int | None:
+        """Byte offset of `t` inside the symmetric allocation, or None if it lives elsewhere."""
+        off = t.data_ptr() - self.buf.data_ptr()
+        if 0 <= off and off + t.numel() * t.element_size() <= self.buf.numel():
+            return off
+        return None
+
+    def alloc(self, numel: int, dtype=torch.float32) -> torch.Tensor:
+        """Persistent tensor inside the symmetric region (same offset on every rank: call in the same order)."""
+        nbytes = _align(numel * torch.empty((), dtype=dtype).element_size(), 256)
+        assert self._persist_at + nbytes <= self.persistent_bytes, "persistent symmetric region exhausted"
+        lo = self.header + self._persist_at
+        self._persist_at += nbytes
+        return self.buf[lo:lo + numel * torch.empty((), dtype=dtype).element_size()].view(dtype)
+
+    def partials(self, n_slots: int) -> torch.Tensor:
+        """(n_slots, MAX_RANKS * MAX_BLOCKS) fp32 view of the sum-of-squares table."""
+        per = self.ext.COMM_MAX_RANKS * self.ext.COMM_MAX_BLOCKS
+        lo = self.ext.COMM_FLAG_BYTES
+        assert n_slots * per * 4 <= self.ext.COMM_PARTIAL_BYTES
+        return self.buf[lo:lo + n_slots * per * 4].view(torch.float32).view(n_slots, per)
+
+    def check(self) -> None:
+        word = self.ext.comm_error_word()
+        code = int(word[0].item())
+        if code:
+            word.zero_()
+            raise RuntimeError(f"a collective gave up waiting for a peer flag (code {code}, rank {self.rank})")
+
+    # -- collectives -----------------------------------------------------------------------------
+    def all_reduce_symmetric_(self, t: torch.Tensor, op: str = "sum", sq_slot: int = -1, blocks: int | None = None):
+        """In-place two-shot all-reduce of a tensor that lives in the symmetric region."""
+        off = self.offset_of(t)
+        assert off is not None and off % 16 == 0 and (t.numel() * t.element_size()) % 16 == 0
+        use_mc = bool(self.mc) and op in ("sum", "avg")
+        self.ext.comm_all_reduce(*self._ctx(), off, t.numel(), _DT[t.dtype], _OPS[op], use_mc, sq_slot,
+                                 blocks or self.blocks)
+        ops.count_launch()
+
+    def all_reduce_(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
+        if self.offset_of(t) is not None and (t.numel() * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0:
+            self.all_reduce_symmetric_(t, op)
+            return t
+        nbytes = t.numel() * t.element_size()
+        padded = _align(nbytes, 16)
+        stage = self._staging(padded, t.dtype)
+        stage[: t.numel()].copy_(t.view(-1))
+        if padded <= ONESHOT_BYTES:
+            out = torch.empty(padded // t.element_size(), dtype=t.dtype, device=t.device)
+            self.ext.comm_all_reduce_oneshot(*self._ctx(), self.staging_off, out, padded // t.element_size(),
+                                             _DT[t.dtype], _OPS[op], min(self.blocks, 8))
+            ops.count_launch()
+            t.view(-1).copy_(out[: t.numel()])
+        else:
+            self.all_reduce_symmetric_(stage, op)
+            t.view(-1).copy_(stage[: t.numel()])
+        return t
+
+    def broadcast_(self, t: torch.Tensor, src: int) -> torch.Tensor:
+        nbytes = _align(t.numel() * t.element_size(), 16)
+        stage = self._staging(nbytes, t.dtype)
+        if self.rank == src:
+            stage[: t.numel()].copy_(t.view(-1))
+        self.ext.comm_broadcast(*self._ctx(), self.staging_off, nbytes // t.element_size(), _DT[t.dtype], src,
+                                bool(self.mc), self.blocks)
+        ops.count_launch()
+        if self.rank != src:
+            t.view(-1).copy_(stage[: t.numel()])
+        return t
+
+    def all_gather(self, src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        n = src.numel()
+        es = src.element_size()
+        chunk = _align(n * es, 16)
+        stage_in = self._staging(chunk, src.dtype)
+        stage_in[:n].copy_(src.view(-1))
+        dst_at = _align(chunk, 256)
+        self._staging(chunk * self.world, src.dtype, at=dst_at)  # bounds check
+        self.ext.comm_all_gather(*self._ctx(), self.staging_off, self.staging_off + dst_at, chunk // es, _DT[src.dtype],
+                                 bool(self.mc), self.blocks)
+        ops.count_launch()
+        gathered = self._staging(chunk * self.world, src.dtype, at=dst_at).view(self.world, chunk // es)[:, :n]
+        out.view(self.world, n).copy_(gathered)
+        return out
+
+    def reduce_scatter(self, src: torch.Tensor, out: torch.Tensor, op: str = "sum") -> torch.Tensor:
+        n = out.numel()
+        es = src.element_size()
+        assert src.numel() == n * self.world
+        chunk = _align(n * es, 16)
+        stage = self._staging(chunk * self.world, src.dtype).view(self.world, chunk // es)
+        stage[:, :n].copy_(src.view(self.world, n))
+        res = torch.empty(chunk // es, dtype=src.dtype, device=src.device)
+        use_mc = bool(self.mc) and op in ("sum", "avg")
+        self.ext.comm_reduce_scatter(*self._ctx(), self.staging_off, res, chunk // es, _DT[src.dtype], _OPS[op], use_mc,
+                                     self.blocks)
+        ops.count_launch()
+        out.view(-1).copy_(res[:n])
+        return out
+
+    def all_to_all(self, src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        es = src.element_size()
+        n = src.numel() // self.world
+        chunk = _align(n * es, 16)
+        stage_in = self._staging(chunk * self.world, src.dtype).view(self.world, chunk // es)
+        stage_in[:, :n].copy_(src.view(self.world, n))
+        dst_at = _align(chunk * self.world, 256)
+        stage_out = self._staging(chunk * self.world, src.dtype, at=dst_at).view(self.world, chunk // es)
+        self.ext.comm_all_to_all(*self._ctx(), self.staging_off, self.staging_off + dst_at, chunk // es, _DT[src.dtype],
+                                 self.blocks)
+        ops.count_launch()
+        out.view(self.world, n).copy_(stage_out[:, :n])
+        return out
+
+    def barrier(self, pretend_world: int | None = None) -> None:
+        self.ext.comm_barrier(*self._ctx(), pretend_world or self.world)
+        ops.count_launch()

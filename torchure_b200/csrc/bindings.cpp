@@ -11,10 +11,13 @@ namespace {
 
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
+int g_sm_reserve = 0;  // SMs the persistent kernels leave free for communication kernels
+
 int num_sms() {
   static int n = 0;
   if (n == 0) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  return n;
+  const int usable = n - g_sm_reserve;
+  return usable > 8 ? usable : 8;
 }
 
 // one error word per process (one process drives one GPU)
@@ -160,6 +163,7 @@ void register_attn(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM: out = A * B^T (operand majors selectable)");
+  m.def("set_sm_reserve", [](int64_t n) { g_sm_reserve = (int)n; }, "persistent kernels use (SM count - n) CTAs");
   m.def("error_word", &error_word, "device int32[4]; [0] is set when a bounded wait of a kernel expired");
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

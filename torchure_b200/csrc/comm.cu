@@ -1,0 +1,311 @@
+// NVLink / NVSwitch collectives written as plain kernels over a symmetric allocation.
+//
+// Transport per kernel: either `multimem` instructions on the multicast mapping (the switch reduces or
+// replicates: NVLS) or plain 16-byte loads/stores on peer pointers.  No TMA and no library call is involved,
+// so nothing here ever issues a multicast TMA load from peer memory.
+//
+// Cross-rank synchronisation is a per-block flag exchange: block b of every rank handshakes with block b of
+// every peer (same grid everywhere).  A flag is raised with CAS 0->1 in the peer's memory and consumed with CAS
+// 1->0 locally, so flags reset themselves.  Every spin is bounded by CommCtx::wait_limit_ns; on expiry the block
+// records kErrPeerFlagWait and the kernel finishes without touching peer memory again.
+#include "comm_api.h"
+#include "common.cuh"
+
+namespace tb {
+
+namespace {
+
+constexpr int CT = 512;  // threads per block
+
+__device__ __forceinline__ uint32_t* flag_ptr(uint64_t base, int phase, int block, int rank) {
+  return reinterpret_cast<uint32_t*>(base) + (phase * kCommMaxBlocks + block) * kCommMaxRanks + rank;
+}
+
+__device__ __forceinline__ uint32_t cas_sys(uint32_t* addr, uint32_t cmp, uint32_t val) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.sys.global.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "l"(addr), "r"(cmp), "r"(val) : "memory");
+  return old;
+}
+
+// Block-level barrier with the same block of every peer.  Returns false if a wait expired.
+__device__ bool block_barrier(const CommCtx& c, int phase, int world) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  __threadfence_system();
+  if (threadIdx.x < world && threadIdx.x != c.rank) {
+    const int peer = threadIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    bool ok = true;
+    // raise my flag in the peer's memory (only if a peer exists; pretend-world barriers have no peer memory)
+    if (peer < c.world) {
+      uint32_t* theirs = flag_ptr(c.peer_bufs[peer], phase, blockIdx.x, c.rank);
+      while (cas_sys(theirs, 0u, 1u) != 0u) {
+        if (globaltimer_ns() - t0 > c.wait_limit_ns || *reinterpret_cast<volatile int*>(c.err) != 0) { ok = false; break; }
+      }
+    }
+    if (ok) {
+      uint32_t* mine = flag_ptr(c.peer_bufs[c.rank], phase, blockIdx.x, peer);
+      while (cas_sys(mine, 1u, 0u) != 1u) {
+        if (globaltimer_ns() - t0 > c.wait_limit_ns || *reinterpret_cast<volatile int*>(c.err) != 0) { ok = false; break; }
+      }
+    }
+    if (!ok) {
+      atomicCAS(c.err, 0, kErrPeerFlagWait);
+      s_fail = 1;
+    }
+  }
+  __syncthreads();
+  return s_fail == 0;
+}
+
+// ---- 16-byte vector helpers ---------------------------------------------------------------------------
+struct V4 { uint32_t x, y, z, w; };
+
+__device__ __forceinline__ V4 ld16(const void* p) {
+  V4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st16(void* p, const V4& v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ V4 mc_ld_reduce_f32(const void* p) {
+  V4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ V4 mc_ld_reduce_bf16(const void* p) {
+  V4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st(void* p, const V4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ float combine(float a, float b, int op) {
+  return op == kOpMax ? fmaxf(a, b) : (op == kOpMin ? fminf(a, b) : a + b);
+}
+
+// 4 fp32 accumulators per 16 B of fp32; 8 per 16 B of bf16
+template <int DT>
+struct Acc {
+  static constexpr int N = DT == kF32 ? 4 : 8;
+  float f[N];
+  __device__ __forceinline__ void load(const V4& v) {
+    if (DT == kF32) {
+      f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    } else {
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        f[2 * k] = __uint_as_float(u[k] << 16);
+        f[2 * k + 1] = __uint_as_float(u[k] & 0xffff0000u);
+      }
+    }
+  }
+  __device__ __forceinline__ V4 store() const {
+    V4 v;
+    if (DT == kF32) {
+      v.x = __float_as_uint(f[0]); v.y = __float_as_uint(f[1]); v.z = __float_as_uint(f[2]); v.w = __float_as_uint(f[3]);
+    } else {
+      v.x = pack_bf16x2(f[0], f[1]); v.y = pack_bf16x2(f[2], f[3]); v.z = pack_bf16x2(f[4], f[5]); v.w = pack_bf16x2(f[6], f[7]);
+    }
+    return v;
+  }
+};
+
+// reduce one 16-byte vector at byte offset `o` over all ranks
+template <int DT>
+__device__ __forceinline__ Acc<DT> reduce_vec(const CommCtx& c, uint64_t o, int op, bool use_mc) {
+  Acc<DT> a;
+  if (use_mc) {
+    a.load(DT == kF32 ? mc_ld_reduce_f32(reinterpret_cast<void*>(c.mc_buf + o))
+                      : mc_ld_reduce_bf16(reinterpret_cast<void*>(c.mc_buf + o)));
+  } else {
+    a.load(ld16(reinterpret_cast<void*>(c.peer_bufs[0] + o)));
+    for (int p = 1; p < c.world; ++p) {
+      Acc<DT> b;
+      b.load(ld16(reinterpret_cast<void*>(c.peer_bufs[p] + o)));
+#pragma unroll
+      for (int k = 0; k < Acc<DT>::N; ++k) a.f[k] = combine(a.f[k], b.f[k], op);
+    }
+  }
+  if (op == kOpAvg) {
+    const float s = 1.f / c.world;
+#pragma unroll
+    for (int k = 0; k < Acc<DT>::N; ++k) a.f[k] *= s;
+  }
+  return a;
+}
+
+__device__ __forceinline__ void write_all(const CommCtx& c, uint64_t o, const V4& v, bool use_mc) {
+  if (use_mc) {
+    mc_st(reinterpret_cast<void*>(c.mc_buf + o), v);
+  } else {
+    for (int p = 0; p < c.world; ++p) st16(reinterpret_cast<void*>(c.peer_bufs[(c.rank + p) % c.world] + o), v);
+  }
+}
+
+__device__ __forceinline__ float block_reduce_sum(float v) {
+  __shared__ float part[CT / 32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = threadIdx.x < CT / 32 ? part[threadIdx.x] : 0.f;
+  if (threadIdx.x < 32) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  }
+  return t;
+}
+
+// ---- kernels ------------------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(CT)
+all_reduce_kernel(CommCtx c, uint64_t off, int64_t nvec, int op, int use_mc, int sq_slot) {
+  if (!block_barrier(c, 0, c.world)) return;
+  const int64_t per = nvec / c.world, rem = nvec % c.world;
+  // slice of this rank (the remainder goes to the last rank)
+  const int64_t lo = per * c.rank, hi = lo + per + (c.rank == c.world - 1 ? rem : 0);
+  float sq = 0.f;
+  for (int64_t i = lo + static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < hi;
+       i += static_cast<int64_t>(gridDim.x) * CT) {
+    const uint64_t o = off + static_cast<uint64_t>(i) * 16;
+    Acc<DT> a = reduce_vec<DT>(c, o, op, use_mc != 0);
+#pragma unroll
+    for (int k = 0; k < Acc<DT>::N; ++k) sq += a.f[k] * a.f[k];
+    write_all(c, o, a.store(), use_mc != 0);
+  }
+  if (sq_slot >= 0) {
+    sq = block_reduce_sum(sq);
+    if (threadIdx.x < c.world) {
+      // publish this block's partial to every rank: table[slot][rank][block]
+      float* table = reinterpret_cast<float*>(c.peer_bufs[threadIdx.x] + kFlagBytes);
+      table[(static_cast<int64_t>(sq_slot) * kCommMaxRanks + c.rank) * kCommMaxBlocks + blockIdx.x] = sq;
+    }
+  }
+  block_barrier(c, 1, c.world);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(CT)
+all_reduce_oneshot_kernel(CommCtx c, uint64_t off, void* out, int64_t nvec, int op) {
+  if (!block_barrier(c, 0, c.world)) return;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
+    Acc<DT> a = reduce_vec<DT>(c, off + static_cast<uint64_t>(i) * 16, op, false);
+    st16(reinterpret_cast<uint8_t*>(out) + i * 16, a.store());
+  }
+  block_barrier(c, 1, c.world);  // nobody may overwrite its staging area while a peer still reads it
+}
+
+__global__ void __launch_bounds__(CT)
+all_gather_kernel(CommCtx c, uint64_t src_off, uint64_t dst_off, int64_t nvec, int use_mc) {
+  if (!block_barrier(c, 0, c.world)) return;  // every rank's destination is free to be written
+  const uint64_t my_dst = dst_off + static_cast<uint64_t>(c.rank) * nvec * 16;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
+    V4 v = ld16(reinterpret_cast<void*>(c.peer_bufs[c.rank] + src_off + i * 16));
+    write_all(c, my_dst + i * 16, v, use_mc != 0);
+  }
+  block_barrier(c, 1, c.world);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(CT)
+reduce_scatter_kernel(CommCtx c, uint64_t off, void* out, int64_t nvec, int op, int use_mc) {
+  if (!block_barrier(c, 0, c.world)) return;
+  const uint64_t base = off + static_cast<uint64_t>(c.rank) * nvec * 16;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
+    Acc<DT> a = reduce_vec<DT>(c, base + i * 16, op, use_mc != 0);
+    st16(reinterpret_cast<uint8_t*>(out) + i * 16, a.store());
+  }
+  block_barrier(c, 1, c.world);
+}
+
+__global__ void __launch_bounds__(CT)
+all_to_all_kernel(CommCtx c, uint64_t src_off, uint64_t dst_off, int64_t nvec) {
+  if (!block_barrier(c, 0, c.world)) return;
+  for (int j = 0; j < c.world; ++j) {
+    const int peer = (c.rank + j) % c.world;  // stagger peers so links are used evenly
+    const uint64_t s = src_off + static_cast<uint64_t>(peer) * nvec * 16;
+    const uint64_t d = dst_off + static_cast<uint64_t>(c.rank) * nvec * 16;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
+      V4 v = ld16(reinterpret_cast<void*>(c.peer_bufs[c.rank] + s + i * 16));
+      st16(reinterpret_cast<void*>(c.peer_bufs[peer] + d + i * 16), v);
+    }
+  }
+  block_barrier(c, 1, c.world);
+}
+
+__global__ void __launch_bounds__(CT)
+broadcast_kernel(CommCtx c, uint64_t off, int64_t nvec, int src, int use_mc) {
+  if (!block_barrier(c, 0, c.world)) return;
+  if (c.rank == src) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
+      V4 v = ld16(reinterpret_cast<void*>(c.peer_bufs[c.rank] + off + i * 16));
+      if (use_mc) mc_st(reinterpret_cast<void*>(c.mc_buf + off + i * 16), v);
+      else
+        for (int p = 0; p < c.world; ++p)
+          if (p != src) st16(reinterpret_cast<void*>(c.peer_bufs[p] + off + i * 16), v);
+    }
+  }
+  block_barrier(c, 1, c.world);
+}
+
+__global__ void __launch_bounds__(CT) barrier_kernel(CommCtx c, int pretend_world) {
+  block_barrier(c, 0, pretend_world);
+}
+
+}  // namespace
+
+#define TB_DT_DISPATCH(dtype, CALL_F32, CALL_BF16) \
+  do { if ((dtype) == kF32) { CALL_F32; } else { CALL_BF16; } } while (0)
+
+void comm_all_reduce(const CommCtx& c, uint64_t off, int64_t n, int dtype, int op, bool use_mc, int sq_slot,
+                     uint32_t, int blocks, cudaStream_t stream) {
+  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
+  TB_DT_DISPATCH(dtype, (all_reduce_kernel<kF32><<<blocks, CT, 0, stream>>>(c, off, nvec, op, use_mc, sq_slot)),
+                 (all_reduce_kernel<kBF16><<<blocks, CT, 0, stream>>>(c, off, nvec, op, use_mc, sq_slot)));
+}
+
+void comm_all_reduce_oneshot(const CommCtx& c, uint64_t off, void* out, int64_t n, int dtype, int op, uint32_t,
+                             int blocks, cudaStream_t stream) {
+  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
+  TB_DT_DISPATCH(dtype, (all_reduce_oneshot_kernel<kF32><<<blocks, CT, 0, stream>>>(c, off, out, nvec, op)),
+                 (all_reduce_oneshot_kernel<kBF16><<<blocks, CT, 0, stream>>>(c, off, out, nvec, op)));
+}
+
+void comm_all_gather(const CommCtx& c, uint64_t src_off, uint64_t dst_off, int64_t n, int dtype, bool use_mc,
+                     uint32_t, int blocks, cudaStream_t stream) {
+  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
+  all_gather_kernel<<<blocks, CT, 0, stream>>>(c, src_off, dst_off, nvec, use_mc);
+}
+
+void comm_reduce_scatter(const CommCtx& c, uint64_t off, void* out, int64_t n, int dtype, int op, bool use_mc,
+                         uint32_t, int blocks, cudaStream_t stream) {
+  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
+  TB_DT_DISPATCH(dtype, (reduce_scatter_kernel<kF32><<<blocks, CT, 0, stream>>>(c, off, out, nvec, op, use_mc)),
+                 (reduce_scatter_kernel<kBF16><<<blocks, CT, 0, stream>>>(c, off, out, nvec, op, use_mc)));
+}
+
+void comm_all_to_all(const CommCtx& c, uint64_t src_off, uint64_t dst_off, int64_t n, int dtype, uint32_t,
+                     int blocks, cudaStream_t stream) {
+  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
+  all_to_all_kernel<<<blocks, CT, 0, stream>>>(c, src_off, dst_off, nvec);
+}
+
+void comm_broadcast(const CommCtx& c, uint64_t off, int64_t n, int dtype, int src, bool use_mc, uint32_t, int blocks,
+                    cudaStream_t stream) {
+  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
+  broadcast_kernel<<<blocks, CT, 0, stream>>>(c, off, nvec, src, use_mc);
+}
+
+void comm_barrier(const CommCtx& c, uint32_t, int pretend_world, cudaStream_t stream) {
+  barrier_kernel<<<1, CT, 0, stream>>>(c, pretend_world);
+}
+
+}  // namespace tb

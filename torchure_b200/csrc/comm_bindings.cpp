@@ -1,3 +1,76 @@
+// Python bindings of the NVLink collective kernels.
+#include <ATen/cuda/CUDAContext.h>
 #include <torch/extension.h>
+
 #include "comm_api.h"
-void register_comm(pybind11::module_& m) { (void)m; }
+
+namespace {
+
+torch::Tensor& comm_err_word() {
+  static torch::Tensor t;
+  if (!t.defined()) t = torch::zeros({4}, torch::dtype(torch::kInt32).device(torch::kCUDA));
+  return t;
+}
+
+tb::CommCtx make_ctx(const std::vector<int64_t>& peers, int64_t mc, int64_t rank, int64_t world, int64_t limit_ns) {
+  TORCH_CHECK((int)peers.size() <= tb::kCommMaxRanks && world <= tb::kCommMaxRanks, "at most 8 ranks per communicator");
+  tb::CommCtx c{};
+  for (size_t i = 0; i < peers.size(); ++i) c.peer_bufs[i] = (uint64_t)peers[i];
+  c.mc_buf = (uint64_t)mc;
+  c.rank = (int)rank;
+  c.world = (int)world;
+  c.err = comm_err_word().data_ptr<int>();
+  c.wait_limit_ns = (uint64_t)limit_ns;
+  c.grid_counter = nullptr;
+  return c;
+}
+
+cudaStream_t cs() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int dt_of(int64_t code) { return code == 0 ? tb::kF32 : tb::kBF16; }
+
+}  // namespace
+
+void register_comm(pybind11::module_& m) {
+  m.attr("COMM_FLAG_BYTES") = tb::kFlagBytes;
+  m.attr("COMM_PARTIAL_BYTES") = tb::kPartialBytes;
+  m.attr("COMM_MAX_BLOCKS") = tb::kCommMaxBlocks;
+  m.attr("COMM_MAX_RANKS") = tb::kCommMaxRanks;
+  m.def("comm_error_word", [] { return comm_err_word(); });
+  m.def("comm_all_reduce", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                              int64_t off, int64_t n, int64_t dtype, int64_t op, bool use_mc, int64_t sq_slot,
+                              int64_t blocks) {
+    tb::comm_all_reduce(make_ctx(peers, mc, rank, world, limit), off, n, dt_of(dtype), (int)op, use_mc, (int)sq_slot, 0,
+                        (int)blocks, cs());
+  });
+  m.def("comm_all_reduce_oneshot", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world,
+                                      int64_t limit, int64_t off, torch::Tensor out, int64_t n, int64_t dtype,
+                                      int64_t op, int64_t blocks) {
+    tb::comm_all_reduce_oneshot(make_ctx(peers, mc, rank, world, limit), off, out.data_ptr(), n, dt_of(dtype), (int)op, 0,
+                                (int)blocks, cs());
+  });
+  m.def("comm_all_gather", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                              int64_t src_off, int64_t dst_off, int64_t n, int64_t dtype, bool use_mc, int64_t blocks) {
+    tb::comm_all_gather(make_ctx(peers, mc, rank, world, limit), src_off, dst_off, n, dt_of(dtype), use_mc, 0, (int)blocks,
+                        cs());
+  });
+  m.def("comm_reduce_scatter", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                                  int64_t off, torch::Tensor out, int64_t n, int64_t dtype, int64_t op, bool use_mc,
+                                  int64_t blocks) {
+    tb::comm_reduce_scatter(make_ctx(peers, mc, rank, world, limit), off, out.data_ptr(), n, dt_of(dtype), (int)op, use_mc,
+                            0, (int)blocks, cs());
+  });
+  m.def("comm_all_to_all", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                              int64_t src_off, int64_t dst_off, int64_t n, int64_t dtype, int64_t blocks) {
+    tb::comm_all_to_all(make_ctx(peers, mc, rank, world, limit), src_off, dst_off, n, dt_of(dtype), 0, (int)blocks, cs());
+  });
+  m.def("comm_broadcast", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                             int64_t off, int64_t n, int64_t dtype, int64_t src, bool use_mc, int64_t blocks) {
+    tb::comm_broadcast(make_ctx(peers, mc, rank, world, limit), off, n, dt_of(dtype), (int)src, use_mc, 0, (int)blocks,
+                       cs());
+  });
+  m.def("comm_barrier", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                           int64_t pretend_world) {
+    tb::comm_barrier(make_ctx(peers, mc, rank, world, limit), 0, (int)pretend_world, cs());
+  });
+}

@@ -69,3 +69,11 @@ def launches() -> int:
 def reset_launches() -> None:
     global _LAUNCHES
     _LAUNCHES = 0
+
+
+def set_compute_sm_reserve(n: int) -> None:
+    """Persistent compute kernels (GEMM) launch on `SM count - n` CTAs, leaving room for communication kernels
+    that must be resident at the same time as the backward pass they overlap."""
+    e = ext()
+    if e is not None:
+        e.set_sm_reserve(int(n))

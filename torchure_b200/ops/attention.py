@@ -1,0 +1,86 @@
+"""Causal GQA attention over the fused projection layout.
+
+Inputs are the buffers the surrounding kernels produce, no transposes or copies:
+
+* ``qk``   (M, (Hq+Hkv)*hd) bf16: normalised, rotated queries then keys, token-major
+* ``qkv``  (M, (Hq+2Hkv)*hd) bf16: the raw QKV projection; only its V columns are read
+* output  ``o`` (M, Hq*hd) bf16 (what o_proj consumes) and ``lse`` (B, Hq, S) fp32 (natural log)
+
+Backward writes dq | dk | dv into one (M, (Hq+2Hkv)*hd) buffer laid out like ``qkv``, which the
+QK-norm/RoPE backward kernel then transforms in place and the QKV dgrad/wgrad GEMMs consume.
+
+``impl="sm100"`` is the hand-written tcgen05 kernel pair (``csrc/attention_sm100.cu``);
+``impl="sdpa"`` routes through ``torch.nn.functional.scaled_dot_product_attention`` and exists for
+A/B comparison and for shapes the kernel does not cover (head_dim != 128, S % 128 != 0, odd GQA ratio).
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.nn.functional as F
+
+from torchure_b200 import ops
+
+_FORCE = os.environ.get("TORCHURE_B200_ATTN", "")  # "sdpa" forces the library path
+
+
+def kernel_supported(S: int, Hq: int, Hkv: int, hd: int) -> bool:
+    ext = ops.ext()
+    if _FORCE == "sdpa" or ext is None or not hasattr(ext, "attn_fwd"):
+        return False
+    return hd == 128 and S % 128 == 0 and Hq % Hkv == 0 and (Hq // Hkv) % 2 == 0
+
+
+def _views(qk, qkv, B, S, Hq, Hkv, hd):
+    q = qk[:, :Hq * hd].view(B, S, Hq, hd).transpose(1, 2)
+    k = qk[:, Hq * hd:].view(B, S, Hkv, hd).transpose(1, 2)
+    v = qkv[:, (Hq + Hkv) * hd:].view(B, S, Hkv, hd).transpose(1, 2)
+    return q, k, v
+
+
+class AttnState:
+    """What backward needs; differs per implementation."""
+
+    __slots__ = ("impl", "o", "lse", "graph")
+
+    def __init__(self, impl, o=None, lse=None, graph=None):
+        self.impl, self.o, self.lse, self.graph = impl, o, lse, graph
+
+
+def attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=True):
+    """Returns (o (M, Hq*hd) bf16, state)."""
+    if kernel_supported(S, Hq, Hkv, hd):
+        ext = ops.ext()
+        o = torch.empty(B * S, Hq * hd, dtype=torch.bfloat16, device=qk.device)
+        lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qk.device)
+        ext.attn_fwd(qk, qkv, o, lse, B, S, Hq, Hkv)
+        ops.count_launch()
+        return o, AttnState("sm100", o, lse)
+    q, k, v = _views(qk, qkv, B, S, Hq, Hkv, hd)
+    if need_grad:
+        with torch.enable_grad():
+            ql, kl, vl = (t.detach().requires_grad_() for t in (q, k, v))
+            out = F.scaled_dot_product_attention(ql, kl, vl, is_causal=True, enable_gqa=Hq != Hkv)
+        o = out.detach().transpose(1, 2).reshape(B * S, Hq * hd)
+        return o, AttnState("sdpa", graph=(out, ql, kl, vl))
+    out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=Hq != Hkv)
+    return out.transpose(1, 2).reshape(B * S, Hq * hd), AttnState("sdpa")
+
+
+def attn_bwd(d_o, qk, qkv, state: AttnState, B, S, Hq, Hkv, hd):
+    """Returns dqkv (M, (Hq+2Hkv)*hd) bf16 = [dq (post-rope) | dk (post-rope) | dv]."""
+    M = B * S
+    dqkv = torch.empty(M, (Hq + 2 * Hkv) * hd, dtype=torch.bfloat16, device=d_o.device)
+    if state.impl == "sm100":
+        ops.ext().attn_bwd(d_o, qk, qkv, state.o, state.lse, dqkv, B, S, Hq, Hkv)
+        ops.count_launch(3)
+        return dqkv
+    out, ql, kl, vl = state.graph
+    g = d_o.view(B, S, Hq, hd).transpose(1, 2)
+    dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), g)
+    dqkv[:, :Hq * hd].view(B, S, Hq, hd).copy_(dq.transpose(1, 2))
+    dqkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, S, Hkv, hd).copy_(dk.transpose(1, 2))
+    dqkv[:, (Hq + Hkv) * hd:].view(B, S, Hkv, hd).copy_(dv.transpose(1, 2))
+    return dqkv

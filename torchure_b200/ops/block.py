@@ -1,0 +1,245 @@
+"""sm_100a execution engine of the decoder: one autograd node per transformer block.
+
+Forward of a block (all bf16 GEMMs on tcgen05, fp32 residual stream)::
+
+    x, h1   = add_rmsnorm(x_in, y_in)            # residual add of the previous sub-layer fused in
+    qkv     = h1 @ Wqkv^T                        # q, k, v projections as ONE GEMM (N = (Hq+2Hkv)*hd)
+    qk      = qknorm_rope(qkv)                   # per-head RMSNorm + RoPE in one pass
+    o       = attention(qk, qkv.v)               # causal GQA flash attention, emits LSE
+    y_a     = o @ Wo^T
+    x2, h2  = add_rmsnorm(x, y_a)
+    gu      = h2 @ [Wgate; Wup]^T                # gate and up as ONE GEMM (N = 2F)
+    y_out   = swiglu(gu) @ Wdown^T               # returned unadded: the next block's norm adds it
+
+Each block returns ``(x2, y_out)``; the sum is never materialised on its own.  Backward mirrors it
+with dgrad (B operand read MN-major, no transposes) and wgrad (both operands MN-major, fp32 output)
+GEMMs.  Weight gradients of the fused projections are returned as row slices of one buffer.
+
+The GEMMs read bf16 *shadow* copies of the fp32 master parameters.  Shadows of q/k/v (and gate/up) are
+adjacent rows of one buffer so the fused GEMM sees a single matrix.  The fused AdamW kernel rewrites the
+shadows at every step; ``refresh()`` re-casts any parameter whose version counter moved otherwise
+(initialisation, ``load_state_dict``, a foreign optimizer).
+"""
+
+from __future__ import annotations
+
+import weakref
+
+import torch
+
+from torchure_b200 import ops
+from torchure_b200.ops import attention as attn_ops
+from torchure_b200.ops import kernels as K
+
+BF16 = torch.bfloat16
+
+_ENGINE_OF_WEIGHT: "weakref.WeakValueDictionary[int, Sm100Engine]" = weakref.WeakValueDictionary()
+
+
+def engine_for_weight(weight: torch.Tensor):
+    return _ENGINE_OF_WEIGHT.get(id(weight))
+
+
+class _LayerShadow:
+    """bf16 compute copies of one block's matrices, laid out for the fused GEMMs."""
+
+    def __init__(self, block, device):
+        g, f = block.gqa, block.ffn
+        D = g.emb_dim
+        nq, nkv = g.num_heads * g.head_dim, g.num_kv_heads * g.head_dim
+        F_ = f.gate_proj.weight.shape[0]
+        self.wqkv = torch.empty(nq + 2 * nkv, D, dtype=BF16, device=device)
+        self.wo = torch.empty(D, nq, dtype=BF16, device=device)
+        self.wgu = torch.empty(2 * F_, D, dtype=BF16, device=device)
+        self.wd = torch.empty(D, F_, dtype=BF16, device=device)
+        self.pairs = [
+            (g.q_proj.weight, self.wqkv[:nq]), (g.k_proj.weight, self.wqkv[nq:nq + nkv]),
+            (g.v_proj.weight, self.wqkv[nq + nkv:]), (g.o_proj.weight, self.wo),
+            (f.gate_proj.weight, self.wgu[:F_]), (f.up_proj.weight, self.wgu[F_:]), (f.down_proj.weight, self.wd),
+        ]
+
+
+class Sm100Engine:
+    def __init__(self, model):
+        self.model = weakref.proxy(model)
+        cfg = model.cfg
+        self.cfg = cfg
+        dev = model.token_emb.weight.device
+        assert cfg["head_dim"] == 128, "the sm_100a engine supports head_dim 128"
+        assert cfg["emb_dim"] % 8 == 0 and cfg["ffn_dim"] % 8 == 0
+        self.layers = [_LayerShadow(b, dev) for b in model.blocks]
+        self.emb_shadow = torch.empty_like(model.token_emb.weight, dtype=BF16)
+        self._pairs = [p for layer in self.layers for p in layer.pairs] + [(model.token_emb.weight, self.emb_shadow)]
+        self.head_shadow = self.emb_shadow
+        if model.lm_head.weight is not model.token_emb.weight:
+            self.head_shadow = torch.empty_like(model.lm_head.weight, dtype=BF16)
+            self._pairs.append((model.lm_head.weight, self.head_shadow))
+        self._versions: dict[int, int] = {}
+        self._optimizer_owned = False
+        self.tied = model.lm_head.weight is model.token_emb.weight
+        self.pending_tied_grad = None      # CE's dW waiting for the embedding backward
+        self.expect_tied_grad = False
+        _ENGINE_OF_WEIGHT[id(model.lm_head.weight)] = self
+        self.dummy = torch.zeros(1, device=dev)
+
+    # -- shadows -----------------------------------------------------------------------------
+    def shadow_pairs(self):
+        """(fp32 parameter, bf16 shadow) pairs; the fused AdamW writes the shadow while it updates the master."""
+        self._optimizer_owned = True
+        return list(self._pairs)
+
+    def refresh(self) -> None:
+        for p, shadow in self._pairs:
+            v = p._version
+            if self._versions.get(id(p)) != v:
+                K.cast_to_bf16(p.detach(), shadow)
+                self._versions[id(p)] = v
+
+    def note_optimizer_step(self) -> None:
+        """The fused AdamW just rewrote every shadow together with its master."""
+        for p, _ in self._pairs:
+            self._versions[id(p)] = p._version
+
+    # -- forward -----------------------------------------------------------------------------
+    def forward_hidden(self, ids: torch.Tensor) -> torch.Tensor:
+        m = self.model
+        self.refresh()
+        B, S = ids.shape
+        cos, sin = m.rope.tables(S, ids.device)
+        x, y = None, None
+        flat_ids = ids.reshape(-1)
+        for i, (block, sh) in enumerate(zip(m.blocks, self.layers)):
+            g = block.gqa
+            qn = g.q_norm.weight if g.qk_norm else self.dummy
+            kn = g.k_norm.weight if g.qk_norm else self.dummy
+            first = i == 0
+            x, y = _BlockFn.apply(
+                self, sh, i, B, S, flat_ids if first else None,
+                m.token_emb.weight if first else None, x, y,
+                block.norm1.weight, g.q_proj.weight, g.k_proj.weight, g.v_proj.weight, g.o_proj.weight, qn, kn,
+                block.norm2.weight, block.ffn.gate_proj.weight, block.ffn.up_proj.weight, block.ffn.down_proj.weight)
+        h = _FinalNormFn.apply(x, y, m.norm.weight, m.norm.eps)
+        if self.tied and torch.is_grad_enabled() and m.token_emb.weight.requires_grad:
+            self.expect_tied_grad = True
+        return h.view(B, S, -1)
+
+    def lm_head(self, h: torch.Tensor) -> torch.Tensor:
+        m = self.model
+        B, S, D = h.shape
+        logits = _LinearFn.apply(h.reshape(B * S, D), m.lm_head.weight, self.head_shadow)
+        return logits.view(B, S, -1)
+
+
+class _BlockFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, eng, sh, layer_idx, B, S, ids, table, x_in, y_in, w1, wq, wk, wv, wo, qn, kn, w2, wg, wu, wd):
+        cfg = eng.cfg
+        Hq, Hkv, hd, eps = cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["norm_eps"]
+        use_norm = cfg["qk_norm"]
+        cos, sin = eng.model.rope.tables(S, w1.device)
+        if ids is not None:
+            x, h1, rstd1 = K.add_rmsnorm(None, None, w1, eps, ids=ids, table=table)
+        else:
+            x, h1, rstd1 = K.add_rmsnorm(x_in, y_in, w1, eps)
+        qkv = K.linear_fwd(h1, sh.wqkv)
+        qk = K.qknorm_rope(qkv, qn, kn, cos, sin, S, Hq, Hkv, eps, use_norm)
+        need_grad = any(ctx.needs_input_grad)
+        o, st = attn_ops.attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=need_grad)
+        y_a = K.linear_fwd(o, sh.wo)
+        x2, h2, rstd2 = K.add_rmsnorm(x, y_a, w2, eps)
+        gu = K.linear_fwd(h2, sh.wgu)
+        act = K.swiglu(gu)
+        y_out = K.linear_fwd(act, sh.wd)
+        ctx.eng, ctx.sh, ctx.dims = eng, sh, (B, S, Hq, Hkv, hd, eps, use_norm)
+        ctx.attn_state = st
+        ctx.first = ids is not None
+        ctx.save_for_backward(ids, x, h1, rstd1, qkv, qk, o, x2, h2, rstd2, gu, act, w1, qn, kn, w2, cos, sin)
+        return x2, y_out
+
+    @staticmethod
+    def backward(ctx, dx2, dy):
+        ids, x, h1, rstd1, qkv, qk, o, x2, h2, rstd2, gu, act, w1, qn, kn, w2, cos, sin = ctx.saved_tensors
+        eng, sh = ctx.eng, ctx.sh
+        B, S, Hq, Hkv, hd, eps, use_norm = ctx.dims
+        dev = x.device
+        D = x.shape[1]
+        nq, nkv = Hq * hd, Hkv * hd
+        # the consumer computed x2 + y_out, so both incoming grads carry the same values
+        if dy is None:
+            dy = dx2.to(BF16)
+        if dx2 is None:
+            dx2 = dy.float()
+        dy = dy.contiguous()
+        # ---- MLP
+        d_act = K.linear_dgrad(dy, sh.wd)
+        dwd = K.linear_wgrad(dy, act, out_dtype=torch.float32)
+        d_gu = K.swiglu_bwd(d_act, gu)
+        del d_act
+        d_h2 = K.linear_dgrad(d_gu, sh.wgu)
+        dwgu = K.linear_wgrad(d_gu, h2, out_dtype=torch.float32)
+        del d_gu
+        dw2 = torch.zeros(D, dtype=torch.float32, device=dev)
+        dx1, dx1_b = K.rmsnorm_bwd(d_h2, x2, w2, rstd2, dx2, dw2)
+        del d_h2
+        # ---- attention
+        d_o = K.linear_dgrad(dx1_b, sh.wo)
+        dwo = K.linear_wgrad(dx1_b, o, out_dtype=torch.float32)
+        dqkv = attn_ops.attn_bwd(d_o, qk, qkv, ctx.attn_state, B, S, Hq, Hkv, hd)
+        ctx.attn_state = None
+        del d_o
+        dqn = torch.zeros(hd, dtype=torch.float32, device=dev)
+        dkn = torch.zeros(hd, dtype=torch.float32, device=dev)
+        K.qknorm_rope_bwd_(dqkv, qkv, qn, kn, cos, sin, dqn, dkn, S, Hq, Hkv, eps, use_norm)
+        d_h1 = K.linear_dgrad(dqkv, sh.wqkv)
+        dwqkv = K.linear_wgrad(dqkv, h1, out_dtype=torch.float32)
+        del dqkv
+        dw1 = torch.zeros(D, dtype=torch.float32, device=dev)
+        want_prev = not ctx.first
+        dx0, dx0_b = K.rmsnorm_bwd(d_h1, x, w1, rstd1, dx1, dw1, want_bf16=want_prev)
+        d_table = None
+        if ctx.first and ctx.needs_input_grad[6]:
+            stash = eng.pending_tied_grad
+            if stash is not None:
+                eng.pending_tied_grad = None
+                d_table = stash  # the head's fp32 dW; the gather's gradient is added into the same buffer
+            else:
+                d_table = torch.zeros(eng.model.token_emb.weight.shape, dtype=torch.float32, device=dev)
+            K.embedding_bwd_(dx0, ids, d_table)
+        F_ = dwgu.shape[0] // 2
+        return (None, None, None, None, None, None, d_table,
+                dx0 if want_prev else None, dx0_b if want_prev else None,
+                dw1, dwqkv[:nq], dwqkv[nq:nq + nkv], dwqkv[nq + nkv:], dwo,
+                dqn if use_norm else None, dkn if use_norm else None,
+                dw2, dwgu[:F_], dwgu[F_:], dwd)
+
+
+class _FinalNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, y, w, eps):
+        x2, h, rstd = K.add_rmsnorm(x, y, w, eps)
+        ctx.save_for_backward(x2, w, rstd)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        x2, w, rstd = ctx.saved_tensors
+        dw = torch.zeros_like(w, dtype=torch.float32)
+        dx, dxb = K.rmsnorm_bwd(dh.contiguous().view(x2.shape).to(BF16), x2, w, rstd, None, dw)
+        return dx, dxb, dw, None
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x @ w^T on the bf16 shadow of an fp32 weight (lm_head when logits are requested)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, shadow):
+        ctx.save_for_backward(x, shadow)
+        return K.linear_fwd(x.contiguous(), shadow)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, shadow = ctx.saved_tensors
+        dy = dy.contiguous().to(BF16)
+        dx = K.linear_dgrad(dy, shadow) if ctx.needs_input_grad[0] else None
+        dw = K.linear_wgrad(dy, x, out_dtype=torch.float32) if ctx.needs_input_grad[1] else None
+        return dx, dw, None

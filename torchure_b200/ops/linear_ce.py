@@ -1,0 +1,91 @@
+"""Chunked fused linear + cross-entropy on sm_100a kernels.
+
+Per chunk of ``chunk_size`` rows (reference algorithm: ``torchure/loss/fused_linear_ce.py:31-93``):
+
+1. ``logits = h_chunk @ W^T``         tcgen05 GEMM, bf16 out (the only (chunk, V) buffer, reused by every chunk)
+2. ``ce_softmax_grad``                one kernel: online max/sum, target gather, per-row loss and, in place,
+                                      ``dlogits = (softmax - onehot) / n_valid`` in bf16 (zero for ignored rows)
+3. ``dH_chunk = dlogits @ W``         tcgen05 GEMM, B operand read MN-major
+4. ``dW (+)= dlogits^T @ h_chunk``    tcgen05 GEMM with fp32 output; the first chunk stores, later chunks
+                                      accumulate through TMA reduce-add, so there is no separate ``+=`` pass
+
+``n_valid`` is counted on the device before the loop, so the mean is folded into step 2 and backward only has
+to multiply by the incoming gradient, which a conditional kernel skips when it is exactly 1.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from torchure_b200 import ops
+from torchure_b200.ops import kernels as K
+
+BF16 = torch.bfloat16
+
+
+class _LinearCESm100(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, chunk_size, w_bf16, engine):
+        N, D = hidden.shape
+        V = weight.shape[0]
+        dev = hidden.device
+        h = hidden if hidden.dtype == BF16 else hidden.to(BF16)
+        h = h.contiguous()
+        n_valid = (labels != ignore_index).sum().clamp_min(1)
+        inv_n = (1.0 / n_valid.float()).reshape(1)
+        row_loss = torch.empty(N, dtype=torch.float32, device=dev)
+        need_dh = ctx.needs_input_grad[0]
+        need_dw = ctx.needs_input_grad[1]
+        d_hidden = torch.empty(N, D, dtype=BF16, device=dev) if need_dh else None
+        d_weight = torch.empty(V, D, dtype=torch.float32, device=dev) if need_dw else None
+        chunk = min(chunk_size, N)
+        ldl = (V + 7) // 8 * 8
+        logits_buf = torch.empty(chunk, ldl, dtype=BF16, device=dev)
+        for lo in range(0, N, chunk):
+            hi = min(N, lo + chunk)
+            hc = h[lo:hi]
+            logits = logits_buf[: hi - lo, :V]
+            K.gemm(hc, w_bf16, out=logits)
+            K.ce_softmax_grad_(logits, labels[lo:hi], row_loss[lo:hi], inv_n, ignore_index)
+            if need_dh:
+                K.gemm(logits, w_bf16, b_mn=True, out=d_hidden[lo:hi])
+            if need_dw:
+                K.gemm(logits, hc, a_mn=True, b_mn=True, out=d_weight, accumulate=lo > 0)
+        loss = row_loss.sum() * inv_n[0]
+        ctx.stash = (d_hidden, d_weight)
+        ctx.engine = engine
+        ctx.hidden_dtype = hidden.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        if ctx.stash is None:
+            raise RuntimeError("fused_linear_cross_entropy: backward ran twice; its grads are consumed in place")
+        d_hidden, d_weight = ctx.stash
+        ctx.stash = None
+        scale = grad_out.float().reshape(1)
+        if d_hidden is not None:
+            K.scale_inplace_(d_hidden, scale)
+            if ctx.hidden_dtype != BF16:
+                d_hidden = d_hidden.to(ctx.hidden_dtype)
+        if d_weight is not None:
+            K.scale_inplace_(d_weight, scale)
+            eng = ctx.engine
+            if eng is not None and eng.expect_tied_grad:
+                # tied embedding: hand the buffer to the gather's backward, which adds its rows and returns it
+                eng.expect_tied_grad = False
+                eng.pending_tied_grad = d_weight
+                d_weight = None
+        return d_hidden, d_weight, None, None, None, None, None
+
+
+def linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size):
+    from torchure_b200.ops.block import engine_for_weight
+
+    eng = engine_for_weight(weight)
+    if eng is not None:
+        eng.refresh()
+        w_bf16 = eng.head_shadow
+    else:
+        w_bf16 = K.cast_to_bf16(weight.detach().contiguous()) if weight.dtype != BF16 else weight.detach()
+    return _LinearCESm100.apply(hidden, weight, labels, ignore_index, chunk_size, w_bf16, eng)
