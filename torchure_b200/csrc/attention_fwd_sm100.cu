@@ -1,0 +1,317 @@
+// Causal GQA flash-attention forward for sm_100a (head_dim 128), tcgen05 + TMEM + TMA.
+//
+// One CTA owns 128 query positions of TWO query heads that share a KV head (GQA), so every K/V tile brought
+// into shared memory feeds four MMAs and both heads do identical causal work.  320 threads:
+//   warp 0      TMA producer: Q of both heads once, then a 2-stage ring of K_j / V_j tiles (128 keys each)
+//   warp 1      MMA issuer:   S_t = Q_t K_j^T (SS, 128x128x128)  and  O_t += P_t V_j (TS: P read from TMEM)
+//   warps 2-5   softmax of head 0, one thread per query row     } while one group runs exp2 on its S tile the
+//   warps 6-9   softmax of head 1                               } tensor core works on the other head's tiles
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  P (bf16) overwrites the first 64 columns of its
+// S tile and is consumed from there as the A operand of the second MMA, so probabilities never touch shared memory.
+// The running maximum is only refreshed when it grew by more than 2^8 (exact after the final 1/l normalisation),
+// which makes rescaling the TMEM accumulator a rare event.  LSE (natural log) is written for backward.
+#include "attn_api.h"
+#include "common.cuh"
+
+namespace tb {
+
+namespace {
+
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int TILE_BYTES = BQ * HD * 2;   // 32 KB: two 64-column halves of 16 KB
+constexpr int HALF_BYTES = 16384;
+constexpr int KV_STAGES = 2;
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 256 + 1024;
+constexpr int NUM_THREADS = 320;
+constexpr float RESCALE_THRESHOLD = 8.f;
+
+struct Bars {
+  uint64_t q_full;
+  uint64_t k_full[KV_STAGES];
+  uint64_t v_full[KV_STAGES];
+  uint64_t kv_empty[KV_STAGES];
+  uint64_t s_full[2];
+  uint64_t p_ready[2];
+  uint64_t o_done[2];
+  uint32_t tmem_slot;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
+                const __grid_constant__ CUtensorMap tmO, float* __restrict__ lse, int B, int S, int Hq, int Hkv,
+                float scale_log2, int* err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                        // [2][32 KB]
+  uint8_t* sKV = smem + 2 * TILE_BYTES;      // [stage][K 32 KB | V 32 KB]
+  Bars* bars = reinterpret_cast<Bars*>(sKV + KV_STAGES * 2 * TILE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = S / BQ;
+  const int ratio = Hq / Hkv;
+  const int pairs = ratio / 2;
+  const int groups = B * Hkv * pairs;
+  const int qblk = nblk - 1 - static_cast<int>(blockIdx.x) / groups;   // heaviest tiles first
+  int g = static_cast<int>(blockIdx.x) % groups;
+  const int pair = g % pairs; g /= pairs;
+  const int kvh = g % Hkv;
+  const int b = g / Hkv;
+  const int h0 = kvh * ratio + pair * 2;    // the two query heads of this CTA: h0, h0 + 1
+  const int row0 = b * S + qblk * BQ;       // first token row of the query tile
+  const int n_kv = qblk + 1;                // causal: KV blocks 0..qblk
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmO);
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_ready[t], 128);
+      mbar_init(&bars->o_done[t], 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (elect_one()) {
+      mbar_expect_tx(&bars->q_full, 2 * TILE_BYTES);
+      for (int t = 0; t < 2; ++t)
+        for (int hf = 0; hf < 2; ++hf)
+          tma_load_2d(sQ + t * TILE_BYTES + hf * HALF_BYTES, &tmQK, &bars->q_full, (h0 + t) * HD + hf * 64, row0);
+      const int kcol = (Hq + kvh) * HD, vcol = (Hq + Hkv + kvh) * HD;
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        if (!mbar_wait(&bars->kv_empty[s], ph ^ 1, err, kErrAttnWait)) break;
+        uint8_t* sK = sKV + s * 2 * TILE_BYTES;
+        uint8_t* sV = sK + TILE_BYTES;
+        const int krow = b * S + j * BKV;
+        mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
+        tma_load_2d(sK, &tmQK, &bars->k_full[s], kcol, krow);
+        tma_load_2d(sK + HALF_BYTES, &tmQK, &bars->k_full[s], kcol + 64, krow);
+        mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
+        tma_load_2d(sV, &tmV, &bars->v_full[s], vcol, krow);
+        tma_load_2d(sV + HALF_BYTES, &tmV, &bars->v_full[s], vcol + 64, krow);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
+      auto issue_s = [&](int t, int stage) {
+        const uint32_t qa = smem_u32(sQ + t * TILE_BYTES);
+        const uint32_t ka = smem_u32(sKV + stage * 2 * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t o = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_f16_ss(tmem_base + t * 128, make_desc_sw128(qa + o, 16, 1024), make_desc_sw128(ka + o, 16, 1024),
+                      idesc_s, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->s_full[t]);
+      };
+      auto issue_pv = [&](int t, int stage, bool first) {
+        const uint32_t va = smem_u32(sKV + stage * 2 * TILE_BYTES + TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8,
+                      make_desc_sw128(va + ks * 2048, HALF_BYTES, 1024), idesc_pv, (first && ks == 0) ? 0u : 1u);
+        }
+        umma_commit(&bars->o_done[t]);
+      };
+      bool ok = mbar_wait(&bars->q_full, 0, err, kErrAttnWait);
+      ok = ok && mbar_wait(&bars->k_full[0], 0, err, kErrAttnWait);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        issue_s(1, 0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        const int sn = (j + 1) % KV_STAGES;
+        const uint32_t phn = ((j + 1) / KV_STAGES) & 1;
+        const bool more = j + 1 < n_kv;
+        if (!mbar_wait(&bars->v_full[s], ph, err, kErrAttnWait)) { ok = false; break; }
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (!mbar_wait(&bars->p_ready[t], j & 1, err, kErrAttnWait)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(t, s, j == 0);
+          if (t == 1) umma_commit(&bars->kv_empty[s]);
+          if (more) {
+            if (t == 0 && !mbar_wait(&bars->k_full[sn], phn, err, kErrAttnWait)) { ok = false; break; }
+            tc_fence_after();
+            issue_s(t, sn);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------ softmax + epilogue
+    const int t = (warp - 2) >> 2;          // which head of the pair
+    const int quarter = warp & 3;           // TMEM lane quarter of this warp
+    const int row = quarter * 32 + lane;    // query row inside the tile
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_sel + t * 128;
+    const uint32_t tO = tmem_base + lane_sel + 256 + t * 128;
+    float m_used = -1e30f, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(&bars->s_full[t], j & 1, err, kErrAttnWait)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = j == n_kv - 1;
+      uint32_t v[32];
+      float mx = -1e30f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_32x32b_x32(tS + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float sv = __uint_as_float(v[i]);
+          if (!diag || c * 32 + i <= row) mx = fmaxf(mx, sv);
+        }
+      }
+      const float m_new = mx * scale_log2;
+      if (j == 0) {
+        m_used = m_new;
+      } else {
+        const bool need = m_new > m_used + RESCALE_THRESHOLD;
+        if (__any_sync(0xffffffffu, need)) {
+          if (!mbar_wait(&bars->o_done[t], (j - 1) & 1, err, kErrAttnWait)) { ok = false; break; }
+          tc_fence_after();
+          const float alpha = need ? fast_exp2(m_used - m_new) : 1.f;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_32x32b_x32(tO + c * 32, v);
+            tmem_ld_wait();
+            uint32_t lo[16], hi[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              lo[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+              hi[i] = __float_as_uint(__uint_as_float(v[16 + i]) * alpha);
+            }
+            tmem_st_32x32b_x16(tO + c * 32, lo);
+            tmem_st_32x32b_x16(tO + c * 32 + 16, hi);
+          }
+          tmem_st_wait();
+          l *= alpha;
+          if (need) m_used = m_new;
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_32x32b_x32(tS + c * 32, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = fast_exp2(__uint_as_float(v[2 * i]) * scale_log2 - m_used);
+          float p1 = fast_exp2(__uint_as_float(v[2 * i + 1]) * scale_log2 - m_used);
+          if (diag) {
+            if (c * 32 + 2 * i > row) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+          }
+          l += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x32b_x16(tS + c * 16, pk);   // P chunk c lands on S columns already consumed
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready[t]);
+    }
+    if (ok && mbar_wait(&bars->o_done[t], (n_kv - 1) & 1, err, kErrAttnWait)) {
+      tc_fence_after();
+      const float inv_l = 1.f / l;
+      lse[(static_cast<int64_t>(b) * Hq + h0 + t) * S + qblk * BQ + row] = (m_used + log2f(l)) * 0.6931471805599453f;
+      uint8_t* stage = sQ + t * TILE_BYTES + quarter * 8192;   // this head's Q tile is dead: reuse it for staging
+      uint32_t v[32];
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_32x32b_x32(tO + c * 32, v);
+        tmem_ld_wait();
+        uint8_t* rowp = stage + (c >> 1) * 4096 + lane * 128;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint4 pk;
+          pk.x = pack_bf16x2(__uint_as_float(v[8 * jj + 0]) * inv_l, __uint_as_float(v[8 * jj + 1]) * inv_l);
+          pk.y = pack_bf16x2(__uint_as_float(v[8 * jj + 2]) * inv_l, __uint_as_float(v[8 * jj + 3]) * inv_l);
+          pk.z = pack_bf16x2(__uint_as_float(v[8 * jj + 4]) * inv_l, __uint_as_float(v[8 * jj + 5]) * inv_l);
+          pk.w = pack_bf16x2(__uint_as_float(v[8 * jj + 6]) * inv_l, __uint_as_float(v[8 * jj + 7]) * inv_l);
+          const int chunk = (c & 1) * 4 + jj;   // 16-byte chunk inside the 128-byte row
+          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7)) << 4)) = pk;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&tmO, stage, (h0 + t) * HD, row0 + quarter * 32);
+        tma_store_2d(&tmO, stage + 4096, (h0 + t) * HD + 64, row0 + quarter * 32);
+        tma_commit_group();
+        tma_wait_group<0>();
+      }
+    }
+  }
+
+  if (*reinterpret_cast<volatile int*>(err) != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows, uint32_t box_cols);
+
+int attn_fwd(const void* qk, const void* qkv, void* o, float* lse, int B, int S, int Hq, int Hkv, int* err,
+             cudaStream_t stream) {
+  if (S % 128 != 0 || Hq % Hkv != 0 || (Hq / Hkv) % 2 != 0) return -1;
+  const uint64_t M = static_cast<uint64_t>(B) * S;
+  CUtensorMap tq, tv, to;
+  int r = make_tmap_2d(&tq, qk, 2, M, static_cast<uint64_t>(Hq + Hkv) * HD, static_cast<uint64_t>(Hq + Hkv) * HD, 128, 64);
+  if (r) return r;
+  r = make_tmap_2d(&tv, qkv, 2, M, static_cast<uint64_t>(Hq + 2 * Hkv) * HD, static_cast<uint64_t>(Hq + 2 * Hkv) * HD, 128, 64);
+  if (r) return r - 100;
+  r = make_tmap_2d(&to, o, 2, M, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(Hq) * HD, 32, 64);
+  if (r) return r - 200;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
+    configured = true;
+  }
+  const int grid = (S / 128) * B * Hkv * ((Hq / Hkv) / 2);
+  const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
+  attn_fwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tq, tv, to, lse, B, S, Hq, Hkv, scale_log2, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace tb

@@ -1,3 +1,38 @@
+// Python bindings of the attention kernels.
+#include <ATen/cuda/CUDAContext.h>
 #include <torch/extension.h>
+
 #include "attn_api.h"
-void register_attn(pybind11::module_& m) { (void)m; }
+
+torch::Tensor attn_err_word();
+
+void register_attn(pybind11::module_& m) {
+  m.def("attn_fwd", [](const torch::Tensor& qk, const torch::Tensor& qkv, torch::Tensor& o, torch::Tensor& lse,
+                       int64_t B, int64_t S, int64_t Hq, int64_t Hkv) {
+    TORCH_CHECK(qk.is_contiguous() && qkv.is_contiguous() && o.is_contiguous() && lse.is_contiguous());
+    TORCH_CHECK(qk.size(1) == (Hq + Hkv) * 128 && qkv.size(1) == (Hq + 2 * Hkv) * 128, "attention: head_dim 128 layout");
+    const int rc = tb::attn_fwd(qk.data_ptr(), qkv.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), (int)B, (int)S,
+                                (int)Hq, (int)Hkv, attn_err_word().data_ptr<int>(),
+                                at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(rc == 0, "attn_fwd failed with code ", rc);
+  });
+  m.def("attn_bwd", [](const torch::Tensor& d_o, const torch::Tensor& qk, const torch::Tensor& qkv,
+                       const torch::Tensor& o, const torch::Tensor& lse, torch::Tensor& dqkv, int64_t B, int64_t S,
+                       int64_t Hq, int64_t Hkv) {
+    TORCH_CHECK(d_o.is_contiguous() && qk.is_contiguous() && qkv.is_contiguous() && o.is_contiguous() &&
+                lse.is_contiguous() && dqkv.is_contiguous());
+    auto stream = at::cuda::getCurrentCUDAStream().stream();
+    // scratch: per-row statistics shared by the dQ and dK/dV kernels
+    torch::Tensor scratch = torch::empty({2, B * Hq * S}, lse.options());
+    float* delta = scratch.data_ptr<float>();
+    float* lse2 = delta + B * Hq * S;
+    int* err = attn_err_word().data_ptr<int>();
+    tb::attn_bwd_prep(d_o.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), delta, lse2, (int)B, (int)S, (int)Hq, stream);
+    int rc = tb::attn_bwd_dq(qk.data_ptr(), qkv.data_ptr(), d_o.data_ptr(), dqkv.data_ptr(), delta, lse2, (int)B, (int)S,
+                             (int)Hq, (int)Hkv, err, stream);
+    TORCH_CHECK(rc == 0, "attn_bwd_dq failed with code ", rc);
+    rc = tb::attn_bwd_dkv(qk.data_ptr(), qkv.data_ptr(), d_o.data_ptr(), dqkv.data_ptr(), delta, lse2, (int)B, (int)S,
+                          (int)Hq, (int)Hkv, err, stream);
+    TORCH_CHECK(rc == 0, "attn_bwd_dkv failed with code ", rc);
+  });
+}

@@ -158,6 +158,8 @@ torch::Tensor error_word() { return err_word(); }
 
 }  // namespace
 
+torch::Tensor attn_err_word() { return err_word(); }
+
 void register_comm(pybind11::module_& m);
 void register_attn(pybind11::module_& m);
 

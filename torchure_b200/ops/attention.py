@@ -28,7 +28,7 @@ _FORCE = os.environ.get("TORCHURE_B200_ATTN", "")  # "sdpa" forces the library p
 
 def kernel_supported(S: int, Hq: int, Hkv: int, hd: int) -> bool:
     ext = ops.ext()
-    if _FORCE == "sdpa" or ext is None or not hasattr(ext, "attn_fwd"):
+    if _FORCE == "sdpa" or ext is None or not (hasattr(ext, "attn_fwd") and hasattr(ext, "attn_bwd")):
         return False
     return hd == 128 and S % 128 == 0 and Hq % Hkv == 0 and (Hq // Hkv) % 2 == 0
 
