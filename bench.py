@@ -152,8 +152,10 @@ def timed_steps(step_fn, k: int, read_loss: bool):
         if read_loss:
             last = float(out["loss"].item())  # device-to-host read of the step's result
     stop.record()
+    enqueue_ms = (time.perf_counter() - t0) * 1e3  # host time to enqueue the k steps
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
+    timed_steps.last_enqueue_ms = enqueue_ms
     dist.barrier()
     return start.elapsed_time(stop), wall_ms, last
 
@@ -190,6 +192,7 @@ def run_ours(args) -> None:
     ops.reset_launches()
     dev_ms, _, _ = timed_steps(step, args.steps, read_loss=False)
     launches = ops.launches()
+    host_enqueue_ms = timed_steps.last_enqueue_ms / args.steps
     e2e_ms, _, last_loss = timed_steps(step, args.steps, read_loss=True)
     clocks = sampler.stop() if rank == 0 else None
     dev_ms, e2e_ms = max_over_ranks(dev_ms), max_over_ranks(e2e_ms)
@@ -213,7 +216,7 @@ def run_ours(args) -> None:
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": trainer.prefetcher.h2d_bytes * trainer.microbatches_per_step,
                     "d2h_bytes_per_step": 4, "last_loss": last_loss},
-            "gpu_launches": launches, "clocks": clocks,
+            "gpu_launches": launches, "host_enqueue_ms_per_step": host_enqueue_ms, "clocks": clocks,
             "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
         }), flush=True)
     dist.destroy_process_group()

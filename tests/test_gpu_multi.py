@@ -1,0 +1,119 @@
+"""Multi-GPU: NVLink collective kernels (peer loads/stores and multimem) against closed forms, and the fused DDP
+reducer against a single-process run.  One process per GPU; skipped with fewer than 2 GPUs."""
+
+import pytest
+import torch
+
+from tests.gpu_dist_utils import run_on_gpus
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+CFG = dict(num_layers=2, num_heads=4, num_kv_heads=2, emb_dim=512, head_dim=128, vocab_size=4096, ffn_dim=1024)
+
+
+def _world():
+    return min(torch.cuda.device_count(), 8)
+
+
+def _collectives(rank, world):
+    from torchure_b200.core import collective as C
+    from torchure_b200.core.mesh import Mesh
+
+    mesh = Mesh({"dp": world})
+    comm = C.enable_sm100(mesh, "dp", 64 << 20)
+    assert comm is not None
+    tri = world * (world + 1) / 2
+    for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 2e-2)):
+        for n in (5, 1024, 70_000, 3_000_001):
+            base = (torch.arange(n, device="cuda") % 251).float() / 251.0
+            x = (base * (rank + 1)).to(dtype)
+            C.all_reduce(x, mesh, "dp", "sum")
+            torch.testing.assert_close(x.float(), (base.to(dtype).float() * tri), rtol=tol, atol=tol * tri)
+            x = (base * (rank + 1)).to(dtype)
+            C.all_reduce(x, mesh, "dp", "avg")
+            torch.testing.assert_close(x.float(), base.to(dtype).float() * tri / world, rtol=tol, atol=tol)
+            x = (base * (rank + 1)).to(dtype)
+            C.all_reduce(x, mesh, "dp", "max")
+            torch.testing.assert_close(x.float(), (base * world).to(dtype).float(), rtol=tol, atol=tol)
+        # broadcast from coordinate 1
+        x = torch.full((1000,), float(rank), device="cuda", dtype=dtype)
+        C.broadcast(x, mesh, "dp", src=1)
+        assert (x == 1).all()
+        # all_gather / reduce_scatter / all_to_all
+        x = torch.full((3, 5), float(rank), device="cuda", dtype=dtype)
+        g = C.all_gather(x, mesh, "dp", 0)
+        assert g.shape == (3 * world, 5)
+        for r in range(world):
+            assert (g[3 * r:3 * r + 3] == r).all()
+        full = (torch.arange(world * 7, device="cuda").float() * (rank + 1)).to(dtype)
+        rs = C.reduce_scatter(full, mesh, "dp", "sum")
+        want = torch.arange(world * 7, device="cuda").float()[rank * 7:(rank + 1) * 7] * tri
+        torch.testing.assert_close(rs.float(), want, rtol=2e-2, atol=1.0 if dtype == torch.bfloat16 else 1e-4)
+        x = torch.tensor([[rank * 100.0 + j] * 4 for j in range(world)], device="cuda", dtype=dtype)
+        a2a = C.all_to_all(x, mesh, "dp", 0, 0)
+        want = torch.tensor([[s * 100.0 + rank] * 4 for s in range(world)], device="cuda", dtype=dtype)
+        torch.testing.assert_close(a2a, want)
+    comm.check()
+
+
+def test_collectives_nvls():
+    run_on_gpus(_collectives, _world())
+
+
+def test_collectives_peer_loads_only():
+    run_on_gpus(_collectives, _world(), env={"TORCHURE_B200_NVLS": "0"})
+
+
+def _ddp_parity(rank, world):
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.models import Qwen3
+    from torchure_b200.objectives import ARObjective
+    from torchure_b200.parallel.ddp import DDP
+
+    mesh = Mesh({"dp": world})
+    torch.manual_seed(100 + rank)  # different init per rank: the constructor must replicate rank 0
+    model = Qwen3(**CFG).cuda()
+    model.init_weights()
+    ddp = DDP(model, mesh, "dp", bucket_mb=1)
+    assert ddp.fused
+    torch.manual_seed(100)
+    single = Qwen3(**CFG).cuda()
+    single.init_weights()
+    for (n, p), (_, q) in zip(model.named_parameters(), single.named_parameters()):
+        assert torch.equal(p, q), n
+    obj = ARObjective(fused_linear_ce=True, ce_chunk_size=256)
+    K = 2
+    for cycle in range(2):
+        ids = torch.randint(0, CFG["vocab_size"], (K, world, 2, 128), device="cuda",
+                            generator=torch.Generator("cuda").manual_seed(cycle))
+        model.zero_grad()
+        single.zero_grad()
+        for k in range(K):
+            ddp.requires_sync = k == K - 1
+            obj.compute_loss(model, {"input_ids": ids[k, rank], "labels": ids[k, rank]}, loss_scale=1 / K).backward()
+        ddp.sync()
+        for k in range(K):
+            flat = ids[k].reshape(world * 2, 128)
+            (obj.compute_loss(single, {"input_ids": flat, "labels": flat}) / K).backward()
+        total = 0.0
+        for (n, p), (_, q) in zip(model.named_parameters(), single.named_parameters()):
+            err = ((p.grad - q.grad).norm() / q.grad.norm().clamp_min(1e-12)).item()
+            assert err < 2e-2, (n, cycle, err)
+            total += p.grad.double().pow(2).sum().item()
+        sq = ddp.sq_norm().item()
+        assert abs(sq - total) < 1e-3 * total, (sq, total)
+        # every rank holds bit-identical reduced gradients and the same norm
+        check = torch.tensor([sq], device="cuda", dtype=torch.float64)
+        lo, hi = check.clone(), check.clone()
+        torch.distributed.all_reduce(lo, op=torch.distributed.ReduceOp.MIN)
+        torch.distributed.all_reduce(hi, op=torch.distributed.ReduceOp.MAX)
+        assert lo.item() == hi.item()
+    ddp.reducer.comm.check()
+
+
+def test_fused_ddp_matches_single_process():
+    run_on_gpus(_ddp_parity, min(_world(), 4))
+
+
+def test_fused_ddp_peer_loads_only():
+    run_on_gpus(_ddp_parity, 2, env={"TORCHURE_B200_NVLS": "0"})

@@ -65,8 +65,9 @@ class _LinearCE(torch.autograd.Function):
 
 
 def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
-                               ignore_index: int = -100, chunk_size: int = 1024) -> torch.Tensor:
-    """hidden (B,S,D) or (N,D); weight (V,D); labels already shifted, (B,S) or (N,)."""
+                               ignore_index: int = -100, chunk_size: int = 1024, loss_scale: float = 1.0) -> torch.Tensor:
+    """hidden (B,S,D) or (N,D); weight (V,D); labels already shifted, (B,S) or (N,).  Returns mean CE * loss_scale
+    (the scale is folded into the gradients that are computed during the forward pass)."""
     if hidden.dim() == 3:
         hidden = hidden.reshape(-1, hidden.shape[-1])
         labels = labels.reshape(-1)
@@ -76,5 +77,6 @@ def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, label
         if ops.available():
             from torchure_b200.ops.linear_ce import linear_ce_sm100
 
-            return linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size)
-    return _LinearCE.apply(hidden, weight, labels, ignore_index, chunk_size)
+            return linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size, loss_scale)
+    loss = _LinearCE.apply(hidden, weight, labels, ignore_index, chunk_size)
+    return loss if loss_scale == 1.0 else loss * loss_scale

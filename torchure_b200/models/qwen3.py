@@ -184,6 +184,7 @@ class Qwen3(nn.Module):
         if tie_embeddings:
             self.lm_head.weight = self.token_emb.weight
         self._engine = None  # sm100 execution state (bf16 shadow weights), built lazily
+        self._grad_sink = None  # object with grad_dest(p) / grad_written(p): where the engine writes weight grads
 
     # -- init ----------------------------------------------------------------------------
     @torch.no_grad()
@@ -207,6 +208,21 @@ class Qwen3(nn.Module):
         from torchure_b200 import ops
 
         return ops.available()
+
+    def fused_param_groups(self):
+        """Parameters whose gradients one fused GEMM produces (rows of Wqkv, rows of [Wgate; Wup]).  A gradient
+        sink that lays each group out contiguously, in this order, receives them with a single wgrad launch."""
+        groups = []
+        for b in self.blocks:
+            groups.append((b.gqa.q_proj.weight, b.gqa.k_proj.weight, b.gqa.v_proj.weight))
+            groups.append((b.ffn.gate_proj.weight, b.ffn.up_proj.weight))
+        return groups
+
+    def set_grad_sink(self, sink) -> None:
+        """Route weight gradients of the sm_100a path straight into `sink` (fused DDP buckets) instead of returning
+        them through autograd.  With a sink installed the loss must be the root of backward (incoming gradient 1):
+        fold any scaling into ``compute_loss(..., loss_scale=)``."""
+        self._grad_sink = sink
 
     def engine(self):
         if self._engine is None:

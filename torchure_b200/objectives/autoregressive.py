@@ -13,11 +13,14 @@ class ARObjective:
         self.fused_linear_ce = fused_linear_ce
         self.ce_chunk_size = ce_chunk_size
 
-    def compute_loss(self, model, batch: dict[str, torch.Tensor]) -> torch.Tensor:
+    def compute_loss(self, model, batch: dict[str, torch.Tensor], loss_scale: float = 1.0) -> torch.Tensor:
+        """Mean next-token CE times `loss_scale` (1/micro-batches under gradient accumulation: folding it here
+        keeps the loss the root of backward, which the fused gradient paths rely on)."""
         if self.fused_linear_ce:
             hidden = model(batch["input_ids"], return_final_hidden=True)
             labels = shift_labels(batch["labels"], self.ignore_index)
             return fused_linear_cross_entropy(hidden, model.lm_head.weight, labels, self.ignore_index,
-                                              self.ce_chunk_size)
+                                              self.ce_chunk_size, loss_scale)
         logits = model(batch["input_ids"])
-        return cross_entropy_loss(batch["labels"], logits, self.ignore_index)
+        loss = cross_entropy_loss(batch["labels"], logits, self.ignore_index)
+        return loss if loss_scale == 1.0 else loss * loss_scale

@@ -52,6 +52,10 @@ class _LayerShadow:
         self.wo = torch.empty(D, nq, dtype=BF16, device=device)
         self.wgu = torch.empty(2 * F_, D, dtype=BF16, device=device)
         self.wd = torch.empty(D, F_, dtype=BF16, device=device)
+        self.params = dict(w1=block.norm1.weight, wq=g.q_proj.weight, wk=g.k_proj.weight, wv=g.v_proj.weight,
+                           wo=g.o_proj.weight, qn=g.q_norm.weight if g.qk_norm else None,
+                           kn=g.k_norm.weight if g.qk_norm else None, w2=block.norm2.weight,
+                           wg=f.gate_proj.weight, wu=f.up_proj.weight, wd=f.down_proj.weight, table=None)
         self.pairs = [
             (g.q_proj.weight, self.wqkv[:nq]), (g.k_proj.weight, self.wqkv[nq:nq + nkv]),
             (g.v_proj.weight, self.wqkv[nq + nkv:]), (g.o_proj.weight, self.wo),
@@ -118,7 +122,7 @@ class Sm100Engine:
                 m.token_emb.weight if first else None, x, y,
                 block.norm1.weight, g.q_proj.weight, g.k_proj.weight, g.v_proj.weight, g.o_proj.weight, qn, kn,
                 block.norm2.weight, block.ffn.gate_proj.weight, block.ffn.up_proj.weight, block.ffn.down_proj.weight)
-        h = _FinalNormFn.apply(x, y, m.norm.weight, m.norm.eps)
+        h = _FinalNormFn.apply(x, y, m.norm.weight, m.norm.eps, self)
         if self.tied and torch.is_grad_enabled() and m.token_emb.weight.requires_grad:
             self.expect_tied_grad = True
         return h.view(B, S, -1)
@@ -161,8 +165,10 @@ class _BlockFn(torch.autograd.Function):
         ids, x, h1, rstd1, qkv, qk, o, x2, h2, rstd2, gu, act, w1, qn, kn, w2, cos, sin = ctx.saved_tensors
         eng, sh = ctx.eng, ctx.sh
         B, S, Hq, Hkv, hd, eps, use_norm = ctx.dims
-        dev = x.device
-        D = x.shape[1]
+        P = dict(sh.params)  # the nn.Parameter objects, which is what a gradient sink is keyed by
+        if ctx.first:
+            P["table"] = eng.model.token_emb.weight
+        out = _GradOut(eng.model._grad_sink, x.device)
         nq, nkv = Hq * hd, Hkv * hd
         # the consumer computed x2 + y_out, so both incoming grads carry the same values
         if dy is None:
@@ -172,60 +178,130 @@ class _BlockFn(torch.autograd.Function):
         dy = dy.contiguous()
         # ---- MLP
         d_act = K.linear_dgrad(dy, sh.wd)
-        dwd = K.linear_wgrad(dy, act, out_dtype=torch.float32)
+        out.wgrad((P["wd"],), dy, act)
         d_gu = K.swiglu_bwd(d_act, gu)
         del d_act
         d_h2 = K.linear_dgrad(d_gu, sh.wgu)
-        dwgu = K.linear_wgrad(d_gu, h2, out_dtype=torch.float32)
+        out.wgrad((P["wg"], P["wu"]), d_gu, h2)
         del d_gu
-        dw2 = torch.zeros(D, dtype=torch.float32, device=dev)
+        dw2 = out.small(P["w2"])
         dx1, dx1_b = K.rmsnorm_bwd(d_h2, x2, w2, rstd2, dx2, dw2)
+        out.done(P["w2"])
         del d_h2
         # ---- attention
         d_o = K.linear_dgrad(dx1_b, sh.wo)
-        dwo = K.linear_wgrad(dx1_b, o, out_dtype=torch.float32)
+        out.wgrad((P["wo"],), dx1_b, o)
         dqkv = attn_ops.attn_bwd(d_o, qk, qkv, ctx.attn_state, B, S, Hq, Hkv, hd)
         ctx.attn_state = None
         del d_o
-        dqn = torch.zeros(hd, dtype=torch.float32, device=dev)
-        dkn = torch.zeros(hd, dtype=torch.float32, device=dev)
+        if use_norm:
+            dqn, dkn = out.small(P["qn"]), out.small(P["kn"])
+        else:
+            dqn = dkn = eng.dummy
         K.qknorm_rope_bwd_(dqkv, qkv, qn, kn, cos, sin, dqn, dkn, S, Hq, Hkv, eps, use_norm)
+        if use_norm:
+            out.done(P["qn"])
+            out.done(P["kn"])
         d_h1 = K.linear_dgrad(dqkv, sh.wqkv)
-        dwqkv = K.linear_wgrad(dqkv, h1, out_dtype=torch.float32)
+        out.wgrad((P["wq"], P["wk"], P["wv"]), dqkv, h1)
         del dqkv
-        dw1 = torch.zeros(D, dtype=torch.float32, device=dev)
+        dw1 = out.small(P["w1"])
         want_prev = not ctx.first
         dx0, dx0_b = K.rmsnorm_bwd(d_h1, x, w1, rstd1, dx1, dw1, want_bf16=want_prev)
-        d_table = None
+        out.done(P["w1"])
         if ctx.first and ctx.needs_input_grad[6]:
+            table = P["table"]
             stash = eng.pending_tied_grad
+            eng.pending_tied_grad = None
             if stash is not None:
-                eng.pending_tied_grad = None
-                d_table = stash  # the head's fp32 dW; the gather's gradient is added into the same buffer
+                d_table = stash  # the head's fp32 dW (possibly the sink's slice); the gather's rows are added to it
+            elif out.sink is not None:
+                d_table, acc = out.sink.grad_dest(table)
+                if not acc:
+                    d_table.zero_()
             else:
-                d_table = torch.zeros(eng.model.token_emb.weight.shape, dtype=torch.float32, device=dev)
+                d_table = torch.zeros(table.shape, dtype=torch.float32, device=x.device)
             K.embedding_bwd_(dx0, ids, d_table)
-        F_ = dwgu.shape[0] // 2
-        return (None, None, None, None, None, None, d_table,
+            if out.sink is not None:
+                out.sink.grad_written(table)
+            else:
+                out.grads[table] = d_table
+        g = out.grads.get
+        return (None, None, None, None, None, None, g(P.get("table")),
                 dx0 if want_prev else None, dx0_b if want_prev else None,
-                dw1, dwqkv[:nq], dwqkv[nq:nq + nkv], dwqkv[nq + nkv:], dwo,
-                dqn if use_norm else None, dkn if use_norm else None,
-                dw2, dwgu[:F_], dwgu[F_:], dwd)
+                g(P["w1"]), g(P["wq"]), g(P["wk"]), g(P["wv"]), g(P["wo"]),
+                g(P["qn"]) if use_norm else None, g(P["kn"]) if use_norm else None,
+                g(P["w2"]), g(P["wg"]), g(P["wu"]), g(P["wd"]))
+
+
+class _GradOut:
+    """Where a block's weight gradients go: into the gradient sink (fused DDP buckets) when one is installed,
+    otherwise into fresh fp32 tensors handed back to autograd."""
+
+    def __init__(self, sink, device):
+        self.sink = sink
+        self.device = device
+        self.grads: dict = {}
+
+    def wgrad(self, params: tuple, dy: torch.Tensor, x: torch.Tensor) -> None:
+        """dW[N, K] = dy[M, N]^T x[M, K]; `params` are the parameters whose rows make up N, in order."""
+        rows = [p.shape[0] for p in params]
+        if self.sink is None:
+            dw = K.linear_wgrad(dy, x, out_dtype=torch.float32)
+            at = 0
+            for p, r in zip(params, rows):
+                self.grads[p] = dw[at:at + r]
+                at += r
+            return
+        dests = [self.sink.grad_dest(p) for p in params]
+        contiguous = all(dests[i][0].data_ptr() + dests[i][0].numel() * 4 == dests[i + 1][0].data_ptr()
+                         for i in range(len(dests) - 1))
+        same_mode = all(d[1] == dests[0][1] for d in dests)
+        if contiguous and same_mode:
+            first = dests[0][0]
+            whole = torch.as_strided(first, (sum(rows), first.shape[1]), (first.shape[1], 1))
+            K.linear_wgrad(dy, x, out=whole, accumulate=dests[0][1])
+        else:
+            at = 0
+            for (dst, acc), r in zip(dests, rows):
+                K.linear_wgrad(dy[:, at:at + r], x, out=dst, accumulate=acc)
+                at += r
+        for p in params:
+            self.sink.grad_written(p)
+
+    def small(self, p: torch.Tensor) -> torch.Tensor:
+        """Zeroed (or running) fp32 destination for a gain gradient that a kernel accumulates with atomics."""
+        if self.sink is None:
+            t = torch.zeros(p.shape, dtype=torch.float32, device=self.device)
+            self.grads[p] = t
+            return t
+        dst, acc = self.sink.grad_dest(p)
+        if not acc:
+            dst.zero_()
+        return dst
+
+    def done(self, p: torch.Tensor) -> None:
+        if self.sink is not None:
+            self.sink.grad_written(p)
 
 
 class _FinalNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, y, w, eps):
+    def forward(ctx, x, y, w, eps, eng):
         x2, h, rstd = K.add_rmsnorm(x, y, w, eps)
-        ctx.save_for_backward(x2, w, rstd)
+        ctx.save_for_backward(x2, rstd)
+        ctx.eng = eng
         return h
 
     @staticmethod
     def backward(ctx, dh):
-        x2, w, rstd = ctx.saved_tensors
-        dw = torch.zeros_like(w, dtype=torch.float32)
-        dx, dxb = K.rmsnorm_bwd(dh.contiguous().view(x2.shape).to(BF16), x2, w, rstd, None, dw)
-        return dx, dxb, dw, None
+        x2, rstd = ctx.saved_tensors
+        w = ctx.eng.model.norm.weight
+        out = _GradOut(ctx.eng.model._grad_sink, x2.device)
+        dw = out.small(w)
+        dx, dxb = K.rmsnorm_bwd(dh.contiguous().view(x2.shape).to(BF16), x2, w.detach(), rstd, None, dw)
+        out.done(w)
+        return dx, dxb, out.grads.get(w), None, None
 
 
 class _LinearFn(torch.autograd.Function):

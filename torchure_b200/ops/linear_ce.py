@@ -25,19 +25,23 @@ BF16 = torch.bfloat16
 
 class _LinearCESm100(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden, weight, labels, ignore_index, chunk_size, w_bf16, engine):
+    def forward(ctx, hidden, weight, labels, ignore_index, chunk_size, w_bf16, engine, loss_scale, sink_dest):
         N, D = hidden.shape
         V = weight.shape[0]
         dev = hidden.device
         h = hidden if hidden.dtype == BF16 else hidden.to(BF16)
         h = h.contiguous()
         n_valid = (labels != ignore_index).sum().clamp_min(1)
-        inv_n = (1.0 / n_valid.float()).reshape(1)
+        inv_n = (loss_scale / n_valid.float()).reshape(1)
         row_loss = torch.empty(N, dtype=torch.float32, device=dev)
         need_dh = ctx.needs_input_grad[0]
         need_dw = ctx.needs_input_grad[1]
         d_hidden = torch.empty(N, D, dtype=BF16, device=dev) if need_dh else None
-        d_weight = torch.empty(V, D, dtype=torch.float32, device=dev) if need_dw else None
+        acc0 = False
+        if need_dw and sink_dest is not None:
+            d_weight, acc0 = sink_dest  # the fused DDP bucket slice of the weight: written in place
+        else:
+            d_weight = torch.empty(V, D, dtype=torch.float32, device=dev) if need_dw else None
         chunk = min(chunk_size, N)
         ldl = (V + 7) // 8 * 8
         logits_buf = torch.empty(chunk, ldl, dtype=BF16, device=dev)
@@ -50,10 +54,11 @@ class _LinearCESm100(torch.autograd.Function):
             if need_dh:
                 K.gemm(logits, w_bf16, b_mn=True, out=d_hidden[lo:hi])
             if need_dw:
-                K.gemm(logits, hc, a_mn=True, b_mn=True, out=d_weight, accumulate=lo > 0)
+                K.gemm(logits, hc, a_mn=True, b_mn=True, out=d_weight, accumulate=acc0 or lo > 0)
         loss = row_loss.sum() * inv_n[0]
         ctx.stash = (d_hidden, d_weight)
         ctx.engine = engine
+        ctx.in_sink = sink_dest is not None
         ctx.hidden_dtype = hidden.dtype
         return loss
 
@@ -69,23 +74,32 @@ class _LinearCESm100(torch.autograd.Function):
             if ctx.hidden_dtype != BF16:
                 d_hidden = d_hidden.to(ctx.hidden_dtype)
         if d_weight is not None:
-            K.scale_inplace_(d_weight, scale)
+            if not ctx.in_sink:  # a sink slice may hold earlier micro-batches: the loss must be the root there
+                K.scale_inplace_(d_weight, scale)
             eng = ctx.engine
             if eng is not None and eng.expect_tied_grad:
                 # tied embedding: hand the buffer to the gather's backward, which adds its rows and returns it
                 eng.expect_tied_grad = False
                 eng.pending_tied_grad = d_weight
                 d_weight = None
-        return d_hidden, d_weight, None, None, None, None, None
+            elif ctx.in_sink:
+                eng.model._grad_sink.grad_written(eng.model.lm_head.weight)
+                d_weight = None
+        return d_hidden, d_weight, None, None, None, None, None, None, None
 
 
-def linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size):
+def linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size, loss_scale=1.0):
     from torchure_b200.ops.block import engine_for_weight
 
     eng = engine_for_weight(weight)
+    sink_dest = None
     if eng is not None:
         eng.refresh()
         w_bf16 = eng.head_shadow
+        sink = eng.model._grad_sink
+        if sink is not None and weight.requires_grad and torch.is_grad_enabled():
+            sink_dest = sink.grad_dest(weight)
     else:
         w_bf16 = K.cast_to_bf16(weight.detach().contiguous()) if weight.dtype != BF16 else weight.detach()
-    return _LinearCESm100.apply(hidden, weight, labels, ignore_index, chunk_size, w_bf16, eng)
+    return _LinearCESm100.apply(hidden, weight, labels, ignore_index, chunk_size, w_bf16, eng, float(loss_scale),
+                                sink_dest)

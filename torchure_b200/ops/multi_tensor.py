@@ -29,17 +29,17 @@ class TensorTable:
         while len(ptrs) < 5:
             ptrs.append([0] * n)
         numel = [t.numel() for t in columns[0]]
-        bt, bc = [], []
-        for i, ne in enumerate(numel):
-            for c in range((ne + CHUNK - 1) // CHUNK):
-                bt.append(i)
-                bc.append(c)
+        import numpy as np
+
+        chunks = [(ne + CHUNK - 1) // CHUNK for ne in numel]
+        bt = np.repeat(np.arange(n, dtype=np.int32), chunks)
+        bc = np.concatenate([np.arange(c, dtype=np.int32) for c in chunks]) if chunks else np.zeros(0, np.int32)
         self.key = tuple(tuple(p) for p in ptrs)
         self.ptrs = torch.tensor(ptrs, dtype=torch.int64).to(dev, non_blocking=True)
         self.numel = torch.tensor(numel, dtype=torch.int64).to(dev, non_blocking=True)
         self.flags = torch.tensor(flags if flags is not None else [0] * n, dtype=torch.int32).to(dev, non_blocking=True)
-        self.bt = torch.tensor(bt, dtype=torch.int32).to(dev, non_blocking=True)
-        self.bc = torch.tensor(bc, dtype=torch.int32).to(dev, non_blocking=True)
+        self.bt = torch.from_numpy(bt).to(dev, non_blocking=True)
+        self.bc = torch.from_numpy(bc).to(dev, non_blocking=True)
         self.keepalive = columns
 
     def args(self):

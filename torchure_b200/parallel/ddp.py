@@ -41,28 +41,40 @@ from torchure_b200.core.collective import MeshLike, all_reduce, broadcast
 
 
 def plan_buckets(params: list[torch.Tensor], cap_bytes: int, merge_small: bool = True,
-                 small_bytes: int | None = None) -> list[list[torch.Tensor]]:
+                 small_bytes: int | None = None, groups=()) -> list[list[torch.Tensor]]:
     """Group `params` (already in launch order) into buckets of about `cap_bytes`.
 
     A bucket closes when the next tensor would overflow it or has another dtype.  With
     `merge_small`, a running bucket smaller than `small_bytes` (default cap/16) is never
-    closed by an overflow: the tensor joins it instead.
+    closed by an overflow: the tensor joins it instead.  `groups` lists tuples of parameters
+    that must sit next to each other, in the given order, inside one bucket (the rows of a
+    fused projection, so one GEMM can write all of their gradients); a group is placed where
+    its first member appears in `params`.
     """
     if small_bytes is None:
         small_bytes = cap_bytes // 16
+    group_of = {id(p): tuple(g) for g in groups for p in g}
+    units: list[list[torch.Tensor]] = []
+    seen: set[int] = set()
+    for p in params:
+        if id(p) in seen:
+            continue
+        unit = list(group_of.get(id(p), (p,)))
+        seen.update(id(q) for q in unit)
+        units.append(unit)
     out: list[list[torch.Tensor]] = []
     run: list[torch.Tensor] = []
     run_bytes = 0
-    for p in params:
-        nbytes = p.numel() * p.element_size()
+    for unit in units:
+        nbytes = sum(p.numel() * p.element_size() for p in unit)
         if run:
-            dtype_change = p.dtype != run[0].dtype
+            dtype_change = unit[0].dtype != run[0].dtype
             overflow = run_bytes + nbytes > cap_bytes
             keep_small = merge_small and run_bytes < small_bytes and not dtype_change
             if dtype_change or (overflow and not keep_small):
                 out.append(run)
                 run, run_bytes = [], 0
-        run.append(p)
+        run.extend(unit)
         run_bytes += nbytes
     if run:
         out.append(run)
@@ -139,13 +151,16 @@ class DDP:
         if self.group_size > 1:
             self._replicate(model)
         params.reverse()
+        groups = model.fused_param_groups() if (self.fused and hasattr(model, "fused_param_groups")) else ()
         self.buckets = [Bucket(i, ps) for i, ps in
-                        enumerate(plan_buckets(params, int(bucket_mb * 1024 * 1024), merge_small))]
+                        enumerate(plan_buckets(params, int(bucket_mb * 1024 * 1024), merge_small, groups=groups))]
         self._bucket_of = {p: b for b in self.buckets for p in b.params}
         if self.fused:
             from torchure_b200.parallel.ddp_fused import FusedReducer
 
             self.reducer = FusedReducer(self)
+            if hasattr(model, "set_grad_sink"):
+                model.set_grad_sink(self.reducer)
         else:
             self.reducer = TorchReducer(self)
         for p in params:
@@ -158,6 +173,11 @@ class DDP:
     def _on_grad_ready(self, param: nn.Parameter) -> None:
         if not self.requires_sync and not self.fused:
             return  # library path: autograd itself accumulates into .grad
+        if self.fused and not self.reducer.absorb(param):
+            return  # nothing arrived through autograd: the producer wrote into the bucket itself (gradient sink)
+        self._count_down(param)
+
+    def _count_down(self, param: nn.Parameter) -> None:
         b = self._bucket_of[param]
         b.pending -= 1
         if b.pending == 0:

@@ -3,21 +3,24 @@
 All buckets are slices of ONE fp32 main-gradient buffer.  With more than one rank that buffer lives in the
 symmetric allocation of the dp axis, so peers read and write it directly over NVLink.
 
-Per bucket, when its last gradient arrives (post-accumulate-grad hook, i.e. while backward is still running):
+Gradients reach a bucket in one of two ways:
 
-1. ``bucket_pack``   one multi-tensor kernel casts the autograd gradients (fp32 or bf16) to fp32 and stores or
-                     accumulates them into the bucket (accumulation over no_sync micro-batches happens here, in
-                     fp32).  With one rank the same kernel also emits the bucket's sum of squares.
-2. ``all_reduce``    (world > 1, sync micro-batch only) one kernel on the communication stream: every rank reduces
-                     its 1/world slice with ``multimem.ld_reduce`` (NVSwitch in-fabric reduction; peer loads when
-                     no multicast mapping exists), applies the 1/world scale, adds the slice's sum of squares to the
-                     shared partial table of every rank and broadcasts the slice with ``multimem.st``.
+* **sink** (models that run on the sm_100a engine): the wgrad GEMM epilogue, the norm-gain kernels and the fused
+  linear+CE write their fp32 results STRAIGHT into the bucket slice (``grad_dest`` / ``grad_written``).  The first
+  write of a step stores, later micro-batches accumulate through the TMA reduce-add epilogue, so the bf16->fp32
+  cast, the no_sync accumulation and the placement into the flat buffer cost no kernel and no extra HBM pass.
+* **hook** (any other parameter): the post-accumulate-grad hook copies or adds the autograd gradient into the slice
+  (``absorb``).
 
-There is no NCCL call and no separate scale or norm kernel; ``sq_norm()`` sums the partial table in a fixed order,
-so every rank derives bit-identical clip coefficients.  After a sync launch ``p.grad`` is a view of the bucket.
+When the last gradient of a bucket has arrived in the sync micro-batch, ONE kernel on the communication stream
+all-reduces it: every rank reduces its 1/world slice with ``multimem.ld_reduce`` (NVSwitch in-fabric reduction; peer
+loads without a multicast mapping), applies the 1/world scale, publishes the slice's sum of squares into every rank's
+partial table and broadcasts the slice with ``multimem.st``.  No NCCL call, no separate scale or norm kernel.
+``sq_norm()`` sums the partial table in a fixed order, so every rank derives bit-identical clip coefficients; with one
+rank it is a single multi-tensor reduction over the flat buffer.  After a sync launch ``p.grad`` is a view of the bucket.
 
-GEMM kernels are persistent and occupy every SM they are given, so while a backward is in flight the reducer
-asks them to leave ``comm_sms`` SMs free for the communication kernels (``ops.set_compute_sm_reserve``).
+GEMM kernels are persistent and occupy every SM they are given, so with more than one rank the reducer asks them to
+leave ``comm_sms`` SMs free for the communication kernels (``ops.set_compute_sm_reserve``).
 """
 
 from __future__ import annotations
@@ -34,8 +37,7 @@ class FusedReducer:
     def __init__(self, ddp, comm_sms: int = 16):
         self.ddp = ddp
         self.world = ddp.group_size
-        params0 = ddp.buckets[0].params
-        dev = params0[0].device
+        dev = ddp.buckets[0].params[0].device
         # 64-element alignment keeps every bucket 256-byte aligned and 16-byte divisible per rank
         offs, total = [], 0
         for b in ddp.buckets:
@@ -55,29 +57,49 @@ class FusedReducer:
             ops.set_compute_sm_reserve(comm_sms)
         else:
             self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
-            self.partials = torch.zeros(len(ddp.buckets), dtype=torch.float32, device=dev)
+            self.partials = None
             self.stream = None
         self.padded = []
+        self._view_of: dict[torch.Tensor, torch.Tensor] = {}
         for b, off in zip(ddp.buckets, offs):
             b.bind(self.flat[off:off + b.numel])
             self.padded.append(self.flat[off:off + (b.numel + 63) // 64 * 64])
-            b.fresh = True  # the next pack stores instead of accumulating
-        self._events: list[torch.cuda.Event] = []
+            for p, v in zip(b.params, b.views):
+                self._view_of[p] = v
+        self._written: set[int] = set()
+
+    # -- sink API: the producer writes into the bucket itself ------------------------------------------------
+    def grad_dest(self, p: torch.Tensor) -> tuple[torch.Tensor, bool]:
+        """(fp32 destination shaped like p, accumulate?) for the gradient of `p` in this backward."""
+        return self._view_of[p], id(p) in self._written
+
+    def grad_written(self, p: torch.Tensor) -> None:
+        """The gradient of `p` for this micro-batch is in its destination (the writes are ordered on the
+        current stream)."""
+        self._written.add(id(p))
+        self.ddp._count_down(p)
+
+    # -- hook path: a gradient arrived through autograd -------------------------------------------------------
+    def absorb(self, p: torch.Tensor) -> bool:
+        """Move an autograd-delivered gradient into its slice.  Returns False when there is none (``p.grad`` is
+        unset or already the slice itself), which is what a hook sees for a parameter served by the sink."""
+        g, v = p.grad, self._view_of[p]
+        if g is None or g.data_ptr() == v.data_ptr():
+            return False
+        if id(p) in self._written:
+            v.add_(g)
+        else:
+            v.copy_(g)
+        self._written.add(id(p))
+        return True
 
     def launch(self, b, sync: bool):
-        grads = [p.grad for p in b.params]
-        local_sq = self.partials[b.index] if (sync and self.world == 1) else None
-        if local_sq is not None:
-            local_sq.zero_()
-        multi_tensor.bucket_pack(grads, b.views, accumulate=not b.fresh, post_scale=1.0, sq_out=local_sq)
-        b.fresh = False
         if not sync:
             for p in b.params:
-                p.grad = None  # the next micro-batch produces a fresh gradient; the sum lives in the bucket
+                p.grad = None  # the running sum lives in the bucket
             return None
         for p, v in zip(b.params, b.views):
             p.grad = v
-        b.fresh = True
         if self.world == 1:
             return _Ready()
         ready = torch.cuda.Event()
@@ -92,8 +114,11 @@ class FusedReducer:
     def wait(self, works) -> None:
         for w in works:
             w.wait()
+        self._written.clear()
 
     def sq_norm(self) -> torch.Tensor:
+        if self.world == 1:
+            return multi_tensor.sq_norm([self.flat])
         return self.partials.sum()
 
 

@@ -201,11 +201,12 @@ class Trainer:
     # -- the step ------------------------------------------------------------------------------
     def micro_train_step(self) -> torch.Tensor:
         batch = next(self.prefetcher)
+        scale = 1.0 / self.microbatches_per_step
         if self.on_gpu:
             with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
-                loss = self.objective.compute_loss(self.model, batch) / self.microbatches_per_step
+                loss = self.objective.compute_loss(self.model, batch, loss_scale=scale)
         else:
-            loss = self.objective.compute_loss(self.model, batch) / self.microbatches_per_step
+            loss = self.objective.compute_loss(self.model, batch, loss_scale=scale)
         loss.backward()
         return loss.detach()
 
