@@ -18,7 +18,7 @@ namespace tb {
 // Returns 0 or a negative code for an argument error.  `err` is a device int that a kernel sets when
 // one of its bounded waits expires.
 int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-              bool a_mn, bool b_mn, int out_mode, int* err, int num_sms, cudaStream_t stream);
+              bool a_mn, bool b_mn, int out_mode, int* err, int num_sms, cudaStream_t stream, int force_splits = 0);
 
 // ---- elementwise / normalisation -------------------------------------------------------------
 // h = rmsnorm(x_new) * w with x_new = x (+ y); optional gather x = table[ids].  Writes x_new when y or ids

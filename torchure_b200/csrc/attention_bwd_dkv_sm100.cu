@@ -29,7 +29,7 @@ constexpr int Q_STAGES = 2;
 constexpr int STAT_BYTES = 1024;          // lse2[128] | delta[128]
 constexpr int STAGE_BYTES = 2 * TILE_BYTES + STAT_BYTES;
 constexpr int SMEM_BYTES = 2 * TILE_BYTES + Q_STAGES * STAGE_BYTES + 256 + 1024;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter)
 
 struct Bars {
   uint64_t kv_full;
@@ -89,7 +89,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_const
     }
     for (int hh = 0; hh < 2; ++hh) {
       mbar_init(&bars->st_full[hh], 1);
-      mbar_init(&bars->pds_ready[hh], 128);
+      mbar_init(&bars->pds_ready[hh], 256);
     }
     mbar_init(&bars->acc_done, 1);
     fence_barrier_init();
@@ -160,11 +160,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_const
         const uint32_t da = smem_u32(stage + TILE_BYTES) + hh * 8192;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ts(tmem_base + 256, tmem_base + hh * 128 + ks * 8, make_desc_sw128(da + ks * 2048, HALF_BYTES, 1024),
+          umma_f16_ts(tmem_base + 256, tmem_base + hh * 128 + (ks >> 1) * 32 + (ks & 1) * 8,
+                      make_desc_sw128(da + ks * 2048, HALF_BYTES, 1024),
                       idesc_acc, (first && ks == 0) ? 0u : 1u);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ts(tmem_base + 384, tmem_base + hh * 128 + 64 + ks * 8,
+          umma_f16_ts(tmem_base + 384, tmem_base + hh * 128 + 64 + (ks >> 1) * 32 + (ks & 1) * 8,
                       make_desc_sw128(qa + ks * 2048, HALF_BYTES, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
       };
       bool ok = mbar_wait(&bars->kv_full, 0, err, kErrAttnWait) && mbar_wait(&bars->q_full[0], 0, err, kErrAttnWait);
@@ -207,36 +208,39 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_const
         tc_fence_after();
         const uint32_t tS = tmem_base + lane_sel + hh * 128;
         const uint32_t tP = tS + 64;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t sv[32], dv[32], pp[16], pd[16];
+        {
+          const int c = (warp - 2) >> 2;   // this warp's 32 of the half's 64 query columns
+          uint32_t sv[32], dv[32];
           tmem_ld_32x32b_x32(tS + c * 32, sv);
           tmem_ld_32x32b_x32(tP + c * 32, dv);
           tmem_ld_wait();
-          const int q0 = hh * 64 + c * 32;
+          {
+            uint32_t pp[16], pd[16];
+            const int q0 = hh * 64 + c * 32;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float2 l2 = *reinterpret_cast<const float2*>(sStat + q0 + 2 * i);
-            const float2 dl = *reinterpret_cast<const float2*>(sStat + 128 + q0 + 2 * i);
-            float p0 = ex2(__uint_as_float(sv[2 * i]) * scale_log2 - l2.x);
-            float p1 = ex2(__uint_as_float(sv[2 * i + 1]) * scale_log2 - l2.y);
-            if (diag) {
-              if (q0 + 2 * i < row) p0 = 0.f;       // query before key: masked
-              if (q0 + 2 * i + 1 < row) p1 = 0.f;
+            for (int i = 0; i < 16; ++i) {
+              const float2 l2 = *reinterpret_cast<const float2*>(sStat + q0 + 2 * i);
+              const float2 dl = *reinterpret_cast<const float2*>(sStat + 128 + q0 + 2 * i);
+              float p0 = ex2(fmaf(__uint_as_float(sv[2 * i]), scale_log2, -l2.x));
+              float p1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), scale_log2, -l2.y));
+              if (diag) {
+                if (q0 + 2 * i < row) p0 = 0.f;       // query before key: masked
+                if (q0 + 2 * i + 1 < row) p1 = 0.f;
+              }
+              pp[i] = pack_bf16x2(p0, p1);
+              pd[i] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * i]) - dl.x) * scale,
+                                  p1 * (__uint_as_float(dv[2 * i + 1]) - dl.y) * scale);
             }
-            pp[i] = pack_bf16x2(p0, p1);
-            pd[i] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * i]) - dl.x) * scale,
-                                p1 * (__uint_as_float(dv[2 * i + 1]) - dl.y) * scale);
+            tmem_st_32x32b_x16(tS + c * 32, pp);   // inside the columns this warp itself consumed
+            tmem_st_32x32b_x16(tP + c * 32, pd);
           }
-          tmem_st_32x32b_x16(tS + c * 16, pp);
-          tmem_st_32x32b_x16(tP + c * 16, pd);
         }
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&bars->pds_ready[hh]);
       }
     }
-    if (ok && mbar_wait(&bars->acc_done, 0, err, kErrAttnWait)) {
+    if (ok && warp < 6 && mbar_wait(&bars->acc_done, 0, err, kErrAttnWait)) {
       tc_fence_after();
       // stage 0's Q/dO tiles are dead: 4 warps x 8 KB of staging
       uint8_t* stage = sStage + quarter * 8192;

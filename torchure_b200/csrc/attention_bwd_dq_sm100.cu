@@ -4,7 +4,7 @@
 //   attn_bwd_dq_kernel     one CTA per (128 query rows, query head): loops over the causal KV blocks
 //                            S  = Q K_j^T            (SS)      -> TMEM S[j&1]
 //                            dP = dO V_j^T           (SS)      -> TMEM dP
-//                            dS = P o (dP - delta) / sqrt(d)   one thread per row; bf16 dS overwrites its S tile
+//                            dS = P o (dP - delta) / sqrt(d)   two threads per row (64 keys each); bf16 dS overwrites S
 //                            dQ += dS K_j            (TS: dS read from TMEM, K_j read MN-major)
 //                          The next S tile is issued while the current dS is being computed (S is double buffered).
 // dQ is accumulated in TMEM over all KV blocks, so there are no atomics and no fp32 dQ buffer in global memory; the
@@ -24,7 +24,7 @@ constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KB
 constexpr int HALF_BYTES = 16384;
 constexpr int KV_STAGES = 2;
 constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + 256 + 1024;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter)
 
 struct Bars {
   uint64_t q_full;
@@ -106,7 +106,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       mbar_init(&bars->kv_empty[s], 1);
     }
     mbar_init(&bars->sd_full, 1);
-    mbar_init(&bars->ds_ready, 128);
+    mbar_init(&bars->ds_ready, 256);
     mbar_init(&bars->dq_done, 1);
     fence_barrier_init();
   }
@@ -176,7 +176,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
         const uint32_t ka = smem_u32(sKV + s * 2 * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          umma_f16_ts(tmem_base + 384, tmem_base + (j & 1) * 128 + ks * 8,
+          // dS keys 0..63 sit at columns 0..31 of the S tile, keys 64..127 at columns 64..95
+          umma_f16_ts(tmem_base + 384, tmem_base + (j & 1) * 128 + (ks >> 2) * 64 + (ks & 3) * 8,
                       make_desc_sw128(ka + ks * 2048, HALF_BYTES, 1024), idesc_ts, (j == 0 && ks == 0) ? 0u : 1u);
         }
         umma_commit(&bars->kv_empty[s]);
@@ -200,31 +201,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       const bool diag = j == n_kv - 1;
       const uint32_t tS = tmem_base + lane_sel + (j & 1) * 128;
       const uint32_t tP = tmem_base + lane_sel + 256;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32], pk[16];
-        tmem_ld_32x32b_x32(tS + c * 32, sv);
-        tmem_ld_32x32b_x32(tP + c * 32, dv);
+      {   // this warp's 64 of the 128 key columns: four TMEM loads in flight, one wait
+        const int hc = (warp - 2) >> 2;
+        uint32_t sv[64], dv[64];
+        tmem_ld_32x32b_x32(tS + hc * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld_32x32b_x32(tS + hc * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        tmem_ld_32x32b_x32(tP + hc * 64, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
+        tmem_ld_32x32b_x32(tP + hc * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = ex2(__uint_as_float(sv[2 * i]) * scale_log2 - my_lse2);
-          float p1 = ex2(__uint_as_float(sv[2 * i + 1]) * scale_log2 - my_lse2);
-          if (diag) {
-            if (c * 32 + 2 * i > row) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int k0 = c2 * 32 + 2 * i;
+            float p0 = ex2(fmaf(__uint_as_float(sv[k0]), scale_log2, -my_lse2));
+            float p1 = ex2(fmaf(__uint_as_float(sv[k0 + 1]), scale_log2, -my_lse2));
+            if (diag) {
+              if (hc * 64 + k0 > row) p0 = 0.f;
+              if (hc * 64 + k0 + 1 > row) p1 = 0.f;
+            }
+            const float d0 = p0 * (__uint_as_float(dv[k0]) - my_delta) * scale;
+            const float d1 = p1 * (__uint_as_float(dv[k0 + 1]) - my_delta) * scale;
+            pk[i] = pack_bf16x2(d0, d1);
           }
-          const float d0 = p0 * (__uint_as_float(dv[2 * i]) - my_delta) * scale;
-          const float d1 = p1 * (__uint_as_float(dv[2 * i + 1]) - my_delta) * scale;
-          pk[i] = pack_bf16x2(d0, d1);
+          tmem_st_32x32b_x16(tS + hc * 64 + c2 * 16, pk);   // inside the columns this warp itself consumed
         }
-        tmem_st_32x32b_x16(tS + c * 16, pk);
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->ds_ready);
     }
-    if (ok && mbar_wait(&bars->dq_done, 0, err, kErrAttnWait)) {
+    if (ok && warp < 6 && mbar_wait(&bars->dq_done, 0, err, kErrAttnWait)) {
       tc_fence_after();
       uint8_t* stage = sQ + quarter * 8192;   // Q is dead once the last S tile has been produced
       const uint32_t tD = tmem_base + lane_sel + 384;

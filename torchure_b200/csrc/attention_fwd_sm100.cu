@@ -181,19 +181,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
       if (!mbar_wait(&bars->s_full[t], j & 1, err, kErrAttnWait)) { ok = false; break; }
       tc_fence_after();
       const bool diag = j == n_kv - 1;
-      uint32_t v[32];
-      float mx = -1e30f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(tS + c * 32, v);
-        tmem_ld_wait();
+      // the whole score row (128 fp32) comes out of TMEM once: four loads in flight, one wait
+      uint32_t sv[128];
+      tmem_ld_32x32b_x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld_32x32b_x32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_32x32b_x32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[64]));
+      tmem_ld_32x32b_x32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&sv[96]));
+      tmem_ld_wait();
+      if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float sv = __uint_as_float(v[i]);
-          if (!diag || c * 32 + i <= row) mx = fmaxf(mx, sv);
-        }
+        for (int i = 0; i < 128; ++i)
+          if (i > row) sv[i] = 0xff800000u;  // -inf: exp2 gives exactly 0
       }
-      const float m_new = mx * scale_log2;
+      float mx0 = -1e30f, mx1 = -1e30f, mx2 = -1e30f, mx3 = -1e30f;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+      }
+      const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
       if (j == 0) {
         m_used = m_new;
       } else {
@@ -202,6 +210,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
           if (!mbar_wait(&bars->o_done[t], (j - 1) & 1, err, kErrAttnWait)) { ok = false; break; }
           tc_fence_after();
           const float alpha = need ? fast_exp2(m_used - m_new) : 1.f;
+          uint32_t v[32];
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             tmem_ld_32x32b_x32(tO + c * 32, v);
@@ -220,24 +229,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
           if (need) m_used = m_new;
         }
       }
-#pragma unroll 1
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(tS + c * 32, v);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = fast_exp2(__uint_as_float(v[2 * i]) * scale_log2 - m_used);
-          float p1 = fast_exp2(__uint_as_float(v[2 * i + 1]) * scale_log2 - m_used);
-          if (diag) {
-            if (c * 32 + 2 * i > row) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > row) p1 = 0.f;
-          }
-          l += p0 + p1;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + 2 * i]), scale_log2, -m_used));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + 2 * i + 1]), scale_log2, -m_used));
+          l0 += p0;
+          l1 += p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        tmem_st_32x32b_x16(tS + c * 16, pk);   // P chunk c lands on S columns already consumed
+        tmem_st_32x32b_x16(tS + c * 16, pk);   // P overwrites the first 64 columns of its own S tile
       }
+      l += l0 + l1;
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_ready[t]);

@@ -38,7 +38,8 @@ T* opt_mptr(c10::optional<torch::Tensor>& t) {
   return t.has_value() && t->defined() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
 }
 
-void gemm(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, bool a_mn, bool b_mn, int64_t out_mode) {
+void gemm(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, bool a_mn, bool b_mn, int64_t out_mode,
+          int64_t splits) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "gemm: bf16 operands");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors");
@@ -52,7 +53,7 @@ void gemm(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, bo
   c10::cuda::CUDAGuard guard(a.device());
   const int rc = tb::gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0),
                                b.stride(0), out.stride(0), a_mn, b_mn, (int)out_mode, err_word().data_ptr<int>(),
-                               num_sms(), cur_stream());
+                               num_sms(), cur_stream(), (int)splits);
   TORCH_CHECK(rc == 0, "gemm_bf16 failed with code ", rc);
 }
 
@@ -164,7 +165,9 @@ void register_comm(pybind11::module_& m);
 void register_attn(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("gemm", &gemm, "bf16 tcgen05 GEMM: out = A * B^T (operand majors selectable)");
+  m.def("gemm", &gemm, "bf16 tcgen05 GEMM: out = A * B^T (operand majors selectable)", pybind11::arg("a"),
+        pybind11::arg("b"), pybind11::arg("out"), pybind11::arg("a_mn"), pybind11::arg("b_mn"), pybind11::arg("out_mode"),
+        pybind11::arg("splits") = 0);
   m.def("set_sm_reserve", [](int64_t n) { g_sm_reserve = (int)n; }, "persistent kernels use (SM count - n) CTAs");
   m.def("error_word", &error_word, "device int32[4]; [0] is set when a bounded wait of a kernel expired");
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);

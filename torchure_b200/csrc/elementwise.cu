@@ -472,7 +472,9 @@ void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids,
 
 void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const float* rstd, const float* dx_in,
                  float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, cudaStream_t stream) {
-  const int grid = std::min((M + 7) / 8, num_sms * 4);
+  // two rows per warp keeps every warp equally loaded and the per-CTA atomics on dw few
+  (void)num_sms;
+  const int grid = std::max(1, (M + 15) / 16);
   const size_t smem = static_cast<size_t>(D) * sizeof(float);
   if (D <= 128 * 8) rmsnorm_bwd_kernel<8><<<grid, 256, smem, stream>>>(dh, x, w, rstd, dx_in, dx, dx_bf16, dw, M, D);
   else if (D <= 128 * 20) rmsnorm_bwd_kernel<20><<<grid, 256, smem, stream>>>(dh, x, w, rstd, dx_in, dx, dx_bf16, dw, M, D);

@@ -17,7 +17,9 @@
 #include "api.h"
 #include "common.cuh"
 
+#include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 namespace tb {
 
@@ -37,7 +39,7 @@ constexpr uint32_t TMEM_COLS = 512;
 template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* err) {
+                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int splits, int* err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi = smem + STAGES * STAGE_BYTES;
@@ -54,6 +56,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_n = (N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (K + BK - 1) / BK;
+  // split-K: work unit u = (tile u % num_tiles, K slice u / num_tiles); slices add into C with TMA reduce-add
+  const int num_units = num_tiles * splits;
+  const int kb_per = (num_kb + splits - 1) / splits;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
@@ -84,10 +89,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int tile = unit % num_tiles;
+        const int kb0 = (unit / num_tiles) * kb_per;
+        const int kb1 = min(num_kb, kb0 + kb_per);
         const int m0 = (tile % num_m) * BM;
         const int n0 = (tile / num_m) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, err, kErrProducerEmptyWait)) { ok = false; break; }
           uint8_t* sA = smem + stage * STAGE_BYTES;
           uint8_t* sB = sA + A_BYTES;
@@ -120,12 +128,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int kb0 = (unit / num_tiles) * kb_per;
+        const int kb1 = min(num_kb, kb0 + kb_per);
+        if (kb0 >= kb1) continue;  // empty K slice: every role skips it
         const int acc = it & 1;
         if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, err, kErrMmaTmemEmptyWait)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, err, kErrMmaFullWait)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
@@ -134,12 +145,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             umma_f16_ss(d_tmem, da + static_cast<uint64_t>(k * a_step), db + static_cast<uint64_t>(k * b_step), idesc,
-                        (kb | k) != 0 ? 1u : 0u);
+                        (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tfull[acc]);
+        ++it;
       }
     }
   } else {
@@ -150,7 +162,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     int slab = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+    for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+      const int tile = unit % num_tiles;
+      if ((unit / num_tiles) * kb_per >= num_kb) continue;  // empty K slice
       const int m0 = (tile % num_m) * BM;
       const int n0 = (tile / num_m) * BN;
       const int acc = it & 1;
@@ -202,6 +216,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      ++it;
     }
     if (lane == 0) tma_wait_group<0>();
   }
@@ -240,9 +255,36 @@ EncodeFn encode_fn() {
 
 }  // namespace
 
-// 2-D row-major tensor [rows, cols] with row stride `ld` elements, box [box_rows, box_cols], 128B swizzle
+// 2-D row-major tensor [rows, cols] with row stride `ld` elements, box [box_rows, box_cols], 128B swizzle.
+// Encoding a tensor map costs several microseconds on the host; activations and weights come back at the same
+// addresses step after step, so encoded maps are cached by their full description.
+namespace {
+struct TmapKey {
+  const void* base; uint64_t rows, cols, ld; uint32_t box_rows, box_cols; int elem_bytes;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           box_cols == o.box_cols && elem_bytes == o.elem_bytes;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.cols * 31 + k.ld * 131 + k.box_rows * 7 + k.box_cols * 3 + k.elem_bytes + (h << 6) + (h >> 2));
+    return static_cast<size_t>(h);
+  }
+};
+}  // namespace
+
 int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_rows, uint32_t box_cols) {
+  static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  const TmapKey key{base, rows, cols, ld, box_rows, box_cols, elem_bytes};
+  auto hit = cache.find(key);
+  if (hit != cache.end()) {
+    std::memcpy(map, &hit->second, sizeof(CUtensorMap));
+    return 0;
+  }
   EncodeFn fn = encode_fn();
   if (!fn) return -10;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return -11;
@@ -255,24 +297,27 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t ro
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -14;
+  if (r != CUDA_SUCCESS) return -14;
+  if (cache.size() > 16384) cache.clear();
+  cache.emplace(key, *map);
+  return 0;
 }
 
 template <bool A_MN, bool B_MN, int OUT>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc, int M, int N, int K, int* err,
-                  int grid, cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc, int M, int N, int K, int splits,
+                  int* err, int grid, cudaStream_t stream) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
     configured = true;
   }
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb_, tc, M, N, K, err);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb_, tc, M, N, K, splits, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-              bool a_mn, bool b_mn, int out_mode, int* err, int num_sms, cudaStream_t stream) {
+              bool a_mn, bool b_mn, int out_mode, int* err, int num_sms, cudaStream_t stream, int force_splits) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
   CUtensorMap ta, tb_, tc;
   int r;
@@ -284,9 +329,28 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_
   r = out_mode == 0 ? make_tmap_2d(&tc, C, 2, M, N, ldc, 32, 64) : make_tmap_2d(&tc, C, 4, M, N, ldc, 32, 32);
   if (r) return r - 200;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < num_sms ? tiles : num_sms;
+  // split-K for fp32 outputs (wgrad: few output tiles, long K): pick the slice count with the least wave time
+  int splits = 1;
+  const int num_kb = (K + BK - 1) / BK;
+  if (force_splits > 0) {
+    splits = force_splits;
+  } else if (out_mode != 0 && num_kb >= 32) {
+    float best = 1e30f;
+    for (int s = 1; s <= 8 && s * 8 <= num_kb; ++s) {
+      const int waves = (tiles * s + num_sms - 1) / num_sms;
+      const float cost = static_cast<float>(waves) / s + 0.02f * (s - 1);
+      if (cost < best - 1e-6f) { best = cost; splits = s; }
+    }
+  }
+  if (splits > 1 && out_mode == 1) {
+    // the slices all add into C: clear it first
+    if (cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, stream) != cudaSuccess) return -22;
+    out_mode = 2;
+  }
+  const int units = tiles * splits;
+  const int grid = units < num_sms ? units : num_sms;
 #define TB_GEMM_CASE(AM, BMN, O) \
-  if (a_mn == AM && b_mn == BMN && out_mode == O) return launch<AM, BMN, O>(ta, tb_, tc, M, N, K, err, grid, stream);
+  if (a_mn == AM && b_mn == BMN && out_mode == O) return launch<AM, BMN, O>(ta, tb_, tc, M, N, K, splits, err, grid, stream);
   TB_GEMM_CASE(false, false, 0)
   TB_GEMM_CASE(false, false, 1)
   TB_GEMM_CASE(false, false, 2)

@@ -16,7 +16,9 @@ import torch
 
 def synthetic_row(seed: int, dp_rank: int, row: int, seq_len: int, vocab_size: int, eos_id: int,
                   mean_doc_len: float) -> np.ndarray:
-    rng = np.random.Generator(np.random.Philox(key=seed, counter=[row, dp_rank, 0, 0]))
+    # the row index and the shard go into the KEY: counters of one key are consecutive blocks of the same stream,
+    # so keying by seed alone and offsetting the counter would make neighbouring rows shifted copies of each other
+    rng = np.random.Generator(np.random.Philox(key=[seed & 0xFFFFFFFFFFFFFFFF, (dp_rank << 44) | row]))
     toks = rng.integers(0, vocab_size, size=seq_len, dtype=np.int64)
     # document ends: gaps are geometric(1/mean); the row starts inside a document
     p = 1.0 / max(1.0, mean_doc_len)

@@ -34,7 +34,7 @@ def check_error() -> None:
 
 # ---- GEMM ---------------------------------------------------------------------------------------
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
-         out_dtype=BF16, accumulate: bool = False) -> torch.Tensor:
+         out_dtype=BF16, accumulate: bool = False, splits: int = 0) -> torch.Tensor:
     """out[M,N] (+)= A * B^T on tcgen05 tensor cores, fp32 accumulation.
 
     a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn); bf16, innermost stride 1.
@@ -46,7 +46,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
     mode = 0 if out.dtype == BF16 else (2 if accumulate else 1)
     assert not (accumulate and out.dtype == BF16), "accumulation needs an fp32 output"
-    _C().gemm(a, b, out, a_mn, b_mn, mode)
+    _C().gemm(a, b, out, a_mn, b_mn, mode, splits)
     ops.count_launch()
     return out
 
