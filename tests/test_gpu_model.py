@@ -88,7 +88,7 @@ def test_training_steps_track_oracle():
     from torchure_b200.optim import build_optimizer
 
     fast, slow = _pair(seed=3)
-    cfg = {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "fused": True}
+    cfg = {"lr": 2e-4, "weight_decay": 0.1, "betas": [0.9, 0.95], "fused": True}
     of, os_ = build_optimizer(fast, "adamw", cfg), build_optimizer(slow, "adamw", dict(cfg, fused=False))
     for p, s in fast.engine().shadow_pairs():
         of.attach_shadow(p, s)
