@@ -54,7 +54,7 @@ class SymmComm:
         self.handle = symm_mem.rendezvous(self.buf, group)
         self.peers = [int(p) for p in self.handle.buffer_ptrs]
         assert self.peers[rank] == self.buf.data_ptr(), "symmetric allocation does not start at the tensor"
-        mc = int(self.handle.multicast_ptr) if self.handle.has_multicast_support(dev.type, dev.index) else 0
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)  # 0 when the fabric offers no multicast mapping
         if os.environ.get("TORCHURE_B200_NVLS", "1") == "0":
             mc = 0
         self.mc = mc
