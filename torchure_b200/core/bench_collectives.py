@@ -1,0 +1,86 @@
+"""Bus-bandwidth sweep of the mesh collectives: our NVLink kernels against the NCCL path of the same call.
+
+    torchrun --nproc-per-node N -m torchure_b200.core.bench_collectives [--max-mb 1024] [--out sweep.json]
+
+For every op (all_reduce, all_gather, reduce_scatter, all_to_all), dtype (bf16, fp32) and per-rank message size
+(powers of two from 1 KiB, N(0,1) values) it times both transports with CUDA events after warm-up, takes the
+maximum over ranks and reports bus bandwidth with the usual conventions (all_reduce: 2(n-1)/n * bytes / t;
+all_gather / reduce_scatter: (n-1)/n * total bytes / t; all_to_all: (n-1)/n * bytes / t).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+import torch.distributed as dist
+
+
+def _time(fn, iters: int) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([start.elapsed_time(stop) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main(argv=None) -> None:
+    from torchure_b200.core import collective as C
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.train.train import init_distributed
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--max-mb", type=int, default=1024)
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args(argv)
+    rank, _, world = init_distributed()
+    mesh = Mesh({"dp": world})
+    ours = Mesh({"dp": world})
+    comm = C.enable_sm100(ours, "dp", max_bytes=(args.max_mb << 20) * (world + 2) + (64 << 20))
+    rows = []
+    sizes = [1 << k for k in range(10, 31) if (1 << k) <= (args.max_mb << 20)]
+    for dtype in (torch.bfloat16, torch.float32):
+        es = 2 if dtype == torch.bfloat16 else 4
+        for nbytes in sizes:
+            n = nbytes // es
+            x = torch.randn(n, device="cuda").to(dtype)
+            big = torch.randn(n * world, device="cuda").to(dtype) if nbytes * world <= (2 << 30) else None
+            iters = 20 if nbytes <= (16 << 20) else 5
+            cases = {
+                "all_reduce": (lambda m: C.all_reduce(x, m, "dp", "sum"), 2 * (world - 1) / world * nbytes),
+                "all_gather": (lambda m: C.all_gather(x, m, "dp", 0), (world - 1) / world * nbytes * world),
+                "all_to_all": (lambda m: C.all_to_all(x[: n // world * world], m, "dp", 0, 0), (world - 1) / world * nbytes),
+            }
+            if big is not None:
+                cases["reduce_scatter"] = (lambda m: C.reduce_scatter(big, m, "dp", "sum"),
+                                           (world - 1) / world * nbytes * world)
+            for op, (fn, bus_bytes) in cases.items():
+                if op == "all_to_all" and n < world:
+                    continue
+                t_ours = _time(lambda: fn(ours), iters)
+                t_nccl = _time(lambda: fn(mesh), iters)
+                rows.append({"op": op, "dtype": str(dtype).split(".")[-1], "bytes": nbytes, "world": world,
+                             "ours_ms": t_ours, "nccl_ms": t_nccl, "ours_busbw_gbs": bus_bytes / t_ours / 1e6,
+                             "nccl_busbw_gbs": bus_bytes / t_nccl / 1e6})
+                if rank == 0:
+                    r = rows[-1]
+                    print(f"{op:14s} {r['dtype']:8s} {nbytes:>11d} B  ours {t_ours * 1e3:9.1f} us {r['ours_busbw_gbs']:7.1f} GB/s"
+                          f" | nccl {t_nccl * 1e3:9.1f} us {r['nccl_busbw_gbs']:7.1f} GB/s", flush=True)
+    comm.check()
+    if rank == 0 and args.out:
+        with open(args.out, "w") as f:
+            json.dump(rows, f, indent=1)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

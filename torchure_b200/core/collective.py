@@ -143,7 +143,7 @@ def all_gather(tensor, mesh: MeshLike, dim: str, gather_dim: int = 0, *, async_o
     src = tensor.movedim(gather_dim, 0).contiguous()
     out = _stacked_output(output_tensor, (n * src.shape[0], *src.shape[1:]), tensor, gather_dim, "gather_dim")
     comm = _sm100_for(tensor, mesh, dim)
-    if comm is not None and comm.supports(src):
+    if comm is not None and comm.supports(src, copies=comm.world + 0.01):
         comm.all_gather(src, out)
         work = _Done()
     else:
@@ -162,7 +162,7 @@ def reduce_scatter(tensor, mesh: MeshLike, dim: str, op: ReduceOpName = "sum", s
     src = tensor.movedim(scatter_dim, 0).contiguous()
     out = _stacked_output(output_tensor, (src.shape[0] // n, *src.shape[1:]), tensor, scatter_dim, "scatter_dim")
     comm = _sm100_for(tensor, mesh, dim)
-    if comm is not None and comm.supports(src):
+    if comm is not None and comm.supports(src, copies=1.01):
         comm.reduce_scatter(src, out, op)
         res = out.movedim(0, scatter_dim)
         return (res, _Done()) if async_op else res
@@ -190,7 +190,7 @@ def all_to_all(tensor, mesh: MeshLike, dim: str, split_dim: int = 0, concat_dim:
     src = tensor.movedim(split_dim, 0).contiguous()
     recv = torch.empty_like(src)
     comm = _sm100_for(tensor, mesh, dim)
-    if comm is not None and comm.supports(src):
+    if comm is not None and comm.supports(src, copies=1.01):
         comm.all_to_all(src, recv)
     else:
         dist.all_to_all_single(recv, src, group=mesh.get_group(dim))

@@ -68,8 +68,17 @@ class SymmComm:
     def _ctx(self):
         return self.peers, self.mc, self.rank, self.world, self.limit_ns
 
-    def supports(self, t: torch.Tensor) -> bool:
-        return t.is_cuda and t.dtype in _DT and t.is_contiguous() and t.numel() > 0
+    def supports(self, t: torch.Tensor, copies: int = 1) -> bool:
+        """True when `t` can go through the kernels; `copies` = staging bytes needed per byte of `t`."""
+        ok = t.is_cuda and t.dtype in _DT and t.is_contiguous() and t.numel() > 0
+        return ok and (copies == 1 or t.numel() * t.element_size() * copies + 4096 <= self.staging_bytes)
+
+    def _pieces(self, t: torch.Tensor):
+        """Flat views of `t` no larger than the staging area (elementwise collectives are chunkable)."""
+        flat = t.view(-1)
+        step = max(1, (self.staging_bytes - 256) // t.element_size() // 8 * 8)
+        for lo in range(0, flat.numel(), step):
+            yield flat[lo:lo + step]
 
     def _staging(self, nbytes: int, dtype, at: int = 0) -> torch.Tensor:
         lo = self.staging_off + at
@@ -116,79 +125,98 @@ class SymmComm:
                                  blocks or self.blocks)
         ops.count_launch()
 
+    # generic collectives on ordinary tensors: ONE kernel each; the staging area is only the exchange medium
+    def _aligned(self, *ts: torch.Tensor) -> bool:
+        return all(t.data_ptr() % 16 == 0 and (t.numel() * t.element_size()) % 16 == 0 for t in ts)
+
+    def _grid(self, nbytes: int) -> int:
+        return max(1, min(self.blocks, (nbytes + 65535) // 65536))
+
     def all_reduce_(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
-        if self.offset_of(t) is not None and (t.numel() * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0:
+        nbytes = t.numel() * t.element_size()
+        if self.offset_of(t) is not None and self._aligned(t):
             self.all_reduce_symmetric_(t, op)
             return t
-        nbytes = t.numel() * t.element_size()
-        padded = _align(nbytes, 16)
-        stage = self._staging(padded, t.dtype)
-        stage[: t.numel()].copy_(t.view(-1))
-        if padded <= ONESHOT_BYTES:
-            out = torch.empty(padded // t.element_size(), dtype=t.dtype, device=t.device)
-            self.ext.comm_all_reduce_oneshot(*self._ctx(), self.staging_off, out, padded // t.element_size(),
-                                             _DT[t.dtype], _OPS[op], min(self.blocks, 8))
-            ops.count_launch()
-            t.view(-1).copy_(out[: t.numel()])
-        else:
-            self.all_reduce_symmetric_(stage, op)
-            t.view(-1).copy_(stage[: t.numel()])
+        if nbytes > self.staging_bytes - 256:
+            for piece in self._pieces(t):
+                self.all_reduce_(piece, op)
+            return t
+        if not self._aligned(t):  # odd sizes: pad through a temporary
+            pad = torch.zeros(_align(nbytes, 16) // t.element_size(), dtype=t.dtype, device=t.device)
+            pad[: t.numel()].copy_(t.view(-1))
+            self.all_reduce_(pad, op)
+            t.view(-1).copy_(pad[: t.numel()])
+            return t
+        oneshot = nbytes <= ONESHOT_BYTES
+        use_mc = bool(self.mc) and op in ("sum", "avg") and not oneshot
+        self.ext.comm_all_reduce_fused(*self._ctx(), self.staging_off, t, t, t.numel(), _DT[t.dtype], _OPS[op], use_mc,
+                                       oneshot, self._grid(nbytes))
+        ops.count_launch()
         return t
 
     def broadcast_(self, t: torch.Tensor, src: int) -> torch.Tensor:
-        nbytes = _align(t.numel() * t.element_size(), 16)
-        stage = self._staging(nbytes, t.dtype)
-        if self.rank == src:
-            stage[: t.numel()].copy_(t.view(-1))
-        self.ext.comm_broadcast(*self._ctx(), self.staging_off, nbytes // t.element_size(), _DT[t.dtype], src,
-                                bool(self.mc), self.blocks)
+        nbytes = t.numel() * t.element_size()
+        if nbytes > self.staging_bytes - 256:
+            for piece in self._pieces(t):
+                self.broadcast_(piece, src)
+            return t
+        if not self._aligned(t):
+            pad = torch.zeros(_align(nbytes, 16) // t.element_size(), dtype=t.dtype, device=t.device)
+            pad[: t.numel()].copy_(t.view(-1))
+            self.broadcast_(pad, src)
+            t.view(-1).copy_(pad[: t.numel()])
+            return t
+        self.ext.comm_broadcast(*self._ctx(), self.staging_off, t, t.numel(), _DT[t.dtype], src, bool(self.mc),
+                                self._grid(nbytes))
         ops.count_launch()
-        if self.rank != src:
-            t.view(-1).copy_(stage[: t.numel()])
         return t
 
+    def _padded(self, t: torch.Tensor, rows: int):
+        """(contiguous 16-byte-padded copy of t viewed (rows, n), n, padded n) for chunked collectives."""
+        es = t.element_size()
+        n = t.numel() // rows
+        pn = _align(n * es, 16) // es
+        if pn == n and t.data_ptr() % 16 == 0:
+            return t.view(rows, n), n, pn
+        buf = torch.zeros(rows, pn, dtype=t.dtype, device=t.device)
+        buf[:, :n].copy_(t.view(rows, n))
+        return buf, n, pn
+
     def all_gather(self, src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        n = src.numel()
-        es = src.element_size()
-        chunk = _align(n * es, 16)
-        stage_in = self._staging(chunk, src.dtype)
-        stage_in[:n].copy_(src.view(-1))
-        dst_at = _align(chunk, 256)
-        self._staging(chunk * self.world, src.dtype, at=dst_at)  # bounds check
-        self.ext.comm_all_gather(*self._ctx(), self.staging_off, self.staging_off + dst_at, chunk // es, _DT[src.dtype],
-                                 bool(self.mc), self.blocks)
+        s2, n, pn = self._padded(src, 1)
+        direct = pn == n and out.data_ptr() % 16 == 0
+        dst = out.view(self.world, n) if direct else torch.empty(self.world, pn, dtype=src.dtype, device=src.device)
+        self._staging(pn * self.world * src.element_size(), src.dtype)  # bounds check
+        self.ext.comm_all_gather(*self._ctx(), self.staging_off, s2, dst, pn, _DT[src.dtype], bool(self.mc),
+                                 self._grid(pn * src.element_size()))
         ops.count_launch()
-        gathered = self._staging(chunk * self.world, src.dtype, at=dst_at).view(self.world, chunk // es)[:, :n]
-        out.view(self.world, n).copy_(gathered)
+        if not direct:
+            out.view(self.world, n).copy_(dst[:, :n])
         return out
 
     def reduce_scatter(self, src: torch.Tensor, out: torch.Tensor, op: str = "sum") -> torch.Tensor:
-        n = out.numel()
-        es = src.element_size()
-        assert src.numel() == n * self.world
-        chunk = _align(n * es, 16)
-        stage = self._staging(chunk * self.world, src.dtype).view(self.world, chunk // es)
-        stage[:, :n].copy_(src.view(self.world, n))
-        res = torch.empty(chunk // es, dtype=src.dtype, device=src.device)
+        s2, n, pn = self._padded(src, self.world)
+        direct = pn == n and out.data_ptr() % 16 == 0
+        dst = out.view(-1) if direct else torch.empty(pn, dtype=src.dtype, device=src.device)
+        self._staging(pn * self.world * src.element_size(), src.dtype)
         use_mc = bool(self.mc) and op in ("sum", "avg")
-        self.ext.comm_reduce_scatter(*self._ctx(), self.staging_off, res, chunk // es, _DT[src.dtype], _OPS[op], use_mc,
-                                     self.blocks)
+        self.ext.comm_reduce_scatter(*self._ctx(), self.staging_off, s2, dst, pn, _DT[src.dtype], _OPS[op], use_mc,
+                                     self._grid(pn * src.element_size()))
         ops.count_launch()
-        out.view(-1).copy_(res[:n])
+        if not direct:
+            out.view(-1).copy_(dst[:n])
         return out
 
     def all_to_all(self, src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        es = src.element_size()
-        n = src.numel() // self.world
-        chunk = _align(n * es, 16)
-        stage_in = self._staging(chunk * self.world, src.dtype).view(self.world, chunk // es)
-        stage_in[:, :n].copy_(src.view(self.world, n))
-        dst_at = _align(chunk * self.world, 256)
-        stage_out = self._staging(chunk * self.world, src.dtype, at=dst_at).view(self.world, chunk // es)
-        self.ext.comm_all_to_all(*self._ctx(), self.staging_off, self.staging_off + dst_at, chunk // es, _DT[src.dtype],
-                                 self.blocks)
+        s2, n, pn = self._padded(src, self.world)
+        direct = pn == n and out.data_ptr() % 16 == 0
+        dst = out.view(self.world, n) if direct else torch.empty(self.world, pn, dtype=src.dtype, device=src.device)
+        self._staging(pn * self.world * src.element_size(), src.dtype)
+        self.ext.comm_all_to_all(*self._ctx(), self.staging_off, s2, dst, pn, _DT[src.dtype],
+                                 self._grid(pn * src.element_size()))
         ops.count_launch()
-        out.view(self.world, n).copy_(stage_out[:, :n])
+        if not direct:
+            out.view(self.world, n).copy_(dst[:, :n])
         return out
 
     def barrier(self, pretend_world: int | None = None) -> None:

@@ -165,6 +165,49 @@ __device__ __forceinline__ float block_reduce_sum(float v) {
 }
 
 // ---- kernels ------------------------------------------------------------------------------------------
+constexpr int UNROLL = 4;  // independent 16-byte transactions in flight per thread
+
+// reduce UNROLL vectors starting at i (stride `step`), bounds-checked against hi
+template <int DT>
+__device__ __forceinline__ void reduce_batch(const CommCtx& c, uint64_t off, int64_t i, int64_t step, int64_t hi, int op,
+                                             bool use_mc, Acc<DT> (&acc)[UNROLL]) {
+  if (use_mc) {
+    V4 raw[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t k = i + u * step;
+      if (k < hi) raw[u] = DT == kF32 ? mc_ld_reduce_f32(reinterpret_cast<void*>(c.mc_buf + off + k * 16))
+                                      : mc_ld_reduce_bf16(reinterpret_cast<void*>(c.mc_buf + off + k * 16));
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) acc[u].load(raw[u]);
+  } else {
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t k = i + u * step;
+      if (k < hi) {
+        V4 raw[kCommMaxRanks];
+        for (int p = 0; p < c.world; ++p) raw[p] = ld16(reinterpret_cast<void*>(c.peer_bufs[p] + off + k * 16));
+        acc[u].load(raw[0]);
+        for (int p = 1; p < c.world; ++p) {
+          Acc<DT> b;
+          b.load(raw[p]);
+#pragma unroll
+          for (int e = 0; e < Acc<DT>::N; ++e) acc[u].f[e] = combine(acc[u].f[e], b.f[e], op);
+        }
+      }
+    }
+  }
+  if (op == kOpAvg) {
+    const float sc = 1.f / c.world;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int e = 0; e < Acc<DT>::N; ++e) acc[u].f[e] *= sc;
+  }
+}
+
+// In-place two-shot all-reduce of data that already lives in the symmetric allocation (DDP buckets).
 template <int DT>
 __global__ void __launch_bounds__(CT)
 all_reduce_kernel(CommCtx c, uint64_t off, int64_t nvec, int op, int use_mc, int sq_slot) {
@@ -172,14 +215,20 @@ all_reduce_kernel(CommCtx c, uint64_t off, int64_t nvec, int op, int use_mc, int
   const int64_t per = nvec / c.world, rem = nvec % c.world;
   // slice of this rank (the remainder goes to the last rank)
   const int64_t lo = per * c.rank, hi = lo + per + (c.rank == c.world - 1 ? rem : 0);
+  const int64_t step = static_cast<int64_t>(gridDim.x) * CT;
   float sq = 0.f;
-  for (int64_t i = lo + static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < hi;
-       i += static_cast<int64_t>(gridDim.x) * CT) {
-    const uint64_t o = off + static_cast<uint64_t>(i) * 16;
-    Acc<DT> a = reduce_vec<DT>(c, o, op, use_mc != 0);
+  for (int64_t i = lo + static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < hi; i += step * UNROLL) {
+    Acc<DT> acc[UNROLL];
+    reduce_batch<DT>(c, off, i, step, hi, op, use_mc != 0, acc);
 #pragma unroll
-    for (int k = 0; k < Acc<DT>::N; ++k) sq += a.f[k] * a.f[k];
-    write_all(c, o, a.store(), use_mc != 0);
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t k = i + u * step;
+      if (k < hi) {
+#pragma unroll
+        for (int e = 0; e < Acc<DT>::N; ++e) sq += acc[u].f[e] * acc[u].f[e];
+        write_all(c, off + k * 16, acc[u].store(), use_mc != 0);
+      }
+    }
   }
   if (sq_slot >= 0) {
     sq = block_reduce_sum(sq);
@@ -192,68 +241,123 @@ all_reduce_kernel(CommCtx c, uint64_t off, int64_t nvec, int op, int use_mc, int
   block_barrier(c, 1, c.world);
 }
 
+// All-reduce of an ordinary local tensor, one launch: copy into my staging area, handshake, reduce, write `out`.
+//   oneshot: every rank reduces the whole message from all staging areas (latency bound sizes)
+//   two-shot: every rank reduces its slice, broadcasts it into all staging areas, handshake, copy out
+// Element i is always handled by block (i / CT) % gridDim on every rank (slices are multiples of gridDim * CT), which is
+// what makes the per-block handshake sufficient.
 template <int DT>
 __global__ void __launch_bounds__(CT)
-all_reduce_oneshot_kernel(CommCtx c, uint64_t off, void* out, int64_t nvec, int op) {
+all_reduce_fused_kernel(CommCtx c, uint64_t off, const void* in, void* out, int64_t nvec, int op, int use_mc, int oneshot) {
+  const int64_t step = static_cast<int64_t>(gridDim.x) * CT;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x;
+  uint8_t* mine = reinterpret_cast<uint8_t*>(c.peer_bufs[c.rank] + off);
+  for (int64_t i = first; i < nvec; i += step) st16(mine + i * 16, ld16(reinterpret_cast<const uint8_t*>(in) + i * 16));
   if (!block_barrier(c, 0, c.world)) return;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
-    Acc<DT> a = reduce_vec<DT>(c, off + static_cast<uint64_t>(i) * 16, op, false);
-    st16(reinterpret_cast<uint8_t*>(out) + i * 16, a.store());
+  if (oneshot) {
+    for (int64_t i = first; i < nvec; i += step * UNROLL) {
+      Acc<DT> acc[UNROLL];
+      reduce_batch<DT>(c, off, i, step, nvec, op, false, acc);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (i + u * step < nvec) st16(reinterpret_cast<uint8_t*>(out) + (i + u * step) * 16, acc[u].store());
+    }
+    block_barrier(c, 1, c.world);  // my staging area may be rewritten only after every peer has read it
+    return;
   }
-  block_barrier(c, 1, c.world);  // nobody may overwrite its staging area while a peer still reads it
+  const int64_t per = ((nvec + c.world - 1) / c.world + step - 1) / step * step;
+  const int64_t lo = per * c.rank;
+  const int64_t hi = lo + per < nvec ? lo + per : nvec;
+  for (int64_t i = lo + first; i < hi; i += step * UNROLL) {
+    Acc<DT> acc[UNROLL];
+    reduce_batch<DT>(c, off, i, step, hi, op, use_mc != 0, acc);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (i + u * step < hi) write_all(c, off + (i + u * step) * 16, acc[u].store(), use_mc != 0);
+  }
+  if (!block_barrier(c, 1, c.world)) return;
+  for (int64_t i = first; i < nvec; i += step) st16(reinterpret_cast<uint8_t*>(out) + i * 16, ld16(mine + i * 16));
 }
 
+// all_gather of local `in` (nvec vectors) into local `out` (world * nvec): my chunk goes straight from `in` into every
+// rank's staging area, handshake, copy out.
 __global__ void __launch_bounds__(CT)
-all_gather_kernel(CommCtx c, uint64_t src_off, uint64_t dst_off, int64_t nvec, int use_mc) {
-  if (!block_barrier(c, 0, c.world)) return;  // every rank's destination is free to be written
+all_gather_kernel(CommCtx c, uint64_t dst_off, const void* in, void* out, int64_t nvec, int use_mc) {
+  const int64_t step = static_cast<int64_t>(gridDim.x) * CT;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x;
+  if (!block_barrier(c, 0, c.world)) return;  // every rank's staging area is free (its previous copy-out is done)
   const uint64_t my_dst = dst_off + static_cast<uint64_t>(c.rank) * nvec * 16;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
-    V4 v = ld16(reinterpret_cast<void*>(c.peer_bufs[c.rank] + src_off + i * 16));
-    write_all(c, my_dst + i * 16, v, use_mc != 0);
-  }
-  block_barrier(c, 1, c.world);
+  for (int64_t i = first; i < nvec; i += step)
+    write_all(c, my_dst + i * 16, ld16(reinterpret_cast<const uint8_t*>(in) + i * 16), use_mc != 0);
+  if (!block_barrier(c, 1, c.world)) return;
+  const uint8_t* mine = reinterpret_cast<const uint8_t*>(c.peer_bufs[c.rank] + dst_off);
+  // chunk r element i was written by block (i / CT) % gridDim of rank r: keep that mapping per chunk
+  for (int r = 0; r < c.world; ++r)
+    for (int64_t i = first; i < nvec; i += step)
+      st16(reinterpret_cast<uint8_t*>(out) + (r * nvec + i) * 16, ld16(mine + (r * nvec + i) * 16));
 }
 
+// reduce_scatter of local `in` (world * nvec) into local `out` (nvec)
 template <int DT>
 __global__ void __launch_bounds__(CT)
-reduce_scatter_kernel(CommCtx c, uint64_t off, void* out, int64_t nvec, int op, int use_mc) {
+reduce_scatter_kernel(CommCtx c, uint64_t off, const void* in, void* out, int64_t nvec, int op, int use_mc) {
+  const int64_t step = static_cast<int64_t>(gridDim.x) * CT;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x;
+  uint8_t* mine = reinterpret_cast<uint8_t*>(c.peer_bufs[c.rank] + off);
+  for (int r = 0; r < c.world; ++r)
+    for (int64_t i = first; i < nvec; i += step)
+      st16(mine + (r * nvec + i) * 16, ld16(reinterpret_cast<const uint8_t*>(in) + (r * nvec + i) * 16));
   if (!block_barrier(c, 0, c.world)) return;
   const uint64_t base = off + static_cast<uint64_t>(c.rank) * nvec * 16;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
-    Acc<DT> a = reduce_vec<DT>(c, base + i * 16, op, use_mc != 0);
-    st16(reinterpret_cast<uint8_t*>(out) + i * 16, a.store());
+  for (int64_t i = first; i < nvec; i += step * UNROLL) {
+    Acc<DT> acc[UNROLL];
+    reduce_batch<DT>(c, base, i, step, nvec, op, use_mc != 0, acc);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (i + u * step < nvec) st16(reinterpret_cast<uint8_t*>(out) + (i + u * step) * 16, acc[u].store());
   }
   block_barrier(c, 1, c.world);
 }
 
+// all_to_all: chunk j of local `in` goes into rank j's staging slot [my rank], handshake, copy out
 __global__ void __launch_bounds__(CT)
-all_to_all_kernel(CommCtx c, uint64_t src_off, uint64_t dst_off, int64_t nvec) {
+all_to_all_kernel(CommCtx c, uint64_t dst_off, const void* in, void* out, int64_t nvec) {
+  const int64_t step = static_cast<int64_t>(gridDim.x) * CT;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x;
   if (!block_barrier(c, 0, c.world)) return;
   for (int j = 0; j < c.world; ++j) {
     const int peer = (c.rank + j) % c.world;  // stagger peers so links are used evenly
-    const uint64_t s = src_off + static_cast<uint64_t>(peer) * nvec * 16;
-    const uint64_t d = dst_off + static_cast<uint64_t>(c.rank) * nvec * 16;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
-      V4 v = ld16(reinterpret_cast<void*>(c.peer_bufs[c.rank] + s + i * 16));
-      st16(reinterpret_cast<void*>(c.peer_bufs[peer] + d + i * 16), v);
-    }
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(in) + static_cast<uint64_t>(peer) * nvec * 16;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(c.peer_bufs[peer] + dst_off + static_cast<uint64_t>(c.rank) * nvec * 16);
+    for (int64_t i = first; i < nvec; i += step) st16(dst + i * 16, ld16(src + i * 16));
   }
-  block_barrier(c, 1, c.world);
+  if (!block_barrier(c, 1, c.world)) return;
+  const uint8_t* mine = reinterpret_cast<const uint8_t*>(c.peer_bufs[c.rank] + dst_off);
+  for (int r = 0; r < c.world; ++r)
+    for (int64_t i = first; i < nvec; i += step)
+      st16(reinterpret_cast<uint8_t*>(out) + (r * nvec + i) * 16, ld16(mine + (r * nvec + i) * 16));
 }
 
+// broadcast of local `buf` (in place): the source writes every staging area, handshake, the others copy out
 __global__ void __launch_bounds__(CT)
-broadcast_kernel(CommCtx c, uint64_t off, int64_t nvec, int src, int use_mc) {
+broadcast_kernel(CommCtx c, uint64_t off, void* buf, int64_t nvec, int src, int use_mc) {
+  const int64_t step = static_cast<int64_t>(gridDim.x) * CT;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x;
   if (!block_barrier(c, 0, c.world)) return;
   if (c.rank == src) {
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * CT) {
-      V4 v = ld16(reinterpret_cast<void*>(c.peer_bufs[c.rank] + off + i * 16));
+    for (int64_t i = first; i < nvec; i += step) {
+      V4 v = ld16(reinterpret_cast<const uint8_t*>(buf) + i * 16);
       if (use_mc) mc_st(reinterpret_cast<void*>(c.mc_buf + off + i * 16), v);
       else
         for (int p = 0; p < c.world; ++p)
           if (p != src) st16(reinterpret_cast<void*>(c.peer_bufs[p] + off + i * 16), v);
     }
   }
-  block_barrier(c, 1, c.world);
+  if (!block_barrier(c, 1, c.world)) return;
+  if (c.rank != src) {
+    const uint8_t* mine = reinterpret_cast<const uint8_t*>(c.peer_bufs[c.rank] + off);
+    for (int64_t i = first; i < nvec; i += step) st16(reinterpret_cast<uint8_t*>(buf) + i * 16, ld16(mine + i * 16));
+  }
 }
 
 __global__ void __launch_bounds__(CT) barrier_kernel(CommCtx c, int pretend_world) {
@@ -265,43 +369,43 @@ __global__ void __launch_bounds__(CT) barrier_kernel(CommCtx c, int pretend_worl
 #define TB_DT_DISPATCH(dtype, CALL_F32, CALL_BF16) \
   do { if ((dtype) == kF32) { CALL_F32; } else { CALL_BF16; } } while (0)
 
+static int64_t vecs(int64_t n, int dtype) { return n * (dtype == kF32 ? 4 : 2) / 16; }
+
 void comm_all_reduce(const CommCtx& c, uint64_t off, int64_t n, int dtype, int op, bool use_mc, int sq_slot,
                      uint32_t, int blocks, cudaStream_t stream) {
-  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
+  const int64_t nvec = vecs(n, dtype);
   TB_DT_DISPATCH(dtype, (all_reduce_kernel<kF32><<<blocks, CT, 0, stream>>>(c, off, nvec, op, use_mc, sq_slot)),
                  (all_reduce_kernel<kBF16><<<blocks, CT, 0, stream>>>(c, off, nvec, op, use_mc, sq_slot)));
 }
 
-void comm_all_reduce_oneshot(const CommCtx& c, uint64_t off, void* out, int64_t n, int dtype, int op, uint32_t,
-                             int blocks, cudaStream_t stream) {
-  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
-  TB_DT_DISPATCH(dtype, (all_reduce_oneshot_kernel<kF32><<<blocks, CT, 0, stream>>>(c, off, out, nvec, op)),
-                 (all_reduce_oneshot_kernel<kBF16><<<blocks, CT, 0, stream>>>(c, off, out, nvec, op)));
+void comm_all_reduce_fused(const CommCtx& c, uint64_t off, const void* in, void* out, int64_t n, int dtype, int op,
+                           bool use_mc, bool oneshot, int blocks, cudaStream_t stream) {
+  const int64_t nvec = vecs(n, dtype);
+  TB_DT_DISPATCH(dtype,
+                 (all_reduce_fused_kernel<kF32><<<blocks, CT, 0, stream>>>(c, off, in, out, nvec, op, use_mc, oneshot)),
+                 (all_reduce_fused_kernel<kBF16><<<blocks, CT, 0, stream>>>(c, off, in, out, nvec, op, use_mc, oneshot)));
 }
 
-void comm_all_gather(const CommCtx& c, uint64_t src_off, uint64_t dst_off, int64_t n, int dtype, bool use_mc,
-                     uint32_t, int blocks, cudaStream_t stream) {
-  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
-  all_gather_kernel<<<blocks, CT, 0, stream>>>(c, src_off, dst_off, nvec, use_mc);
-}
-
-void comm_reduce_scatter(const CommCtx& c, uint64_t off, void* out, int64_t n, int dtype, int op, bool use_mc,
-                         uint32_t, int blocks, cudaStream_t stream) {
-  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
-  TB_DT_DISPATCH(dtype, (reduce_scatter_kernel<kF32><<<blocks, CT, 0, stream>>>(c, off, out, nvec, op, use_mc)),
-                 (reduce_scatter_kernel<kBF16><<<blocks, CT, 0, stream>>>(c, off, out, nvec, op, use_mc)));
-}
-
-void comm_all_to_all(const CommCtx& c, uint64_t src_off, uint64_t dst_off, int64_t n, int dtype, uint32_t,
+void comm_all_gather(const CommCtx& c, uint64_t dst_off, const void* in, void* out, int64_t n, int dtype, bool use_mc,
                      int blocks, cudaStream_t stream) {
-  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
-  all_to_all_kernel<<<blocks, CT, 0, stream>>>(c, src_off, dst_off, nvec);
+  all_gather_kernel<<<blocks, CT, 0, stream>>>(c, dst_off, in, out, vecs(n, dtype), use_mc);
 }
 
-void comm_broadcast(const CommCtx& c, uint64_t off, int64_t n, int dtype, int src, bool use_mc, uint32_t, int blocks,
+void comm_reduce_scatter(const CommCtx& c, uint64_t off, const void* in, void* out, int64_t n, int dtype, int op,
+                         bool use_mc, int blocks, cudaStream_t stream) {
+  const int64_t nvec = vecs(n, dtype);
+  TB_DT_DISPATCH(dtype, (reduce_scatter_kernel<kF32><<<blocks, CT, 0, stream>>>(c, off, in, out, nvec, op, use_mc)),
+                 (reduce_scatter_kernel<kBF16><<<blocks, CT, 0, stream>>>(c, off, in, out, nvec, op, use_mc)));
+}
+
+void comm_all_to_all(const CommCtx& c, uint64_t dst_off, const void* in, void* out, int64_t n, int dtype, int blocks,
+                     cudaStream_t stream) {
+  all_to_all_kernel<<<blocks, CT, 0, stream>>>(c, dst_off, in, out, vecs(n, dtype));
+}
+
+void comm_broadcast(const CommCtx& c, uint64_t off, void* buf, int64_t n, int dtype, int src, bool use_mc, int blocks,
                     cudaStream_t stream) {
-  const int64_t nvec = n * (dtype == kF32 ? 4 : 2) / 16;
-  broadcast_kernel<<<blocks, CT, 0, stream>>>(c, off, nvec, src, use_mc);
+  broadcast_kernel<<<blocks, CT, 0, stream>>>(c, off, buf, vecs(n, dtype), src, use_mc);
 }
 
 void comm_barrier(const CommCtx& c, uint32_t, int pretend_world, cudaStream_t stream) {

@@ -31,26 +31,26 @@ enum CommDtype : int { kF32 = 0, kBF16 = 1 };
 // In-place all-reduce of `n` elements at byte offset `off` of the symmetric allocation (two-shot: every rank
 // reduces its 1/world slice and broadcasts it).  use_mc selects multimem.ld_reduce/multimem.st (sum/avg only).
 // sq_slot >= 0: the sum of squares of this rank's reduced fp32 slice is stored into every rank's partial table
-// at [sq_slot][rank].  `generation` must increase by one per launch on a communicator.
+// at [sq_slot][rank][block].
 void comm_all_reduce(const CommCtx& c, uint64_t off, int64_t n, int dtype, int op, bool use_mc, int sq_slot,
                      uint32_t generation, int blocks, cudaStream_t stream);
-// One-shot all-reduce for small messages: every rank reads all peers and writes `out` (local, may be outside
-// the symmetric allocation).
-void comm_all_reduce_oneshot(const CommCtx& c, uint64_t off, void* out, int64_t n, int dtype, int op,
-                             uint32_t generation, int blocks, cudaStream_t stream);
-// all_gather: my `n` elements at `src_off` are written to offset dst_off + rank*n*elt of every rank.
-void comm_all_gather(const CommCtx& c, uint64_t src_off, uint64_t dst_off, int64_t n, int dtype, bool use_mc,
-                     uint32_t generation, int blocks, cudaStream_t stream);
-// reduce_scatter: input of world*n elements at `off` on every rank; rank r writes reduce(slice r) to `out` (local).
-void comm_reduce_scatter(const CommCtx& c, uint64_t off, void* out, int64_t n, int dtype, int op, bool use_mc,
-                         uint32_t generation, int blocks, cudaStream_t stream);
-// all_to_all: chunk j (n elements) of my input at src_off goes to rank j's dst_off + rank*n*elt.
-void comm_all_to_all(const CommCtx& c, uint64_t src_off, uint64_t dst_off, int64_t n, int dtype,
-                     uint32_t generation, int blocks, cudaStream_t stream);
-// broadcast: rank `src` writes its n elements at `off` to the same offset of every rank.
-void comm_broadcast(const CommCtx& c, uint64_t off, int64_t n, int dtype, int src, bool use_mc, uint32_t generation,
-                    int blocks, cudaStream_t stream);
-// cross-rank barrier only (also the bounded-wait self test: with world == 1 and expect_peers > 1 nothing ever
+// The launchers below work on ordinary LOCAL tensors (`in`, `out`, `buf`: 16-byte aligned, byte size a multiple of 16)
+// and use the symmetric staging area at `off` / `dst_off` as the exchange medium, all inside one kernel launch.
+void comm_all_reduce_fused(const CommCtx& c, uint64_t off, const void* in, void* out, int64_t n, int dtype, int op,
+                           bool use_mc, bool oneshot, int blocks, cudaStream_t stream);
+// all_gather: out[r * n + i] = rank r's in[i]; staging needs world * n elements.
+void comm_all_gather(const CommCtx& c, uint64_t dst_off, const void* in, void* out, int64_t n, int dtype, bool use_mc,
+                     int blocks, cudaStream_t stream);
+// reduce_scatter: in holds world * n elements, out receives reduce over ranks of slice [rank]; staging world * n.
+void comm_reduce_scatter(const CommCtx& c, uint64_t off, const void* in, void* out, int64_t n, int dtype, int op,
+                         bool use_mc, int blocks, cudaStream_t stream);
+// all_to_all: in/out hold world chunks of n elements; staging world * n.
+void comm_all_to_all(const CommCtx& c, uint64_t dst_off, const void* in, void* out, int64_t n, int dtype, int blocks,
+                     cudaStream_t stream);
+// broadcast (in place on buf) from rank `src`; staging n elements.
+void comm_broadcast(const CommCtx& c, uint64_t off, void* buf, int64_t n, int dtype, int src, bool use_mc, int blocks,
+                    cudaStream_t stream);
+// cross-rank barrier only (also the bounded-wait self test: with world == 1 and pretend_world > 1 nothing ever
 // arrives and the kernel records kErrPeerFlagWait).
 void comm_barrier(const CommCtx& c, uint32_t generation, int pretend_world, cudaStream_t stream);
 

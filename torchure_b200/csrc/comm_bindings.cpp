@@ -43,31 +43,35 @@ void register_comm(pybind11::module_& m) {
     tb::comm_all_reduce(make_ctx(peers, mc, rank, world, limit), off, n, dt_of(dtype), (int)op, use_mc, (int)sq_slot, 0,
                         (int)blocks, cs());
   });
-  m.def("comm_all_reduce_oneshot", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world,
-                                      int64_t limit, int64_t off, torch::Tensor out, int64_t n, int64_t dtype,
-                                      int64_t op, int64_t blocks) {
-    tb::comm_all_reduce_oneshot(make_ctx(peers, mc, rank, world, limit), off, out.data_ptr(), n, dt_of(dtype), (int)op, 0,
-                                (int)blocks, cs());
+  m.def("comm_all_reduce_fused", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                                    int64_t off, torch::Tensor in, torch::Tensor out, int64_t n, int64_t dtype,
+                                    int64_t op, bool use_mc, bool oneshot, int64_t blocks) {
+    tb::comm_all_reduce_fused(make_ctx(peers, mc, rank, world, limit), off, in.data_ptr(), out.data_ptr(), n,
+                              dt_of(dtype), (int)op, use_mc, oneshot, (int)blocks, cs());
   });
   m.def("comm_all_gather", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
-                              int64_t src_off, int64_t dst_off, int64_t n, int64_t dtype, bool use_mc, int64_t blocks) {
-    tb::comm_all_gather(make_ctx(peers, mc, rank, world, limit), src_off, dst_off, n, dt_of(dtype), use_mc, 0, (int)blocks,
-                        cs());
+                              int64_t dst_off, torch::Tensor in, torch::Tensor out, int64_t n, int64_t dtype,
+                              bool use_mc, int64_t blocks) {
+    tb::comm_all_gather(make_ctx(peers, mc, rank, world, limit), dst_off, in.data_ptr(), out.data_ptr(), n, dt_of(dtype),
+                        use_mc, (int)blocks, cs());
   });
   m.def("comm_reduce_scatter", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
-                                  int64_t off, torch::Tensor out, int64_t n, int64_t dtype, int64_t op, bool use_mc,
-                                  int64_t blocks) {
-    tb::comm_reduce_scatter(make_ctx(peers, mc, rank, world, limit), off, out.data_ptr(), n, dt_of(dtype), (int)op, use_mc,
-                            0, (int)blocks, cs());
+                                  int64_t off, torch::Tensor in, torch::Tensor out, int64_t n, int64_t dtype, int64_t op,
+                                  bool use_mc, int64_t blocks) {
+    tb::comm_reduce_scatter(make_ctx(peers, mc, rank, world, limit), off, in.data_ptr(), out.data_ptr(), n, dt_of(dtype),
+                            (int)op, use_mc, (int)blocks, cs());
   });
   m.def("comm_all_to_all", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
-                              int64_t src_off, int64_t dst_off, int64_t n, int64_t dtype, int64_t blocks) {
-    tb::comm_all_to_all(make_ctx(peers, mc, rank, world, limit), src_off, dst_off, n, dt_of(dtype), 0, (int)blocks, cs());
+                              int64_t dst_off, torch::Tensor in, torch::Tensor out, int64_t n, int64_t dtype,
+                              int64_t blocks) {
+    tb::comm_all_to_all(make_ctx(peers, mc, rank, world, limit), dst_off, in.data_ptr(), out.data_ptr(), n, dt_of(dtype),
+                        (int)blocks, cs());
   });
   m.def("comm_broadcast", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
-                             int64_t off, int64_t n, int64_t dtype, int64_t src, bool use_mc, int64_t blocks) {
-    tb::comm_broadcast(make_ctx(peers, mc, rank, world, limit), off, n, dt_of(dtype), (int)src, use_mc, 0, (int)blocks,
-                       cs());
+                             int64_t off, torch::Tensor buf, int64_t n, int64_t dtype, int64_t src, bool use_mc,
+                             int64_t blocks) {
+    tb::comm_broadcast(make_ctx(peers, mc, rank, world, limit), off, buf.data_ptr(), n, dt_of(dtype), (int)src, use_mc,
+                       (int)blocks, cs());
   });
   m.def("comm_barrier", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
                            int64_t pretend_world) {

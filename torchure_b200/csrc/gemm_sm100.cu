@@ -334,7 +334,7 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_
   const int num_kb = (K + BK - 1) / BK;
   if (force_splits > 0) {
     splits = force_splits;
-  } else if (out_mode != 0 && num_kb >= 32) {
+  } else if (out_mode != 0 && num_kb >= 32 && tiles < 2 * num_sms) {
     float best = 1e30f;
     for (int s = 1; s <= 8 && s * 8 <= num_kb; ++s) {
       const int waves = (tiles * s + num_sms - 1) / num_sms;

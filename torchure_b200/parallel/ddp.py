@@ -130,7 +130,7 @@ class TorchReducer:
 
 class DDP:
     def __init__(self, model: nn.Module, mesh: MeshLike, dim: str = "dp", bucket_mb: float = 25,
-                 fused: bool | None = None, merge_small: bool = True, grad_dtype=None):
+                 fused: bool | None = None, merge_small: bool = True, comm_sms: int = 16, sm_reserve: int = 0):
         self.mesh, self.dim = mesh, dim
         self.group_size = mesh.size(dim)
         self.requires_sync = True
@@ -158,7 +158,7 @@ class DDP:
         if self.fused:
             from torchure_b200.parallel.ddp_fused import FusedReducer
 
-            self.reducer = FusedReducer(self)
+            self.reducer = FusedReducer(self, comm_sms=comm_sms, sm_reserve=sm_reserve)
             if hasattr(model, "set_grad_sink"):
                 model.set_grad_sink(self.reducer)
         else:

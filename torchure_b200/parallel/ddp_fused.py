@@ -19,8 +19,9 @@ partial table and broadcasts the slice with ``multimem.st``.  No NCCL call, no s
 ``sq_norm()`` sums the partial table in a fixed order, so every rank derives bit-identical clip coefficients; with one
 rank it is a single multi-tensor reduction over the flat buffer.  After a sync launch ``p.grad`` is a view of the bucket.
 
-GEMM kernels are persistent and occupy every SM they are given, so with more than one rank the reducer asks them to
-leave ``comm_sms`` SMs free for the communication kernels (``ops.set_compute_sm_reserve``).
+The communication kernel needs almost no shared memory and few registers, so its CTAs become resident NEXT TO the
+persistent GEMM CTAs (one per SM, shared-memory bound) instead of waiting for them; ``sm_reserve`` > 0 additionally
+keeps that many SMs free of GEMM CTAs (``ops.set_compute_sm_reserve``) for fabrics where co-residency is not enough.
 """
 
 from __future__ import annotations
@@ -34,7 +35,7 @@ from torchure_b200.ops import multi_tensor
 class FusedReducer:
     fused = True
 
-    def __init__(self, ddp, comm_sms: int = 16):
+    def __init__(self, ddp, comm_sms: int = 16, sm_reserve: int = 0):
         self.ddp = ddp
         self.world = ddp.group_size
         dev = ddp.buckets[0].params[0].device
@@ -54,7 +55,7 @@ class FusedReducer:
             self.partials = self.comm.partials(len(ddp.buckets))
             self.partials.zero_()
             self.stream = torch.cuda.Stream(device=dev, priority=-1)
-            ops.set_compute_sm_reserve(comm_sms)
+            ops.set_compute_sm_reserve(sm_reserve)
         else:
             self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
             self.partials = None

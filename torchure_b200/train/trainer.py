@@ -119,7 +119,8 @@ class Trainer:
     def _parallelize(self, model):
         ddp_cfg = self.config.get("ddp", {})
         self.ddp = DDP(model, self.mesh, dim="dp", bucket_mb=ddp_cfg.get("bucket_mb", 25),
-                       fused=ddp_cfg.get("fused"), merge_small=ddp_cfg.get("merge_small", True))
+                       fused=ddp_cfg.get("fused"), merge_small=ddp_cfg.get("merge_small", True),
+                       comm_sms=ddp_cfg.get("comm_sms", 16), sm_reserve=ddp_cfg.get("sm_reserve", 0))
         return model
 
     def _wire_engine(self) -> None:
