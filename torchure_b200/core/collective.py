@@ -239,6 +239,20 @@ def send_recv(send: torch.Tensor | None, recv: torch.Tensor | None, mesh: MeshLi
     return recv
 
 
+def isend(tensor: torch.Tensor, mesh: MeshLike, dim: str, dst: int):
+    """Start sending `tensor` to coordinate `dst` of the `dim` group; returns a work handle to ``wait()`` on later.
+    The tensor must stay alive and unmodified until then (pipeline schedules post sends and move on)."""
+    group = mesh.get_group(dim)
+    return dist.isend(tensor.contiguous(), dist.get_global_rank(group, dst), group=group)
+
+
+def recv(tensor: torch.Tensor, mesh: MeshLike, dim: str, src: int) -> torch.Tensor:
+    """Blocking receive into `tensor` from coordinate `src` of the `dim` group."""
+    group = mesh.get_group(dim)
+    dist.recv(tensor, dist.get_global_rank(group, src), group=group)
+    return tensor
+
+
 def barrier(mesh: MeshLike | None = None, dim: str | None = None) -> None:
     """Block until every rank of the `dim` group (the world without a mesh) has arrived."""
     dist.barrier(group=None if mesh is None else mesh.get_group(dim))

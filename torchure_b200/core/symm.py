@@ -3,7 +3,7 @@
 One ``SymmComm`` per mesh axis group.  It owns a symmetric allocation (every rank of the group maps
 every other rank's copy, plus an NVSwitch multicast mapping when the fabric offers one), laid out as::
 
-    [ flags 64 KiB | sum-of-squares partials 512 KiB | persistent region (DDP buckets) | staging area ]
+    [ flags 64 KiB | sum-of-squares partials 1 MiB | persistent region (DDP buckets) | staging area ]
 
 The bootstrap (allocation, handle exchange, peer and multicast mapping) uses
 ``torch.distributed._symmetric_memory``; every byte moved afterwards is moved by the kernels of
@@ -37,7 +37,7 @@ def _align(n: int, a: int) -> int:
 
 class SymmComm:
     def __init__(self, group, rank: int, world: int, staging_bytes: int = 64 << 20, persistent_bytes: int = 0,
-                 wait_limit_s: float = 30.0, blocks: int = 32):
+                 wait_limit_s: float = 30.0, blocks: int = 128):
         import torch.distributed._symmetric_memory as symm_mem
 
         ext = ops.ext()

@@ -11,9 +11,9 @@
 namespace tb {
 
 constexpr int kCommMaxRanks = 8;
-constexpr int kCommMaxBlocks = 64;
+constexpr int kCommMaxBlocks = 128;
 constexpr int kFlagBytes = 64 * 1024;   // [2 barriers][kCommMaxBlocks][kCommMaxRanks] uint32 + spare
-constexpr int kPartialBytes = 512 * 1024;  // sum-of-squares partials [256 slots][ranks][blocks] fp32
+constexpr int kPartialBytes = 1024 * 1024;  // sum-of-squares partials [256 slots][ranks][blocks] fp32
 
 struct CommCtx {
   uint64_t peer_bufs[kCommMaxRanks];  // device-visible base address of every rank's allocation

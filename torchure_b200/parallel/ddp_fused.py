@@ -49,7 +49,8 @@ class FusedReducer:
             from torchure_b200.core.symm import SymmComm
 
             self.comm = SymmComm(ddp.mesh.get_group(ddp.dim), ddp.mesh.coordinate(ddp.dim), self.world,
-                                 staging_bytes=4096, persistent_bytes=total * 4 + 4096, blocks=comm_sms)
+                                 staging_bytes=4096, persistent_bytes=total * 4 + 4096)
+            self.comm_sms = comm_sms
             self.flat = self.comm.alloc(total, torch.float32)
             self.flat.zero_()
             self.partials = self.comm.partials(len(ddp.buckets))
@@ -107,7 +108,10 @@ class FusedReducer:
         ready.record()
         with torch.cuda.stream(self.stream):
             self.stream.wait_event(ready)
-            self.comm.all_reduce_symmetric_(self.padded[b.index], "avg", sq_slot=b.index)
+            # buckets reduced under the rest of backward share the SMs with it; the last bucket has the GPU to itself
+            last = b.index == len(self.ddp.buckets) - 1
+            self.comm.all_reduce_symmetric_(self.padded[b.index], "avg", sq_slot=b.index,
+                                            blocks=self.comm.blocks if last else self.comm_sms)
             done = torch.cuda.Event()
             done.record()
         return _Ready(done)

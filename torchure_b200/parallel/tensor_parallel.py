@@ -1,0 +1,170 @@
+"""Tensor parallelism (Megatron-style column/row split) and sequence parallelism for the decoder block.
+
+The reference has no TP code (roadmap only: column-wise q/k/v/gate/up, row-wise o/down, vocab-parallel head with
+loss-parallel CE, SP as all-gather / reduce-scatter pairs).  Building blocks here:
+
+* ``ColumnParallelLinear``  y_local = x W_local^T, W split along the output dim.  forward: identity on x (or
+  all-gather along the sequence when ``sequence_parallel``); backward: all-reduce of dx (or reduce-scatter).
+* ``RowParallelLinear``     y = sum_ranks x_local W_local^T, W split along the input dim.  forward: all-reduce (or
+  reduce-scatter along the sequence); backward: identity (or all-gather).
+* ``parallelize_block``     rewrites a ``TransformerBlock`` in place: q/k/v/gate/up become column-parallel (whole KV
+  heads per rank), o/down row-parallel; per-head q/k norms are replicated.
+* ``vocab_parallel_cross_entropy``  loss-parallel CE on vocabulary shards: two all-reduces per call (max, then
+  sum-exp and target logit together).
+
+Collectives go through ``core.collective`` (NVLink kernels on GPUs, gloo on CPU).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from torchure_b200.core.collective import all_gather, all_reduce, reduce_scatter
+
+
+class _CopyToTP(torch.autograd.Function):
+    """identity forward, all-reduce backward"""
+
+    @staticmethod
+    def forward(ctx, x, mesh, dim):
+        ctx.mesh, ctx.dim = mesh, dim
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        all_reduce(g, ctx.mesh, ctx.dim, "sum")
+        return g, None, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """all-reduce forward, identity backward"""
+
+    @staticmethod
+    def forward(ctx, x, mesh, dim):
+        x = x.contiguous()
+        all_reduce(x, mesh, dim, "sum")
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None, None
+
+
+class _GatherSeq(torch.autograd.Function):
+    """sequence-parallel entry: all-gather along dim 1 forward, reduce-scatter backward"""
+
+    @staticmethod
+    def forward(ctx, x, mesh, dim):
+        ctx.mesh, ctx.dim = mesh, dim
+        return all_gather(x.contiguous(), mesh, dim, gather_dim=1)
+
+    @staticmethod
+    def backward(ctx, g):
+        return reduce_scatter(g.contiguous(), ctx.mesh, ctx.dim, "sum", scatter_dim=1), None, None
+
+
+class _ScatterSeq(torch.autograd.Function):
+    """sequence-parallel exit: reduce-scatter along dim 1 forward, all-gather backward"""
+
+    @staticmethod
+    def forward(ctx, x, mesh, dim):
+        ctx.mesh, ctx.dim = mesh, dim
+        return reduce_scatter(x.contiguous(), mesh, dim, "sum", scatter_dim=1)
+
+    @staticmethod
+    def backward(ctx, g):
+        return all_gather(g.contiguous(), ctx.mesh, ctx.dim, gather_dim=1), None, None
+
+
+class ColumnParallelLinear(nn.Module):
+    def __init__(self, full: nn.Linear, mesh, dim: str, sequence_parallel: bool = False, split_sizes=None):
+        super().__init__()
+        n, r = mesh.size(dim), mesh.coordinate(dim)
+        rows = full.weight.shape[0]
+        assert rows % n == 0, f"output dim {rows} is not divisible by tp={n}"
+        per = rows // n
+        self.weight = nn.Parameter(full.weight.detach()[r * per:(r + 1) * per].clone())
+        self.mesh, self.dim, self.sp = mesh, dim, sequence_parallel
+
+    def forward(self, x):
+        x = _GatherSeq.apply(x, self.mesh, self.dim) if self.sp else _CopyToTP.apply(x, self.mesh, self.dim)
+        return F.linear(x, self.weight)
+
+
+class RowParallelLinear(nn.Module):
+    def __init__(self, full: nn.Linear, mesh, dim: str, sequence_parallel: bool = False):
+        super().__init__()
+        n, r = mesh.size(dim), mesh.coordinate(dim)
+        cols = full.weight.shape[1]
+        assert cols % n == 0, f"input dim {cols} is not divisible by tp={n}"
+        per = cols // n
+        self.weight = nn.Parameter(full.weight.detach()[:, r * per:(r + 1) * per].clone())
+        self.mesh, self.dim, self.sp = mesh, dim, sequence_parallel
+
+    def forward(self, x):
+        y = F.linear(x, self.weight)
+        return _ScatterSeq.apply(y, self.mesh, self.dim) if self.sp else _ReduceFromTP.apply(y, self.mesh, self.dim)
+
+
+def parallelize_block(block, mesh, dim: str = "tp", sequence_parallel: bool = False) -> None:
+    """Shard one TransformerBlock over the `dim` axis in place (heads and FFN columns split evenly)."""
+    n = mesh.size(dim)
+    g = block.gqa
+    assert g.num_heads % n == 0 and g.num_kv_heads % n == 0, "tp must divide the query and KV head counts"
+    g.q_proj = ColumnParallelLinear(g.q_proj, mesh, dim, sequence_parallel)
+    g.k_proj = ColumnParallelLinear(g.k_proj, mesh, dim, sequence_parallel)
+    g.v_proj = ColumnParallelLinear(g.v_proj, mesh, dim, sequence_parallel)
+    g.o_proj = RowParallelLinear(g.o_proj, mesh, dim, sequence_parallel)
+    g.num_heads //= n
+    g.num_kv_heads //= n
+    f = block.ffn
+    f.gate_proj = ColumnParallelLinear(f.gate_proj, mesh, dim, sequence_parallel)
+    f.up_proj = ColumnParallelLinear(f.up_proj, mesh, dim, sequence_parallel)
+    f.down_proj = RowParallelLinear(f.down_proj, mesh, dim, sequence_parallel)
+
+
+def parallelize_model(model, mesh, dim: str = "tp") -> None:
+    """Tensor-parallel decoder: every block sharded, embedding / norms / head replicated.  Forces the torch path
+    (the sm_100a engine expects unsharded fused projections)."""
+    for b in model.blocks:
+        parallelize_block(b, mesh, dim)
+    model.impl = "torch"
+
+
+class _VocabParallelCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits_local, labels, mesh, dim, ignore_index):
+        n, r = mesh.size(dim), mesh.coordinate(dim)
+        vloc = logits_local.shape[-1]
+        lo = r * vloc
+        lf = logits_local.float()
+        mx = lf.max(dim=-1).values
+        all_reduce(mx, mesh, dim, "max")
+        ex = torch.exp(lf - mx[:, None])
+        keep = labels != ignore_index
+        mine = keep & (labels >= lo) & (labels < lo + vloc)
+        idx = torch.where(mine, labels - lo, torch.zeros_like(labels))
+        tgt = torch.where(mine, lf.gather(1, idx[:, None]).squeeze(1), torch.zeros_like(mx))
+        packed = torch.stack([ex.sum(-1), tgt], dim=0)  # one all-reduce for both
+        all_reduce(packed, mesh, dim, "sum")
+        sumexp, tgt = packed[0], packed[1]
+        n_valid = keep.sum().clamp_min(1)
+        loss = torch.where(keep, torch.log(sumexp) + mx - tgt, torch.zeros_like(mx)).sum() / n_valid
+        probs = ex / sumexp[:, None]
+        probs[torch.arange(labels.numel(), device=labels.device)[mine], idx[mine]] -= 1.0
+        ctx.save_for_backward((probs * keep[:, None] / n_valid).to(logits_local.dtype))
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        (d,) = ctx.saved_tensors
+        return d * g, None, None, None, None
+
+
+def vocab_parallel_cross_entropy(logits_local: torch.Tensor, labels: torch.Tensor, mesh, dim: str = "tp",
+                                 ignore_index: int = -100) -> torch.Tensor:
+    """Mean CE where `logits_local` (N, V/tp) holds this rank's vocabulary slice [r*V/tp, (r+1)*V/tp)."""
+    return _VocabParallelCE.apply(logits_local, labels, mesh, dim, ignore_index)
