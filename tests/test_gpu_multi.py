@@ -117,3 +117,46 @@ def test_fused_ddp_matches_single_process():
 
 def test_fused_ddp_peer_loads_only():
     run_on_gpus(_ddp_parity, 2, env={"TORCHURE_B200_NVLS": "0"})
+
+
+def _gemm_comm(rank, world):
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.core.symm import SymmComm
+    from torchure_b200.ops import kernels
+    from torchure_b200.ops.gemm_comm import SymmetricOperand, ag_gemm, gemm_rs
+
+    mesh = Mesh({"tp": world})
+    comm = SymmComm(mesh.get_group("tp"), rank, world, staging_bytes=1 << 20, persistent_bytes=256 << 20)
+    rows, K, N = 512, 1024, 768
+    M = rows * world
+    # all-gather -> GEMM: A row-sharded, B local
+    a_sh = SymmetricOperand(comm, (rows, K), torch.bfloat16)
+    g = torch.Generator("cuda").manual_seed(7)
+    a_full = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    a_sh.tensor.copy_(a_full[rank * rows:(rank + 1) * rows])
+    for _ in range(2):  # twice: the handshake flags must re-arm
+        out = ag_gemm(comm, a_sh, b)
+        ref = a_full.float() @ b.float().t()
+        err = ((out.float() - ref).norm() / ref.norm()).item()
+        assert err < 5e-3, ("ag_gemm", err)
+    # GEMM -> reduce-scatter: K split over ranks
+    Kl = 512
+    a_loc = torch.randn(M, Kl, device="cuda", generator=torch.Generator("cuda").manual_seed(100 + rank)).bfloat16()
+    b_loc = torch.randn(N, Kl, device="cuda", generator=torch.Generator("cuda").manual_seed(200 + rank)).bfloat16()
+    c_sh = SymmetricOperand(comm, (rows, N), torch.float32)
+    partial = a_loc.float() @ b_loc.float().t()
+    torch.distributed.all_reduce(partial)
+    for _ in range(2):
+        got = gemm_rs(comm, a_loc, b_loc, c_sh)
+        torch.cuda.synchronize()
+        want = partial[rank * rows:(rank + 1) * rows]
+        err = ((got - want).norm() / want.norm()).item()
+        assert err < 1e-3, ("gemm_rs", err)
+        torch.distributed.barrier()
+    comm.check()
+    kernels.check_error()
+
+
+def test_fused_gemm_collectives():
+    run_on_gpus(_gemm_comm, min(_world(), 4))

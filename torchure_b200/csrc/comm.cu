@@ -9,6 +9,7 @@
 // 1->0 locally, so flags reset themselves.  Every spin is bounded by CommCtx::wait_limit_ns; on expiry the block
 // records kErrPeerFlagWait and the kernel finishes without touching peer memory again.
 #include "comm_api.h"
+#include "comm_device.cuh"
 #include "common.cuh"
 
 namespace tb {
@@ -16,48 +17,6 @@ namespace tb {
 namespace {
 
 constexpr int CT = 512;  // threads per block
-
-__device__ __forceinline__ uint32_t* flag_ptr(uint64_t base, int phase, int block, int rank) {
-  return reinterpret_cast<uint32_t*>(base) + (phase * kCommMaxBlocks + block) * kCommMaxRanks + rank;
-}
-
-__device__ __forceinline__ uint32_t cas_sys(uint32_t* addr, uint32_t cmp, uint32_t val) {
-  uint32_t old;
-  asm volatile("atom.acq_rel.sys.global.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "l"(addr), "r"(cmp), "r"(val) : "memory");
-  return old;
-}
-
-// Block-level barrier with the same block of every peer.  Returns false if a wait expired.
-__device__ bool block_barrier(const CommCtx& c, int phase, int world) {
-  __shared__ int s_fail;
-  if (threadIdx.x == 0) s_fail = 0;
-  __syncthreads();
-  __threadfence_system();
-  if (threadIdx.x < world && threadIdx.x != c.rank) {
-    const int peer = threadIdx.x;
-    const uint64_t t0 = globaltimer_ns();
-    bool ok = true;
-    // raise my flag in the peer's memory (only if a peer exists; pretend-world barriers have no peer memory)
-    if (peer < c.world) {
-      uint32_t* theirs = flag_ptr(c.peer_bufs[peer], phase, blockIdx.x, c.rank);
-      while (cas_sys(theirs, 0u, 1u) != 0u) {
-        if (globaltimer_ns() - t0 > c.wait_limit_ns || *reinterpret_cast<volatile int*>(c.err) != 0) { ok = false; break; }
-      }
-    }
-    if (ok) {
-      uint32_t* mine = flag_ptr(c.peer_bufs[c.rank], phase, blockIdx.x, peer);
-      while (cas_sys(mine, 1u, 0u) != 1u) {
-        if (globaltimer_ns() - t0 > c.wait_limit_ns || *reinterpret_cast<volatile int*>(c.err) != 0) { ok = false; break; }
-      }
-    }
-    if (!ok) {
-      atomicCAS(c.err, 0, kErrPeerFlagWait);
-      s_fail = 1;
-    }
-  }
-  __syncthreads();
-  return s_fail == 0;
-}
 
 // ---- 16-byte vector helpers ---------------------------------------------------------------------------
 struct V4 { uint32_t x, y, z, w; };

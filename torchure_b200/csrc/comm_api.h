@@ -54,4 +54,10 @@ void comm_broadcast(const CommCtx& c, uint64_t off, void* buf, int64_t n, int dt
 // arrives and the kernel records kErrPeerFlagWait).
 void comm_barrier(const CommCtx& c, uint32_t generation, int pretend_world, cudaStream_t stream);
 
+// Fused compute + collective tcgen05 GEMMs (gemm_sm100.cu).
+int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, const void* B, void* C, int M, int N, int K, int64_t ldb, int64_t ldc,
+                 int num_sms, cudaStream_t stream);
+int gemm_rs_bf16(const CommCtx& c, const void* A, const void* B, uint64_t c_off, int M, int N, int K, int64_t lda,
+                 int64_t ldb, int num_sms, cudaStream_t stream);
+
 }  // namespace tb

@@ -73,6 +73,22 @@ void register_comm(pybind11::module_& m) {
     tb::comm_broadcast(make_ctx(peers, mc, rank, world, limit), off, buf.data_ptr(), n, dt_of(dtype), (int)src, use_mc,
                        (int)blocks, cs());
   });
+  m.def("ag_gemm", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit, int64_t a_off,
+                      torch::Tensor b, torch::Tensor c, int64_t M, int64_t K) {
+    TORCH_CHECK(b.stride(1) == 1 && c.stride(1) == 1 && b.size(1) == K && c.size(0) == M && c.size(1) == b.size(0));
+    const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    const int rc = tb::ag_gemm_bf16(make_ctx(peers, mc, rank, world, limit), a_off, b.data_ptr(), c.data_ptr(), (int)M,
+                                    (int)b.size(0), (int)K, b.stride(0), c.stride(0), sms, cs());
+    TORCH_CHECK(rc == 0, "ag_gemm failed with code ", rc);
+  });
+  m.def("gemm_rs", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                      torch::Tensor a, torch::Tensor b, int64_t c_off) {
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1));
+    const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    const int rc = tb::gemm_rs_bf16(make_ctx(peers, mc, rank, world, limit), a.data_ptr(), b.data_ptr(), c_off,
+                                    (int)a.size(0), (int)b.size(0), (int)a.size(1), a.stride(0), b.stride(0), sms, cs());
+    TORCH_CHECK(rc == 0, "gemm_rs failed with code ", rc);
+  });
   m.def("comm_barrier", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
                            int64_t pretend_world) {
     tb::comm_barrier(make_ctx(peers, mc, rank, world, limit), 0, (int)pretend_world, cs());

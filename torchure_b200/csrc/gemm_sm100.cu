@@ -15,6 +15,7 @@
 // (dy W) and wgrad (dy^T x) without any transpose kernel.  Edges are handled by TMA (zero fill on
 // loads, clipping on stores); every coordinate passed to TMA is a multiple of 32 elements.
 #include "api.h"
+#include "comm_device.cuh"
 #include "common.cuh"
 
 #include <cstring>
@@ -36,10 +37,20 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 
-template <bool A_MN, bool B_MN, int OUT>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int splits, int* err) {
+// Fused GEMM + collective: per-rank tensor maps over the same symmetric buffer on every peer.
+//   COMM == 1  all-gather -> GEMM: A row-block r lives on rank r; every CTA loads its A tiles straight from the
+//              owner's memory with plain (non-multicast) TMA loads over NVLink.
+//   COMM == 2  GEMM -> reduce-scatter: C row-block r belongs to rank r; every CTA adds its partial tiles into the
+//              owner's fp32 buffer with TMA reduce-add over NVLink.
+struct GemmComm {
+  CUtensorMap maps[kCommMaxRanks];
+  CommCtx c;
+  int rows_per_rank;
+};
+
+template <bool A_MN, bool B_MN, int OUT, int COMM>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, int M,
+                                          int N, int K, int splits, int* err, const GemmComm* gc) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi = smem + STAGES * STAGE_BYTES;
@@ -82,8 +93,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  bool peers_ok = true;
+  if (COMM != 0) peers_ok = block_barrier(gc->c, 4, gc->c.world);  // every peer's operand / zeroed output is in place
 
-  if (warp == 0) {
+  if (!peers_ok) {
+    // a peer never showed up: skip the work, fall through to the teardown
+  } else if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (elect_one()) {
       int stage = 0;
@@ -101,7 +116,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sB = sA + A_BYTES;
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           const int k0 = kb * BK;
-          if (!A_MN) {
+          if (COMM == 1) {
+            const int owner = m0 / gc->rows_per_rank;
+            tma_load_2d(sA, &gc->maps[owner], &full[stage], k0, m0 - owner * gc->rows_per_rank);
+          } else if (!A_MN) {
             tma_load_2d(sA, &tmA, &full[stage], k0, m0);
           } else {
 #pragma unroll
@@ -210,8 +228,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (OUT == 2) tma_reduce_add_2d(&tmC, buf, n0 + c * COLS, m0 + q * 32);
-            else tma_store_2d(&tmC, buf, n0 + c * COLS, m0 + q * 32);
+            if (COMM == 2) {
+              const int owner = m0 / gc->rows_per_rank;
+              tma_reduce_add_2d(&gc->maps[owner], buf, n0 + c * COLS, m0 - owner * gc->rows_per_rank + q * 32);
+            } else if (OUT == 2) {
+              tma_reduce_add_2d(&tmC, buf, n0 + c * COLS, m0 + q * 32);
+            } else {
+              tma_store_2d(&tmC, buf, n0 + c * COLS, m0 + q * 32);
+            }
             tma_commit_group();
           }
         }
@@ -227,12 +251,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
+  if (COMM != 0 && peers_ok) block_barrier(gc->c, 6, gc->c.world);  // every peer's loads / adds have landed
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+template <bool A_MN, bool B_MN, int OUT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int splits, int* err) {
+  gemm_body<A_MN, B_MN, OUT, 0>(tmA, tmB, tmC, M, N, K, splits, err, nullptr);
+}
+
+template <int COMM>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ GemmComm gc, int M, int N, int K,
+                 int* err) {
+  // COMM 1: bf16 store of C; COMM 2: fp32 reduce-add of C into the owners
+  gemm_body<false, false, COMM == 1 ? 0 : 2, COMM>(tmA, tmB, tmC, M, N, K, 1, err, &gc);
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -362,6 +403,68 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_
   TB_GEMM_CASE(true, false, 0)
 #undef TB_GEMM_CASE
   return -2;
+}
+
+// A_r [M/world, K] bf16 sits at byte offset a_off of every rank's symmetric allocation; B [N, K] and C [M, N] (bf16)
+// are local.  C = concat_r(A_r) * B^T.
+int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, const void* B, void* C, int M, int N, int K, int64_t ldb, int64_t ldc,
+                 int num_sms, cudaStream_t stream) {
+  if (M % (c.world * BM) != 0) return -3;
+  GemmComm gc{};
+  gc.c = c;
+  gc.rows_per_rank = M / c.world;
+  for (int r = 0; r < c.world; ++r) {
+    int rc = make_tmap_2d(&gc.maps[r], reinterpret_cast<const void*>(c.peer_bufs[r] + a_off), 2, gc.rows_per_rank, K, K,
+                          BM, 64);
+    if (rc) return rc;
+  }
+  CUtensorMap tb_, tc;
+  int rc = make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
+  if (rc) return rc - 100;
+  rc = make_tmap_2d(&tc, C, 2, M, N, ldc, 32, 64);
+  if (rc) return rc - 200;
+  auto kern = gemm_comm_kernel<1>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
+    configured = true;
+  }
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  const int cap = num_sms < kCommMaxBlocks ? num_sms : kCommMaxBlocks;  // the handshake has one flag row per CTA
+  const int grid = tiles < cap ? tiles : cap;
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(gc.maps[c.rank], tb_, tc, gc, M, N, K, c.err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+// A [M, K_local], B [N, K_local] bf16 local; the fp32 output shard [M/world, N] sits at byte offset c_off of every
+// rank's symmetric allocation and must be zero on entry.  out_r = sum over ranks of (A B^T)[rows of r].
+int gemm_rs_bf16(const CommCtx& c, const void* A, const void* B, uint64_t c_off, int M, int N, int K, int64_t lda,
+                 int64_t ldb, int num_sms, cudaStream_t stream) {
+  if (M % (c.world * BM) != 0) return -3;
+  GemmComm gc{};
+  gc.c = c;
+  gc.rows_per_rank = M / c.world;
+  for (int r = 0; r < c.world; ++r) {
+    int rc = make_tmap_2d(&gc.maps[r], reinterpret_cast<const void*>(c.peer_bufs[r] + c_off), 4, gc.rows_per_rank, N, N,
+                          32, 32);
+    if (rc) return rc;
+  }
+  CUtensorMap ta, tb_;
+  int rc = make_tmap_2d(&ta, A, 2, M, K, lda, BM, 64);
+  if (rc) return rc - 100;
+  rc = make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
+  if (rc) return rc - 200;
+  auto kern = gemm_comm_kernel<2>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
+    configured = true;
+  }
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  const int cap = num_sms < kCommMaxBlocks ? num_sms : kCommMaxBlocks;
+  const int grid = tiles < cap ? tiles : cap;
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb_, gc.maps[c.rank], gc, M, N, K, c.err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 }  // namespace tb

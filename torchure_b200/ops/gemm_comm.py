@@ -1,0 +1,52 @@
+"""Fused tensor-core GEMM + NVLink collective (one kernel each).
+
+``ag_gemm``   all-gather -> GEMM.  Every rank holds a row block ``A_r`` of the activation in the symmetric
+              allocation; the kernel computes ``concat_r(A_r) @ B^T`` and its CTAs fetch remote A tiles directly from
+              the owning GPU with plain TMA loads over NVLink, overlapped tile by tile with tcgen05 MMAs.  No gathered
+              copy of A is ever written.  (FSDP parameter all-gather fused into the first consuming GEMM: pass the
+              weight shard as ``A`` and the activation as ``B`` to get the transposed product.)
+``gemm_rs``   GEMM -> reduce-scatter.  Every rank multiplies its K-slice (``A [M, K/n] @ B [N, K/n]^T``) and the
+              epilogue adds each fp32 tile into the row block of the rank that owns it with TMA reduce-add over
+              NVLink; after the kernel rank r holds ``sum_ranks(partial)[rows of r]``.  (Row-parallel TP output, FSDP
+              gradient reduce-scatter.)
+
+Both handshake with the same CTA index on every peer before touching remote memory and after the last remote access
+(bounded waits, status word on expiry).  Operands are bf16, ``M`` must be a multiple of ``128 * world``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from torchure_b200 import ops
+
+
+class SymmetricOperand:
+    """A tensor allocated inside a communicator's symmetric region (same offset on every rank)."""
+
+    def __init__(self, comm, shape, dtype):
+        self.comm = comm
+        numel = 1
+        for s in shape:
+            numel *= s
+        self.tensor = comm.alloc(numel, dtype).view(*shape)
+        self.offset = comm.offset_of(self.tensor)
+
+
+def ag_gemm(comm, a_shard: SymmetricOperand, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] = concat_ranks(a_shard)[M, K] @ b[N, K]^T, bf16."""
+    rows, K = a_shard.tensor.shape
+    M = rows * comm.world
+    if out is None:
+        out = torch.empty(M, b.shape[0], dtype=torch.bfloat16, device=b.device)
+    ops.ext().ag_gemm(*comm._ctx(), a_shard.offset, b, out, M, K)
+    ops.count_launch()
+    return out
+
+
+def gemm_rs(comm, a: torch.Tensor, b: torch.Tensor, out_shard: SymmetricOperand) -> torch.Tensor:
+    """out_shard[M/world, N] (fp32, zeroed here) = rows of this rank of sum_ranks(a @ b^T)."""
+    out_shard.tensor.zero_()
+    ops.ext().gemm_rs(*comm._ctx(), a, b, out_shard.offset)
+    ops.count_launch()
+    return out_shard.tensor
