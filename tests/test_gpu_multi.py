@@ -127,19 +127,20 @@ def _gemm_comm(rank, world):
 
     mesh = Mesh({"tp": world})
     comm = SymmComm(mesh.get_group("tp"), rank, world, staging_bytes=1 << 20, persistent_bytes=256 << 20)
-    rows, K, N = 512, 1024, 768
-    M = rows * world
-    # all-gather -> GEMM: A row-sharded, B local
-    a_sh = SymmetricOperand(comm, (rows, K), torch.bfloat16)
-    g = torch.Generator("cuda").manual_seed(7)
-    a_full = torch.randn(M, K, device="cuda", generator=g).bfloat16()
-    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
-    a_sh.tensor.copy_(a_full[rank * rows:(rank + 1) * rows])
-    for _ in range(2):  # twice: the handshake flags must re-arm
-        out = ag_gemm(comm, a_sh, b)
-        ref = a_full.float() @ b.float().t()
-        err = ((out.float() - ref).norm() / ref.norm()).item()
-        assert err < 5e-3, ("ag_gemm", err)
+    # all-gather -> GEMM: A row-sharded, B local; two shapes on one communicator (the arrival words are shared)
+    for rows, K, N in ((256, 512, 512), (512, 1024, 768)):
+        M = rows * world
+        a_sh = SymmetricOperand(comm, (rows, K), torch.bfloat16)
+        g = torch.Generator("cuda").manual_seed(7)
+        a_full = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+        a_sh.tensor.copy_(a_full[rank * rows:(rank + 1) * rows])
+        for _ in range(2):  # twice: the handshake flags must re-arm
+            out, gathered = ag_gemm(comm, a_sh, b, return_gathered=True)
+            ref = a_full.float() @ b.float().t()
+            err = ((out.float() - ref).norm() / ref.norm()).item()
+            assert err < 5e-3, ("ag_gemm", err)
+            assert torch.equal(gathered, a_full)
     # GEMM -> reduce-scatter: K split over ranks
     Kl = 512
     a_loc = torch.randn(M, Kl, device="cuda", generator=torch.Generator("cuda").manual_seed(100 + rank)).bfloat16()

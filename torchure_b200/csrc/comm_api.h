@@ -55,8 +55,12 @@ void comm_broadcast(const CommCtx& c, uint64_t off, void* buf, int64_t n, int dt
 void comm_barrier(const CommCtx& c, uint32_t generation, int pretend_world, cudaStream_t stream);
 
 // Fused compute + collective tcgen05 GEMMs (gemm_sm100.cu).
-int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, const void* B, void* C, int M, int N, int K, int64_t ldb, int64_t ldc,
-                 int num_sms, cudaStream_t stream);
+// ag_gemm: C[M, N] = concat_ranks(A_r)[M, K] * B[N, K]^T.  A_r ([M/world, K] bf16) sits at byte offset a_off of every
+// rank's symmetric allocation; the assembled A ([M, K] bf16) is written at byte offset g_off of every rank's
+// allocation (each rank pushes its shard to all); `epoch` is the 1-based count of ag_gemm calls made on this
+// communicator (the arrival words compare against it).
+int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, uint64_t g_off, uint32_t epoch, const void* B, void* C, int M, int N,
+                 int K, int64_t ldb, int64_t ldc, int num_sms, cudaStream_t stream);
 int gemm_rs_bf16(const CommCtx& c, const void* A, const void* B, uint64_t c_off, int M, int N, int K, int64_t lda,
                  int64_t ldb, int num_sms, cudaStream_t stream);
 

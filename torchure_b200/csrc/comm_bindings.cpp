@@ -74,10 +74,10 @@ void register_comm(pybind11::module_& m) {
                        (int)blocks, cs());
   });
   m.def("ag_gemm", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit, int64_t a_off,
-                      torch::Tensor b, torch::Tensor c, int64_t M, int64_t K) {
+                      int64_t g_off, int64_t epoch, torch::Tensor b, torch::Tensor c, int64_t M, int64_t K) {
     TORCH_CHECK(b.stride(1) == 1 && c.stride(1) == 1 && b.size(1) == K && c.size(0) == M && c.size(1) == b.size(0));
     const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-    const int rc = tb::ag_gemm_bf16(make_ctx(peers, mc, rank, world, limit), a_off, b.data_ptr(), c.data_ptr(), (int)M,
+    const int rc = tb::ag_gemm_bf16(make_ctx(peers, mc, rank, world, limit), a_off, g_off, (uint32_t)epoch, b.data_ptr(), c.data_ptr(), (int)M,
                                     (int)b.size(0), (int)K, b.stride(0), c.stride(0), sms, cs());
     TORCH_CHECK(rc == 0, "ag_gemm failed with code ", rc);
   });

@@ -38,15 +38,100 @@ constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 
 // Fused GEMM + collective: per-rank tensor maps over the same symmetric buffer on every peer.
-//   COMM == 1  all-gather -> GEMM: A row-block r lives on rank r; every CTA loads its A tiles straight from the
-//              owner's memory with plain (non-multicast) TMA loads over NVLink.
+//   COMM == 1  all-gather -> GEMM: A row-block r lives on rank r.  Every remote row crosses NVLink once: the
+//              kernel runs four extra copy warps per CTA that push this rank's shard into the gathered copy of every
+//              rank (multimem.st through the switch, or one posted store per peer; 32-row segments round-robin over
+//              CTAs) and then set the segment's arrival word on every peer; tiles are ordered local rows first, so
+//              the tensor cores start at once, and the TMA producer of a tile on remote rows waits (bounded) for the
+//              owner's arrival words.
+//              The gathered copy is an output too (the backward pass needs it for the weight gradient).
 //   COMM == 2  GEMM -> reduce-scatter: C row-block r belongs to rank r; every CTA adds its partial tiles into the
 //              owner's fp32 buffer with TMA reduce-add over NVLink.
 struct GemmComm {
   CUtensorMap maps[kCommMaxRanks];
   CommCtx c;
   int rows_per_rank;
+  // COMM == 1 only
+  uint64_t a_off;       // byte offset of the A shard inside every rank's symmetric allocation
+  uint64_t g_off;       // byte offset of the gathered [M, K] bf16 copy inside every rank's symmetric allocation
+  uint32_t* ready;      // [row block][segment]: epoch of the last call whose copy of that segment is complete
+  uint32_t epoch;       // this call's epoch (1-based, monotonic per communicator)
 };
+
+constexpr int kAgMaxRowBlocks = 2048;      // arrival words live at [32 KiB, 64 KiB) of the flag area
+constexpr uint64_t kAgReadyOffset = 32768;
+constexpr int kAgSeg = 4;                  // copy segments per 128-row block
+constexpr int kAgSegRows = BM / kAgSeg;    // 32 rows
+static_assert(kAgSeg == 4, "the consumer polls a block's arrival words with one 16-byte load");
+constexpr int kAgUnroll = 16;              // 16-byte loads in flight per thread
+constexpr int kAgThreads = NUM_THREADS + 128;  // the all-gather kernel adds four copy warps (6..9)
+
+struct V4u { uint32_t x, y, z, w; };
+__device__ __forceinline__ V4u local_ld16(const void* p) {
+  V4u v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void peer_st16(void* p, const V4u& v) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void mc_st16(void* p, const V4u& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Gather phase of the all-gather -> GEMM kernel, run by the four copy warps (128 threads) of every CTA: PUSH this
+// rank's own shard into the gathered copy of every rank (posted stores need no round trip, unlike peer loads).
+// With a multicast mapping one multimem.st reaches all ranks through the switch; otherwise one store per peer.
+// Items = (row block of my shard, 32-row segment), round-robin over CTAs, in the order the peers consume them.
+// After a segment is written everywhere, its arrival word on every peer is set to this call's epoch.
+__device__ __forceinline__ void ag_copy_phase(const GemmComm* gc, int K, int tid) {
+  const CommCtx& c = gc->c;
+  const int bpr = gc->rows_per_rank / BM;  // row blocks per rank
+  const int items = bpr * kAgSeg;
+  const int64_t row_bytes = static_cast<int64_t>(K) * 2;
+  const int64_t seg_bytes = row_bytes * kAgSegRows;
+  // a multicast store also comes back to the sender, which at two ranks doubles the inbound traffic for nothing
+  const bool use_mc = c.mc_buf != 0 && c.world > 2;
+  for (int it = blockIdx.x; it < items; it += gridDim.x) {
+    const int j = it / kAgSeg, seg = it % kAgSeg;
+    const int mb = c.rank * bpr + j;  // global row block
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(c.peer_bufs[c.rank] + gc->a_off) +
+                         (static_cast<int64_t>(j) * BM + seg * kAgSegRows) * row_bytes;
+    const uint64_t dst_off = gc->g_off + (static_cast<int64_t>(mb) * BM + seg * kAgSegRows) * row_bytes;
+    for (int64_t off = static_cast<int64_t>(tid) * 16; off < seg_bytes; off += 128 * 16 * kAgUnroll) {
+      V4u v[kAgUnroll];
+#pragma unroll
+      for (int u = 0; u < kAgUnroll; ++u) {
+        const int64_t o = off + static_cast<int64_t>(u) * 128 * 16;
+        if (o < seg_bytes) v[u] = local_ld16(src + o);
+      }
+      if (use_mc) {
+#pragma unroll
+        for (int u = 0; u < kAgUnroll; ++u) {
+          const int64_t o = off + static_cast<int64_t>(u) * 128 * 16;
+          if (o < seg_bytes) mc_st16(reinterpret_cast<void*>(c.mc_buf + dst_off + o), v[u]);
+        }
+      } else {
+        for (int p = 0; p < c.world; ++p) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(c.peer_bufs[p] + dst_off);
+#pragma unroll
+          for (int u = 0; u < kAgUnroll; ++u) {
+            const int64_t o = off + static_cast<int64_t>(u) * 128 * 16;
+            if (o < seg_bytes) peer_st16(dst + o, v[u]);
+          }
+        }
+      }
+    }
+    fence_proxy_async_all();  // the consumers read these bytes through TMA
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (tid < c.world && tid != c.rank) {
+      uint32_t* flag = reinterpret_cast<uint32_t*>(c.peer_bufs[tid] + kAgReadyOffset) + mb * kAgSeg + seg;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(gc->epoch) : "memory");
+    }
+  }
+}
 
 template <bool A_MN, bool B_MN, int OUT, int COMM>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, int M,
@@ -70,6 +155,23 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   // split-K: work unit u = (tile u % num_tiles, K slice u / num_tiles); slices add into C with TMA reduce-add
   const int num_units = num_tiles * splits;
   const int kb_per = (num_kb + splits - 1) / splits;
+  // tile -> (m0, n0).  Default: M fastest, so that concurrently running CTAs share a weight tile in L2.
+  // COMM == 1: grouped by owning rank, this rank's rows first, then the peers' in ring order (all N columns of a
+  // group before the next group), so that no tile on remote rows is visited before every local tile was handed out.
+  const int bpr = (COMM == 1) ? gc->rows_per_rank / BM : 1;
+  auto tile_coords = [&](int tile, int& m0, int& n0) {
+    if (COMM == 1) {
+      const int per_group = bpr * num_n;
+      const int g = tile / per_group, rem = tile - g * per_group;
+      int owner = g + gc->c.rank;
+      if (owner >= gc->c.world) owner -= gc->c.world;
+      n0 = (rem / bpr) * BN;
+      m0 = (owner * bpr + rem % bpr) * BM;
+    } else {
+      m0 = (tile % num_m) * BM;
+      n0 = (tile / num_m) * BN;
+    }
+  };
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
@@ -108,17 +210,41 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         const int tile = unit % num_tiles;
         const int kb0 = (unit / num_tiles) * kb_per;
         const int kb1 = min(num_kb, kb0 + kb_per);
-        const int m0 = (tile % num_m) * BM;
-        const int n0 = (tile / num_m) * BN;
+        int m0, n0;
+        tile_coords(tile, m0, n0);
+        int owner = 0;
+        if (COMM == 1) {
+          owner = m0 / gc->rows_per_rank;
+          if (owner != gc->c.rank) {
+            // the gathered copy of this row block must be complete (bounded wait)
+            // one 16-byte relaxed load covers the block's four arrival words (peers write them into this GPU's
+            // memory, so the poll is an L2 hit); a single acquire fence follows once all four carry this epoch
+            const uint32_t* flag = gc->ready + (m0 / BM) * kAgSeg;
+            const uint64_t t0 = globaltimer_ns();
+            for (;;) {
+              uint32_t f0, f1, f2, f3;
+              asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(f0), "=r"(f1), "=r"(f2), "=r"(f3) : "l"(flag) : "memory");
+              const uint32_t e = gc->epoch;
+              if (static_cast<int32_t>(f0 - e) >= 0 && static_cast<int32_t>(f1 - e) >= 0 &&
+                  static_cast<int32_t>(f2 - e) >= 0 && static_cast<int32_t>(f3 - e) >= 0) break;
+              if (*reinterpret_cast<volatile int*>(err) != 0) { ok = false; break; }
+              if (globaltimer_ns() - t0 > gc->c.wait_limit_ns) { atomicCAS(err, 0, kErrPeerFlagWait); ok = false; break; }
+              __nanosleep(100);
+            }
+            if (!ok) break;
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+            fence_proxy_async_all();
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, err, kErrProducerEmptyWait)) { ok = false; break; }
           uint8_t* sA = smem + stage * STAGE_BYTES;
           uint8_t* sB = sA + A_BYTES;
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           const int k0 = kb * BK;
-          if (COMM == 1) {
-            const int owner = m0 / gc->rows_per_rank;
-            tma_load_2d(sA, &gc->maps[owner], &full[stage], k0, m0 - owner * gc->rows_per_rank);
+          if (COMM == 1 && owner == gc->c.rank) {
+            tma_load_2d(sA, &gc->maps[owner], &full[stage], k0, m0 - owner * gc->rows_per_rank);  // my own shard
           } else if (!A_MN) {
             tma_load_2d(sA, &tmA, &full[stage], k0, m0);
           } else {
@@ -172,6 +298,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         ++it;
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------ copy warps (COMM == 1 only) ---------------
+    if (COMM == 1) ag_copy_phase(gc, K, threadIdx.x - NUM_THREADS);
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -183,8 +312,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
       const int tile = unit % num_tiles;
       if ((unit / num_tiles) * kb_per >= num_kb) continue;  // empty K slice
-      const int m0 = (tile % num_m) * BM;
-      const int n0 = (tile / num_m) * BN;
+      int m0, n0;
+      tile_coords(tile, m0, n0);
       const int acc = it & 1;
       if (!mbar_wait(&tfull[acc], (it >> 1) & 1, err, kErrEpilogueTmemFullWait)) { ok = false; break; }
       tc_fence_after();
@@ -251,7 +380,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
-  if (COMM != 0 && peers_ok) block_barrier(gc->c, 6, gc->c.world);  // every peer's loads / adds have landed
+  if (COMM == 2 && peers_ok) block_barrier(gc->c, 6, gc->c.world);  // every peer's adds have landed
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -268,7 +397,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int COMM>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(COMM == 1 ? kAgThreads : NUM_THREADS, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ GemmComm gc, int M, int N, int K,
                  int* err) {
@@ -407,19 +536,24 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_
 
 // A_r [M/world, K] bf16 sits at byte offset a_off of every rank's symmetric allocation; B [N, K] and C [M, N] (bf16)
 // are local.  C = concat_r(A_r) * B^T.
-int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, const void* B, void* C, int M, int N, int K, int64_t ldb, int64_t ldc,
-                 int num_sms, cudaStream_t stream) {
-  if (M % (c.world * BM) != 0) return -3;
+int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, uint64_t g_off, uint32_t epoch, const void* B, void* C, int M, int N,
+                 int K, int64_t ldb, int64_t ldc, int num_sms, cudaStream_t stream) {
+  if (M % (c.world * BM) != 0 || K % 8 != 0 || M / BM > kAgMaxRowBlocks) return -3;
   GemmComm gc{};
   gc.c = c;
   gc.rows_per_rank = M / c.world;
-  for (int r = 0; r < c.world; ++r) {
-    int rc = make_tmap_2d(&gc.maps[r], reinterpret_cast<const void*>(c.peer_bufs[r] + a_off), 2, gc.rows_per_rank, K, K,
-                          BM, 64);
-    if (rc) return rc;
-  }
-  CUtensorMap tb_, tc;
-  int rc = make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
+  gc.a_off = a_off;
+  gc.g_off = g_off;
+  gc.ready = reinterpret_cast<uint32_t*>(c.peer_bufs[c.rank] + kAgReadyOffset);
+  gc.epoch = epoch;
+  // only the map of this rank's own shard is used (local tiles); remote rows are read from the gathered copy
+  int rc = make_tmap_2d(&gc.maps[c.rank], reinterpret_cast<const void*>(c.peer_bufs[c.rank] + a_off), 2,
+                        gc.rows_per_rank, K, K, BM, 64);
+  if (rc) return rc;
+  CUtensorMap ta, tb_, tc;
+  rc = make_tmap_2d(&ta, reinterpret_cast<const void*>(c.peer_bufs[c.rank] + g_off), 2, M, K, K, BM, 64);
+  if (rc) return rc - 300;
+  rc = make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
   if (rc) return rc - 100;
   rc = make_tmap_2d(&tc, C, 2, M, N, ldc, 32, 64);
   if (rc) return rc - 200;
@@ -432,7 +566,7 @@ int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, const void* B, void* C, int M
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int cap = num_sms < kCommMaxBlocks ? num_sms : kCommMaxBlocks;  // the handshake has one flag row per CTA
   const int grid = tiles < cap ? tiles : cap;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(gc.maps[c.rank], tb_, tc, gc, M, N, K, c.err);
+  kern<<<grid, kAgThreads, SMEM_BYTES, stream>>>(ta, tb_, tc, gc, M, N, K, c.err);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
