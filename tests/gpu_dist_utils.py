@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import os
+import tempfile
 import traceback
 from datetime import timedelta
 
@@ -13,12 +14,14 @@ import torch.multiprocessing as mp
 from tests.dist_utils import free_port
 
 
-def _entry(rank, world, port, fn, args, errq, env):
+def _entry(rank, world, port, fn, args, errq, env, store_path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), LOCAL_RANK=str(rank),
                       WORLD_SIZE=str(world), **env)
     try:
         torch.cuda.set_device(rank)
-        dist.init_process_group("nccl", rank=rank, world_size=world, timeout=timedelta(seconds=120),
+        # a file store: no listening socket, so a port that another process grabbed cannot fail the rendezvous
+        store = dist.FileStore(store_path, world)
+        dist.init_process_group("nccl", store=store, rank=rank, world_size=world, timeout=timedelta(seconds=120),
                                 device_id=torch.device(f"cuda:{rank}"))
         fn(rank, world, *args)
         torch.cuda.synchronize()
@@ -34,7 +37,10 @@ def run_on_gpus(fn, world: int, *args, timeout_s: int = 300, env: dict | None = 
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq, env or {})) for r in range(world)]
+    store_dir = tempfile.mkdtemp(prefix="tb_gpu_store_")
+    store_path = os.path.join(store_dir, "store")
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq, env or {}, store_path))
+             for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

@@ -141,6 +141,9 @@ def _gemm_comm(rank, world):
             err = ((out.float() - ref).norm() / ref.norm()).item()
             assert err < 5e-3, ("ag_gemm", err)
             assert torch.equal(gathered, a_full)
+        out = ag_gemm(comm, a_sh, b.t().contiguous(), b_mn=True)  # same product, B stored [K, N]
+        err = ((out.float() - ref).norm() / ref.norm()).item()
+        assert err < 5e-3, ("ag_gemm b_mn", err)
     # GEMM -> reduce-scatter: K split over ranks
     Kl = 512
     a_loc = torch.randn(M, Kl, device="cuda", generator=torch.Generator("cuda").manual_seed(100 + rank)).bfloat16()
@@ -155,9 +158,57 @@ def _gemm_comm(rank, world):
         err = ((got - want).norm() / want.norm()).item()
         assert err < 1e-3, ("gemm_rs", err)
         torch.distributed.barrier()
+    got = gemm_rs(comm, a_loc, b_loc.t().contiguous(), c_sh, b_mn=True)
+    torch.cuda.synchronize()
+    err = ((got - want).norm() / want.norm()).item()
+    assert err < 1e-3, ("gemm_rs b_mn", err)
     comm.check()
     kernels.check_error()
 
 
 def test_fused_gemm_collectives():
     run_on_gpus(_gemm_comm, min(_world(), 4))
+
+
+def _sp_fused_linears(rank, world):
+    import torch.nn as nn
+
+    from torchure_b200.core import collective
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.ops import kernels
+    from torchure_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear, _fused_comm
+
+    mesh = Mesh({"tp": world})
+    collective.enable_sm100(mesh, "tp", max_bytes=64 << 20, persistent_bytes=128 << 20)
+    torch.manual_seed(3)
+    D, F, S = 512, 1024, 256 * world
+    up, down = nn.Linear(D, F, bias=False).cuda(), nn.Linear(F, D, bias=False).cuda()
+    x_full = torch.randn(1, S, D, device="cuda")
+    dy_full = torch.randn(1, S, D, device="cuda")
+    rows = S // world
+    # fp32 oracle on the full problem
+    xr = x_full.clone().requires_grad_(True)
+    yr = down(torch.relu(up(xr)))
+    yr.backward(dy_full)
+    col = ColumnParallelLinear(up, mesh, "tp", sequence_parallel=True)
+    row = RowParallelLinear(down, mesh, "tp", sequence_parallel=True)
+    xs = x_full[:, rank * rows:(rank + 1) * rows].bfloat16().requires_grad_(True)
+    assert _fused_comm(xs, mesh, "tp") is not None, "the fused path must be the one under test"
+    ys = row(torch.relu(col(xs)))
+    ys.backward(dy_full[:, rank * rows:(rank + 1) * rows].bfloat16())
+    torch.cuda.synchronize()
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+    per_f = F // world
+    errs = {"y": rel(ys, yr[:, rank * rows:(rank + 1) * rows]),
+            "dx": rel(xs.grad, xr.grad[:, rank * rows:(rank + 1) * rows]),
+            "dw_col": rel(col.weight.grad, up.weight.grad[rank * per_f:(rank + 1) * per_f]),
+            "dw_row": rel(row.weight.grad, down.weight.grad[:, rank * per_f:(rank + 1) * per_f])}
+    assert max(errs.values()) < 2e-2, errs
+    kernels.check_error()
+
+
+def test_sequence_parallel_fused_linears():
+    run_on_gpus(_sp_fused_linears, min(_world(), 4))

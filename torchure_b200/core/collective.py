@@ -60,11 +60,13 @@ class _Done:
 _SM100: dict[tuple[int, str], object] = {}
 
 
-def enable_sm100(mesh: MeshLike, dim: str, max_bytes: int = 64 << 20):
+def enable_sm100(mesh: MeshLike, dim: str, max_bytes: int = 64 << 20, persistent_bytes: int = 0):
     """Attach a symmetric-memory communicator to `dim`; CUDA collectives then use our kernels.
 
     Collective over the axis group.  Returns the communicator (None when the axis has one
     rank or the tensor lives on the CPU, in which case the torch transport stays active).
+    `persistent_bytes` reserves room for long-lived symmetric tensors (operands of the fused
+    GEMM+collective kernels, gradient buckets).
     """
     if mesh.size(dim) == 1 or not torch.cuda.is_available():
         return None
@@ -72,7 +74,7 @@ def enable_sm100(mesh: MeshLike, dim: str, max_bytes: int = 64 << 20):
     if key not in _SM100:
         from torchure_b200.core.symm import SymmComm
 
-        _SM100[key] = SymmComm(mesh.get_group(dim), mesh.coordinate(dim), mesh.size(dim), max_bytes)
+        _SM100[key] = SymmComm(mesh.get_group(dim), mesh.coordinate(dim), mesh.size(dim), max_bytes, persistent_bytes)
     return _SM100[key]
 
 

@@ -60,8 +60,9 @@ void comm_barrier(const CommCtx& c, uint32_t generation, int pretend_world, cuda
 // allocation (each rank pushes its shard to all); `epoch` is the 1-based count of ag_gemm calls made on this
 // communicator (the arrival words compare against it).
 int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, uint64_t g_off, uint32_t epoch, const void* B, void* C, int M, int N,
-                 int K, int64_t ldb, int64_t ldc, int num_sms, cudaStream_t stream);
+                 int K, int64_t ldb, int64_t ldc, bool b_mn, int num_sms, cudaStream_t stream);
 int gemm_rs_bf16(const CommCtx& c, const void* A, const void* B, uint64_t c_off, int M, int N, int K, int64_t lda,
-                 int64_t ldb, int num_sms, cudaStream_t stream);
+                 int64_t ldb, bool b_mn, int num_sms, cudaStream_t stream);
+// b_mn: B is stored [K, N] (MN-major) instead of [N, K].
 
 }  // namespace tb

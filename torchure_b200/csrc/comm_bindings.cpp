@@ -74,19 +74,21 @@ void register_comm(pybind11::module_& m) {
                        (int)blocks, cs());
   });
   m.def("ag_gemm", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit, int64_t a_off,
-                      int64_t g_off, int64_t epoch, torch::Tensor b, torch::Tensor c, int64_t M, int64_t K) {
-    TORCH_CHECK(b.stride(1) == 1 && c.stride(1) == 1 && b.size(1) == K && c.size(0) == M && c.size(1) == b.size(0));
+                      int64_t g_off, int64_t epoch, torch::Tensor b, torch::Tensor c, int64_t M, int64_t K, bool b_mn) {
+    const int64_t N = b_mn ? b.size(1) : b.size(0);
+    TORCH_CHECK(b.stride(1) == 1 && c.stride(1) == 1 && (b_mn ? b.size(0) : b.size(1)) == K && c.size(0) == M && c.size(1) == N);
     const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-    const int rc = tb::ag_gemm_bf16(make_ctx(peers, mc, rank, world, limit), a_off, g_off, (uint32_t)epoch, b.data_ptr(), c.data_ptr(), (int)M,
-                                    (int)b.size(0), (int)K, b.stride(0), c.stride(0), sms, cs());
+    const int rc = tb::ag_gemm_bf16(make_ctx(peers, mc, rank, world, limit), a_off, g_off, (uint32_t)epoch, b.data_ptr(),
+                                    c.data_ptr(), (int)M, (int)N, (int)K, b.stride(0), c.stride(0), b_mn, sms, cs());
     TORCH_CHECK(rc == 0, "ag_gemm failed with code ", rc);
   });
   m.def("gemm_rs", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
-                      torch::Tensor a, torch::Tensor b, int64_t c_off) {
-    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1));
+                      torch::Tensor a, torch::Tensor b, int64_t c_off, bool b_mn) {
+    const int64_t N = b_mn ? b.size(1) : b.size(0);
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == (b_mn ? b.size(0) : b.size(1)));
     const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
     const int rc = tb::gemm_rs_bf16(make_ctx(peers, mc, rank, world, limit), a.data_ptr(), b.data_ptr(), c_off,
-                                    (int)a.size(0), (int)b.size(0), (int)a.size(1), a.stride(0), b.stride(0), sms, cs());
+                                    (int)a.size(0), (int)N, (int)a.size(1), a.stride(0), b.stride(0), b_mn, sms, cs());
     TORCH_CHECK(rc == 0, "gemm_rs failed with code ", rc);
   });
   m.def("comm_barrier", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,

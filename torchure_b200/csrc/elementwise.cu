@@ -162,43 +162,185 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const float* __restrict
 }
 
 // ---------------------------------------------------------------------------------------------
-// QK-norm + RoPE.  One warp per (row, head); hd == 128: lane l holds elements (2l, 2l+1) and (64+2l, 64+2l+1)
+// rmsnorm backward for D <= 1024: one 16-warp CTA per SM owns a contiguous range of rows; a warp keeps its row's x
+// and dh in registers between the dot-product pass and the output pass (each byte is read once), and the weight
+// gradient leaves the CTA as 16-byte vector reductions (one per four columns per CTA).
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void red_add_v4(float* p, const float4& v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+template <int MAX_VEC>
+__global__ void __launch_bounds__(512, 1)
+rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __restrict__ x, const float* __restrict__ w,
+                        const float* __restrict__ rstd, const float* __restrict__ dx_in, float* __restrict__ dx,
+                        __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw, int M, int D) {
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
+  const int nvec = D >> 2;
+  const int lo = static_cast<int>(static_cast<int64_t>(M) * blockIdx.x / gridDim.x);
+  const int hi = static_cast<int>(static_cast<int64_t>(M) * (blockIdx.x + 1) / gridDim.x);
+  float4 dw_acc[MAX_VEC];
+#pragma unroll
+  for (int j = 0; j < MAX_VEC; ++j) dw_acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int row = lo + wid; row < hi; row += 16) {
+    const int64_t off = static_cast<int64_t>(row) * D;
+    float4 xv[MAX_VEC];
+    uint2 dv[MAX_VEC];
+#pragma unroll
+    for (int j = 0; j < MAX_VEC; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        xv[j] = reinterpret_cast<const float4*>(x + off)[i];
+        dv[j] = reinterpret_cast<const uint2*>(dh + off)[i];
+      }
+    }
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAX_VEC; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        const float4 g = reinterpret_cast<const float4*>(w)[i];
+        const float2 a = bf2_to_f2(dv[j].x), b = bf2_to_f2(dv[j].y);
+        xv[j].x *= r; xv[j].y *= r; xv[j].z *= r; xv[j].w *= r;  // normalised row from here on
+        dot += (a.x * g.x) * xv[j].x + (a.y * g.y) * xv[j].y + (b.x * g.z) * xv[j].z + (b.y * g.w) * xv[j].w;
+      }
+    }
+    dot = warp_sum(dot) / D;
+#pragma unroll
+    for (int j = 0; j < MAX_VEC; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        const float4 g = reinterpret_cast<const float4*>(w)[i];
+        const float2 a = bf2_to_f2(dv[j].x), b = bf2_to_f2(dv[j].y);
+        float4 o;
+        o.x = r * (a.x * g.x - xv[j].x * dot);
+        o.y = r * (a.y * g.y - xv[j].y * dot);
+        o.z = r * (b.x * g.z - xv[j].z * dot);
+        o.w = r * (b.y * g.w - xv[j].w * dot);
+        if (dx_in) {
+          const float4 p = reinterpret_cast<const float4*>(dx_in + off)[i];
+          o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+        }
+        reinterpret_cast<float4*>(dx + off)[i] = o;
+        if (dx_bf16) {
+          uint2 ob;
+          ob.x = f2_to_bf2(o.x, o.y);
+          ob.y = f2_to_bf2(o.z, o.w);
+          reinterpret_cast<uint2*>(dx_bf16 + off)[i] = ob;
+        }
+        dw_acc[j].x += a.x * xv[j].x; dw_acc[j].y += a.y * xv[j].y;
+        dw_acc[j].z += b.x * xv[j].z; dw_acc[j].w += b.y * xv[j].w;
+      }
+    }
+  }
+  // 16 warps -> one partial per column in shared memory -> one vector reduction per four columns
+  extern __shared__ float red[];  // [16][D]
+#pragma unroll
+  for (int j = 0; j < MAX_VEC; ++j) {
+    const int i = lane + j * 32;
+    if (i < nvec) reinterpret_cast<float4*>(red + wid * D)[i] = dw_acc[j];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const float4 v = reinterpret_cast<const float4*>(red + k * D)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    red_add_v4(dw + 4 * i, acc);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// QK-norm + RoPE, hd == 128.  One warp per token row; 16 lanes per head, so a warp instruction covers two heads
+// with one 16-byte access per lane (lane sub = lane & 15 holds elements 8*sub .. 8*sub+7).  The rotation pairs
+// element i with i + 64, i.e. lane sub with lane sub ^ 8.  cos/sin of the row and both gain vectors are loaded once
+// per row and reused by all heads.
+// ---------------------------------------------------------------------------------------------
+constexpr int QK_UNROLL = 4;      // forward: head pairs in flight per warp (4 x 16 B per lane)
+constexpr int QK_BWD_UNROLL = 2;  // backward reads two tensors per head pair
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), d = bf2_to_f2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = f2_to_bf2(f[0], f[1]); u.y = f2_to_bf2(f[2], f[3]); u.z = f2_to_bf2(f[4], f[5]); u.w = f2_to_bf2(f[6], f[7]);
+  return u;
+}
+__device__ __forceinline__ float group16_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
+  float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
 __global__ void __launch_bounds__(256)
 qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ qw,
                        const float* __restrict__ kw, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                        __nv_bfloat16* __restrict__ out, int M, int S, int Hq, int Hkv, float eps, int use_norm) {
   const int heads = Hq + Hkv;
-  const int64_t gw = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (gw >= static_cast<int64_t>(M) * heads) return;
-  const int row = static_cast<int>(gw / heads);
-  const int head = static_cast<int>(gw % heads);
+  if (row >= M) return;
+  const int sub = lane & 15, hsel = lane >> 4;
+  const bool is_hi = sub >= 8;
   const int in_ld = (Hq + 2 * Hkv) * 128, out_ld = heads * 128;
-  const __nv_bfloat16* src = qkv + static_cast<int64_t>(row) * in_ld + head * 128;
-  const float* gain = head < Hq ? qw : kw;
-  float2 lo = bf2_to_f2(reinterpret_cast<const uint32_t*>(src)[lane]);
-  float2 hi = bf2_to_f2(reinterpret_cast<const uint32_t*>(src)[32 + lane]);
-  if (use_norm) {
-    float ss = warp_sum(lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y);
-    const float r = rsqrtf(ss * (1.f / 128.f) + eps);
-    float2 g0 = reinterpret_cast<const float2*>(gain)[lane], g1 = reinterpret_cast<const float2*>(gain)[32 + lane];
-    // the reference normalises in bf16 precision before RoPE (its q_norm returns bf16)
-    lo = bf2_to_f2(f2_to_bf2(lo.x * r * g0.x, lo.y * r * g0.y));
-    hi = bf2_to_f2(f2_to_bf2(hi.x * r * g1.x, hi.y * r * g1.y));
-  }
+  const __nv_bfloat16* src = qkv + static_cast<int64_t>(row) * in_ld + sub * 8;
+  __nv_bfloat16* dst = out + static_cast<int64_t>(row) * out_ld + sub * 8;
   const int pos = row % S;
-  const float2 c0 = reinterpret_cast<const float2*>(cos_t + static_cast<int64_t>(pos) * 128)[lane];
-  const float2 s0 = reinterpret_cast<const float2*>(sin_t + static_cast<int64_t>(pos) * 128)[lane];
-  // both halves share the angle: cos[i] == cos[i+64]
-  float2 olo = make_float2(lo.x * c0.x - hi.x * s0.x, lo.y * c0.y - hi.y * s0.y);
-  float2 ohi = make_float2(hi.x * c0.x + lo.x * s0.x, hi.y * c0.y + lo.y * s0.y);
-  __nv_bfloat16* dst = out + static_cast<int64_t>(row) * out_ld + head * 128;
-  reinterpret_cast<uint32_t*>(dst)[lane] = f2_to_bf2(olo.x, olo.y);
-  reinterpret_cast<uint32_t*>(dst)[32 + lane] = f2_to_bf2(ohi.x, ohi.y);
+  float c[8], sn[8], gq[8], gk[8];
+  load8f(cos_t + static_cast<int64_t>(pos) * 128 + (sub & 7) * 8, c);  // cos[i] == cos[i + 64]
+  load8f(sin_t + static_cast<int64_t>(pos) * 128 + (sub & 7) * 8, sn);
+  if (use_norm) {
+    load8f(qw + sub * 8, gq);
+    load8f(kw + sub * 8, gk);
+  }
+  const int pairs = (heads + 1) >> 1;
+  for (int hp = 0; hp < pairs; hp += QK_UNROLL) {
+    uint4 u[QK_UNROLL];
+#pragma unroll
+    for (int k = 0; k < QK_UNROLL; ++k) {
+      const int h = 2 * (hp + k) + hsel;
+      u[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (h < heads) u[k] = *reinterpret_cast<const uint4*>(src + h * 128);
+    }
+#pragma unroll
+    for (int k = 0; k < QK_UNROLL; ++k) {
+      const int h = 2 * (hp + k) + hsel;
+      float x[8];
+      unpack8(u[k], x);
+      if (use_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+        ss = group16_sum(ss);
+        const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+        // the reference normalises in bf16 precision before RoPE (its q_norm returns bf16)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = x[e] * r * (h < Hq ? gq[e] : gk[e]);
+        uint4 rounded = pack8(x);
+        unpack8(rounded, x);
+      }
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float p = __shfl_xor_sync(0xffffffffu, x[e], 8);
+        o[e] = is_hi ? x[e] * c[e] + p * sn[e] : x[e] * c[e] - p * sn[e];
+      }
+      if (h < heads) *reinterpret_cast<uint4*>(dst + h * 128) = pack8(o);
+    }
+  }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ qkv,
                        const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ cos_t,
                        const float* __restrict__ sin_t, float* __restrict__ dqw, float* __restrict__ dkw, int M, int S,
@@ -206,53 +348,84 @@ qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __
   const int heads = Hq + Hkv;
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
-  const int64_t total = static_cast<int64_t>(M) * heads;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * 8;
+  const int sub = lane & 15, hsel = lane >> 4;
+  const bool is_hi = sub >= 8;
   const int ld = (Hq + 2 * Hkv) * 128;
-  // per-warp gain-gradient partials: [0] q, [1] k
-  float2 gq0 = make_float2(0.f, 0.f), gq1 = gq0, gk0 = gq0, gk1 = gq0;
-  for (int64_t gw = static_cast<int64_t>(blockIdx.x) * 8 + wid; gw < total; gw += stride) {
-    const int row = static_cast<int>(gw / heads);
-    const int head = static_cast<int>(gw % heads);
-    __nv_bfloat16* dptr = dqkv + static_cast<int64_t>(row) * ld + head * 128;
-    float2 dlo = bf2_to_f2(reinterpret_cast<const uint32_t*>(dptr)[lane]);
-    float2 dhi = bf2_to_f2(reinterpret_cast<const uint32_t*>(dptr)[32 + lane]);
+  const int pairs = (heads + 1) >> 1;
+  float gq[8], gk[8], aq[8], ak[8];  // gains and this lane's gain-gradient partials
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { gq[e] = gk[e] = 1.f; aq[e] = ak[e] = 0.f; }
+  if (use_norm) {
+    load8f(qw + sub * 8, gq);
+    load8f(kw + sub * 8, gk);
+  }
+  for (int row = blockIdx.x * 8 + wid; row < M; row += gridDim.x * 8) {
     const int pos = row % S;
-    const float2 c0 = reinterpret_cast<const float2*>(cos_t + static_cast<int64_t>(pos) * 128)[lane];
-    const float2 s0 = reinterpret_cast<const float2*>(sin_t + static_cast<int64_t>(pos) * 128)[lane];
-    // transpose of the rotation
-    float2 nlo = make_float2(dlo.x * c0.x + dhi.x * s0.x, dlo.y * c0.y + dhi.y * s0.y);
-    float2 nhi = make_float2(dhi.x * c0.x - dlo.x * s0.x, dhi.y * c0.y - dlo.y * s0.y);
-    if (use_norm) {
-      const __nv_bfloat16* src = qkv + static_cast<int64_t>(row) * ld + head * 128;
-      float2 xlo = bf2_to_f2(reinterpret_cast<const uint32_t*>(src)[lane]);
-      float2 xhi = bf2_to_f2(reinterpret_cast<const uint32_t*>(src)[32 + lane]);
-      float ss = warp_sum(xlo.x * xlo.x + xlo.y * xlo.y + xhi.x * xhi.x + xhi.y * xhi.y);
-      const float r = rsqrtf(ss * (1.f / 128.f) + eps);
-      const float* gain = head < Hq ? qw : kw;
-      float2 g0 = reinterpret_cast<const float2*>(gain)[lane], g1 = reinterpret_cast<const float2*>(gain)[32 + lane];
-      float2 hlo = make_float2(xlo.x * r, xlo.y * r), hhi = make_float2(xhi.x * r, xhi.y * r);
-      float dot = warp_sum(nlo.x * g0.x * hlo.x + nlo.y * g0.y * hlo.y + nhi.x * g1.x * hhi.x + nhi.y * g1.y * hhi.y) *
-                  (1.f / 128.f);
-      if (head < Hq) {
-        gq0.x += nlo.x * hlo.x; gq0.y += nlo.y * hlo.y; gq1.x += nhi.x * hhi.x; gq1.y += nhi.y * hhi.y;
-      } else {
-        gk0.x += nlo.x * hlo.x; gk0.y += nlo.y * hlo.y; gk1.x += nhi.x * hhi.x; gk1.y += nhi.y * hhi.y;
+    float c[8], sn[8];
+    load8f(cos_t + static_cast<int64_t>(pos) * 128 + (sub & 7) * 8, c);
+    load8f(sin_t + static_cast<int64_t>(pos) * 128 + (sub & 7) * 8, sn);
+    __nv_bfloat16* dptr = dqkv + static_cast<int64_t>(row) * ld + sub * 8;
+    const __nv_bfloat16* xptr = qkv + static_cast<int64_t>(row) * ld + sub * 8;
+    for (int hp = 0; hp < pairs; hp += QK_BWD_UNROLL) {
+      uint4 du[QK_BWD_UNROLL], xu[QK_BWD_UNROLL];
+#pragma unroll
+      for (int k = 0; k < QK_BWD_UNROLL; ++k) {
+        const int h = 2 * (hp + k) + hsel;
+        du[k] = xu[k] = make_uint4(0u, 0u, 0u, 0u);
+        if (h < heads) {
+          du[k] = *reinterpret_cast<const uint4*>(dptr + h * 128);
+          if (use_norm) xu[k] = *reinterpret_cast<const uint4*>(xptr + h * 128);
+        }
       }
-      nlo = make_float2(r * (nlo.x * g0.x - hlo.x * dot), r * (nlo.y * g0.y - hlo.y * dot));
-      nhi = make_float2(r * (nhi.x * g1.x - hhi.x * dot), r * (nhi.y * g1.y - hhi.y * dot));
+#pragma unroll
+      for (int k = 0; k < QK_BWD_UNROLL; ++k) {
+        const int h = 2 * (hp + k) + hsel;
+        float d[8], n[8];
+        unpack8(du[k], d);
+        // transpose of the rotation
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float p = __shfl_xor_sync(0xffffffffu, d[e], 8);
+          n[e] = is_hi ? d[e] * c[e] - p * sn[e] : d[e] * c[e] + p * sn[e];
+        }
+        if (use_norm) {
+          float x[8];
+          unpack8(xu[k], x);
+          float ss = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+          ss = group16_sum(ss);
+          const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+          const bool is_q = h < Hq;
+          float dot = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            x[e] *= r;  // normalised value
+            dot += n[e] * (is_q ? gq[e] : gk[e]) * x[e];
+          }
+          dot = group16_sum(dot) * (1.f / 128.f);
+          if (h < heads) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              if (is_q) aq[e] += n[e] * x[e]; else ak[e] += n[e] * x[e];
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) n[e] = r * (n[e] * (is_q ? gq[e] : gk[e]) - x[e] * dot);
+        }
+        if (h < heads) *reinterpret_cast<uint4*>(dptr + h * 128) = pack8(n);
+      }
     }
-    reinterpret_cast<uint32_t*>(dptr)[lane] = f2_to_bf2(nlo.x, nlo.y);
-    reinterpret_cast<uint32_t*>(dptr)[32 + lane] = f2_to_bf2(nhi.x, nhi.y);
   }
   if (use_norm) {
     __shared__ float red[2][128];
-    if (threadIdx.x < 256) red[threadIdx.x >> 7][threadIdx.x & 127] = 0.f;
+    red[threadIdx.x >> 7][threadIdx.x & 127] = 0.f;
     __syncthreads();
-    atomicAdd(&red[0][2 * lane], gq0.x); atomicAdd(&red[0][2 * lane + 1], gq0.y);
-    atomicAdd(&red[0][64 + 2 * lane], gq1.x); atomicAdd(&red[0][64 + 2 * lane + 1], gq1.y);
-    atomicAdd(&red[1][2 * lane], gk0.x); atomicAdd(&red[1][2 * lane + 1], gk0.y);
-    atomicAdd(&red[1][64 + 2 * lane], gk1.x); atomicAdd(&red[1][64 + 2 * lane + 1], gk1.y);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      atomicAdd(&red[0][sub * 8 + e], aq[e]);
+      atomicAdd(&red[1][sub * 8 + e], ak[e]);
+    }
     __syncthreads();
     if (threadIdx.x < 128) atomicAdd(&dqw[threadIdx.x], red[0][threadIdx.x]);
     else atomicAdd(&dkw[threadIdx.x - 128], red[1][threadIdx.x - 128]);
@@ -473,7 +646,16 @@ void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids,
 void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const float* rstd, const float* dx_in,
                  float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, cudaStream_t stream) {
   // two rows per warp keeps every warp equally loaded and the per-CTA atomics on dw few
-  (void)num_sms;
+  if (D <= 128 * 8 && M >= 4 * num_sms) {
+    static bool configured = false;
+    const size_t smem16 = static_cast<size_t>(16) * D * sizeof(float);
+    if (!configured) {
+      cudaFuncSetAttribute(rmsnorm_bwd_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 1024 * 4);
+      configured = true;
+    }
+    rmsnorm_bwd_rows_kernel<8><<<num_sms, 512, smem16, stream>>>(dh, x, w, rstd, dx_in, dx, dx_bf16, dw, M, D);
+    return;
+  }
   const int grid = std::max(1, (M + 15) / 16);
   const size_t smem = static_cast<size_t>(D) * sizeof(float);
   if (D <= 128 * 8) rmsnorm_bwd_kernel<8><<<grid, 256, smem, stream>>>(dh, x, w, rstd, dx_in, dx, dx_bf16, dw, M, D);
@@ -485,17 +667,14 @@ void qknorm_rope_fwd(const __nv_bfloat16* qkv, const float* qw, const float* kw,
                      __nv_bfloat16* out, int M, int S, int Hq, int Hkv, int hd, float eps, int use_norm,
                      cudaStream_t stream) {
   (void)hd;  // 128 only (checked by the caller)
-  const int64_t warps = static_cast<int64_t>(M) * (Hq + Hkv);
-  qknorm_rope_fwd_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, stream>>>(qkv, qw, kw, cos, sin, out, M, S, Hq,
-                                                                               Hkv, eps, use_norm);
+  qknorm_rope_fwd_kernel<<<(M + 7) / 8, 256, 0, stream>>>(qkv, qw, kw, cos, sin, out, M, S, Hq, Hkv, eps, use_norm);
 }
 
 void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
                      const float* sin, float* dqw, float* dkw, int M, int S, int Hq, int Hkv, int hd, float eps,
                      int use_norm, int num_sms, cudaStream_t stream) {
   (void)hd;
-  const int64_t warps = static_cast<int64_t>(M) * (Hq + Hkv);
-  const int grid = static_cast<int>(std::min<int64_t>((warps + 7) / 8, static_cast<int64_t>(num_sms) * 8));
+  const int grid = std::min((M + 7) / 8, num_sms * 8);  // one warp per row, persistent
   qknorm_rope_bwd_kernel<<<grid, 256, 0, stream>>>(dqkv, qkv, qw, kw, cos, sin, dqw, dkw, M, S, Hq, Hkv, eps,
                                                    use_norm);
 }

@@ -396,13 +396,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   gemm_body<A_MN, B_MN, OUT, 0>(tmA, tmB, tmC, M, N, K, splits, err, nullptr);
 }
 
-template <int COMM>
+template <int COMM, bool B_MN>
 __global__ void __launch_bounds__(COMM == 1 ? kAgThreads : NUM_THREADS, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ GemmComm gc, int M, int N, int K,
                  int* err) {
   // COMM 1: bf16 store of C; COMM 2: fp32 reduce-add of C into the owners
-  gemm_body<false, false, COMM == 1 ? 0 : 2, COMM>(tmA, tmB, tmC, M, N, K, 1, err, &gc);
+  gemm_body<false, B_MN, COMM == 1 ? 0 : 2, COMM>(tmA, tmB, tmC, M, N, K, 1, err, &gc);
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -537,7 +537,7 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_
 // A_r [M/world, K] bf16 sits at byte offset a_off of every rank's symmetric allocation; B [N, K] and C [M, N] (bf16)
 // are local.  C = concat_r(A_r) * B^T.
 int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, uint64_t g_off, uint32_t epoch, const void* B, void* C, int M, int N,
-                 int K, int64_t ldb, int64_t ldc, int num_sms, cudaStream_t stream) {
+                 int K, int64_t ldb, int64_t ldc, bool b_mn, int num_sms, cudaStream_t stream) {
   if (M % (c.world * BM) != 0 || K % 8 != 0 || M / BM > kAgMaxRowBlocks) return -3;
   GemmComm gc{};
   gc.c = c;
@@ -553,15 +553,15 @@ int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, uint64_t g_off, uint32_t epoc
   CUtensorMap ta, tb_, tc;
   rc = make_tmap_2d(&ta, reinterpret_cast<const void*>(c.peer_bufs[c.rank] + g_off), 2, M, K, K, BM, 64);
   if (rc) return rc - 300;
-  rc = make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
+  rc = b_mn ? make_tmap_2d(&tb_, B, 2, K, N, ldb, 64, 64) : make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
   if (rc) return rc - 100;
   rc = make_tmap_2d(&tc, C, 2, M, N, ldc, 32, 64);
   if (rc) return rc - 200;
-  auto kern = gemm_comm_kernel<1>;
-  static bool configured = false;
-  if (!configured) {
+  auto kern = b_mn ? gemm_comm_kernel<1, true> : gemm_comm_kernel<1, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[b_mn]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
-    configured = true;
+    configured[b_mn] = true;
   }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int cap = num_sms < kCommMaxBlocks ? num_sms : kCommMaxBlocks;  // the handshake has one flag row per CTA
@@ -573,7 +573,7 @@ int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, uint64_t g_off, uint32_t epoc
 // A [M, K_local], B [N, K_local] bf16 local; the fp32 output shard [M/world, N] sits at byte offset c_off of every
 // rank's symmetric allocation and must be zero on entry.  out_r = sum over ranks of (A B^T)[rows of r].
 int gemm_rs_bf16(const CommCtx& c, const void* A, const void* B, uint64_t c_off, int M, int N, int K, int64_t lda,
-                 int64_t ldb, int num_sms, cudaStream_t stream) {
+                 int64_t ldb, bool b_mn, int num_sms, cudaStream_t stream) {
   if (M % (c.world * BM) != 0) return -3;
   GemmComm gc{};
   gc.c = c;
@@ -586,13 +586,13 @@ int gemm_rs_bf16(const CommCtx& c, const void* A, const void* B, uint64_t c_off,
   CUtensorMap ta, tb_;
   int rc = make_tmap_2d(&ta, A, 2, M, K, lda, BM, 64);
   if (rc) return rc - 100;
-  rc = make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
+  rc = b_mn ? make_tmap_2d(&tb_, B, 2, K, N, ldb, 64, 64) : make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
   if (rc) return rc - 200;
-  auto kern = gemm_comm_kernel<2>;
-  static bool configured = false;
-  if (!configured) {
+  auto kern = b_mn ? gemm_comm_kernel<2, true> : gemm_comm_kernel<2, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[b_mn]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
-    configured = true;
+    configured[b_mn] = true;
   }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int cap = num_sms < kCommMaxBlocks ? num_sms : kCommMaxBlocks;

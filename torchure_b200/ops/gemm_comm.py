@@ -37,8 +37,8 @@ class SymmetricOperand:
 
 
 def ag_gemm(comm, a_shard: SymmetricOperand, b: torch.Tensor, out: torch.Tensor | None = None,
-            gathered: SymmetricOperand | None = None, return_gathered: bool = False):
-    """out[M, N] = concat_ranks(a_shard)[M, K] @ b[N, K]^T, bf16.
+            gathered: SymmetricOperand | None = None, return_gathered: bool = False, b_mn: bool = False):
+    """out[M, N] = concat_ranks(a_shard)[M, K] @ b[N, K]^T, bf16 (`b_mn`: b is stored [K, N] and used untransposed).
 
     `gathered` ([M, K], symmetric: every rank pushes its shard into every rank's copy) receives the assembled A; one
     is allocated per (M, K) and kept on the communicator when none is passed.
@@ -46,21 +46,21 @@ def ag_gemm(comm, a_shard: SymmetricOperand, b: torch.Tensor, out: torch.Tensor 
     rows, K = a_shard.tensor.shape
     M = rows * comm.world
     if out is None:
-        out = torch.empty(M, b.shape[0], dtype=torch.bfloat16, device=b.device)
+        out = torch.empty(M, b.shape[1] if b_mn else b.shape[0], dtype=torch.bfloat16, device=b.device)
     if gathered is None:
         cache = comm.__dict__.setdefault("_ag_gathered", {})
         if (M, K) not in cache:
             cache[(M, K)] = SymmetricOperand(comm, (M, K), torch.bfloat16)
         gathered = cache[(M, K)]
     comm.ag_epoch = getattr(comm, "ag_epoch", 0) + 1
-    ops.ext().ag_gemm(*comm._ctx(), a_shard.offset, gathered.offset, comm.ag_epoch, b, out, M, K)
+    ops.ext().ag_gemm(*comm._ctx(), a_shard.offset, gathered.offset, comm.ag_epoch, b, out, M, K, b_mn)
     ops.count_launch()
     return (out, gathered.tensor) if return_gathered else out
 
 
-def gemm_rs(comm, a: torch.Tensor, b: torch.Tensor, out_shard: SymmetricOperand) -> torch.Tensor:
-    """out_shard[M/world, N] (fp32, zeroed here) = rows of this rank of sum_ranks(a @ b^T)."""
+def gemm_rs(comm, a: torch.Tensor, b: torch.Tensor, out_shard: SymmetricOperand, b_mn: bool = False) -> torch.Tensor:
+    """out_shard[M/world, N] (fp32, zeroed here) = rows of this rank of sum_ranks(a @ b^T) (`b_mn`: b stored [K, N])."""
     out_shard.tensor.zero_()
-    ops.ext().gemm_rs(*comm._ctx(), a, b, out_shard.offset)
+    ops.ext().gemm_rs(*comm._ctx(), a, b, out_shard.offset, b_mn)
     ops.count_launch()
     return out_shard.tensor

@@ -13,6 +13,12 @@ loss-parallel CE, SP as all-gather / reduce-scatter pairs).  Building blocks her
   sum-exp and target logit together).
 
 Collectives go through ``core.collective`` (NVLink kernels on GPUs, gloo on CPU).
+
+On GPUs with an sm_100a communicator attached to the axis (``collective.enable_sm100``), bf16 activations and one
+sequence per micro-batch (token-major rows, a multiple of 128 per rank), the sequence-parallel linears run as ONE
+kernel each: ``ag_gemm`` (all-gather -> GEMM) for the column-parallel forward and the row-parallel input gradient,
+``gemm_rs`` (GEMM -> reduce-scatter) for the row-parallel forward and the column-parallel input gradient
+(``ops/gemm_comm.py``).  Everything else falls back to collective + matmul.
 """
 
 from __future__ import annotations
@@ -79,6 +85,98 @@ class _ScatterSeq(torch.autograd.Function):
         return all_gather(g.contiguous(), ctx.mesh, ctx.dim, gather_dim=1), None, None
 
 
+def _fused_comm(x: torch.Tensor, mesh, dim: str):
+    """The axis' sm_100a communicator if the fused GEMM+collective kernels can take `x` (tokens of ONE sequence shard
+    as rows), else None."""
+    from torchure_b200.core.collective import _sm100_for
+
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        return None
+    comm = _sm100_for(x, mesh, dim)
+    if comm is None:
+        return None
+    rows = x.numel() // x.shape[-1]
+    lead_ok = x.dim() == 2 or all(d == 1 for d in x.shape[:-2])
+    return comm if lead_ok and rows % 128 == 0 and x.shape[-1] % 64 == 0 else None
+
+
+def _workspace(comm, kind: str, shape, dtype):
+    """Persistent symmetric operand per (kind, shape): reused by every layer (calls are ordered on one stream and
+    every fused kernel handshakes with its peers before it touches their memory)."""
+    from torchure_b200.ops.gemm_comm import SymmetricOperand
+
+    cache = comm.__dict__.setdefault("_tp_workspaces", {})
+    key = (kind, tuple(shape), dtype)
+    if key not in cache:
+        cache[key] = SymmetricOperand(comm, shape, dtype)
+    return cache[key]
+
+
+class _ColumnSPFused(torch.autograd.Function):
+    """y[M, N/tp] = all_gather_rows(x_shard)[M, K] @ w[N/tp, K]^T in one kernel; backward: one GEMM->reduce-scatter
+    kernel for dx, a re-gather plus the wgrad GEMM for dw."""
+
+    @staticmethod
+    def forward(ctx, x, w, comm, mesh, dim):
+        from torchure_b200.ops.gemm_comm import ag_gemm
+
+        rows, K = x.shape
+        a = _workspace(comm, "ag_in", (rows, K), torch.bfloat16)
+        a.tensor.copy_(x)
+        g = _workspace(comm, "ag_full", (rows * comm.world, K), torch.bfloat16)
+        wb = w.to(torch.bfloat16)
+        y = ag_gemm(comm, a, wb, gathered=g)
+        ctx.save_for_backward(x, wb)
+        ctx.comm, ctx.mesh, ctx.dim, ctx.w_dtype = comm, mesh, dim, w.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from torchure_b200.ops import kernels
+        from torchure_b200.ops.gemm_comm import gemm_rs
+
+        x, wb = ctx.saved_tensors
+        comm = ctx.comm
+        dy = dy.contiguous()
+        c = _workspace(comm, "rs_out", (x.shape[0], x.shape[1]), torch.float32)
+        dx = gemm_rs(comm, dy, wb, c, b_mn=True).to(torch.bfloat16)   # dy [M, N/tp] @ w [N/tp, K]
+        xg = all_gather(x, ctx.mesh, ctx.dim, gather_dim=0)
+        dw = kernels.linear_wgrad(dy, xg, out_dtype=torch.float32).to(ctx.w_dtype)
+        return dx, dw, None, None, None
+
+
+class _RowSPFused(torch.autograd.Function):
+    """y_shard[M/tp, N] = reduce_scatter_rows(x[M, K/tp] @ w[N, K/tp]^T) in one kernel; backward: one all-gather->GEMM
+    kernel for dx whose gathered dy also feeds the wgrad GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, w, comm, mesh, dim):
+        from torchure_b200.ops.gemm_comm import gemm_rs
+
+        M = x.shape[0]
+        wb = w.to(torch.bfloat16)
+        c = _workspace(comm, "rs_out", (M // comm.world, wb.shape[0]), torch.float32)
+        y = gemm_rs(comm, x.contiguous(), wb, c).to(torch.bfloat16)
+        ctx.save_for_backward(x, wb)
+        ctx.comm, ctx.w_dtype = comm, w.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from torchure_b200.ops import kernels
+        from torchure_b200.ops.gemm_comm import ag_gemm
+
+        x, wb = ctx.saved_tensors
+        comm = ctx.comm
+        rows, N = dy.shape
+        a = _workspace(comm, "ag_in", (rows, N), torch.bfloat16)
+        a.tensor.copy_(dy)
+        g = _workspace(comm, "ag_full", (rows * comm.world, N), torch.bfloat16)
+        dx, dyg = ag_gemm(comm, a, wb, gathered=g, return_gathered=True, b_mn=True)  # dy_full [M, N] @ w [N, K/tp]
+        dw = kernels.linear_wgrad(dyg, x, out_dtype=torch.float32).to(ctx.w_dtype)
+        return dx, dw, None, None, None
+
+
 class ColumnParallelLinear(nn.Module):
     def __init__(self, full: nn.Linear, mesh, dim: str, sequence_parallel: bool = False, split_sizes=None):
         super().__init__()
@@ -90,8 +188,13 @@ class ColumnParallelLinear(nn.Module):
         self.mesh, self.dim, self.sp = mesh, dim, sequence_parallel
 
     def forward(self, x):
+        if self.sp:
+            comm = _fused_comm(x, self.mesh, self.dim)
+            if comm is not None:
+                y = _ColumnSPFused.apply(x.reshape(-1, x.shape[-1]), self.weight, comm, self.mesh, self.dim)
+                return y.view(*x.shape[:-2], -1, y.shape[-1])
         x = _GatherSeq.apply(x, self.mesh, self.dim) if self.sp else _CopyToTP.apply(x, self.mesh, self.dim)
-        return F.linear(x, self.weight)
+        return F.linear(x, self.weight.to(x.dtype))
 
 
 class RowParallelLinear(nn.Module):
@@ -105,7 +208,13 @@ class RowParallelLinear(nn.Module):
         self.mesh, self.dim, self.sp = mesh, dim, sequence_parallel
 
     def forward(self, x):
-        y = F.linear(x, self.weight)
+        if self.sp:
+            n = self.mesh.size(self.dim)
+            comm = _fused_comm(x, self.mesh, self.dim)
+            if comm is not None and (x.numel() // x.shape[-1]) % (128 * n) == 0:
+                y = _RowSPFused.apply(x.reshape(-1, x.shape[-1]), self.weight, comm, self.mesh, self.dim)
+                return y.view(*x.shape[:-2], -1, y.shape[-1])
+        y = F.linear(x, self.weight.to(x.dtype))
         return _ScatterSeq.apply(y, self.mesh, self.dim) if self.sp else _ReduceFromTP.apply(y, self.mesh, self.dim)
 
 
