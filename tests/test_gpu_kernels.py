@@ -231,3 +231,34 @@ def test_bucket_pack():
     torch.testing.assert_close(sq, want.pow(2).sum(), rtol=1e-4, atol=1e-3)
     multi_tensor.bucket_pack(grads, views, True, 0.5, None)
     torch.testing.assert_close(flat, want)  # (x + x) * 0.5
+
+
+def test_poison_and_verify_mode():
+    """Every wrapper output is pre-filled with NaN; a kernel that left any element unwritten would be reported."""
+    from torchure_b200.models.qwen3 import RotaryEmbedding
+    from torchure_b200.ops import attention, debug, kernels
+
+    debug.enable(True)
+    try:
+        torch.manual_seed(0)
+        M, D, Fd, S, Hq, Hkv = 300, 512, 640, 256, 4, 2   # ragged M and N: edge tiles must be covered too
+        x = torch.randn(M, D, device="cuda")
+        w = torch.rand(D, device="cuda") + 0.5
+        _, h, rstd = kernels.add_rmsnorm(x, (torch.randn(M, D, device="cuda") * 0.1).bfloat16(), w, 1e-6)
+        gu = kernels.linear_fwd(h, torch.randn(2 * Fd, D, device="cuda").bfloat16())
+        act = kernels.swiglu(gu)
+        kernels.swiglu_bwd(torch.randn_like(act), gu)
+        kernels.linear_wgrad(torch.randn(M, 2 * Fd, device="cuda").bfloat16(), h, out_dtype=torch.float32)
+        kernels.rmsnorm_bwd(torch.randn(M, D, device="cuda").bfloat16(), x, w, rstd, None, torch.zeros(D, device="cuda"))
+        qkv = torch.randn(2 * S, (Hq + 2 * Hkv) * 128, device="cuda").bfloat16()
+        cos, sin = RotaryEmbedding(128).tables(S, "cuda")
+        qk = kernels.qknorm_rope(qkv, w[:128].clone(), w[:128].clone(), cos, sin, S, Hq, Hkv, 1e-6)
+        o, state = attention.attn_fwd(qk, qkv, 2, S, Hq, Hkv, 128)
+        attention.attn_bwd(torch.randn_like(o), qk, qkv, state, 2, S, Hq, Hkv, 128)
+        assert debug.verify() >= 10
+        # and the check itself fires: an output that no kernel writes keeps its sentinels
+        debug.new_output("never_written", 8, dtype=torch.float32, device="cuda")
+        with pytest.raises(RuntimeError, match="never_written"):
+            debug.verify()
+    finally:
+        debug.enable(False)

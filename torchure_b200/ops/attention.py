@@ -22,6 +22,7 @@ import torch
 import torch.nn.functional as F
 
 from torchure_b200 import ops
+from torchure_b200.ops.debug import new_output
 
 _FORCE = os.environ.get("TORCHURE_B200_ATTN", "")  # "sdpa" forces the library path
 
@@ -53,8 +54,8 @@ def attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=True):
     """Returns (o (M, Hq*hd) bf16, state)."""
     if kernel_supported(S, Hq, Hkv, hd):
         ext = ops.ext()
-        o = torch.empty(B * S, Hq * hd, dtype=torch.bfloat16, device=qk.device)
-        lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qk.device)
+        o = new_output("attn_fwd.o", B * S, Hq * hd, dtype=torch.bfloat16, device=qk.device)
+        lse = new_output("attn_fwd.lse", B, Hq, S, dtype=torch.float32, device=qk.device)
         ext.attn_fwd(qk, qkv, o, lse, B, S, Hq, Hkv)
         ops.count_launch()
         return o, AttnState("sm100", o, lse)
@@ -72,7 +73,7 @@ def attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=True):
 def attn_bwd(d_o, qk, qkv, state: AttnState, B, S, Hq, Hkv, hd):
     """Returns dqkv (M, (Hq+2Hkv)*hd) bf16 = [dq (post-rope) | dk (post-rope) | dv]."""
     M = B * S
-    dqkv = torch.empty(M, (Hq + 2 * Hkv) * hd, dtype=torch.bfloat16, device=d_o.device)
+    dqkv = new_output("attn_bwd.dqkv", M, (Hq + 2 * Hkv) * hd, dtype=torch.bfloat16, device=d_o.device)
     if state.impl == "sm100":
         ops.ext().attn_bwd(d_o, qk, qkv, state.o, state.lse, dqkv, B, S, Hq, Hkv)
         ops.count_launch(3)

@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from torchure_b200 import ops
+from torchure_b200.ops.debug import new_output
 
 BF16 = torch.bfloat16
 
@@ -43,7 +44,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     N = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         assert not accumulate
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        out = new_output("gemm", M, N, dtype=out_dtype, device=a.device)
     mode = 0 if out.dtype == BF16 else (2 if accumulate else 1)
     assert not (accumulate and out.dtype == BF16), "accumulation needs an fp32 output"
     _C().gemm(a, b, out, a_mn, b_mn, mode, splits)
@@ -75,11 +76,11 @@ def add_rmsnorm(x, y, w, eps, *, ids=None, table=None, need_x_out=True):
     else:
         M, D = x.shape
         dev = x.device
-    h = torch.empty(M, D, dtype=BF16, device=dev)
-    rstd = torch.empty(M, dtype=torch.float32, device=dev)
+    h = new_output("add_rmsnorm.h", M, D, dtype=BF16, device=dev)
+    rstd = new_output("add_rmsnorm.rstd", M, dtype=torch.float32, device=dev)
     x_out = None
     if (y is not None or ids is not None) and need_x_out:
-        x_out = torch.empty(M, D, dtype=torch.float32, device=dev)
+        x_out = new_output("add_rmsnorm.x_out", M, D, dtype=torch.float32, device=dev)
     _C().add_rmsnorm_fwd(x, y, ids, table, w, x_out, h, rstd, eps)
     ops.count_launch()
     return (x_out if x_out is not None else x), h, rstd
@@ -87,15 +88,15 @@ def add_rmsnorm(x, y, w, eps, *, ids=None, table=None, need_x_out=True):
 
 def rmsnorm_bwd(dh, x, w, rstd, dx_in, dw, want_bf16=True):
     """dx = dx_in + d rmsnorm(x)^T dh (fp32), optional bf16 copy; dw += sum_rows(dh * xhat)."""
-    dx = torch.empty_like(x)
-    dxb = torch.empty(x.shape, dtype=BF16, device=x.device) if want_bf16 else None
+    dx = new_output("rmsnorm_bwd.dx", x.shape, dtype=x.dtype, device=x.device)
+    dxb = new_output("rmsnorm_bwd.dx_bf16", x.shape, dtype=BF16, device=x.device) if want_bf16 else None
     _C().rmsnorm_bwd(dh, x, w, rstd, dx_in, dx, dxb, dw)
     ops.count_launch()
     return dx, dxb
 
 
 def qknorm_rope(qkv, qw, kw, cos, sin, S, Hq, Hkv, eps, use_norm=True):
-    out = torch.empty(qkv.shape[0], (Hq + Hkv) * 128, dtype=BF16, device=qkv.device)
+    out = new_output("qknorm_rope", qkv.shape[0], (Hq + Hkv) * 128, dtype=BF16, device=qkv.device)
     _C().qknorm_rope_fwd(qkv, qw, kw, cos, sin, out, S, Hq, Hkv, eps, use_norm)
     ops.count_launch()
     return out
@@ -108,14 +109,14 @@ def qknorm_rope_bwd_(dqkv, qkv, qw, kw, cos, sin, dqw, dkw, S, Hq, Hkv, eps, use
 
 
 def swiglu(gu):
-    act = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=BF16, device=gu.device)
+    act = new_output("swiglu", gu.shape[0], gu.shape[1] // 2, dtype=BF16, device=gu.device)
     _C().swiglu_fwd(gu, act)
     ops.count_launch()
     return act
 
 
 def swiglu_bwd(dact, gu):
-    dgu = torch.empty_like(gu)
+    dgu = new_output("swiglu_bwd", gu.shape, dtype=gu.dtype, device=gu.device)
     _C().swiglu_bwd(dact, gu, dgu)
     ops.count_launch()
     return dgu
