@@ -254,7 +254,28 @@ class Trainer:
             print(f"peak cuda mem: {torch.cuda.max_memory_allocated() / 2**30:.2f} GiB")
         return history
 
+    def _mfu(self, tokens_per_step: int, seconds: float) -> float | None:
+        """Model FLOPs utilisation against the nominal dense bf16 peak (2.25 PFLOP/s per B200); None off-GPU or when the
+        config does not pin the FLOP count (no explicit ffn_dim)."""
+        mcfg = self.config["model"]
+        if not self.on_gpu or mcfg.get("name") != "qwen3_dense" or "ffn_dim" not in mcfg["config"]:
+            return None
+        from torchure_b200.models.qwen3 import flops_per_token
+
+        flops = flops_per_token(mcfg["config"], self.config["data"]["seq_len"]) * tokens_per_step
+        return flops / seconds / (2.25e15 * self.world_size)
+
     def _log_metrics(self, metrics: dict, step: int, tokens_per_step: int, seconds: float) -> None:
+        jsonl = self.config.get("logging", {}).get("jsonl")
+        if jsonl:
+            import json
+
+            rec = {"step": step, "loss": metrics["loss"].item(), "grad_norm": metrics["grad_norm"].item(),
+                   "lr": self.scheduler.get_last_lr()[0], "tokens": step * tokens_per_step,
+                   "tps": tokens_per_step / seconds, "step_time": seconds, "mfu": self._mfu(tokens_per_step, seconds)}
+            os.makedirs(os.path.dirname(os.path.abspath(jsonl)), exist_ok=True)
+            with open(jsonl, "a") as f:
+                f.write(json.dumps(rec) + "\n")
         if self.wandb_run is None:
             return
         self.wandb_run.log({
