@@ -182,6 +182,7 @@ def run_ours(args) -> None:
     cfg = bench_config(args.model, world, args.steps * 2 + args.warmup + 8, args.micro_batch, args.ce_chunk)
     if args.torch_path:
         cfg["compile"] = False
+    cfg["cuda_graph"] = bool(args.graph) and not args.torch_path
     trainer = Trainer(cfg, rank, local_rank, world, benchmark=True)
     step = trainer.train_step_untimed
     for _ in range(max(5, args.warmup)):
@@ -212,7 +213,8 @@ def run_ours(args) -> None:
                        "global_batch": mbs * world, "micro_batch": mbs, "seq_len": SEQ_LEN,
                        "parallelism": f"dp{world}", "ce_chunk": args.ce_chunk, "grad_clip": 1.0,
                        "l2": "per-step working set (>10 GB) exceeds the 126 MB L2; no explicit flush",
-                       "kernels": "sm100" if ops.available() and not args.torch_path else "torch-oracle"},
+                       "kernels": "sm100" if ops.available() and not args.torch_path else "torch-oracle",
+                       "launch": "cuda-graph replay" if trainer.use_cuda_graph else "eager"},
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": trainer.prefetcher.h2d_bytes * trainer.microbatches_per_step,
                     "d2h_bytes_per_step": 4, "last_loss": last_loss},
@@ -232,6 +234,7 @@ def main() -> None:
     ap.add_argument("--micro-batch", type=int, default=None)
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--torch-path", action="store_true", help="ours: run the PyTorch oracle path (A/B)")
+    ap.add_argument("--graph", type=int, default=0, help="ours: replay the device step from one CUDA graph (1) or launch eagerly (0)")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         sys.exit(relaunch_under_torchrun(args))

@@ -6,12 +6,10 @@ a torn checkpoint is never resumed from.  Device side: a collective kernel whose
 after its (short) wait limit, records a status word that the host reads, and leaves the context usable.
 """
 
-import os
 import time
 
 import pytest
 import torch
-import torch.distributed as dist
 
 from tests.dist_utils import run_distributed
 

@@ -64,9 +64,11 @@ struct TensorList {           // device-resident table (built once per parameter
   int n_blocks;
 };
 constexpr int kChunkElems = 16384;
-// fp32 master p, fp32/bf16 grad g (flag bit0 = grad is bf16), m, v fp32, optional bf16 shadow (ptr 0 = none)
+// fp32 master p, fp32/bf16 grad g (flag bit0 = grad is bf16), m, v fp32, optional bf16 shadow (ptr 0 = none).
+// `hyper` (optional, device): {lr, bias1, bias2} overriding the scalar arguments at run time.
 void adamw_multi(const TensorList& t, float lr, float beta1, float beta2, float eps, float weight_decay,
-                 float bias1, float bias2, const float* grad_scale, int maximize, cudaStream_t stream);
+                 float bias1, float bias2, const float* grad_scale, int maximize, const float* hyper,
+                 cudaStream_t stream);
 // out[0] += sum over all tensors of x^2 (flag bit0 = bf16)
 void sqnorm_multi(const TensorList& t, float* out, cudaStream_t stream);
 void scale_multi(const TensorList& t, const float* scale, cudaStream_t stream);

@@ -35,4 +35,12 @@ void register_attn(pybind11::module_& m) {
                           (int)Hq, (int)Hkv, err, stream);
     TORCH_CHECK(rc == 0, "attn_bwd_dkv failed with code ", rc);
   });
+  // the statistics pass alone (profiling and tests)
+  m.def("attn_bwd_prep", [](const torch::Tensor& d_o, const torch::Tensor& o, const torch::Tensor& lse,
+                            torch::Tensor& delta, torch::Tensor& lse2, int64_t B, int64_t S, int64_t Hq) {
+    TORCH_CHECK(d_o.is_contiguous() && o.is_contiguous() && lse.is_contiguous() && delta.is_contiguous() &&
+                lse2.is_contiguous());
+    tb::attn_bwd_prep(d_o.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                      lse2.data_ptr<float>(), (int)B, (int)S, (int)Hq, at::cuda::getCurrentCUDAStream().stream());
+  });
 }

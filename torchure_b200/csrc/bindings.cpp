@@ -136,9 +136,11 @@ tb::TensorList as_list(const torch::Tensor& ptrs, const torch::Tensor& numel, co
 
 void adamw_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
                  const torch::Tensor& bt, const torch::Tensor& bc, double lr, double b1, double b2, double eps,
-                 double wd, double bias1, double bias2, c10::optional<torch::Tensor> grad_scale, bool maximize) {
+                 double wd, double bias1, double bias2, c10::optional<torch::Tensor> grad_scale, bool maximize,
+                 c10::optional<torch::Tensor> hyper) {
   tb::adamw_multi(as_list(ptrs, numel, flags, bt, bc), (float)lr, (float)b1, (float)b2, (float)eps, (float)wd,
-                  (float)bias1, (float)bias2, opt_ptr<float>(grad_scale), maximize ? 1 : 0, cur_stream());
+                  (float)bias1, (float)bias2, opt_ptr<float>(grad_scale), maximize ? 1 : 0, opt_ptr<float>(hyper),
+                  cur_stream());
 }
 void sqnorm_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
                   const torch::Tensor& bt, const torch::Tensor& bc, torch::Tensor& out) {

@@ -19,14 +19,15 @@ namespace tb {
 // ---- programmatic dependent launch ----------------------------------------------------------------
 // Kernels launched through launch_pdl may be scheduled while the previous kernel of the stream is still draining;
 // each of them executes pdl_wait() before its first global-memory access, which blocks until that previous kernel
-// has completed and its writes are visible.  Only the launch latency overlaps.  TORCHURE_B200_PDL=0 disables it.
+// has completed and its writes are visible.  Only the launch latency overlaps.  Off unless TORCHURE_B200_PDL=1: on
+// this stack the step is bound by the host's enqueue rate, not by the device-side launch gap, and it measured no gain.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 inline bool pdl_enabled() {
   static const bool on = [] {
     const char* e = std::getenv("TORCHURE_B200_PDL");
-    return !(e && e[0] == '0');
+    return e && e[0] == '1';
   }();
   return on;
 }

@@ -265,8 +265,8 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
 // element i with i + 64, i.e. lane sub with lane sub ^ 8.  cos/sin of the row and both gain vectors are loaded once
 // per row and reused by all heads.
 // ---------------------------------------------------------------------------------------------
-constexpr int QK_UNROLL = 4;      // forward: head pairs in flight per warp (4 x 16 B per lane)
-constexpr int QK_BWD_UNROLL = 2;  // backward reads two tensors per head pair
+constexpr int QK_UNROLL = 12;     // forward: head pairs in flight per warp (a whole 24-head row: 12 x 16 B per lane)
+constexpr int QK_BWD_UNROLL = 4;  // backward reads two tensors per head pair (8 x 16 B per lane in flight)
 
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), d = bf2_to_f2(u.w);
@@ -287,7 +287,7 @@ __device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
   f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ qw,
                        const float* __restrict__ kw, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                        __nv_bfloat16* __restrict__ out, int M, int S, int Hq, int Hkv, float eps, int use_norm) {

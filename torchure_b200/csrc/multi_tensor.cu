@@ -39,7 +39,12 @@ __device__ __forceinline__ float load_grad(const void* g, bool is_bf16, int64_t 
 
 __global__ void __launch_bounds__(MT_THREADS)
 adamw_kernel(TensorList t, float lr, float beta1, float beta2, float eps, float wd, float bias1, float bias2,
-             const float* __restrict__ grad_scale, int maximize) {
+             const float* __restrict__ grad_scale, int maximize, const float* __restrict__ hyper) {
+  if (hyper) {  // step-dependent scalars read from device memory: the launch can be replayed from a CUDA graph
+    lr = hyper[0];
+    bias1 = hyper[1];
+    bias2 = hyper[2];
+  }
   const int ti = t.block_tensor[blockIdx.x];
   const int64_t n = t.numel[ti];
   const int64_t lo = static_cast<int64_t>(t.block_chunk[blockIdx.x]) * kChunkElems;
@@ -158,10 +163,10 @@ bucket_pack_kernel(TensorList t, int accumulate, float post_scale, float* __rest
 }  // namespace
 
 void adamw_multi(const TensorList& t, float lr, float beta1, float beta2, float eps, float weight_decay, float bias1,
-                 float bias2, const float* grad_scale, int maximize, cudaStream_t stream) {
+                 float bias2, const float* grad_scale, int maximize, const float* hyper, cudaStream_t stream) {
   if (t.n_blocks <= 0) return;
   adamw_kernel<<<t.n_blocks, MT_THREADS, 0, stream>>>(t, lr, beta1, beta2, eps, weight_decay, bias1, bias2,
-                                                      grad_scale, maximize);
+                                                      grad_scale, maximize, hyper);
 }
 
 void sqnorm_multi(const TensorList& t, float* out, cudaStream_t stream) {

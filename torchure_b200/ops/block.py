@@ -27,7 +27,6 @@ import weakref
 
 import torch
 
-from torchure_b200 import ops
 from torchure_b200.ops import attention as attn_ops
 from torchure_b200.ops import kernels as K
 

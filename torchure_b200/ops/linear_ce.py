@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import torch
 
-from torchure_b200 import ops
 from torchure_b200.ops import kernels as K
 
 BF16 = torch.bfloat16

@@ -35,11 +35,15 @@ class TensorTable:
         bt = np.repeat(np.arange(n, dtype=np.int32), chunks)
         bc = np.concatenate([np.arange(c, dtype=np.int32) for c in chunks]) if chunks else np.zeros(0, np.int32)
         self.key = tuple(tuple(p) for p in ptrs)
-        self.ptrs = torch.tensor(ptrs, dtype=torch.int64).to(dev, non_blocking=True)
-        self.numel = torch.tensor(numel, dtype=torch.int64).to(dev, non_blocking=True)
-        self.flags = torch.tensor(flags if flags is not None else [0] * n, dtype=torch.int32).to(dev, non_blocking=True)
-        self.bt = torch.from_numpy(bt).to(dev, non_blocking=True)
-        self.bc = torch.from_numpy(bc).to(dev, non_blocking=True)
+        # uploads go through pinned staging that lives as long as the table: an asynchronous copy from pinned memory
+        # is legal while a stream is being captured (the copy node re-reads the same, unchanged, host bytes)
+        host = [torch.tensor(ptrs, dtype=torch.int64), torch.tensor(numel, dtype=torch.int64),
+                torch.tensor(flags if flags is not None else [0] * n, dtype=torch.int32),
+                torch.from_numpy(bt), torch.from_numpy(bc)]
+        if dev.type == "cuda":
+            host = [h.pin_memory() for h in host]
+        self.host = host
+        self.ptrs, self.numel, self.flags, self.bt, self.bc = (h.to(dev, non_blocking=True) for h in host)
         self.keepalive = columns
 
     def args(self):
@@ -80,12 +84,13 @@ def scale_(tensors: list[torch.Tensor], scale: torch.Tensor) -> None:
 
 
 def adamw_step(params, grads, exp_avgs, exp_avg_sqs, shadows, lr, beta1, beta2, eps, weight_decay, step,
-               grad_scale=None, maximize=False) -> None:
+               grad_scale=None, maximize=False, hyper=None) -> None:
+    """`hyper`: optional device tensor {lr, 1 - beta1^t, 1 - beta2^t} that overrides lr/step at run time (graph replay)."""
     tab = _table("adamw", [params, grads, exp_avgs, exp_avg_sqs, shadows], _bf16_flags(grads))
     bias1 = 1.0 - beta1 ** step
     bias2 = 1.0 - beta2 ** step
     gs = grad_scale.to(torch.float32) if grad_scale is not None else None
-    ops.ext().adamw_multi(*tab.args(), lr, beta1, beta2, eps, weight_decay, bias1, bias2, gs, maximize)
+    ops.ext().adamw_multi(*tab.args(), lr, beta1, beta2, eps, weight_decay, bias1, bias2, gs, maximize, hyper)
     ops.count_launch()
 
 

@@ -2,7 +2,8 @@
 
     python -m torchure_b200.ops.profile_case <case> [--iters N]
 
-Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, qknorm_rope, ce, adamw.  Each case builds inputs
+Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, attn_prep, rmsnorm, rmsnorm_bwd, qknorm_rope,
+qknorm_rope_bwd, ce, adamw.  Each case builds inputs
 larger than the 126 MB L2 but well under a few GB, launches the kernel `iters` times (default 4) and prints the
 CUDA-event time of the last launch with the achieved FLOP/s or bytes/s, so the same command serves a plain timing run
 and an `ncu -k regex:<kernel> -s 2 -c 1` capture.
@@ -70,6 +71,28 @@ def main(argv=None) -> None:
         w = torch.ones(hd, device=dev)
         fn = lambda: K.qknorm_rope(qkv, w, w, cos, sin, S, Hq, Hkv, 1e-6, True)
         bytes_ = 2 * M * (Hq + Hkv) * hd * 2
+    elif args.case == "qknorm_rope_bwd":
+        qkv = torch.randn(M, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
+        dqkv = torch.randn(M, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
+        cos, sin = RotaryEmbedding(hd).tables(S, dev)
+        w = torch.ones(hd, device=dev)
+        dqw, dkw = torch.zeros(hd, device=dev), torch.zeros(hd, device=dev)
+        fn = lambda: K.qknorm_rope_bwd_(dqkv, qkv, w, w, cos, sin, dqw, dkw, S, Hq, Hkv, 1e-6, True)
+        bytes_ = 3 * M * (Hq + Hkv) * hd * 2   # read dqkv and qkv (q, k columns), write dqkv
+    elif args.case == "rmsnorm_bwd":
+        rows = 4 * M
+        x, dh = torch.randn(rows, D, device=dev), torch.randn(rows, D, device=dev).bfloat16()
+        dx_in = torch.randn(rows, D, device=dev)
+        w, dw = torch.ones(D, device=dev), torch.zeros(D, device=dev)
+        rstd = torch.rsqrt(x.pow(2).mean(-1) + 1e-6)
+        fn = lambda: K.rmsnorm_bwd(dh, x, w, rstd, dx_in, dw)
+        bytes_ = rows * D * (2 + 4 + 4 + 4 + 2)   # dh, x, dx_in read; dx fp32 and bf16 written
+    elif args.case == "attn_prep":
+        d_o, o = (torch.randn(4 * M, Hq * hd, device=dev).bfloat16() for _ in range(2))
+        lse = torch.randn(4 * B, Hq, S, device=dev)
+        delta, lse2 = torch.empty_like(lse), torch.empty_like(lse)
+        fn = lambda: ops.ext().attn_bwd_prep(d_o, o, lse, delta, lse2, 4 * B, S, Hq)
+        bytes_ = 2 * 4 * M * Hq * hd * 2
     elif args.case == "ce":
         V, C = 151936, 1024
         logits = torch.randn(C, V, device=dev).bfloat16()

@@ -22,6 +22,9 @@ class AdamW(torch.optim.AdamW):
         super().__init__(params, lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay, **kw)
         self._grad_scale: torch.Tensor | None = None
         self._shadow: dict[torch.Tensor, torch.Tensor] = {}
+        self._hyper: list[torch.Tensor] | None = None   # per group {lr, bias1, bias2} on the device
+        self._hyper_cur: int | None = None
+        self._graph_groups: dict[int, list[torch.Tensor]] = {}
 
     # -- hooks for the trainer -------------------------------------------------------------
     def set_grad_scale(self, coef: torch.Tensor | None) -> None:
@@ -60,24 +63,19 @@ class AdamW(torch.optim.AdamW):
             return loss if closure is not None else out
         from torchure_b200.ops import multi_tensor
 
-        for group in self.param_groups:
+        capturing = torch.cuda.is_current_stream_capturing()
+        for gi, group in enumerate(self.param_groups):
             ps = [p for p in group["params"] if p.grad is not None]
             if not ps:
                 continue
-            for p in ps:
-                st = self.state[p]
-                if len(st) == 0:
-                    st["step"] = torch.tensor(0.0, dtype=torch.float32)
-                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
-                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
-            # every tensor of a group steps together; read the count once on the host
-            step0 = self.state[ps[0]]["step"]
-            t = int(step0.item()) + 1
-            for p in ps:
-                self.state[p]["step"] = torch.tensor(float(t), dtype=torch.float32)
+            t, lr = self._advance_group(group, ps)
             b1, b2 = group["betas"]
-            lr = group["lr"]
-            lr = float(lr.item()) if torch.is_tensor(lr) else float(lr)
+            hyper = None
+            if self._hyper is not None:
+                # lr and the bias corrections come from device memory, so the launch can be replayed from a graph
+                if not capturing:
+                    self._upload_hyper(gi, lr, 1.0 - b1 ** t, 1.0 - b2 ** t)
+                hyper = self._hyper[gi]
             multi_tensor.adamw_step(
                 params=ps,
                 grads=[p.grad for p in ps],
@@ -85,6 +83,73 @@ class AdamW(torch.optim.AdamW):
                 exp_avg_sqs=[self.state[p]["exp_avg_sq"] for p in ps],
                 shadows=[self._shadow.get(p) for p in ps],
                 lr=lr, beta1=b1, beta2=b2, eps=group["eps"], weight_decay=group["weight_decay"],
-                step=t, grad_scale=scale, maximize=group.get("maximize", False),
+                step=t, grad_scale=scale, maximize=group.get("maximize", False), hyper=hyper,
             )
+            self._graph_groups[gi] = ps
         return loss
+
+    def _advance_group(self, group, ps) -> tuple[int, float]:
+        """Host bookkeeping of one step for one group: state init, step count, current lr."""
+        for p in ps:
+            st = self.state[p]
+            if len(st) == 0:
+                st["step"] = torch.tensor(0.0, dtype=torch.float32)
+                st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+        # every tensor of a group steps together; read the count once on the host
+        t = int(self.state[ps[0]]["step"].item()) + 1
+        for p in ps:
+            self.state[p]["step"] = torch.tensor(float(t), dtype=torch.float32)
+        lr = group["lr"]
+        return t, (float(lr.item()) if torch.is_tensor(lr) else float(lr))
+
+    # -- CUDA-graph support -----------------------------------------------------------------------------
+    def enable_device_hyper(self, ring: int = 8) -> None:
+        """Keep {lr, 1-beta1^t, 1-beta2^t} of every group in device memory, refreshed from a ring of pinned host
+        slots before each launch.  A captured step then never bakes a step-dependent scalar into a kernel node."""
+        if self._hyper is not None:
+            return
+        dev = self.param_groups[0]["params"][0].device
+        n = len(self.param_groups)
+        self._hyper = [torch.zeros(3, dtype=torch.float32, device=dev) for _ in range(n)]
+        self._hyper_host = torch.zeros(ring, n, 3, dtype=torch.float32).pin_memory()
+        self._hyper_events = [None] * ring
+        self._hyper_slot = 0
+
+    def _upload_hyper(self, gi: int, lr: float, bias1: float, bias2: float) -> None:
+        if gi == 0 or self._hyper_cur is None:
+            slot = self._hyper_slot
+            self._hyper_slot = (slot + 1) % self._hyper_host.shape[0]
+            ev = self._hyper_events[slot]
+            if ev is not None:
+                ev.synchronize()  # the copy that last read this slot has run
+            self._hyper_cur = slot
+        slot = self._hyper_cur
+        self._hyper_host[slot, gi, 0] = lr
+        self._hyper_host[slot, gi, 1] = bias1
+        self._hyper_host[slot, gi, 2] = bias2
+        self._hyper[gi].copy_(self._hyper_host[slot, gi], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._hyper_events[slot] = ev
+
+    def host_state(self) -> dict:
+        """Step counters, for undoing the bookkeeping of a step that was only captured, not executed."""
+        return {id(p): st["step"].clone() for p, st in self.state.items() if "step" in st}
+
+    def restore_host_state(self, snap: dict) -> None:
+        for p, st in self.state.items():
+            if id(p) in snap:
+                st["step"] = snap[id(p)].clone()
+
+    def host_advance(self) -> None:
+        """The host half of ``step()`` for a step whose kernels are replayed from a graph: advance the counters and
+        refresh the device-resident scalars (stream-ordered before the replay)."""
+        assert self._hyper is not None and self._graph_groups, "capture a step with enable_device_hyper() first"
+        for gi, group in enumerate(self.param_groups):
+            ps = self._graph_groups.get(gi)
+            if not ps:
+                continue
+            t, lr = self._advance_group(group, ps)
+            b1, b2 = group["betas"]
+            self._upload_hyper(gi, lr, 1.0 - b1 ** t, 1.0 - b2 ** t)

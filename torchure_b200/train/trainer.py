@@ -81,6 +81,9 @@ class Trainer:
         self.num_train_steps = opt_cfg["scheduler"]["total_steps"]
         self.max_norm = opt_cfg.get("max_norm")
         self._wire_engine()
+        self.use_cuda_graph = bool(self.config.get("cuda_graph", False)) and self.on_gpu
+        self._graph = None
+        self._graph_eager_left = int(self.config.get("cuda_graph_warmup", 3))
 
         self.dataloader = self._build_dataloader()
         data_cfg = self.config["data"]
@@ -200,8 +203,9 @@ class Trainer:
         return state["step"]
 
     # -- the step ------------------------------------------------------------------------------
-    def micro_train_step(self) -> torch.Tensor:
-        batch = next(self.prefetcher)
+    def micro_train_step(self, batch=None) -> torch.Tensor:
+        if batch is None:
+            batch = next(self.prefetcher)
         scale = 1.0 / self.microbatches_per_step
         if self.on_gpu:
             with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
@@ -211,13 +215,16 @@ class Trainer:
         loss.backward()
         return loss.detach()
 
-    def train_step_untimed(self) -> dict[str, torch.Tensor]:
+    def _device_step(self, batches=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Everything of one optimizer step that runs on the device: micro-batches, gradient reduction, clipping,
+        AdamW.  `batches` (one dict per micro-batch) are used instead of the prefetcher when given."""
+        K = self.microbatches_per_step
         loss = torch.zeros((), device=self.device)
         self.ddp.requires_sync = False
-        for _ in range(self.microbatches_per_step - 1):
-            loss += self.micro_train_step()
+        for i in range(K - 1):
+            loss += self.micro_train_step(batches[i] if batches else None)
         self.ddp.requires_sync = True
-        loss += self.micro_train_step()
+        loss += self.micro_train_step(batches[K - 1] if batches else None)
         self.ddp.sync()
         sq = self.ddp.sq_norm()
         params = [p for p in self.model.parameters() if p.requires_grad]
@@ -229,10 +236,56 @@ class Trainer:
             grad_norm = clip_grad_norm(params, self.mesh, self.max_norm, shard_dims=())
         self.optimizer.step()
         self.optimizer.zero_grad()
+        return loss, grad_norm
+
+    def train_step_untimed(self) -> dict[str, torch.Tensor]:
+        if self.use_cuda_graph:
+            loss, grad_norm = self._graph_step()
+        else:
+            loss, grad_norm = self._device_step()
         self.scheduler.step()
         if self.dp_size > 1:
             all_reduce(loss, self.mesh, "dp", "avg")
         return {"loss": loss, "grad_norm": grad_norm}
+
+    # -- CUDA-graph replay of the device step ----------------------------------------------------
+    def _graph_step(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """Replay the whole device step (forward, backward, bucket all-reduces on the communication stream, clip,
+        AdamW) from ONE captured CUDA graph.  The first `cuda_graph_warmup` steps run eagerly (they fill the
+        tensor-map and pointer-table caches and size the allocator), the next one is captured, and every later step
+        copies its batch into the graph's static input tensors, refreshes the device-resident lr / bias-correction
+        scalars and replays.  Nothing step-dependent is baked into a node: the clip coefficient and the optimizer
+        scalars are read from device memory, and the peer-flag handshakes of the collectives carry no sequence
+        numbers."""
+        from torchure_b200 import ops
+
+        K = self.microbatches_per_step
+        fetched = [next(self.prefetcher) for _ in range(K)]
+        if self._graph is None and self._graph_eager_left > 0:
+            self._graph_eager_left -= 1
+            self.optimizer.enable_device_hyper()
+            return self._device_step(fetched)
+        if self._graph is None:
+            self._static_batches = [{k: v.clone() for k, v in b.items()} for b in fetched]
+            snap = self.optimizer.host_state()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            n0 = ops.launches()
+            with torch.cuda.graph(graph):
+                self._static_out = self._device_step(self._static_batches)
+            self._graph_launches = ops.launches() - n0
+            ops.count_launch(-self._graph_launches)        # capture launched nothing
+            self.optimizer.restore_host_state(snap)        # ... and stepped nothing
+            self._graph = graph
+        else:
+            for dst, src in zip(self._static_batches, fetched):
+                for k, v in src.items():
+                    dst[k].copy_(v, non_blocking=True)
+        self.optimizer.host_advance()
+        self._graph.replay()
+        ops.count_launch(self._graph_launches)
+        loss, grad_norm = self._static_out
+        return loss.clone(), grad_norm.clone()
 
     train_step = record_time(train_step_untimed)
 
