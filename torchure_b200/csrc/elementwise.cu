@@ -260,21 +260,21 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
 }
 
 // ---------------------------------------------------------------------------------------------
-// QK-norm + RoPE, hd == 128.  One warp per token row; 16 lanes per head, so a warp instruction covers two heads
-// with one 16-byte access per lane (lane sub = lane & 15 holds elements 8*sub .. 8*sub+7).  The rotation pairs
-// element i with i + 64, i.e. lane sub with lane sub ^ 8.  cos/sin of the row and both gain vectors are loaded once
-// per row and reused by all heads.
+// QK-norm + RoPE, hd == 128.  One warp per token row; 16 lanes per head, so a warp instruction covers two heads.
+// Lane sub = lane & 15 holds elements 4*sub .. 4*sub+3 AND 64+4*sub .. 64+4*sub+3 of its head (two 8-byte accesses):
+// the rotation pairs element i with i + 64, so both partners sit in the same lane and need no shuffle.  cos/sin of
+// the row and both gain vectors are loaded once per row and reused by all heads.
 // ---------------------------------------------------------------------------------------------
-constexpr int QK_UNROLL = 12;     // forward: head pairs in flight per warp (a whole 24-head row: 12 x 16 B per lane)
-constexpr int QK_BWD_UNROLL = 4;  // backward reads two tensors per head pair (8 x 16 B per lane in flight)
+constexpr int QK_UNROLL = 4;      // forward: head pairs in flight per warp
+constexpr int QK_BWD_UNROLL = 1;  // backward: one head pair per iteration, the next pair's loads prefetched
 
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y), c = bf2_to_f2(u.z), d = bf2_to_f2(u.w);
-  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+__device__ __forceinline__ void unpack4(const uint2& u, float (&f)[4]) {
+  float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-  uint4 u;
-  u.x = f2_to_bf2(f[0], f[1]); u.y = f2_to_bf2(f[2], f[3]); u.z = f2_to_bf2(f[4], f[5]); u.w = f2_to_bf2(f[6], f[7]);
+__device__ __forceinline__ uint2 pack4(const float (&f)[4]) {
+  uint2 u;
+  u.x = f2_to_bf2(f[0], f[1]); u.y = f2_to_bf2(f[2], f[3]);
   return u;
 }
 __device__ __forceinline__ float group16_sum(float v) {
@@ -282,12 +282,12 @@ __device__ __forceinline__ float group16_sum(float v) {
   for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
-__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
-  float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
-  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+__device__ __forceinline__ void load4f(const float* p, float (&f)[4]) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
 }
 
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256)
 qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ qw,
                        const float* __restrict__ kw, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                        __nv_bfloat16* __restrict__ out, int M, int S, int Hq, int Hkv, float eps, int use_norm) {
@@ -298,51 +298,62 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __res
   const int lane = threadIdx.x & 31;
   if (row >= M) return;
   const int sub = lane & 15, hsel = lane >> 4;
-  const bool is_hi = sub >= 8;
   const int in_ld = (Hq + 2 * Hkv) * 128, out_ld = heads * 128;
-  const __nv_bfloat16* src = qkv + static_cast<int64_t>(row) * in_ld + sub * 8;
-  __nv_bfloat16* dst = out + static_cast<int64_t>(row) * out_ld + sub * 8;
+  const __nv_bfloat16* src = qkv + static_cast<int64_t>(row) * in_ld + sub * 4;
+  __nv_bfloat16* dst = out + static_cast<int64_t>(row) * out_ld + sub * 4;
   const int pos = row % S;
-  float c[8], sn[8], gq[8], gk[8];
-  load8f(cos_t + static_cast<int64_t>(pos) * 128 + (sub & 7) * 8, c);  // cos[i] == cos[i + 64]
-  load8f(sin_t + static_cast<int64_t>(pos) * 128 + (sub & 7) * 8, sn);
+  float c[4], sn[4], gq_lo[4], gq_hi[4], gk_lo[4], gk_hi[4];
+  load4f(cos_t + static_cast<int64_t>(pos) * 128 + sub * 4, c);  // cos[i] == cos[i + 64]
+  load4f(sin_t + static_cast<int64_t>(pos) * 128 + sub * 4, sn);
   if (use_norm) {
-    load8f(qw + sub * 8, gq);
-    load8f(kw + sub * 8, gk);
+    load4f(qw + sub * 4, gq_lo); load4f(qw + 64 + sub * 4, gq_hi);
+    load4f(kw + sub * 4, gk_lo); load4f(kw + 64 + sub * 4, gk_hi);
   }
   const int pairs = (heads + 1) >> 1;
   for (int hp = 0; hp < pairs; hp += QK_UNROLL) {
-    uint4 u[QK_UNROLL];
+    uint2 ulo[QK_UNROLL], uhi[QK_UNROLL];
 #pragma unroll
     for (int k = 0; k < QK_UNROLL; ++k) {
       const int h = 2 * (hp + k) + hsel;
-      u[k] = make_uint4(0u, 0u, 0u, 0u);
-      if (h < heads) u[k] = *reinterpret_cast<const uint4*>(src + h * 128);
+      ulo[k] = uhi[k] = make_uint2(0u, 0u);
+      if (h < heads) {
+        ulo[k] = *reinterpret_cast<const uint2*>(src + h * 128);
+        uhi[k] = *reinterpret_cast<const uint2*>(src + h * 128 + 64);
+      }
     }
 #pragma unroll
     for (int k = 0; k < QK_UNROLL; ++k) {
       const int h = 2 * (hp + k) + hsel;
-      float x[8];
-      unpack8(u[k], x);
+      float lo[4], hi[4];
+      unpack4(ulo[k], lo);
+      unpack4(uhi[k], hi);
       if (use_norm) {
         float ss = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+        for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
         ss = group16_sum(ss);
         const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+        const bool is_q = h < Hq;
         // the reference normalises in bf16 precision before RoPE (its q_norm returns bf16)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] = x[e] * r * (h < Hq ? gq[e] : gk[e]);
-        uint4 rounded = pack8(x);
-        unpack8(rounded, x);
+        for (int e = 0; e < 4; ++e) {
+          lo[e] = lo[e] * r * (is_q ? gq_lo[e] : gk_lo[e]);
+          hi[e] = hi[e] * r * (is_q ? gq_hi[e] : gk_hi[e]);
+        }
+        const uint2 rl = pack4(lo), rh = pack4(hi);
+        unpack4(rl, lo);
+        unpack4(rh, hi);
       }
-      float o[8];
+      float olo[4], ohi[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float p = __shfl_xor_sync(0xffffffffu, x[e], 8);
-        o[e] = is_hi ? x[e] * c[e] + p * sn[e] : x[e] * c[e] - p * sn[e];
+      for (int e = 0; e < 4; ++e) {
+        olo[e] = lo[e] * c[e] - hi[e] * sn[e];
+        ohi[e] = hi[e] * c[e] + lo[e] * sn[e];
       }
-      if (h < heads) *reinterpret_cast<uint4*>(dst + h * 128) = pack8(o);
+      if (h < heads) {
+        *reinterpret_cast<uint2*>(dst + h * 128) = pack4(olo);
+        *reinterpret_cast<uint2*>(dst + h * 128 + 64) = pack4(ohi);
+      }
     }
   }
 }
@@ -358,48 +369,73 @@ qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
   const int sub = lane & 15, hsel = lane >> 4;
-  const bool is_hi = sub >= 8;
   const int ld = (Hq + 2 * Hkv) * 128;
   const int pairs = (heads + 1) >> 1;
-  float gq[8], gk[8], aq[8], ak[8];  // gains and this lane's gain-gradient partials
+  // gains and this lane's gain-gradient partials: [0..3] elements 4*sub.., [4..7] elements 64+4*sub..
+  float gq[8], gk[8], aq[8], ak[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) { gq[e] = gk[e] = 1.f; aq[e] = ak[e] = 0.f; }
   if (use_norm) {
-    load8f(qw + sub * 8, gq);
-    load8f(kw + sub * 8, gk);
+    float t[4];
+    load4f(qw + sub * 4, t);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) gq[e] = t[e];
+    load4f(qw + 64 + sub * 4, t);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) gq[4 + e] = t[e];
+    load4f(kw + sub * 4, t);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) gk[e] = t[e];
+    load4f(kw + 64 + sub * 4, t);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) gk[4 + e] = t[e];
   }
   for (int row = blockIdx.x * 8 + wid; row < M; row += gridDim.x * 8) {
     const int pos = row % S;
-    float c[8], sn[8];
-    load8f(cos_t + static_cast<int64_t>(pos) * 128 + (sub & 7) * 8, c);
-    load8f(sin_t + static_cast<int64_t>(pos) * 128 + (sub & 7) * 8, sn);
-    __nv_bfloat16* dptr = dqkv + static_cast<int64_t>(row) * ld + sub * 8;
-    const __nv_bfloat16* xptr = qkv + static_cast<int64_t>(row) * ld + sub * 8;
-    for (int hp = 0; hp < pairs; hp += QK_BWD_UNROLL) {
-      uint4 du[QK_BWD_UNROLL], xu[QK_BWD_UNROLL];
-#pragma unroll
-      for (int k = 0; k < QK_BWD_UNROLL; ++k) {
-        const int h = 2 * (hp + k) + hsel;
-        du[k] = xu[k] = make_uint4(0u, 0u, 0u, 0u);
-        if (h < heads) {
-          du[k] = *reinterpret_cast<const uint4*>(dptr + h * 128);
-          if (use_norm) xu[k] = *reinterpret_cast<const uint4*>(xptr + h * 128);
+    float c[4], sn[4];
+    load4f(cos_t + static_cast<int64_t>(pos) * 128 + sub * 4, c);
+    load4f(sin_t + static_cast<int64_t>(pos) * 128 + sub * 4, sn);
+    __nv_bfloat16* dptr = dqkv + static_cast<int64_t>(row) * ld + sub * 4;
+    const __nv_bfloat16* xptr = qkv + static_cast<int64_t>(row) * ld + sub * 4;
+    // software pipeline: the loads of head pair hp + 1 are in flight while pair hp is processed
+    uint2 dl[1], dh[1], xl[1], xh[1], ndl, ndh, nxl, nxh;
+    auto fetch = [&](int hp, uint2& a0, uint2& a1, uint2& b0, uint2& b1) {
+      const int h = 2 * hp + hsel;
+      a0 = a1 = b0 = b1 = make_uint2(0u, 0u);
+      if (hp < pairs && h < heads) {
+        a0 = *reinterpret_cast<const uint2*>(dptr + h * 128);
+        a1 = *reinterpret_cast<const uint2*>(dptr + h * 128 + 64);
+        if (use_norm) {
+          b0 = *reinterpret_cast<const uint2*>(xptr + h * 128);
+          b1 = *reinterpret_cast<const uint2*>(xptr + h * 128 + 64);
         }
       }
+    };
+    fetch(0, ndl, ndh, nxl, nxh);
+    for (int hp = 0; hp < pairs; hp += QK_BWD_UNROLL) {
+      dl[0] = ndl; dh[0] = ndh; xl[0] = nxl; xh[0] = nxh;
+      fetch(hp + 1, ndl, ndh, nxl, nxh);
 #pragma unroll
       for (int k = 0; k < QK_BWD_UNROLL; ++k) {
         const int h = 2 * (hp + k) + hsel;
-        float d[8], n[8];
-        unpack8(du[k], d);
+        float dlo[4], dhi[4], n[8];
+        unpack4(dl[k], dlo);
+        unpack4(dh[k], dhi);
         // transpose of the rotation
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float p = __shfl_xor_sync(0xffffffffu, d[e], 8);
-          n[e] = is_hi ? d[e] * c[e] - p * sn[e] : d[e] * c[e] + p * sn[e];
+        for (int e = 0; e < 4; ++e) {
+          n[e] = dlo[e] * c[e] + dhi[e] * sn[e];
+          n[4 + e] = dhi[e] * c[e] - dlo[e] * sn[e];
         }
         if (use_norm) {
           float x[8];
-          unpack8(xu[k], x);
+          {
+            float t0[4], t1[4];
+            unpack4(xl[k], t0);
+            unpack4(xh[k], t1);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { x[e] = t0[e]; x[4 + e] = t1[e]; }
+          }
           float ss = 0.f;
 #pragma unroll
           for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
@@ -422,22 +458,34 @@ qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __
 #pragma unroll
           for (int e = 0; e < 8; ++e) n[e] = r * (n[e] * (is_q ? gq[e] : gk[e]) - x[e] * dot);
         }
-        if (h < heads) *reinterpret_cast<uint4*>(dptr + h * 128) = pack8(n);
+        if (h < heads) {
+          float o0[4], o1[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { o0[e] = n[e]; o1[e] = n[4 + e]; }
+          *reinterpret_cast<uint2*>(dptr + h * 128) = pack4(o0);
+          *reinterpret_cast<uint2*>(dptr + h * 128 + 64) = pack4(o1);
+        }
       }
     }
   }
   if (use_norm) {
-    __shared__ float red[2][128];
+    __shared__ __align__(16) float red[2][128];
     red[threadIdx.x >> 7][threadIdx.x & 127] = 0.f;
     __syncthreads();
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      atomicAdd(&red[0][sub * 8 + e], aq[e]);
-      atomicAdd(&red[1][sub * 8 + e], ak[e]);
+    for (int e = 0; e < 4; ++e) {
+      atomicAdd(&red[0][sub * 4 + e], aq[e]);
+      atomicAdd(&red[0][64 + sub * 4 + e], aq[4 + e]);
+      atomicAdd(&red[1][sub * 4 + e], ak[e]);
+      atomicAdd(&red[1][64 + sub * 4 + e], ak[4 + e]);
     }
     __syncthreads();
-    if (threadIdx.x < 128) atomicAdd(&dqw[threadIdx.x], red[0][threadIdx.x]);
-    else atomicAdd(&dkw[threadIdx.x - 128], red[1][threadIdx.x - 128]);
+    // one 16-byte reduction per four columns per CTA; the grid is two CTAs per SM, so few of them meet in L2
+    if (threadIdx.x < 64) {
+      const int which = threadIdx.x >> 5, i = threadIdx.x & 31;
+      const float4 v = *reinterpret_cast<const float4*>(&red[which][4 * i]);
+      red_add_v4((which ? dkw : dqw) + 4 * i, v);
+    }
   }
 }
 
@@ -687,7 +735,7 @@ void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float*
                      const float* sin, float* dqw, float* dkw, int M, int S, int Hq, int Hkv, int hd, float eps,
                      int use_norm, int num_sms, cudaStream_t stream) {
   (void)hd;
-  const int grid = std::min((M + 7) / 8, num_sms * 8);  // one warp per row, persistent
+  const int grid = std::min((M + 7) / 8, num_sms * 2);  // persistent: two CTAs per SM, a warp walks rows
   launch_pdl(qknorm_rope_bwd_kernel, dim3(grid), dim3(256), 0, stream, dqkv, qkv, qw, kw, cos, sin, dqw, dkw, M, S, Hq, Hkv, eps,
                                                    use_norm);
 }
