@@ -234,7 +234,7 @@ def main() -> None:
     ap.add_argument("--micro-batch", type=int, default=None)
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--torch-path", action="store_true", help="ours: run the PyTorch oracle path (A/B)")
-    ap.add_argument("--graph", type=int, default=0, help="ours: replay the device step from one CUDA graph (1) or launch eagerly (0)")
+    ap.add_argument("--graph", type=int, default=1, help="ours: replay the device step from one CUDA graph (1) or launch eagerly (0)")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         sys.exit(relaunch_under_torchrun(args))
