@@ -1,6 +1,6 @@
 """Bus-bandwidth sweep of the mesh collectives: our NVLink kernels against the NCCL path of the same call.
 
-    torchrun --nproc-per-node N -m torchure_b200.core.bench_collectives [--max-mb 1024] [--out sweep.json]
+    torchrun --nproc-per-node N -m torchure_b200.core.bench_collectives [--max-mb 1024] [--stride 1] [--out sweep.json]
 
 For every op (all_reduce, all_gather, reduce_scatter, all_to_all), dtype (bf16, fp32) and per-rank message size
 (powers of two from 1 KiB, N(0,1) values) it times both transports with CUDA events after warm-up, takes the
@@ -41,13 +41,14 @@ def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=int, default=1024)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--stride", type=int, default=1, help="take every stride-th power of two (a quick sweep)")
     args = ap.parse_args(argv)
     rank, _, world = init_distributed()
     mesh = Mesh({"dp": world})
     ours = Mesh({"dp": world})
     comm = C.enable_sm100(ours, "dp", max_bytes=(args.max_mb << 20) * (world + 2) + (64 << 20))
     rows = []
-    sizes = [1 << k for k in range(10, 31) if (1 << k) <= (args.max_mb << 20)]
+    sizes = [1 << k for k in range(10, 31, args.stride) if (1 << k) <= (args.max_mb << 20)]
     for dtype in (torch.bfloat16, torch.float32):
         es = 2 if dtype == torch.bfloat16 else 4
         for nbytes in sizes:
