@@ -4,7 +4,8 @@
 
 Shapes of the headline model's head: hidden states 8192 x 1024 bf16 ~ N(0, 1), weight 151936 x 1024 ~ N(0, 0.02),
 uniform int64 targets; the weight is the fp32 master both trainers hold (each casts it to bf16 itself).  "ours" is
-``loss.fused_linear_cross_entropy`` (tcgen05 logits / dgrad / wgrad GEMMs around the ``ce_softmax_grad`` kernel, fp32 dW accumulated by TMA reduce-add); "reference" is the unmodified
+``loss.fused_linear_cross_entropy`` (tcgen05 logits / dgrad / wgrad GEMMs around the ``ce_softmax_grad`` kernel,
+fp32 dW accumulated by TMA reduce-add); "reference" is the unmodified
 ``torchure.loss.fused_linear_ce.fused_linear_cross_entropy`` imported from ``baseline/_ref`` (torch.compile'd chunk
 function, cuBLAS).  Each timed iteration is loss forward + ``loss.backward()``; CUDA events, after warm-up.
 """
