@@ -165,16 +165,18 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const float* __restrict
 }
 
 // ---------------------------------------------------------------------------------------------
-// rmsnorm backward for D <= 1024: one 16-warp CTA per SM owns a contiguous range of rows; a warp keeps its row's x
-// and dh in registers between the dot-product pass and the output pass (each byte is read once), and the weight
-// gradient leaves the CTA as 16-byte vector reductions (one per four columns per CTA).
+// rmsnorm backward for D <= 1024: four 4-warp CTAs per SM, each owning a contiguous range of rows; a warp keeps its
+// row's x and dh in registers between the dot-product pass and the output pass (each byte is read once), and the
+// weight gradient leaves the CTA as 16-byte vector reductions (one per four columns per CTA).  The CTAs are small
+// (16 K registers, 16 KB shared memory) so that they also fit on an SM that hosts a CTA of a gradient all-reduce
+// kernel; one 64 K-register CTA per SM had to wait for those SMs and ran in two waves during DDP steps.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void red_add_v4(float* p, const float4& v) {
   asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-template <int MAX_VEC>
-__global__ void __launch_bounds__(512, 1)
+template <int MAX_VEC, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
 rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __restrict__ x, const float* __restrict__ w,
                         const float* __restrict__ rstd, const float* __restrict__ dx_in, float* __restrict__ dx,
                         __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw, int M, int D) {
@@ -188,7 +190,7 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
   float4 dw_acc[MAX_VEC];
 #pragma unroll
   for (int j = 0; j < MAX_VEC; ++j) dw_acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int row = lo + wid; row < hi; row += 16) {
+  for (int row = lo + wid; row < hi; row += WARPS) {
     const int64_t off = static_cast<int64_t>(row) * D;
     float4 xv[MAX_VEC];
     uint2 dv[MAX_VEC];
@@ -240,8 +242,8 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
       }
     }
   }
-  // 16 warps -> one partial per column in shared memory -> one vector reduction per four columns
-  extern __shared__ float red[];  // [16][D]
+  // WARPS warps -> one partial per column in shared memory -> one vector reduction per four columns
+  extern __shared__ float red[];  // [WARPS][D]
 #pragma unroll
   for (int j = 0; j < MAX_VEC; ++j) {
     const int i = lane + j * 32;
@@ -251,7 +253,7 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
+    for (int k = 0; k < WARPS; ++k) {
       const float4 v = reinterpret_cast<const float4*>(red + k * D)[i];
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
@@ -358,7 +360,8 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __res
   }
 }
 
-__global__ void __launch_bounds__(256, 2)
+// 4-warp CTAs (14 K registers): they fit next to a CTA of a gradient all-reduce kernel on the same SM
+__global__ void __launch_bounds__(128, 4)
 qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ qkv,
                        const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ cos_t,
                        const float* __restrict__ sin_t, float* __restrict__ dqw, float* __restrict__ dkw, int M, int S,
@@ -390,7 +393,7 @@ qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __
 #pragma unroll
     for (int e = 0; e < 4; ++e) gk[4 + e] = t[e];
   }
-  for (int row = blockIdx.x * 8 + wid; row < M; row += gridDim.x * 8) {
+  for (int row = blockIdx.x * 4 + wid; row < M; row += gridDim.x * 4) {
     const int pos = row % S;
     float c[4], sn[4];
     load4f(cos_t + static_cast<int64_t>(pos) * 128 + sub * 4, c);
@@ -470,7 +473,7 @@ qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __
   }
   if (use_norm) {
     __shared__ __align__(16) float red[2][128];
-    red[threadIdx.x >> 7][threadIdx.x & 127] = 0.f;
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) (&red[0][0])[i] = 0.f;
     __syncthreads();
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -708,13 +711,10 @@ void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const 
                  float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, cudaStream_t stream) {
   // two rows per warp keeps every warp equally loaded and the per-CTA atomics on dw few
   if (D <= 128 * 8 && M >= 4 * num_sms) {
-    static bool configured = false;
-    const size_t smem16 = static_cast<size_t>(16) * D * sizeof(float);
-    if (!configured) {
-      cudaFuncSetAttribute(rmsnorm_bwd_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 1024 * 4);
-      configured = true;
-    }
-    launch_pdl(rmsnorm_bwd_rows_kernel<8>, dim3(num_sms), dim3(512), smem16, stream, dh, x, w, rstd, dx_in, dx, dx_bf16, dw, M, D);
+    constexpr int W = 4;
+    const size_t smem_w = static_cast<size_t>(W) * D * sizeof(float);
+    launch_pdl(rmsnorm_bwd_rows_kernel<8, W>, dim3(num_sms * (16 / W)), dim3(W * 32), smem_w, stream, dh, x, w, rstd,
+               dx_in, dx, dx_bf16, dw, M, D);
     return;
   }
   const int grid = std::max(1, (M + 15) / 16);
@@ -735,8 +735,8 @@ void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float*
                      const float* sin, float* dqw, float* dkw, int M, int S, int Hq, int Hkv, int hd, float eps,
                      int use_norm, int num_sms, cudaStream_t stream) {
   (void)hd;
-  const int grid = std::min((M + 7) / 8, num_sms * 2);  // persistent: two CTAs per SM, a warp walks rows
-  launch_pdl(qknorm_rope_bwd_kernel, dim3(grid), dim3(256), 0, stream, dqkv, qkv, qw, kw, cos, sin, dqw, dkw, M, S, Hq, Hkv, eps,
+  const int grid = std::min((M + 3) / 4, num_sms * 4);  // persistent: four 4-warp CTAs per SM, a warp walks rows
+  launch_pdl(qknorm_rope_bwd_kernel, dim3(grid), dim3(128), 0, stream, dqkv, qkv, qw, kw, cos, sin, dqw, dkw, M, S, Hq, Hkv, eps,
                                                    use_norm);
 }
 
