@@ -10,7 +10,9 @@ import torch.nn.functional as F
 
 from tests.tiny import PARITY, TINY
 
-REF = "/root/reference"
+# the reference package: an explicit checkout (TORCHURE_REFERENCE_DIR) or the offline install under baseline/_ref
+_HERE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.environ.get("TORCHURE_REFERENCE_DIR") or os.path.join(_HERE, "baseline", "_ref")
 
 
 @pytest.mark.parametrize("shape", [(2, 128, 64, 1000, 64), (2, 256, 128, 5000, 512), (1, 100, 32, 300, 33)])
@@ -89,7 +91,7 @@ def test_init_statistics():
     assert m.lm_head.weight is m.token_emb.weight
 
 
-@pytest.mark.skipif(not os.path.isdir(REF), reason="reference tree not mounted")
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "torchure")), reason="reference package not available")
 def test_matches_reference_model_cpu_fp32():
     sys.path.insert(0, REF)
     try:
