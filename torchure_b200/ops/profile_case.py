@@ -3,7 +3,7 @@
     python -m torchure_b200.ops.profile_case <case> [--iters N]
 
 Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, attn_prep, rmsnorm, rmsnorm_bwd, qknorm_rope,
-qknorm_rope_bwd, ce, adamw.  Each case builds inputs
+qknorm_rope_bwd, swiglu, swiglu_bwd, ce, adamw.  Each case builds inputs
 larger than the 126 MB L2 but well under a few GB, launches the kernel `iters` times (default 4) and prints the
 CUDA-event time of the last launch with the achieved FLOP/s or bytes/s, so the same command serves a plain timing run
 and an `ncu -k regex:<kernel> -s 2 -c 1` capture.
@@ -93,6 +93,16 @@ def main(argv=None) -> None:
         delta, lse2 = torch.empty_like(lse), torch.empty_like(lse)
         fn = lambda: ops.ext().attn_bwd_prep(d_o, o, lse, delta, lse2, 4 * B, S, Hq)
         bytes_ = 2 * 4 * M * Hq * hd * 2
+    elif args.case in ("swiglu", "swiglu_bwd"):
+        rows = 2 * M
+        gu = torch.randn(rows, 2 * F_, device=dev).bfloat16()
+        if args.case == "swiglu":
+            fn = lambda: K.swiglu(gu)
+            bytes_ = rows * F_ * 2 * 3          # gate, up read; act written
+        else:
+            dact = torch.randn(rows, F_, device=dev).bfloat16()
+            fn = lambda: K.swiglu_bwd(dact, gu)
+            bytes_ = rows * F_ * 2 * 5          # dact, gate, up read; dgate, dup written
     elif args.case == "ce":
         V, C = 151936, 1024
         logits = torch.randn(C, V, device=dev).bfloat16()
