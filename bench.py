@@ -20,8 +20,12 @@ barrier and a device synchronise on both sides; the reported time is the maximum
 ranks.  The working set of a step (>10 GB of weights and activations) is far larger than
 the 126 MB L2, so no explicit L2 flush is needed.  ``e2e`` repeats the K steps with the
 per-step host-to-device batch copy from pinned memory (always part of a step) and a
-device-to-host read of the step's loss inside the timed region.  SM clocks and throttle
-reasons are sampled with nvidia-smi during the timed region.
+device-to-host read of the step's loss inside the timed region.  Neither arm synchronises
+inside the timed steps of ``value`` and ``e2e`` (``config.sync_per_step`` false: the reference's
+step body is called without its ``record_time`` bracket); ``synced`` repeats the K steps through
+each side's public sync-bracketed ``train_step``.  ``kernel_census`` comes from one extra
+untimed step under ``torch.profiler``.  SM clocks and throttle reasons are sampled with
+nvidia-smi during the timed region.
 """
 
 from __future__ import annotations
@@ -174,6 +178,54 @@ def timed_steps(step_fn, k: int, read_loss: bool):
     return start.elapsed_time(stop), wall_ms, last
 
 
+def shared_config(model: str, cfg: dict, world: int, ce_chunk: int) -> dict:
+    """The `config` object both arms print: identical keys and values for identical work."""
+    mbs = cfg["data"]["micro_batch_size"]
+    return {"model": f"qwen3-{model}", "ffn_dim": cfg["model"]["config"]["ffn_dim"], "global_batch": mbs * world,
+            "micro_batch": mbs, "seq_len": cfg["data"]["seq_len"], "parallelism": f"dp{world}", "ce_chunk": ce_chunk,
+            "grad_clip": 1.0, "ddp_bucket_mb": cfg["ddp"]["bucket_mb"], "sync_per_step": False,
+            "l2": "per-step working set (>10 GB) exceeds the 126 MB L2; no explicit flush"}
+
+
+def kernel_census(step_fn, top: int = 40) -> dict:
+    """One extra, untimed step under torch.profiler: launches and device time per kernel name, with the kernels
+    of this repository, NCCL's and everything else (library / framework kernels) counted apart."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step_fn()
+        torch.cuda.synchronize()
+    rows = {}
+    for ev in prof.events():
+        if ev.device_type.name != "CUDA" or not ev.name or ev.name.startswith(("Memcpy", "Memset")):
+            continue
+        r = rows.setdefault(ev.name, [0, 0.0])
+        r[0] += 1
+        r[1] += ev.device_time if hasattr(ev, "device_time") else ev.cuda_time
+    own_marks = ("tb::", "gemm_bf16_kernel", "gemm_comm_kernel", "attn_", "rmsnorm", "qknorm", "swiglu", "ce_softmax",
+                 "adamw_kernel", "all_reduce_kernel", "all_gather_kernel", "reduce_scatter_kernel", "all_to_all_kernel",
+                 "broadcast_kernel", "barrier_kernel", "embedding_bwd", "cast_", "scale_", "sqnorm", "bucket_pack",
+                 "finalize_kernel")
+
+    def kind(name: str) -> str:
+        if "nccl" in name.lower():
+            return "nccl"
+        return "own" if any(m in name for m in own_marks) else "other"
+
+    out = {"own": {"launches": 0, "us": 0.0}, "nccl": {"launches": 0, "us": 0.0}, "other": {"launches": 0, "us": 0.0}}
+    for name, (n, us) in rows.items():
+        k = kind(name)
+        out[k]["launches"] += n
+        out[k]["us"] += us
+    ranked = sorted(rows.items(), key=lambda kv: -kv[1][1])[:top]
+    out["top"] = [{"name": n[:96], "kind": kind(n), "launches": c, "us": round(us, 1)} for n, (c, us) in ranked]
+    for k in ("own", "nccl", "other"):
+        out[k]["us"] = round(out[k]["us"], 1)
+    return out
+
+
 def max_over_ranks(x: float) -> float:
     import torch
     import torch.distributed as dist
@@ -209,12 +261,21 @@ def run_ours(args) -> None:
     launches = ops.launches()
     host_enqueue_ms = timed_steps.last_enqueue_ms / args.steps
     e2e_ms, _, last_loss = timed_steps(step, args.steps, read_loss=True)
+    # the same steps through the public sync-bracketed `train_step` (how the reference times itself)
+    sync_ms, _, _ = timed_steps(lambda: trainer.train_step()[0], args.steps, read_loss=False)
     clocks = sampler.stop() if rank == 0 else None
-    dev_ms, e2e_ms = max_over_ranks(dev_ms), max_over_ranks(e2e_ms)
+    trainer.check_device_errors()   # an expired device-side wait would make every number above meaningless
+    dev_ms, e2e_ms, sync_ms = max_over_ranks(dev_ms), max_over_ranks(e2e_ms), max_over_ranks(sync_ms)
+    census = None
+    if args.census:
+        eager = trainer.use_cuda_graph
+        trainer.use_cuda_graph = False        # kernels inside a replayed graph carry no names in the profiler
+        step()
+        census = kernel_census(step) if rank == 0 else step()
+        trainer.use_cuda_graph = eager
     tokens = SEQ_LEN * cfg["data"]["global_batch_size"] * args.steps
     if rank == 0:
         value = tokens / (dev_ms / 1e3)
-        mbs = cfg["data"]["micro_batch_size"]
         print(json.dumps({
             "metric": "Qwen3-0.6B bf16 global tokens/sec @seq4096 bs2/GPU" if args.model == "0.6b"
                       else "Qwen3-4B bf16 global tokens/sec @seq4096 bs1/GPU",
@@ -223,12 +284,12 @@ def run_ours(args) -> None:
             "scaling": "weak", "vs_baseline": value / (PUBLISHED_TPS_1GPU_H100 * world) if args.model == "0.6b" else None,
             "vs_baseline_note": "published reference number is 54.5k tok/s on 1x H100 NVL (no B200 number exists)",
             "dtype": "bf16", "data": "synthetic packed uniform tokens, random-init weights",
-            "config": {"model": f"qwen3-{args.model}", "ffn_dim": MODELS[args.model]["ffn_dim"],
-                       "global_batch": mbs * world, "micro_batch": mbs, "seq_len": SEQ_LEN,
-                       "parallelism": f"dp{world}", "ce_chunk": args.ce_chunk, "grad_clip": 1.0,
-                       "l2": "per-step working set (>10 GB) exceeds the 126 MB L2; no explicit flush",
-                       "kernels": "sm100" if ops.available() and not args.torch_path else "torch-oracle",
-                       "launch": "cuda-graph replay" if trainer.use_cuda_graph else "eager"},
+            "config": shared_config(args.model, cfg, world, args.ce_chunk),
+            "kernels": "sm100" if ops.available() and not args.torch_path else "torch-oracle",
+            "launch": "cuda-graph replay" if trainer.use_cuda_graph else "eager",
+            "synced": {"value": tokens / (sync_ms / 1e3), "unit": "tokens/s", "ms_per_step": sync_ms / args.steps,
+                       "note": "device synchronize before and after every step (Trainer.train_step)"},
+            "kernel_census": census,
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": trainer.prefetcher.h2d_bytes * trainer.microbatches_per_step,
                     "d2h_bytes_per_step": 4, "last_loss": last_loss,
@@ -250,6 +311,7 @@ def main() -> None:
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--torch-path", action="store_true", help="ours: run the PyTorch oracle path (A/B)")
     ap.add_argument("--graph", type=int, default=1, help="ours: replay the device step from one CUDA graph (1) or launch eagerly (0)")
+    ap.add_argument("--census", type=int, default=1, help="one extra untimed step under torch.profiler: kernel census")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         sys.exit(relaunch_under_torchrun(args))
@@ -257,7 +319,8 @@ def main() -> None:
         from baseline.run_reference import run_reference
 
         run_reference(args, bench_config(args.model, args.gpus, args.steps * 2 + args.warmup + 8,
-                                         args.micro_batch, args.ce_chunk), timed_steps, max_over_ranks, ClockSampler)
+                                         args.micro_batch, args.ce_chunk), timed_steps, max_over_ranks, ClockSampler,
+                      shared_config, kernel_census)
     else:
         run_ours(args)
 

@@ -1,6 +1,6 @@
 """Bus-bandwidth sweep of the mesh collectives: our NVLink kernels against the NCCL path of the same call.
 
-    torchrun --nproc-per-node N -m torchure_b200.core.bench_collectives [--max-mb 1024] [--stride 1] [--out sweep.json]
+    torchrun --nproc-per-node N -m benchmarks.bench_collectives [--max-mb 1024] [--stride 1] [--out sweep.json]
 
 For every op (all_reduce, all_gather, reduce_scatter, all_to_all), dtype (bf16, fp32) and per-rank message size
 (powers of two from 1 KiB, N(0,1) values) it times both transports with CUDA events after warm-up, takes the

@@ -1,6 +1,6 @@
 """Fused GEMM+collective kernels against their unfused equivalents (one rank per GPU, launched with torchrun).
 
-    torchrun --nproc-per-node 2 --master-addr 127.0.0.1 -m torchure_b200.ops.bench_gemm_comm
+    torchrun --nproc-per-node 2 --master-addr 127.0.0.1 -m benchmarks.bench_gemm_comm
 
 For every shape: ``ag_gemm`` vs NCCL ``all_gather_into_tensor`` followed by the tcgen05 GEMM, and ``gemm_rs`` vs the
 GEMM followed by NCCL ``reduce_scatter_tensor`` of the fp32 product.  Device time with CUDA events, max over ranks,

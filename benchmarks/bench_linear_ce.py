@@ -1,6 +1,6 @@
 """Standalone fused linear + cross-entropy: forward + backward time, this repo against the reference.
 
-    python -m torchure_b200.loss.bench_linear_ce [--impl ours|reference|both] [--chunk 4096] [--iters 10]
+    python -m benchmarks.bench_linear_ce [--impl ours|reference|both] [--chunk 4096] [--iters 10]
 
 Shapes of the headline model's head: hidden states 8192 x 1024 bf16 ~ N(0, 1), weight 151936 x 1024 ~ N(0, 0.02),
 uniform int64 targets; the weight is the fp32 master both trainers hold (each casts it to bf16 itself).  "ours" is
@@ -60,7 +60,7 @@ def main(argv=None) -> None:
         out["ours_ms"] = ms
         out["ours_tflops"] = flops / ms / 1e9
     if args.impl in ("reference", "both"):
-        ref_root = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "baseline", "_ref")
+        ref_root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
         if not os.path.isdir(os.path.join(ref_root, "torchure")):
             out["reference_unavailable"] = "baseline/_ref/torchure is not installed"
         else:

@@ -1,8 +1,8 @@
 """Small, self-contained launches of single kernels for profiling and timing.
 
-    python -m torchure_b200.ops.profile_case <case> [--iters N]
+    python -m benchmarks.profile_case <case> [--iters N]
 
-Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd, attn_prep, rmsnorm, rmsnorm_bwd, qknorm_rope,
+Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd (single pass), attn_bwd_split, attn_prep, rmsnorm, rmsnorm_bwd, qknorm_rope,
 qknorm_rope_bwd, swiglu, swiglu_bwd, ce, adamw.  Each case builds inputs
 larger than the 126 MB L2 but well under a few GB, launches the kernel `iters` times (default 4) and prints the
 CUDA-event time of the last launch with the achieved FLOP/s or bytes/s, so the same command serves a plain timing run
@@ -45,7 +45,7 @@ def main(argv=None) -> None:
         out = torch.empty(2 * F_, D, dtype=torch.float32, device=dev)
         fn = lambda: K.gemm(a, b, a_mn=True, b_mn=True, out=out)
         flops = 2.0 * M * 2 * F_ * D
-    elif args.case in ("attn_fwd", "attn_bwd"):
+    elif args.case in ("attn_fwd", "attn_bwd", "attn_bwd_split"):
         qk = torch.randn(M, (Hq + Hkv) * hd, device=dev).bfloat16()
         qkv = torch.randn(M, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
         o = torch.empty(M, Hq * hd, dtype=torch.bfloat16, device=dev)
@@ -58,8 +58,12 @@ def main(argv=None) -> None:
             ops.ext().attn_fwd(qk, qkv, o, lse, B, S, Hq, Hkv)
             d_o = torch.randn(M, Hq * hd, device=dev).bfloat16()
             dqkv = torch.empty_like(qkv)
-            fn = lambda: ops.ext().attn_bwd(d_o, qk, qkv, o, lse, dqkv, B, S, Hq, Hkv)
-            flops = 7 * unit  # S and dP are recomputed in both gradient kernels: 3 + 4 products
+            if args.case == "attn_bwd":
+                fn = lambda: ops.ext().attn_bwd_fused(d_o, qk, qkv, o, lse, dqkv, B, S, Hq, Hkv)
+                flops = 5 * unit
+            else:
+                fn = lambda: ops.ext().attn_bwd(d_o, qk, qkv, o, lse, dqkv, B, S, Hq, Hkv)
+                flops = 7 * unit  # S and dP are recomputed in both gradient kernels: 3 + 4 products
     elif args.case == "rmsnorm":
         x, y = torch.randn(4 * M, D, device=dev), torch.randn(4 * M, D, device=dev).bfloat16()
         w = torch.ones(D, device=dev)

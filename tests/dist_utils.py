@@ -35,7 +35,7 @@ def _entry(rank, world, port, fn, args, errq, timeout_s):
             dist.destroy_process_group()
 
 
-def run_distributed(fn, world_size: int, *args, timeout_s: int = 60):
+def run_distributed(fn, world_size: int, *args, timeout_s: int = 60, join_s: int | None = None):
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
     port = free_port()
@@ -44,7 +44,7 @@ def run_distributed(fn, world_size: int, *args, timeout_s: int = 60):
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout_s * 3)
+        p.join(join_s or timeout_s * 3)   # process start-up (spawn + import torch) counts against this, not timeout_s
     errors = []
     while not errq.empty():
         errors.append(errq.get())

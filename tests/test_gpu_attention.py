@@ -30,7 +30,8 @@ def _oracle(qk, qkv, B, S, Hq, Hkv):
 
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,scale", [(1, 128, 2, 1, 1.0), (2, 512, 4, 2, 1.0), (1, 1024, 8, 2, 1.0),
-                                              (1, 512, 2, 1, 4.0), (2, 2048, 4, 2, 0.3)])
+                                              (1, 512, 2, 1, 4.0), (2, 2048, 4, 2, 0.3), (1, 4096, 16, 8, 1.0),
+                                              (1, 4096, 32, 8, 1.0)])
 def test_attn_fwd(B, S, Hq, Hkv, scale):
     from torchure_b200 import ops
     from torchure_b200.ops import kernels
@@ -45,10 +46,37 @@ def test_attn_fwd(B, S, Hq, Hkv, scale):
     torch.testing.assert_close(lse, rl, rtol=2e-3, atol=2e-3)
 
 
-@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 2, 1), (1, 256, 2, 1), (2, 512, 4, 2), (1, 1024, 8, 2)])
-def test_attn_bwd(B, S, Hq, Hkv):
+def _grads_oracle(qk, qkv, d_o, B, S, Hq, Hkv):
+    """fp32 reference gradients, one (batch, kv head) group at a time so the S x S scores of long sequences fit."""
+    from torchure_b200.ops import oracle
+
+    hd, r = 128, Hq // Hkv
+    dq = torch.empty(B, S, Hq, hd, device="cuda")
+    dk = torch.empty(B, S, Hkv, hd, device="cuda")
+    dv = torch.empty(B, S, Hkv, hd, device="cuda")
+    qa = qk[:, :Hq * hd].float().view(B, S, Hq, hd)
+    ka = qk[:, Hq * hd:].float().view(B, S, Hkv, hd)
+    va = qkv[:, (Hq + Hkv) * hd:].float().reshape(B, S, Hkv, hd)
+    ga = d_o.float().view(B, S, Hq, hd)
+    for b in range(B):
+        for g in range(Hkv):
+            q = qa[b:b + 1, :, g * r:(g + 1) * r].clone().requires_grad_()
+            k = ka[b:b + 1, :, g:g + 1].clone().requires_grad_()
+            v = va[b:b + 1, :, g:g + 1].clone().requires_grad_()
+            o, _ = oracle.attention(q, k, v)
+            o.backward(ga[b:b + 1, :, g * r:(g + 1) * r])
+            dq[b, :, g * r:(g + 1) * r], dk[b, :, g], dv[b, :, g] = q.grad[0], k.grad[0, :, 0], v.grad[0, :, 0]
+    return dq, dk, dv
+
+
+@pytest.mark.parametrize("entry", ["attn_bwd_fused", "attn_bwd"])
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 2, 1), (1, 256, 2, 1), (2, 512, 4, 2), (1, 1024, 8, 2), (1, 384, 2, 1),
+                                        (1, 4096, 16, 8), (1, 4096, 32, 8)])
+def test_attn_bwd(B, S, Hq, Hkv, entry):
+    """Both backward implementations (single pass, two kernels) against fp32 autograd of the dense formula, up to
+    the benchmark shapes (16/8 and 32/8 heads at 4096 tokens)."""
     from torchure_b200 import ops
-    from torchure_b200.ops import kernels, oracle
+    from torchure_b200.ops import kernels
 
     hd = 128
     qk, qkv = _inputs(B, S, Hq, Hkv, seed=1)
@@ -57,16 +85,12 @@ def test_attn_bwd(B, S, Hq, Hkv):
     ops.ext().attn_fwd(qk, qkv, o, lse, B, S, Hq, Hkv)
     d_o = torch.randn(B * S, Hq * hd, device="cuda").bfloat16()
     dqkv = torch.zeros(B * S, (Hq + 2 * Hkv) * hd, dtype=torch.bfloat16, device="cuda")
-    ops.ext().attn_bwd(d_o, qk, qkv, o, lse, dqkv, B, S, Hq, Hkv)
+    getattr(ops.ext(), entry)(d_o, qk, qkv, o, lse, dqkv, B, S, Hq, Hkv)
     kernels.check_error()
-    q = qk[:, :Hq * hd].float().view(B, S, Hq, hd).requires_grad_()
-    k = qk[:, Hq * hd:].float().view(B, S, Hkv, hd).requires_grad_()
-    v = qkv[:, (Hq + Hkv) * hd:].float().reshape(B, S, Hkv, hd).requires_grad_()
-    ro, _ = oracle.attention(q, k, v)
-    ro.backward(d_o.float().view(B, S, Hq, hd))
+    rq, rk, rv = _grads_oracle(qk, qkv, d_o, B, S, Hq, Hkv)
     dq = dqkv[:, :Hq * hd].view(B, S, Hq, hd)
     dk = dqkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, S, Hkv, hd)
     dv = dqkv[:, (Hq + Hkv) * hd:].view(B, S, Hkv, hd)
-    assert relerr(dv, v.grad) < 1.5e-2, ("dv", relerr(dv, v.grad))
-    assert relerr(dq, q.grad) < 1.5e-2, ("dq", relerr(dq, q.grad))
-    assert relerr(dk, k.grad) < 1.5e-2, ("dk", relerr(dk, k.grad))
+    assert relerr(dv, rv) < 1.5e-2, ("dv", relerr(dv, rv))
+    assert relerr(dq, rq) < 1.5e-2, ("dq", relerr(dq, rq))
+    assert relerr(dk, rk) < 1.5e-2, ("dk", relerr(dk, rk))

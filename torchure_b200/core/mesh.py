@@ -18,6 +18,7 @@ from __future__ import annotations
 import itertools
 import math
 
+import torch
 import torch.distributed as dist
 
 
@@ -60,10 +61,23 @@ class Mesh:
                 for mv in itertools.product(*moving_ranges)
             ]
 
+    @staticmethod
+    def _world_timeout():
+        """The timeout the world group was initialised with; axis groups inherit it, so that a rank that stops
+        joining collectives ends its peers' next collective after that bound instead of the library default
+        (tens of minutes).  None when the backend does not expose it."""
+        try:
+            pg = dist.distributed_c10d._get_default_group()
+            dev = torch.device("cuda" if dist.get_backend(pg) == "nccl" else "cpu")
+            return pg._get_backend(dev).options._timeout
+        except Exception:
+            return None
+
     def _make_groups(self, name: str, axes: tuple[str, ...]) -> None:
         # new_group is collective: all ranks create all groups, in the same order
+        timeout = self._world_timeout()
         for members in self._lines(axes):
-            group = dist.new_group(members)
+            group = dist.new_group(members, timeout=timeout) if timeout is not None else dist.new_group(members)
             if self.rank in members:
                 self.groups[name] = group
                 self._members[name] = members

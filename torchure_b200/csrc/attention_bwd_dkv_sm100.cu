@@ -310,12 +310,7 @@ int attn_bwd_dkv(const void* qk, const void* qkv, const void* d_o, void* dqkv, c
   if (r) return r - 200;
   r = make_tmap_2d(&tdq, dqkv, 2, M, wqkv, wqkv, 32, 64);
   if (r) return r - 300;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-      return -20;
-    configured = true;
-  }
+  if (!ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_dkv_kernel), SMEM_BYTES)) return -20;
   const int grid = (S / 128) * B * Hkv;
   const float scale = 1.f / sqrtf(static_cast<float>(HD));
   launch_pdl(attn_bwd_dkv_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tv, tdo, tdq, delta, lse2, B, S, Hq, Hkv, scale,

@@ -299,11 +299,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
 
 }  // namespace
 
-void attn_bwd_prep(const void* d_o, const void* o, const float* lse, float* delta, float* lse2, int B, int S, int Hq,
-                   cudaStream_t stream) {
+int attn_bwd_prep(const void* d_o, const void* o, const float* lse, float* delta, float* lse2, int B, int S, int Hq,
+                  cudaStream_t stream) {
   const int64_t warps = static_cast<int64_t>(B) * S;  // one warp per token row
-  launch_pdl(attn_bwd_prep_kernel, dim3(static_cast<int>((warps + 7) / 8)), dim3(256), 0, stream, 
-      reinterpret_cast<const __nv_bfloat16*>(d_o), reinterpret_cast<const __nv_bfloat16*>(o), lse, delta, lse2, B, S, Hq);
+  return launch_pdl(attn_bwd_prep_kernel, dim3(static_cast<int>((warps + 7) / 8)), dim3(256), 0, stream, 
+      reinterpret_cast<const __nv_bfloat16*>(d_o), reinterpret_cast<const __nv_bfloat16*>(o), lse, delta, lse2, B, S, Hq) == cudaSuccess ? 0 : -21;
 }
 
 int attn_bwd_dq(const void* qk, const void* qkv, const void* d_o, void* dqkv, const float* delta, const float* lse2,
@@ -320,12 +320,7 @@ int attn_bwd_dq(const void* qk, const void* qkv, const void* d_o, void* dqkv, co
   if (r) return r - 200;
   r = make_tmap_2d(&tdq, dqkv, 2, M, wqkv, wqkv, 32, 64);
   if (r) return r - 300;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-      return -20;
-    configured = true;
-  }
+  if (!ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_dq_kernel), SMEM_BYTES)) return -20;
   const int grid = (S / 128) * B * Hq;
   const float scale = 1.f / sqrtf(static_cast<float>(HD));
   launch_pdl(attn_bwd_dq_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tv, tdo, tdq, delta, lse2, B, S, Hq, Hkv, scale,

@@ -1,0 +1,450 @@
+// Flash-attention backward in ONE pass: dQ, dK and dV from five tile products per (query block, key block) pair.
+//
+// One CTA owns 128 keys of one KV head and visits every (query head of the GQA group, visible query block) pair, so
+// dK and dV are reduced over query heads and query blocks in TMEM.  Scores are computed TRANSPOSED (keys on TMEM
+// lanes, queries on columns); probabilities and score gradients then already have the layout the tensor core wants
+// for the A operand of the dV and dK products and never leave TMEM.  The score gradient is additionally written to
+// shared memory as the B operand of the third product, dQ^T = K^T dS^T, whose fp32 tile is added to a global fp32
+// dQ accumulator (the only quantity that crosses CTAs); a light kernel converts that accumulator to bf16.
+//
+// A query block is processed as two halves of 64 queries that ping-pong between two TMEM buffers of 128 columns:
+//     S^T_h  = K Q_h^T          (SS, 128x64x128)   columns [0, 64)
+//     dP^T_h = V dO_h^T         (SS, 128x64x128)   columns [64, 128)
+//     P^T_h  = exp2(S^T_h c - lse2[q]);  dS^T_h = P^T_h o (dP^T_h - delta[q]) / sqrt(d)
+//                               bf16 P^T_h / dS^T_h -> 8 + 8 columns inside each warp's own 16 S^T columns; dS^T_h also
+//                               goes to shared memory
+//     dV    += P^T_h  dO_h      (TS, 128x128x64)   columns 256..383
+//     dK    += dS^T_h Q_h       (TS, 128x128x64)   columns 384..511
+//     dQ^T_h = K^T dS^T_h       (SS, 128x64x128, both operands MN-major)   columns [64, 128) of the half's buffer
+// 576 threads: TMA warp, MMA warp, 16 compute warps (four per TMEM lane quarter, 16 query columns each).  While the
+// compute warps work on one half the tensor core runs the other half's products; after each half they drain the
+// previous half's dQ^T tile with fp32 reductions to global memory.
+//
+// `causal`: query block qb sees key blocks <= qb (Sq == Skv); otherwise every query sees every key (the off-diagonal
+// steps of ring attention).  Because partial dQ tiles are added in whatever order CTAs finish, dQ is not bitwise
+// reproducible from run to run; the two-kernel backward (attention_bwd_dq/dkv) is.
+#include "attn_api.h"
+#include "common.cuh"
+
+namespace tb {
+
+int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows, uint32_t box_cols);
+
+namespace {
+
+constexpr int HD = 128;
+constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KB
+constexpr int HALF_BYTES = 16384;
+constexpr int Q_STAGES = 2;
+constexpr int STAT_BYTES = 1024;          // lse2[128] | delta[128]
+constexpr int STAGE_BYTES = 2 * TILE_BYTES + STAT_BYTES;
+constexpr int DS_BYTES = 128 * 64 * 2;    // dS^T of one half: 128 key rows x 64 queries, bf16
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_USED = 2 * TILE_BYTES + Q_STAGES * STAGE_BYTES + 2 * DS_BYTES + BAR_BYTES;
+constexpr int SMEM_BYTES = 232448;        // the whole 227 KB: SMEM_USED plus alignment slack
+static_assert(SMEM_USED <= SMEM_BYTES, "shared-memory plan exceeds the per-CTA limit");
+constexpr int COMPUTE_WARPS = 16;
+constexpr int NUM_THREADS = (2 + COMPUTE_WARPS) * 32;
+
+struct Bars {
+  uint64_t kv_full;
+  uint64_t q_full[Q_STAGES];
+  uint64_t q_empty[Q_STAGES];
+  uint64_t st_full[2];      // S^T_h and dP^T_h are in TMEM
+  uint64_t pds_ready[2];    // P^T_h, dS^T_h written (one arrival per compute warp)
+  uint64_t dq_full[2];      // dV/dK/dQ^T products of half h have completed
+  uint64_t dq_drained[2];   // dQ^T_h has been read out of TMEM (one arrival per compute warp)
+  uint64_t acc_done;
+  uint32_t tmem_slot;
+};
+static_assert(sizeof(Bars) <= BAR_BYTES, "barrier block");
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+struct FusedArgs {
+  float* dq_acc;
+  int64_t ld_dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int64_t ld_dkv;
+  const float* delta;
+  const float* lse2;
+  int B, Sq, Skv, Hq, Hkv;
+  int q_col0, k_col0, v_col0;
+  int causal;
+  int dbg;   // diagnostics: bit 0 skips the dQ reductions, bit 1 skips the dQ product as well
+  float scale, scale_log2;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                      const __grid_constant__ FusedArgs a, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  {
+    uint32_t dyn;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+    if (static_cast<uint32_t>(smem - smem_raw) + SMEM_USED > dyn) {   // uniform over the CTA: nothing is set up yet
+      if (threadIdx.x == 0) atomicCAS(err, 0, kErrAttnWait);
+      return;
+    }
+  }
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sStage = smem + 2 * TILE_BYTES;                 // [stage][Q 32 KB | dO 32 KB | stats 1 KB]
+  uint8_t* sDS = sStage + Q_STAGES * STAGE_BYTES;          // [half][128 key rows x 128 B]
+  Bars* bars = reinterpret_cast<Bars*>(sDS + 2 * DS_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = a.Sq / 128;
+  const int ratio = a.Hq / a.Hkv;
+  const int groups = a.B * a.Hkv;
+  const int kblk = static_cast<int>(blockIdx.x) / groups;   // causal: block 0 sees the most query blocks, it goes first
+  const int g = static_cast<int>(blockIdx.x) % groups;
+  const int kvh = g % a.Hkv, b = g / a.Hkv;
+  const int krow0 = b * a.Skv + kblk * 128;
+  const int qb0 = a.causal ? kblk : 0;       // first visible query block
+  const int n_qb = nqb - qb0;
+  const int n_iter = n_qb * ratio;           // iteration = (query head of the group, query block)
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+    mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < Q_STAGES; ++s) {
+      mbar_init(&bars->q_full[s], 1);
+      mbar_init(&bars->q_empty[s], 1);
+    }
+    for (int hh = 0; hh < 2; ++hh) {
+      mbar_init(&bars->st_full[hh], 1);
+      mbar_init(&bars->pds_ready[hh], COMPUTE_WARPS);
+      mbar_init(&bars->dq_full[hh], 1);
+      mbar_init(&bars->dq_drained[hh], COMPUTE_WARPS);
+    }
+    mbar_init(&bars->acc_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_slot, 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (elect_one()) {
+      const int kcol = a.k_col0 + kvh * HD, vcol = a.v_col0 + kvh * HD;
+      mbar_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
+      tma_load_2d(sK, &tmK, &bars->kv_full, kcol, krow0);
+      tma_load_2d(sK + HALF_BYTES, &tmK, &bars->kv_full, kcol + 64, krow0);
+      tma_load_2d(sV, &tmV, &bars->kv_full, vcol, krow0);
+      tma_load_2d(sV + HALF_BYTES, &tmV, &bars->kv_full, vcol + 64, krow0);
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % Q_STAGES;
+        const uint32_t ph = (it / Q_STAGES) & 1;
+        if (!mbar_wait(&bars->q_empty[s], ph ^ 1, err, kErrAttnWait)) break;
+        const int h = kvh * ratio + it / n_qb;
+        const int qb = qb0 + it % n_qb;
+        const int qrow = b * a.Sq + qb * 128;
+        uint8_t* sQ = sStage + s * STAGE_BYTES;
+        uint8_t* sDO = sQ + TILE_BYTES;
+        float* sStat = reinterpret_cast<float*>(sDO + TILE_BYTES);
+        mbar_expect_tx(&bars->q_full[s], 2 * TILE_BYTES + STAT_BYTES);
+        tma_load_2d(sQ, &tmQ, &bars->q_full[s], a.q_col0 + h * HD, qrow);
+        tma_load_2d(sQ + HALF_BYTES, &tmQ, &bars->q_full[s], a.q_col0 + h * HD + 64, qrow);
+        tma_load_2d(sDO, &tmDO, &bars->q_full[s], h * HD, qrow);
+        tma_load_2d(sDO + HALF_BYTES, &tmDO, &bars->q_full[s], h * HD + 64, qrow);
+        const int64_t stat = (static_cast<int64_t>(b) * a.Hq + h) * a.Sq + qb * 128;
+        bulk_load_1d(sStat, a.lse2 + stat, 512, &bars->q_full[s]);
+        bulk_load_1d(sStat + 128, a.delta + stat, 512, &bars->q_full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);   // S^T / dP^T halves: N = 64 queries
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, false, true);  // A in TMEM, B MN-major, N = 128 (hd)
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, true, true);     // K^T (MN-major) x dS^T (MN-major)
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      auto issue_s = [&](int hh, const uint8_t* stage) {
+        const uint32_t qa = smem_u32(stage) + hh * 8192;                 // query rows 64h.. of the Q tile
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t o = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_f16_ss(tmem_base + hh * 128, make_desc_sw128(ka + o, 16, 1024), make_desc_sw128(qa + o, 16, 1024),
+                      idesc_st, ks != 0 ? 1u : 0u);
+        }
+      };
+      auto issue_dp = [&](int hh, const uint8_t* stage) {
+        const uint32_t da = smem_u32(stage + TILE_BYTES) + hh * 8192;    // same rows of dO
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t o = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_f16_ss(tmem_base + hh * 128 + 64, make_desc_sw128(va + o, 16, 1024), make_desc_sw128(da + o, 16, 1024),
+                      idesc_st, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->st_full[hh]);
+      };
+      // dV += P^T_h dO_h ; dK += dS^T_h Q_h ; dQ^T_h = K^T dS^T_h
+      auto issue_acc = [&](int hh, const uint8_t* stage, bool first) {
+        const uint32_t qa = smem_u32(stage) + hh * 8192;
+        const uint32_t da = smem_u32(stage + TILE_BYTES) + hh * 8192;
+        const uint32_t dsa = smem_u32(sDS + hh * DS_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ts(tmem_base + 256, tmem_base + hh * 128 + ks * 16, make_desc_sw128(da + ks * 2048, HALF_BYTES, 1024),
+                      idesc_acc, (first && ks == 0) ? 0u : 1u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ts(tmem_base + 384, tmem_base + hh * 128 + ks * 16 + 8,
+                      make_desc_sw128(qa + ks * 2048, HALF_BYTES, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
+        if (!(a.dbg & 2))
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 16 rows of K (both 64-wide d halves) and of dS^T
+          umma_f16_ss(tmem_base + hh * 128 + 64, make_desc_sw128(ka + ks * 2048, HALF_BYTES, 1024),
+                      make_desc_sw128(dsa + ks * 2048, HALF_BYTES, 1024), idesc_dq, ks != 0 ? 1u : 0u);
+        umma_commit(&bars->dq_full[hh]);
+      };
+      bool ok = mbar_wait(&bars->kv_full, 0, err, kErrAttnWait) && mbar_wait(&bars->q_full[0], 0, err, kErrAttnWait);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, sStage);
+        issue_dp(0, sStage);
+        issue_s(1, sStage);
+        issue_dp(1, sStage);
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int s = it % Q_STAGES, sn = (it + 1) % Q_STAGES;
+        const uint32_t phn = ((it + 1) / Q_STAGES) & 1;
+        const bool more = it + 1 < n_iter;
+        const uint8_t* stage = sStage + s * STAGE_BYTES;
+        const uint8_t* next = sStage + sn * STAGE_BYTES;
+        for (int hh = 0; hh < 2 && ok; ++hh) {
+          if (!mbar_wait(&bars->pds_ready[hh], it & 1, err, kErrAttnWait)) { ok = false; break; }
+          tc_fence_after();
+          issue_acc(hh, stage, it == 0 && hh == 0);
+          if (hh == 1) umma_commit(&bars->q_empty[s]);
+          if (more) {
+            if (hh == 0 && !mbar_wait(&bars->q_full[sn], phn, err, kErrAttnWait)) { ok = false; break; }
+            tc_fence_after();
+            issue_s(hh, next);       // overwrites P^T_h / dS^T_h: ordered behind the products that read them
+            // the dP^T columns still hold dQ^T_h until the compute warps have read it
+            if (!mbar_wait(&bars->dq_drained[hh], it & 1, err, kErrAttnWait)) { ok = false; break; }
+            tc_fence_after();
+            issue_dp(hh, next);
+          }
+        }
+      }
+      if (ok) umma_commit(&bars->acc_done);
+    }
+  } else {
+    // ------------------------------------------------ compute warps
+    const int quarter = warp & 3;             // TMEM lane quarter this warp may touch
+    const int cg = (warp - 2) >> 2;           // which 16 of a half's 64 query columns
+    const int row = quarter * 32 + lane;      // key inside the block (S^T, dP^T) / head-dim index (dQ^T)
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ok = true;
+    // dQ^T_h of half-step (pit, ph): 16 query columns of this warp, one head-dim index per lane -> fp32 reductions
+    auto drain = [&](int pit, int ph) -> bool {
+      if (!mbar_wait(&bars->dq_full[ph], pit & 1, err, kErrAttnWait)) return false;
+      tc_fence_after();
+      uint32_t v[16];
+      tmem_ld_32x32b_x16(tmem_base + lane_sel + ph * 128 + 64 + cg * 16, v);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->dq_drained[ph]);
+      const int h = kvh * ratio + pit / n_qb;
+      const int qb = qb0 + pit % n_qb;
+      float* dst = a.dq_acc + (static_cast<int64_t>(b) * a.Sq + qb * 128 + ph * 64 + cg * 16) * a.ld_dq + h * HD + row;
+      if (!(a.dbg & 1)) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) red_add_f32(dst + j * a.ld_dq, __uint_as_float(v[j]));
+      }
+      return true;
+    };
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int s = it % Q_STAGES;
+      const bool diag = a.causal && (it % n_qb) == 0;     // query block == key block
+      const float* sStat = reinterpret_cast<const float*>(sStage + s * STAGE_BYTES + 2 * TILE_BYTES);
+      for (int hh = 0; hh < 2; ++hh) {
+        if (!mbar_wait(&bars->st_full[hh], it & 1, err, kErrAttnWait)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tH = tmem_base + lane_sel + hh * 128;
+        uint32_t sv[16], dv[16];
+        tmem_ld_32x32b_x16(tH + cg * 16, sv);
+        tmem_ld_32x32b_x16(tH + 64 + cg * 16, dv);
+        tmem_ld_wait();
+        uint32_t pp[8], pd[8];
+        const int q0 = hh * 64 + cg * 16;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 l2 = *reinterpret_cast<const float2*>(sStat + q0 + 2 * i);
+          const float2 dl = *reinterpret_cast<const float2*>(sStat + 128 + q0 + 2 * i);
+          float p0 = ex2(fmaf(__uint_as_float(sv[2 * i]), a.scale_log2, -l2.x));
+          float p1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), a.scale_log2, -l2.y));
+          if (diag) {
+            if (q0 + 2 * i < row) p0 = 0.f;       // query before key: masked
+            if (q0 + 2 * i + 1 < row) p1 = 0.f;
+          }
+          pp[i] = pack_bf16x2(p0, p1);
+          pd[i] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * i]) - dl.x) * a.scale,
+                              p1 * (__uint_as_float(dv[2 * i + 1]) - dl.y) * a.scale);
+        }
+        // both land inside the 16 S^T columns this warp itself consumed, so the warps need no barrier among them
+        tmem_st_32x32b_x8(tH + cg * 16, pp);
+        tmem_st_32x32b_x8(tH + cg * 16 + 8, pd);
+        {   // dS^T row of this key, queries q0..q0+15: two 16-byte chunks of the 128-byte swizzled row
+          uint8_t* rowp = sDS + hh * DS_BYTES + row * 128;
+          *reinterpret_cast<uint4*>(rowp + (((2 * cg) ^ (row & 7)) << 4)) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
+          *reinterpret_cast<uint4*>(rowp + (((2 * cg + 1) ^ (row & 7)) << 4)) = make_uint4(pd[4], pd[5], pd[6], pd[7]);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->pds_ready[hh]);
+        // the other half's products of the previous half-step ran meanwhile: take its dQ^T out
+        if (hh == 1) {
+          if (!drain(it, 0)) { ok = false; break; }
+        } else if (it > 0) {
+          if (!drain(it - 1, 1)) { ok = false; break; }
+        }
+      }
+    }
+    if (ok && n_iter > 0) ok = drain(n_iter - 1, 1);
+    if (ok && mbar_wait(&bars->acc_done, 0, err, kErrAttnWait)) {
+      tc_fence_after();
+      // dV and dK: this warp's 32 of the 128 head-dim columns, one key row per lane, written straight to global memory
+      const int kcol = kvh * HD + cg * 32;
+      for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_sel + 256 + which * 128 + cg * 32, v);
+        tmem_ld_wait();
+        __nv_bfloat16* dst = (which == 0 ? a.dv : a.dk) + static_cast<int64_t>(krow0 + row) * a.ld_dkv + kcol;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint4 pk;
+          pk.x = pack_bf16x2(__uint_as_float(v[8 * jj + 0]), __uint_as_float(v[8 * jj + 1]));
+          pk.y = pack_bf16x2(__uint_as_float(v[8 * jj + 2]), __uint_as_float(v[8 * jj + 3]));
+          pk.z = pack_bf16x2(__uint_as_float(v[8 * jj + 4]), __uint_as_float(v[8 * jj + 5]));
+          pk.w = pack_bf16x2(__uint_as_float(v[8 * jj + 6]), __uint_as_float(v[8 * jj + 7]));
+          *reinterpret_cast<uint4*>(dst + 8 * jj) = pk;
+        }
+      }
+    }
+  }
+
+  if (*reinterpret_cast<volatile int*>(err) != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// dst[r, c] (bf16, row stride ld_dst) = src[r, c] (fp32, row stride ld_src), c < cols (a multiple of 8)
+__global__ void __launch_bounds__(256)
+cast_rows_kernel(const float* __restrict__ src, int64_t ld_src, __nv_bfloat16* __restrict__ dst, int64_t ld_dst,
+                 int64_t rows, int cols) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int per_row = cols / 8;
+  const int64_t total = rows * per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / per_row;
+    const int c = static_cast<int>(i % per_row) * 8;
+    const float4 x = *reinterpret_cast<const float4*>(src + r * ld_src + c);
+    const float4 y = *reinterpret_cast<const float4*>(src + r * ld_src + c + 4);
+    uint4 pk;
+    pk.x = pack_bf16x2(x.x, x.y);
+    pk.y = pack_bf16x2(x.z, x.w);
+    pk.z = pack_bf16x2(y.x, y.y);
+    pk.w = pack_bf16x2(y.z, y.w);
+    *reinterpret_cast<uint4*>(dst + r * ld_dst + c) = pk;
+  }
+}
+
+}  // namespace
+
+int attn_bwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, const void* d_o, float* dq_acc,
+                   int64_t ld_dq, void* dk, void* dv, int64_t ld_dkv, const float* delta, const float* lse2, int B,
+                   int Sq, int Skv, int Hq, int Hkv, bool causal, int* err, cudaStream_t stream) {
+  if (Sq % 128 != 0 || Skv % 128 != 0 || Hq % Hkv != 0 || B <= 0 || Sq <= 0 || Skv <= 0) return -1;
+  if (causal && Sq != Skv) return -2;
+  if (ld_dq % 4 != 0 || ld_dkv % 8 != 0 || (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15))
+    return -3;
+  const uint64_t Mq = static_cast<uint64_t>(B) * Sq, Mk = static_cast<uint64_t>(B) * Skv;
+  CUtensorMap tq, tk, tv, tdo;
+  int r = make_tmap_2d(&tq, q.ptr, 2, Mq, q.ld, q.ld, 128, 64);
+  if (r) return r;
+  r = make_tmap_2d(&tk, k.ptr, 2, Mk, k.ld, k.ld, 128, 64);
+  if (r) return r - 100;
+  r = make_tmap_2d(&tv, v.ptr, 2, Mk, v.ld, v.ld, 128, 64);
+  if (r) return r - 200;
+  r = make_tmap_2d(&tdo, d_o, 2, Mq, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(Hq) * HD, 128, 64);
+  if (r) return r - 300;
+  if (!ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_fused_kernel), SMEM_BYTES)) return -20;
+  FusedArgs a{};
+  a.dq_acc = dq_acc;
+  a.ld_dq = ld_dq;
+  a.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  a.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.ld_dkv = ld_dkv;
+  a.delta = delta;
+  a.lse2 = lse2;
+  a.B = B; a.Sq = Sq; a.Skv = Skv; a.Hq = Hq; a.Hkv = Hkv;
+  a.q_col0 = static_cast<int>(q.col0);
+  a.k_col0 = static_cast<int>(k.col0);
+  a.v_col0 = static_cast<int>(v.col0);
+  a.causal = causal ? 1 : 0;
+  {
+    const char* e = std::getenv("TORCHURE_B200_ATTN_DBG");
+    a.dbg = e ? atoi(e) : 0;
+  }
+  a.scale = 1.f / sqrtf(static_cast<float>(HD));
+  a.scale_log2 = a.scale * 1.4426950408889634f;
+  const int grid = (Skv / 128) * B * Hkv;
+  if (launch_pdl(attn_bwd_fused_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tk, tv, tdo, a, err) !=
+      cudaSuccess)
+    return -21;
+  return 0;
+}
+
+int cast_rows_f32_to_bf16(const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int cols,
+                          cudaStream_t stream) {
+  if (cols % 8 != 0 || ld_src % 4 != 0 || ld_dst % 8 != 0) return -1;
+  const int64_t total = rows * (cols / 8);
+  const int grid = static_cast<int>(total / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  return launch_pdl(cast_rows_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, stream, src, ld_src,
+                    reinterpret_cast<__nv_bfloat16*>(dst), ld_dst, rows, cols) == cudaSuccess
+             ? 0
+             : -21;
+}
+
+}  // namespace tb

@@ -311,11 +311,7 @@ int attn_fwd(const void* qk, const void* qkv, void* o, float* lse, int B, int S,
   if (r) return r - 100;
   r = make_tmap_2d(&to, o, 2, M, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(Hq) * HD, 32, 64);
   if (r) return r - 200;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
-    configured = true;
-  }
+  if (!ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel), SMEM_BYTES)) return -20;
   const int grid = (S / 128) * B * Hkv * ((Hq / Hkv) / 2);
   const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
   launch_pdl(attn_fwd_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tv, to, lse, B, S, Hq, Hkv, scale_log2, err);

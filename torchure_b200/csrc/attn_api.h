@@ -12,11 +12,33 @@ int attn_fwd(const void* qk, const void* qkv, void* o, float* lse, int B, int S,
 
 // Backward.  `delta` and `lse2` are scratch rows of B*Hq*S floats each, filled by attn_bwd_prep and read by the two
 // gradient kernels.  dqkv [B*S, (Hq+2Hkv)*128] bf16 receives dq | dk | dv (gradients w.r.t. the rotated q and k).
-void attn_bwd_prep(const void* d_o, const void* o, const float* lse, float* delta, float* lse2, int B, int S, int Hq,
-                   cudaStream_t stream);
+int attn_bwd_prep(const void* d_o, const void* o, const float* lse, float* delta, float* lse2, int B, int S, int Hq,
+                  cudaStream_t stream);
 int attn_bwd_dq(const void* qk, const void* qkv, const void* d_o, void* dqkv, const float* delta, const float* lse2,
                 int B, int S, int Hq, int Hkv, int* err, cudaStream_t stream);
 int attn_bwd_dkv(const void* qk, const void* qkv, const void* d_o, void* dqkv, const float* delta, const float* lse2,
                  int B, int S, int Hq, int Hkv, int* err, cudaStream_t stream);
+
+// One operand of the fused backward: bf16 matrix [rows, ld] (row stride ld elements, 16-byte aligned base and rows);
+// head h occupies columns [col0 + 128 h, col0 + 128 h + 128).
+struct AttnOperand {
+  const void* ptr;
+  int64_t ld;
+  int64_t col0;
+};
+
+// Single-pass backward (attention_bwd_fused_sm100.cu): five tile products per block pair instead of seven.
+//   q [B*Sq rows], k / v [B*Skv rows], d_o [B*Sq, Hq*128] bf16; delta / lse2 [B, Hq, Sq] from attn_bwd_prep
+//   dq_acc  fp32 [B*Sq, ld_dq], head h at column 128 h: every CTA ADDS its partial dQ tiles, so it must hold zeros
+//           (or a running sum to extend) on entry
+//   dk, dv  bf16 destinations of the first row of KV head 0 (row stride ld_dkv elements, 16-byte aligned)
+//   causal  query block qb sees key blocks <= qb (needs Sq == Skv); false = every query sees every key
+// Needs Sq % 128 == 0, Skv % 128 == 0 and Hq % Hkv == 0.
+int attn_bwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, const void* d_o, float* dq_acc,
+                   int64_t ld_dq, void* dk, void* dv, int64_t ld_dkv, const float* delta, const float* lse2, int B,
+                   int Sq, int Skv, int Hq, int Hkv, bool causal, int* err, cudaStream_t stream);
+// dst[r, c] (bf16, row stride ld_dst) = src[r, c] (fp32, row stride ld_src) for c < cols (a multiple of 8)
+int cast_rows_f32_to_bf16(const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int cols,
+                          cudaStream_t stream);
 
 }  // namespace tb

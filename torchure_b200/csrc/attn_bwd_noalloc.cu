@@ -36,15 +36,17 @@ float* scratch_for_current_device() {
 extern "C" int tb_attn_bwd_noalloc(const void* d_o, const void* qk, const void* qkv, const void* o, const float* lse,
                                    void* dqkv, int B, int S, int Hq, int Hkv, int* status, cudaStream_t stream) {
   if (!d_o || !qk || !qkv || !o || !lse || !dqkv || !status) return -1;
-  if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || S % 128 != 0 || Hq % Hkv != 0) return -2;
+  // the same shapes the forward pass accepts: whole 128-token blocks and an even number of query heads per KV head
+  if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || S % 128 != 0 || Hq % Hkv != 0 || (Hq / Hkv) % 2 != 0) return -2;
   const long long rows = static_cast<long long>(B) * Hq * S;
   if (rows > TB_ATTN_BWD_NOALLOC_MAX_ROWS) return -30;  // larger problems need the allocating entry point
   float* scratch = scratch_for_current_device();
   if (scratch == nullptr) return -31;
   float* delta = scratch;
   float* lse2 = scratch + TB_ATTN_BWD_NOALLOC_MAX_ROWS;
-  tb::attn_bwd_prep(d_o, o, lse, delta, lse2, B, S, Hq, stream);
-  int rc = tb::attn_bwd_dq(qk, qkv, d_o, dqkv, delta, lse2, B, S, Hq, Hkv, status, stream);
+  int rc = tb::attn_bwd_prep(d_o, o, lse, delta, lse2, B, S, Hq, stream);
+  if (rc != 0) return rc;
+  rc = tb::attn_bwd_dq(qk, qkv, d_o, dqkv, delta, lse2, B, S, Hq, Hkv, status, stream);
   if (rc != 0) return rc;
   return tb::attn_bwd_dkv(qk, qkv, d_o, dqkv, delta, lse2, B, S, Hq, Hkv, status, stream);
 }

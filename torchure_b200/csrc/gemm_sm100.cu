@@ -479,11 +479,7 @@ template <bool A_MN, bool B_MN, int OUT>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc, int M, int N, int K, int splits,
                   int* err, int grid, cudaStream_t stream) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
-    configured = true;
-  }
+  if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kern), SMEM_BYTES)) return -20;
   return launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, ta, tb_, tc, M, N, K, splits, err) ==
                  cudaSuccess
              ? 0
@@ -562,11 +558,7 @@ int ag_gemm_bf16(const CommCtx& c, uint64_t a_off, uint64_t g_off, uint32_t epoc
   rc = make_tmap_2d(&tc, C, 2, M, N, ldc, 32, 64);
   if (rc) return rc - 200;
   auto kern = b_mn ? gemm_comm_kernel<1, true> : gemm_comm_kernel<1, false>;
-  static bool configured[2] = {false, false};
-  if (!configured[b_mn]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
-    configured[b_mn] = true;
-  }
+  if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kern), SMEM_BYTES)) return -20;
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int cap = num_sms < kCommMaxBlocks ? num_sms : kCommMaxBlocks;  // the handshake has one flag row per CTA
   const int grid = tiles < cap ? tiles : cap;
@@ -593,11 +585,7 @@ int gemm_rs_bf16(const CommCtx& c, const void* A, const void* B, uint64_t c_off,
   rc = b_mn ? make_tmap_2d(&tb_, B, 2, K, N, ldb, 64, 64) : make_tmap_2d(&tb_, B, 2, N, K, ldb, BN, 64);
   if (rc) return rc - 200;
   auto kern = b_mn ? gemm_comm_kernel<2, true> : gemm_comm_kernel<2, false>;
-  static bool configured[2] = {false, false};
-  if (!configured[b_mn]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
-    configured[b_mn] = true;
-  }
+  if (!ensure_dynamic_smem(reinterpret_cast<const void*>(kern), SMEM_BYTES)) return -20;
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int cap = num_sms < kCommMaxBlocks ? num_sms : kCommMaxBlocks;
   const int grid = tiles < cap ? tiles : cap;

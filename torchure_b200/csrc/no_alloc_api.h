@@ -20,13 +20,15 @@ extern "C" {
 //   o    [B*S, Hq*128] bf16, lse [B, Hq, S] fp32   saved by the forward pass
 //   dqkv [B*S, (Hq+2Hkv)*128]   bf16 OUT: dq | dk | dv
 //   status                      device int, OUT: set non-zero if a bounded wait inside a kernel expired (zero it first)
+// Shapes as for the forward pass: S a multiple of 128, Hq a multiple of Hkv with an even ratio.
 // Returns 0 on success, a negative code on a bad argument, -30 if B*Hq*S exceeds TB_ATTN_BWD_NOALLOC_MAX_ROWS and
 // -31 if the scratch symbol could not be resolved on the current device.
 //
 // No device memory is allocated or freed, here or in anything it calls.  The per-row statistics live in one
 // static device array of 2 * TB_ATTN_BWD_NOALLOC_MAX_ROWS floats (4 MiB) that every GPU loading this library holds
-// until the process exits.  The FIRST call on a device resolves the array's address (cudaGetSymbolAddress) and sets
-// kernel attributes, so make that first call outside any stream capture.  All calls share the array and it keeps
+// until the process exits.  The FIRST call on each device resolves the array's address (cudaGetSymbolAddress)
+// and sets that device's kernel attributes (both are kept per device, so several GPUs may be driven from one
+// process), so make that first call outside any stream capture.  All calls share the array and it keeps
 // whatever the previous call left there; nothing in it needs clearing because each call rewrites the rows it
 // reads.  Two calls that overlap on the GPU (different streams) would race on it: order them.
 int tb_attn_bwd_noalloc(const void* d_o, const void* qk, const void* qkv, const void* o, const float* lse, void* dqkv,

@@ -9,7 +9,11 @@ Inputs are the buffers the surrounding kernels produce, no transposes or copies:
 Backward writes dq | dk | dv into one (M, (Hq+2Hkv)*hd) buffer laid out like ``qkv``, which the
 QK-norm/RoPE backward kernel then transforms in place and the QKV dgrad/wgrad GEMMs consume.
 
-``impl="sm100"`` is the hand-written tcgen05 kernel pair (``csrc/attention_sm100.cu``);
+``impl="sm100"`` is the hand-written tcgen05 kernel set: ``csrc/attention_fwd_sm100.cu`` forward and, for
+backward, either the single-pass kernel ``csrc/attention_bwd_fused_sm100.cu`` (default: five tile products per
+block pair, dQ partial tiles added into an fp32 accumulator, so dQ is not bitwise repeatable) or the two-kernel
+path ``csrc/attention_bwd_dq_sm100.cu`` + ``csrc/attention_bwd_dkv_sm100.cu`` (seven products, no atomics, bitwise
+repeatable; ``set_backward("split")`` or ``TORCHURE_B200_ATTN_BWD=split``).
 ``impl="sdpa"`` routes through ``torch.nn.functional.scaled_dot_product_attention`` and exists for
 A/B comparison and for shapes the kernel does not cover (head_dim != 128, S % 128 != 0, odd GQA ratio).
 """
@@ -25,6 +29,15 @@ from torchure_b200 import ops
 from torchure_b200.ops.debug import new_output
 
 _FORCE = os.environ.get("TORCHURE_B200_ATTN", "")  # "sdpa" forces the library path
+_BWD = os.environ.get("TORCHURE_B200_ATTN_BWD", "fused")
+
+
+def set_backward(mode: str) -> None:
+    """Choose the backward of the sm100 path: "fused" (single pass, fp32 dQ reductions) or "split" (two kernels,
+    deterministic)."""
+    global _BWD
+    assert mode in ("fused", "split")
+    _BWD = mode
 
 
 def kernel_supported(S: int, Hq: int, Hkv: int, hd: int) -> bool:
@@ -75,8 +88,12 @@ def attn_bwd(d_o, qk, qkv, state: AttnState, B, S, Hq, Hkv, hd):
     M = B * S
     dqkv = new_output("attn_bwd.dqkv", M, (Hq + 2 * Hkv) * hd, dtype=torch.bfloat16, device=d_o.device)
     if state.impl == "sm100":
-        ops.ext().attn_bwd(d_o, qk, qkv, state.o, state.lse, dqkv, B, S, Hq, Hkv)
-        ops.count_launch(3)
+        if _BWD == "fused":
+            ops.ext().attn_bwd_fused(d_o, qk, qkv, state.o, state.lse, dqkv, B, S, Hq, Hkv)
+            ops.count_launch(4)  # statistics, accumulator clear, fused kernel, dQ conversion
+        else:
+            ops.ext().attn_bwd(d_o, qk, qkv, state.o, state.lse, dqkv, B, S, Hq, Hkv)
+            ops.count_launch(3)
         return dqkv
     out, ql, kl, vl = state.graph
     g = d_o.view(B, S, Hq, hd).transpose(1, 2)

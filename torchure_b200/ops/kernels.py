@@ -33,6 +33,17 @@ def check_error() -> None:
         raise RuntimeError(f"sm_100a kernel reported an expired wait: code {code} ({names.get(code, 'unknown')})")
 
 
+def check_comm_error(rank: int | None = None) -> None:
+    """Synchronise and raise if a collective or fused GEMM+collective kernel gave up waiting for a peer."""
+    word = _C().comm_error_word()
+    code = int(word[0].item())
+    if code != 0:
+        word.zero_()
+        where = "" if rank is None else f" on rank {rank}"
+        raise RuntimeError(f"a collective gave up waiting for a peer flag{where} (code {code}); its output is "
+                           "incomplete and every later collective bails out until the word is cleared")
+
+
 # ---- GEMM ---------------------------------------------------------------------------------------
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
          out_dtype=BF16, accumulate: bool = False, splits: int = 0) -> torch.Tensor:

@@ -3,7 +3,9 @@
 A ``TensorTable`` records, for a fixed list of tensors, up to five pointer columns, the element counts,
 per-tensor flags and the (tensor, chunk) assignment of every thread block.  It is uploaded once; while the
 underlying storages stay where they are (parameters, optimizer state, bucket views), every later launch
-reuses it.  Tables are rebuilt only when a pointer changes (fresh autograd grads).
+reuses it.  Tables are rebuilt only when a pointer changes (fresh autograd grads).  A table holds addresses, not
+tensors: it keeps nothing alive, and there is one live table per (operation, tensor sizes, flags) slot, so fresh
+gradients arriving at new addresses every step replace the previous table instead of piling up.
 """
 
 from __future__ import annotations
@@ -44,7 +46,6 @@ class TensorTable:
             host = [h.pin_memory() for h in host]
         self.host = host
         self.ptrs, self.numel, self.flags, self.bt, self.bc = (h.to(dev, non_blocking=True) for h in host)
-        self.keepalive = columns
 
     def args(self):
         return self.ptrs, self.numel, self.flags, self.bt, self.bc
@@ -54,13 +55,18 @@ _CACHE: dict[tuple, TensorTable] = {}
 
 
 def _table(tag: str, columns, flags=None) -> TensorTable:
-    key = (tag,) + tuple(tuple((t.data_ptr() if t is not None else 0) for t in col) for col in columns)
-    tab = _CACHE.get(key)
-    if tab is None:
+    first = columns[0]
+    slot = (tag, len(columns), tuple(t.numel() for t in first), tuple(flags) if flags is not None else (),
+            first[0].device.index)
+    ptrs = [tuple((t.data_ptr() if t is not None else 0) for t in col) for col in columns]
+    while len(ptrs) < 5:
+        ptrs.append((0,) * len(first))
+    tab = _CACHE.get(slot)
+    if tab is None or tab.key != tuple(ptrs):
         if len(_CACHE) > 256:
             _CACHE.clear()
-        tab = TensorTable(columns, flags)
-        _CACHE[key] = tab
+        tab = TensorTable(columns, flags)   # replaces (and thereby drops) the slot's previous table
+        _CACHE[slot] = tab
     return tab
 
 

@@ -153,10 +153,29 @@ class Trainer:
                                     name=self.run_name, id=self.resume_wandb_id,
                                     resume="must" if self.resume_wandb_id else None, config=self.config)
 
+    # -- device error words ---------------------------------------------------------------------
+    def check_device_errors(self) -> None:
+        """Raise if any kernel of this process recorded an expired bounded wait (GEMM / attention pipeline waits,
+        peer-flag handshakes of the collectives, arrival polls of the fused GEMM+collective kernels).  Such a
+        kernel returns early and leaves its output unwritten or unreduced, and the words are sticky, so training
+        on would silently diverge.  Reading the words synchronises; it is called where the host synchronises
+        anyway: at the logging cadence, before a checkpoint is written and after a timed benchmark region."""
+        if not self.on_gpu:
+            return
+        from torchure_b200 import ops
+
+        if not ops.available():
+            return
+        from torchure_b200.ops import kernels as K
+
+        K.check_error()
+        K.check_comm_error(self.rank)
+
     # -- checkpoint / resume -------------------------------------------------------------------
     @debug_time
     def checkpoint(self, step: int) -> None:
         """Write the state after `step` completed steps; rank 0 writes replicas, every dp rank its loader."""
+        self.check_device_errors()   # never persist the result of a step whose kernels gave up
         if self.rank == 0:
             self.checkpointer.save_model(self.model, step)
             self.checkpointer.save_optimizer(self.optimizer, step)
@@ -301,6 +320,7 @@ class Trainer:
             metrics, seconds = self.train_step()
             history.append({"loss": float(metrics["loss"]), "grad_norm": float(metrics["grad_norm"]),
                             "seconds": seconds})
+            self.check_device_errors()
             if self.rank == 0:
                 print(self._line(step, metrics, seconds, tokens_per_step), flush=True)
         if self.rank == 0 and self.on_gpu:
@@ -346,6 +366,8 @@ class Trainer:
                 done = step + 1
                 if (done % self.save_steps == 0 and step != 0) or done == self.num_train_steps:
                     self.checkpoint(done)
+                if done % self.log_every == 0 or done == self.num_train_steps:
+                    self.check_device_errors()   # every rank, at the cadence at which rank 0 reads the loss anyway
                 if self.rank == 0:
                     self._log_metrics(metrics, done, tokens_per_step, seconds)
                     if done % self.log_every == 0 or done == self.num_train_steps:
