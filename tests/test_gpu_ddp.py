@@ -114,3 +114,44 @@ def test_trainer_cuda_graph_matches_eager(pg, tmp_path):
     # the optimizer's host bookkeeping advanced once per step, capture included
     st = graphed.optimizer.state[next(iter(graphed.model.parameters()))]
     assert int(st["step"].item()) == 8
+
+
+def _gpu_cfg(run_name, graph=True, resume=None, save_steps=1000, steps=8):
+    return {
+        "model": {"name": "qwen3_dense", "config": dict(CFG)},
+        "mesh": {"dp": 1}, "seed": 1, "cuda_graph": graph, "cuda_graph_warmup": 1,
+        "optimizer": {"name": "adamw", "config": {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "fused": True},
+                      "max_norm": 1.0,
+                      "scheduler": {"type": "wsd", "warmup_ratio": 0.3, "decay_ratio": 0.3, "total_steps": steps}},
+        "objective": {"name": "AR", "config": {"ignore_index": -100, "fused_linear_ce": True, "ce_chunk_size": 256}},
+        "data": {"name": "synthetic", "synthetic": True, "seed": 3, "mean_doc_len": 64, "eos_id": 0, "num_workers": 0,
+                 "global_batch_size": 4, "micro_batch_size": 2, "seq_len": 256},
+        "checkpointing": {"save_steps": save_steps, "resume": resume}, "run_name": run_name,
+    }
+
+
+def test_trainer_resume_gpu_with_graph_replay(pg, tmp_path):
+    """Checkpoint / resume through the GPU path: bf16 shadow weights, device-resident AdamW scalars and the captured
+    step all restart from the files.  8 straight steps against 4 steps + checkpoint + 4 resumed steps (both replay
+    the device step from a CUDA graph).  The gradient kernels use fp32 atomics, so the comparison is to rounding
+    noise, not bitwise."""
+    os.environ["TORCHURE_B200_HOME"] = str(tmp_path)
+    from torchure_b200.train.trainer import Trainer
+
+    straight = Trainer(_gpu_cfg("gpu_straight"), 0, 0, 1, benchmark=True)
+    straight.train()
+    first = Trainer(_gpu_cfg("gpu_resumed", save_steps=4), 0, 0, 1, benchmark=True)
+    first.num_train_steps = 4
+    first.train()
+    assert first._graph is not None
+    second = Trainer(_gpu_cfg("gpu_resumed", resume="auto"), 0, 0, 1, benchmark=True)
+    assert second.start_step == 4
+    second.train()
+    assert second._graph is not None
+    assert int(second.optimizer.state[next(iter(second.model.parameters()))]["step"].item()) == 8
+    assert abs(second.scheduler.get_last_lr()[0] - straight.scheduler.get_last_lr()[0]) < 1e-12
+    for (n, p), (_, q) in zip(straight.model.named_parameters(), second.model.named_parameters()):
+        assert relerr(q, p) < 5e-3, n
+    # the shadows the GEMMs read are the bf16 image of the resumed masters
+    for p, shadow in second.model.engine().shadow_pairs():
+        assert relerr(shadow, p.detach().bfloat16()) < 1e-6

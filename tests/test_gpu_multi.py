@@ -212,3 +212,166 @@ def _sp_fused_linears(rank, world):
 
 def test_sequence_parallel_fused_linears():
     run_on_gpus(_sp_fused_linears, min(_world(), 4))
+
+
+# ---- sharded training on the engine and the Trainer on several GPUs -------------------------------------------------
+def _fsdp_parity(rank, world):
+    """EngineFSDP against one unsharded model: reduce-scattered gradients, the published norm, two AdamW steps on
+    the shards, the in-place all-gather of the bf16 weights."""
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.models import Qwen3
+    from torchure_b200.objectives import ARObjective
+    from torchure_b200.optim import build_optimizer
+    from torchure_b200.parallel.fsdp_engine import EngineFSDP
+
+    mesh = Mesh({"dp_shard": world})
+    torch.manual_seed(100 + rank)
+    model = Qwen3(**CFG).cuda()
+    model.init_weights()
+    torch.manual_seed(100)
+    single = Qwen3(**CFG).cuda()
+    single.init_weights()
+    fsdp = EngineFSDP(model, mesh, "dp_shard")
+    opt_cfg = {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "fused": True}
+    opt = build_optimizer(None, "adamw", opt_cfg, params=fsdp.optimizer_params())
+    fsdp.attach_shadows(opt)
+    ref_opt = build_optimizer(single, "adamw", opt_cfg)
+    for p, shadow in single.engine().shadow_pairs():
+        ref_opt.attach_shadow(p, shadow)
+    obj = ARObjective(fused_linear_ce=True, ce_chunk_size=256)
+    K = 2
+    ref_names = dict(single.named_parameters())
+    for cycle in range(3):
+        ids = torch.randint(0, CFG["vocab_size"], (K, world, 2, 128), device="cuda",
+                            generator=torch.Generator("cuda").manual_seed(cycle))
+        single.zero_grad()
+        fsdp.begin_step()
+        for k in range(K):
+            fsdp.requires_sync = k == K - 1
+            obj.compute_loss(model, {"input_ids": ids[k, rank], "labels": ids[k, rank]}, loss_scale=1 / K).backward()
+        fsdp.sync()
+        for k in range(K):
+            flat = ids[k].reshape(world * 2, 128)
+            (obj.compute_loss(single, {"input_ids": flat, "labels": flat}) / K).backward()
+        total = 0.0
+        for u in fsdp.units:
+            for m in u.mats:
+                want = torch.cat([ref_names[n].grad for n in m.names], dim=0)
+                lo = rank * m.per
+                err = ((m.shard.grad - want[lo:lo + m.per]).norm() / want.norm().clamp_min(1e-12)).item()
+                assert err < 2e-2, (m.name, cycle, err)
+                total += want.double().pow(2).sum().item()
+        names = {p: n for n, p in model.named_parameters()}
+        for p in fsdp.gains:
+            want = ref_names[names[p]].grad
+            err = ((p.grad - want).norm() / want.norm().clamp_min(1e-12)).item()
+            assert err < 3e-2, (names[p], cycle, err)
+            total += want.double().pow(2).sum().item()
+        sq = fsdp.sq_norm().item()
+        assert abs(sq - total) < 2e-3 * total, (sq, total)
+        opt.step()
+        fsdp.mark_updated()
+        opt.zero_grad()
+        ref_opt.step()
+    sd = fsdp.full_state_dict()
+    for n, q in single.named_parameters():
+        err = ((sd[n] - q).norm() / q.norm()).item()
+        assert err < 2e-3, (n, err)
+    fsdp.comm.check()
+
+
+def test_engine_fsdp_matches_single_process():
+    run_on_gpus(_fsdp_parity, min(_world(), 4))
+
+
+def test_engine_fsdp_peer_loads_only():
+    run_on_gpus(_fsdp_parity, 2, env={"TORCHURE_B200_NVLS": "0"})
+
+
+def _trainer_cfg(mesh, run_name, global_batch, graph=True, steps=6):
+    return {
+        "model": {"name": "qwen3_dense", "config": dict(CFG)},
+        "mesh": dict(mesh), "seed": 1, "cuda_graph": graph, "cuda_graph_warmup": 1,
+        "optimizer": {"name": "adamw", "config": {"lr": 1e-3, "weight_decay": 0.1, "betas": [0.9, 0.95], "fused": True},
+                      "max_norm": 1.0,
+                      "scheduler": {"type": "wsd", "warmup_ratio": 0.3, "decay_ratio": 0.3, "total_steps": steps}},
+        "objective": {"name": "AR", "config": {"ignore_index": -100, "fused_linear_ce": True, "ce_chunk_size": 256}},
+        "data": {"name": "synthetic", "synthetic": True, "seed": 3, "mean_doc_len": 64, "eos_id": 0, "num_workers": 0,
+                 "global_batch_size": global_batch, "micro_batch_size": 2, "seq_len": 256},
+        "ddp": {"bucket_mb": 1},
+        "checkpointing": {"save_steps": 1000, "resume": None}, "run_name": run_name,
+    }
+
+
+def _trainer_strategies(rank, world, home, out):
+    """Trainer end to end on `world` GPUs, CUDA-graph replay on: DDP and FSDP (selected by the mesh alone) must follow
+    the same loss and gradient-norm trajectory, and an FSDP checkpoint must resume."""
+    import os
+
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    steps = 6
+    ddp = Trainer(_trainer_cfg({"dp": world}, "t_ddp", 4 * world, steps=steps), rank, rank, world, benchmark=True)
+    h_ddp = ddp.train_n_step_test(steps)
+    assert ddp._graph is not None
+    del ddp
+    torch.cuda.empty_cache()
+    cfg = _trainer_cfg({"dp_shard": world}, "t_fsdp", 4 * world, steps=steps)
+    cfg["checkpointing"]["save_steps"] = 3
+    fsdp = Trainer(cfg, rank, rank, world, benchmark=True)
+    assert type(fsdp.ddp).__name__ == "EngineFSDP"
+    fsdp.train()
+    fsdp.check_device_errors()
+    # the same run, resumed from its step-3 checkpoint (sharded optimizer files), must end where the straight run did
+    cfg2 = _trainer_cfg({"dp_shard": world}, "t_fsdp", 4 * world, steps=steps)
+    cfg2["checkpointing"]["resume"] = 3
+    again = Trainer(cfg2, rank, rank, world, benchmark=True)
+    assert again.start_step == 3
+    again.train()
+    a, b = fsdp.ddp.full_state_dict(), again.ddp.full_state_dict()
+    for n in a:
+        err = ((a[n] - b[n]).norm() / a[n].norm()).item()
+        assert err < 5e-3, (n, err)
+    del fsdp, again
+    torch.cuda.empty_cache()
+    f2 = Trainer(_trainer_cfg({"dp_shard": world}, "t_fsdp2", 4 * world, steps=steps), rank, rank, world, benchmark=True)
+    h_fsdp = f2.train_n_step_test(steps)
+    assert f2._graph is not None
+    for x, y in zip(h_ddp, h_fsdp):
+        assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(x["loss"]), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(x["grad_norm"]), (x, y)
+    if rank == 0:
+        torch.save({"ddp": h_ddp, "fsdp": h_fsdp}, out)
+
+
+def test_trainer_ddp_and_fsdp_on_gpus(tmp_path):
+    run_on_gpus(_trainer_strategies, min(_world(), 4), str(tmp_path), str(tmp_path / "h.pt"), timeout_s=600)
+    got = torch.load(tmp_path / "h.pt")
+    assert got["ddp"][-1]["loss"] < got["ddp"][0]["loss"]
+
+
+def _trainer_vs_single(rank, world, home, out, emulate):
+    import os
+
+    os.environ["TORCHURE_B200_HOME"] = home
+    from tests.test_trainer_parity import _Interleaved
+    from torchure_b200.train.trainer import Trainer
+
+    cfg = _trainer_cfg({"dp": world}, f"t_par_{world}", 4 * max(world, emulate), graph=True)
+    tr = Trainer(cfg, rank, rank, world, benchmark=True)
+    if emulate:
+        tr.prefetcher = _Interleaved(cfg, emulate)
+    hist = tr.train_n_step_test(6)
+    if rank == 0:
+        torch.save(hist, out)
+
+
+def test_trainer_two_gpus_match_one(tmp_path):
+    """2-GPU DDP through the Trainer (graph replay, fused reducer) against ONE GPU fed the same rows."""
+    run_on_gpus(_trainer_vs_single, 2, str(tmp_path), str(tmp_path / "two.pt"), 0, timeout_s=600)
+    run_on_gpus(_trainer_vs_single, 1, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=600)
+    two, one = torch.load(tmp_path / "two.pt"), torch.load(tmp_path / "one.pt")
+    for x, y in zip(two, one):
+        assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)

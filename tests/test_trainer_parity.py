@@ -3,7 +3,10 @@
 * Parity: tiny Qwen3-style decoder (hidden 256, 4 layers, 4/2 heads, head_dim 64, ffn 768, vocab 4096),
   seq 256, micro-batch 2 per rank, 2 accumulation steps via no_sync, 5 AdamW steps with clip 1.0:
   world_size=2 DDP must match one process fed the same rows.
-* Resume exactness: 3 steps + checkpoint + 2 resumed steps == 5 straight steps, bitwise.
+* The same comparison for FSDP2 (mesh ``dp_shard: 2``) and HSDP (``dp_replicate: 2, dp_shard: 2``), selected by
+  the mesh of the config alone.
+* Resume exactness: 3 steps + checkpoint + 2 resumed steps == 5 straight steps, bitwise; for FSDP the checkpoint
+  holds an unsharded ``model.pt`` and one ``optimizer_shard{r}.pt`` per shard.
 """
 
 import os
@@ -45,8 +48,76 @@ def _run(rank, world, cfg, home, out, emulate_world):
     if emulate_world:
         tr.prefetcher = _Interleaved(cfg, emulate_world)
     hist = tr.train_n_step_test(STEPS)
+    params = _weights(tr)
     if rank == 0:
-        torch.save({"hist": hist, "params": {n: p.detach().clone() for n, p in tr.model.named_parameters()}}, out)
+        torch.save({"hist": hist, "params": params}, out)
+
+
+def _weights(tr):
+    """Unsharded fp32 weights under the model's keys (a collective when the strategy shards them)."""
+    if getattr(tr, "sharded", False):
+        sd = tr.ddp.full_state_dict()
+        return {n: sd[n].detach().clone() for n, _ in tr.model.named_parameters()}
+    return {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+
+
+def _compare(a, b):
+    for x, y in zip(a["hist"], b["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"]))
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"]))
+    assert a["hist"][0]["loss"] > 8.0  # ~ln(4096) = 8.3 at init
+    for n in b["params"]:
+        x, y = a["params"][n], b["params"][n]
+        diff = (x - y).abs()
+        off = (diff > 1e-5 + 1e-4 * y.abs()).float().mean().item()
+        # Adam moves a weight by up to lr per step whatever the size of its gradient, so a gradient that is zero up
+        # to summation order may step the other way: a handful of elements differ by a few lr, nothing else may
+        assert off < 1e-5, f"{n}: {off:.2e} of the elements differ"
+        assert diff.max().item() < 5 * 3e-4, f"{n}: max difference {diff.max().item():.2e}"
+
+
+def test_fsdp_and_hsdp_match_single_process(tmp_path):
+    """The mesh alone selects the strategy: dp_shard -> FSDP2 units, dp_replicate x dp_shard -> HSDP."""
+    one_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
+    run_distributed(_run, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=240)
+    fsdp_cfg = parity_config(world=2, steps=STEPS, accumulation=2, mesh={"dp_shard": 2})
+    run_distributed(_run, 2, fsdp_cfg, str(tmp_path), str(tmp_path / "fsdp.pt"), 0, timeout_s=240)
+    _compare(torch.load(tmp_path / "fsdp.pt"), torch.load(tmp_path / "one.pt"))
+    one4_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
+    run_distributed(_run, 1, one4_cfg, str(tmp_path), str(tmp_path / "one4.pt"), 4, timeout_s=240)
+    hsdp_cfg = parity_config(world=4, steps=STEPS, accumulation=1, mesh={"dp_replicate": 2, "dp_shard": 2})
+    run_distributed(_run, 4, hsdp_cfg, str(tmp_path), str(tmp_path / "hsdp.pt"), 0, timeout_s=240)
+    _compare(torch.load(tmp_path / "hsdp.pt"), torch.load(tmp_path / "one4.pt"))
+
+
+def _run_fsdp_resume(rank, world, home, out):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    mesh = {"dp_shard": 2}
+    straight = Trainer(parity_config(2, steps=5, run_name="fs_straight", accumulation=1, mesh=mesh), rank, rank, world,
+                       device="cpu")
+    straight.train()
+    first = Trainer(parity_config(2, steps=5, run_name="fs_resumed", accumulation=1, save_steps=3, mesh=mesh), rank,
+                    rank, world, device="cpu")
+    first.num_train_steps = 3
+    first.train()
+    second = Trainer(parity_config(2, steps=5, run_name="fs_resumed", accumulation=1, resume="auto", save_steps=1000,
+                                   mesh=mesh), rank, rank, world, device="cpu")
+    assert second.start_step == 3
+    second.train()
+    a, b = _weights(straight), _weights(second)
+    if rank == 0:
+        torch.save({"a": a, "b": b}, out)
+
+
+def test_fsdp_resume_is_exact(tmp_path):
+    run_distributed(_run_fsdp_resume, 2, str(tmp_path), str(tmp_path / "r.pt"), timeout_s=240)
+    got = torch.load(tmp_path / "r.pt")
+    for n in got["a"]:
+        assert torch.equal(got["a"][n], got["b"][n]), n
+    files = sorted(os.listdir(tmp_path / "checkpoints" / "fs_resumed" / "3"))
+    assert "model.pt" in files and "optimizer_shard0.pt" in files and "optimizer_shard1.pt" in files, files
 
 
 def test_ddp_world2_matches_single_process(tmp_path):
@@ -55,13 +126,7 @@ def test_ddp_world2_matches_single_process(tmp_path):
     assert ddp_cfg["data"]["global_batch_size"] == one_cfg["data"]["global_batch_size"] == 8
     run_distributed(_run, 2, ddp_cfg, str(tmp_path), str(tmp_path / "ddp.pt"), 0, timeout_s=240)
     run_distributed(_run, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=240)
-    a, b = torch.load(tmp_path / "ddp.pt"), torch.load(tmp_path / "one.pt")
-    for x, y in zip(a["hist"], b["hist"]):
-        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"]))
-        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"]))
-    assert a["hist"][0]["loss"] > 8.0  # ~ln(4096) = 8.3 at init
-    for n in a["params"]:
-        torch.testing.assert_close(a["params"][n], b["params"][n], rtol=1e-4, atol=1e-5, msg=lambda m: f"{n}: {m}")  # Adam amplifies summation-order noise on near-zero gradients
+    _compare(torch.load(tmp_path / "ddp.pt"), torch.load(tmp_path / "one.pt"))  # Adam amplifies summation-order noise
 
 
 def _run_resume(rank, world, home, out):

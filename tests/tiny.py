@@ -10,10 +10,10 @@ PARITY = dict(num_layers=4, num_heads=4, num_kv_heads=2, emb_dim=256, head_dim=6
 
 
 def parity_config(world: int, steps: int = 5, run_name: str = "parity", accumulation: int = 2, resume=None,
-                  save_steps: int = 1000) -> dict:
+                  save_steps: int = 1000, mesh: dict | None = None) -> dict:
     return {
         "model": {"name": "qwen3_dense", "config": dict(PARITY)},
-        "mesh": {"dp": world},
+        "mesh": dict(mesh) if mesh is not None else {"dp": world},
         "seed": 1234,
         "optimizer": {"name": "adamw", "config": {"lr": 3e-4, "weight_decay": 0.1, "betas": [0.9, 0.95],
                                                   "fused": False},

@@ -5,7 +5,9 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
 
     model         {name, config{num_layers, num_heads, num_kv_heads, emb_dim, head_dim, vocab_size,
                    [ffn_dim], [norm_eps], [rope_theta], [impl]}}
-    mesh          {axis: size, ...}   product == WORLD_SIZE, must contain "dp"
+    mesh          {axis: size, ...}   product == WORLD_SIZE.  Data axes: "dp" (DDP), or "dp_shard" (FSDP2) with an
+                  optional "dp_replicate" in front of it (HSDP); "tp" shards every block (Megatron column/row split);
+                  "cp" splits the sequence (ring attention).  At least one data axis is required.
     optimizer     {name, config{lr, weight_decay, betas, fused}, [max_norm],
                    scheduler{type, warmup_ratio, decay_ratio, total_steps}}
     objective     {name, config{ignore_index, fused_linear_ce, ce_chunk_size}}
@@ -13,6 +15,8 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
                    num_workers, global_batch_size, micro_batch_size, seq_len, [pack_batch], [packer],
                    synthetic extras: vocab_size, eos_id, mean_doc_len}
     [ddp]         {bucket_mb, [fused], [merge_small]}
+    [fsdp]        {[comm_sms]}
+    [tp]          {[sequence_parallel]}
     [comm]        {backend: "sm100" | "torch", [max_bytes]}
     checkpointing {save_steps, resume: null|"auto"|int, [resume_scheduler]}
     run_name      str
@@ -26,6 +30,8 @@ from __future__ import annotations
 import json
 import math
 
+DATA_AXES = ("dp", "dp_replicate", "dp_shard")
+MESH_AXES = DATA_AXES + ("tp", "cp", "pp", "ep")
 REQUIRED = ("model", "mesh", "optimizer", "objective", "data", "checkpointing", "run_name")
 
 
@@ -44,8 +50,18 @@ def validate_config(cfg: dict, world_size: int | None = None) -> dict:
         if key not in cfg:
             raise ConfigError(f"config is missing the {key!r} section")
     mesh = cfg["mesh"]
-    if "dp" not in mesh:
-        raise ConfigError('mesh must define a "dp" axis')
+    unknown = [a for a in mesh if a not in MESH_AXES]
+    if unknown:
+        raise ConfigError(f"unknown mesh axes {unknown}; known: {list(MESH_AXES)}")
+    data_axes = [a for a in mesh if a in DATA_AXES]
+    if not data_axes:
+        raise ConfigError('mesh must define a data axis: "dp", or "dp_shard" (optionally after "dp_replicate")')
+    if "dp" in mesh and ("dp_shard" in mesh or "dp_replicate" in mesh):
+        raise ConfigError('"dp" (DDP) cannot be combined with "dp_shard" / "dp_replicate" (FSDP / HSDP)')
+    if "dp_replicate" in mesh and "dp_shard" not in mesh:
+        raise ConfigError('"dp_replicate" needs a "dp_shard" axis (HSDP); use "dp" for plain replication')
+    if "dp_replicate" in mesh and list(mesh).index("dp_replicate") > list(mesh).index("dp_shard"):
+        raise ConfigError('"dp_replicate" must come before "dp_shard" in the mesh')
     if world_size is not None and math.prod(mesh.values()) != world_size:
         raise ConfigError(f"mesh {mesh} does not cover world size {world_size}")
     opt = cfg["optimizer"]
@@ -60,7 +76,7 @@ def validate_config(cfg: dict, world_size: int | None = None) -> dict:
     for key in ("global_batch_size", "micro_batch_size", "seq_len"):
         if key not in data:
             raise ConfigError(f"data.{key} is required")
-    dp = mesh["dp"]
+    dp = math.prod(mesh[a] for a in data_axes)
     per_backward = data["micro_batch_size"] * dp
     if data["global_batch_size"] % per_backward != 0:
         raise ConfigError(

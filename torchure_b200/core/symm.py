@@ -125,6 +125,36 @@ class SymmComm:
                                  blocks or self.blocks)
         ops.count_launch()
 
+    def all_gather_inplace_(self, fulls: list[torch.Tensor], blocks: int | None = None) -> None:
+        """Each tensor of `fulls` lives in the symmetric region and is `world` equal row chunks; this rank's chunk
+        (already written locally) is replicated into every peer's copy.  One kernel, no staging, no copy-out."""
+        offs, sizes = [], []
+        for t in fulls:
+            off = self.offset_of(t)
+            nbytes = t.numel() * t.element_size()
+            assert off is not None and t.is_contiguous() and nbytes % (16 * self.world) == 0 and off % 16 == 0
+            offs.append(off)
+            sizes.append(nbytes // self.world)
+        for lo in range(0, len(offs), self.ext.COMM_MAX_SEGMENTS):
+            hi = lo + self.ext.COMM_MAX_SEGMENTS
+            self.ext.comm_all_gather_inplace(*self._ctx(), offs[lo:hi], sizes[lo:hi], bool(self.mc) and self.world > 2,
+                                             blocks or self.blocks)
+            ops.count_launch()
+
+    def reduce_scatter_symmetric(self, fulls: list[torch.Tensor], outs: list[torch.Tensor], op: str = "avg",
+                                 sq_slot: int = -1, blocks: int | None = None) -> None:
+        """outs[i] (local fp32, 1/world of fulls[i]) = op over ranks of this rank's row chunk of fulls[i], which lives
+        in the symmetric region.  One kernel; the peers' copies are read in place."""
+        assert len(fulls) == len(outs) <= self.ext.COMM_MAX_SEGMENTS
+        offs = []
+        for t, o in zip(fulls, outs):
+            off = self.offset_of(t)
+            assert off is not None and t.dtype == torch.float32 and t.numel() == o.numel() * self.world
+            offs.append(off)
+        use_mc = bool(self.mc) and op in ("sum", "avg")
+        self.ext.comm_reduce_scatter_symm(*self._ctx(), offs, outs, _OPS[op], use_mc, sq_slot, blocks or self.blocks)
+        ops.count_launch()
+
     # generic collectives on ordinary tensors: ONE kernel each; the staging area is only the exchange medium
     def _aligned(self, *ts: torch.Tensor) -> bool:
         return all(t.data_ptr() % 16 == 0 and (t.numel() * t.element_size()) % 16 == 0 for t in ts)

@@ -22,9 +22,11 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_
 
 // ---- elementwise / normalisation -------------------------------------------------------------
 // h = rmsnorm(x_new) * w with x_new = x (+ y); optional gather x = table[ids].  Writes x_new when y or ids
-// is given.  x/x_out fp32 [M,D], y bf16 [M,D], h bf16 [M,D], rstd fp32 [M].
-void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids, const float* table, const float* w,
-                     float* x_out, __nv_bfloat16* h, float* rstd, int M, int D, float eps, cudaStream_t stream);
+// is given.  x/x_out fp32 [M,D], y bf16 [M,D], h bf16 [M,D], rstd fp32 [M].  With ids, rows come from `table` (fp32)
+// or, when table_bf16 is given, from that bf16 copy (an x_out is required then: the row is re-read from it).
+void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids, const float* table,
+                     const __nv_bfloat16* table_bf16, const float* w, float* x_out, __nv_bfloat16* h, float* rstd, int M,
+                     int D, float eps, cudaStream_t stream);
 // dx = dx_in + d rmsnorm; dw += sum_rows(dh * xhat).  dx_bf16 (optional) receives a bf16 copy of dx.
 void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const float* rstd, const float* dx_in,
                  float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, cudaStream_t stream);
@@ -32,10 +34,11 @@ void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const 
 void qknorm_rope_fwd(const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos, const float* sin,
                      __nv_bfloat16* out, int M, int S, int Hq, int Hkv, int hd, float eps, int use_norm,
                      cudaStream_t stream);
-// in place on the q/k column ranges of dqkv [M, (Hq+2Hkv)*hd]; dqw/dkw fp32 [hd] accumulate
+// in place on the q/k column ranges of dqkv [M, (Hq+2Hkv)*hd]; dqw/dkw fp32 [hd] accumulate.  dq_acc (optional):
+// head-major fp32 [B, Hq, S, hd] holding dq instead of the q columns of dqkv (they are only written then).
 void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
-                     const float* sin, float* dqw, float* dkw, int M, int S, int Hq, int Hkv, int hd, float eps,
-                     int use_norm, int num_sms, cudaStream_t stream);
+                     const float* sin, float* dqw, float* dkw, const float* dq_acc, int M, int S, int Hq, int Hkv, int hd,
+                     float eps, int use_norm, int num_sms, cudaStream_t stream);
 void swiglu_fwd(const __nv_bfloat16* gu, __nv_bfloat16* act, int M, int F, cudaStream_t stream);
 void swiglu_bwd(const __nv_bfloat16* dact, const __nv_bfloat16* gu, __nv_bfloat16* dgu, int M, int F,
                 cudaStream_t stream);

@@ -11,14 +11,20 @@
 //     S^T_h  = K Q_h^T          (SS, 128x64x128)   columns [0, 64)
 //     dP^T_h = V dO_h^T         (SS, 128x64x128)   columns [64, 128)
 //     P^T_h  = exp2(S^T_h c - lse2[q]);  dS^T_h = P^T_h o (dP^T_h - delta[q]) / sqrt(d)
-//                               bf16 P^T_h / dS^T_h -> 8 + 8 columns inside each warp's own 16 S^T columns; dS^T_h also
-//                               goes to shared memory
+//                               bf16 P^T_h / dS^T_h -> 16 + 16 columns inside each warp's own 32 S^T columns; dS^T_h
+//                               also goes to shared memory
 //     dV    += P^T_h  dO_h      (TS, 128x128x64)   columns 256..383
 //     dK    += dS^T_h Q_h       (TS, 128x128x64)   columns 384..511
 //     dQ^T_h = K^T dS^T_h       (SS, 128x64x128, both operands MN-major)   columns [64, 128) of the half's buffer
-// 576 threads: TMA warp, MMA warp, 16 compute warps (four per TMEM lane quarter, 16 query columns each).  While the
+// 320 threads: TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter, 32 query columns each).  While the
 // compute warps work on one half the tensor core runs the other half's products; after each half they drain the
-// previous half's dQ^T tile with fp32 reductions to global memory.
+// previous half's dQ^T tile with fp32 reductions to global memory.  Measured on B200 the kernel is bound by the
+// L2's fp32 reduction rate (64 KB of partial dQ per block pair, about 2.5 TB/s over the whole GPU): neither halving
+// the instruction count, nor dedicated drain warps, nor 16-byte vector reductions moved its time, so the simplest
+// of those variants is kept.  The element-wise part runs on packed fp32 pairs
+// (fma.rn.f32x2) with every constant folded into the row statistics (-lse*log2e and -delta/sqrt(d), written by the
+// statistics kernel below, which also clears the dQ accumulator).  The accumulator is head-major
+// ([B, Hq, Sq, 128] fp32) so that the 32 reductions of a thread differ by compile-time offsets.
 //
 // `causal`: query block qb sees key blocks <= qb (Sq == Skv); otherwise every query sees every key (the off-diagonal
 // steps of ring attention).  Because partial dQ tiles are added in whatever order CTAs finish, dQ is not bitwise
@@ -37,14 +43,14 @@ constexpr int HD = 128;
 constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KB
 constexpr int HALF_BYTES = 16384;
 constexpr int Q_STAGES = 2;
-constexpr int STAT_BYTES = 1024;          // lse2[128] | delta[128]
+constexpr int STAT_BYTES = 1024;          // -lse2[128] | -delta*scale[128]
 constexpr int STAGE_BYTES = 2 * TILE_BYTES + STAT_BYTES;
 constexpr int DS_BYTES = 128 * 64 * 2;    // dS^T of one half: 128 key rows x 64 queries, bf16
 constexpr int BAR_BYTES = 256;
 constexpr int SMEM_USED = 2 * TILE_BYTES + Q_STAGES * STAGE_BYTES + 2 * DS_BYTES + BAR_BYTES;
 constexpr int SMEM_BYTES = 232448;        // the whole 227 KB: SMEM_USED plus alignment slack
 static_assert(SMEM_USED <= SMEM_BYTES, "shared-memory plan exceeds the per-CTA limit");
-constexpr int COMPUTE_WARPS = 16;
+constexpr int COMPUTE_WARPS = 8;
 constexpr int NUM_THREADS = (2 + COMPUTE_WARPS) * 32;
 
 struct Bars {
@@ -66,6 +72,23 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// two fp32 lanes per instruction (Blackwell FFMA2 / FMUL2)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)),
+        "l"(reinterpret_cast<const uint64_t&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return d;
+}
+
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(smem_dst)),
@@ -74,17 +97,15 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
 }
 
 struct FusedArgs {
-  float* dq_acc;
-  int64_t ld_dq;
+  float* dq_acc;     // [B, Hq, Sq, 128] fp32
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   int64_t ld_dkv;
-  const float* delta;
-  const float* lse2;
+  const float* nds;    // [B, Hq, Sq]  -delta / sqrt(d)
+  const float* nlse2;  // [B, Hq, Sq]  -lse * log2(e)
   int B, Sq, Skv, Hq, Hkv;
   int q_col0, k_col0, v_col0;
   int causal;
-  int dbg;   // diagnostics: bit 0 skips the dQ reductions, bit 1 skips the dQ product as well
   float scale, scale_log2;
 };
 
@@ -175,8 +196,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tma_load_2d(sDO, &tmDO, &bars->q_full[s], h * HD, qrow);
         tma_load_2d(sDO + HALF_BYTES, &tmDO, &bars->q_full[s], h * HD + 64, qrow);
         const int64_t stat = (static_cast<int64_t>(b) * a.Hq + h) * a.Sq + qb * 128;
-        bulk_load_1d(sStat, a.lse2 + stat, 512, &bars->q_full[s]);
-        bulk_load_1d(sStat + 128, a.delta + stat, 512, &bars->q_full[s]);
+        bulk_load_1d(sStat, a.nlse2 + stat, 512, &bars->q_full[s]);
+        bulk_load_1d(sStat + 128, a.nds + stat, 512, &bars->q_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -185,73 +206,83 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);   // S^T / dP^T halves: N = 64 queries
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, false, true);  // A in TMEM, B MN-major, N = 128 (hd)
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, true, true);     // K^T (MN-major) x dS^T (MN-major)
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-      auto issue_s = [&](int hh, const uint8_t* stage) {
-        const uint32_t qa = smem_u32(stage) + hh * 8192;                 // query rows 64h.. of the Q tile
+      // Descriptors are built once per operand; a K step only adds a constant to the 14-bit address field (16-byte
+      // units; every operand lies below 256 KB, so the sum never carries into the next field).
+      const uint64_t dK_k = make_desc_sw128(smem_u32(sK), 16, 1024);                  // K, K-major (S^T)
+      const uint64_t dV_k = make_desc_sw128(smem_u32(sV), 16, 1024);                  // V, K-major (dP^T)
+      const uint64_t dK_mn = make_desc_sw128(smem_u32(sK), HALF_BYTES, 1024);         // K^T, MN-major (dQ^T)
+      uint64_t dQ_k[Q_STAGES], dO_k[Q_STAGES], dQ_mn[Q_STAGES], dO_mn[Q_STAGES], dDS[2];
+#pragma unroll
+      for (int st = 0; st < Q_STAGES; ++st) {
+        const uint32_t qa = smem_u32(sStage + st * STAGE_BYTES), oa = qa + TILE_BYTES;
+        dQ_k[st] = make_desc_sw128(qa, 16, 1024);
+        dO_k[st] = make_desc_sw128(oa, 16, 1024);
+        dQ_mn[st] = make_desc_sw128(qa, HALF_BYTES, 1024);
+        dO_mn[st] = make_desc_sw128(oa, HALF_BYTES, 1024);
+      }
+      dDS[0] = make_desc_sw128(smem_u32(sDS), HALF_BYTES, 1024);
+      dDS[1] = make_desc_sw128(smem_u32(sDS + DS_BYTES), HALF_BYTES, 1024);
+      constexpr uint64_t kHalfRows = 8192 >> 4;     // 64 query rows of a K-major / MN-major tile
+      auto issue_s = [&](int hh, int st) {
+        const uint64_t qd = dQ_k[st] + hh * kHalfRows;                   // query rows 64h.. of the Q tile
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t o = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_f16_ss(tmem_base + hh * 128, make_desc_sw128(ka + o, 16, 1024), make_desc_sw128(qa + o, 16, 1024),
-                      idesc_st, ks != 0 ? 1u : 0u);
+          const uint64_t o = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
+          umma_f16_ss(tmem_base + hh * 128, dK_k + o, qd + o, idesc_st, ks != 0 ? 1u : 0u);
         }
       };
-      auto issue_dp = [&](int hh, const uint8_t* stage) {
-        const uint32_t da = smem_u32(stage + TILE_BYTES) + hh * 8192;    // same rows of dO
+      auto issue_dp = [&](int hh, int st) {
+        const uint64_t od = dO_k[st] + hh * kHalfRows;                   // same rows of dO
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t o = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_f16_ss(tmem_base + hh * 128 + 64, make_desc_sw128(va + o, 16, 1024), make_desc_sw128(da + o, 16, 1024),
-                      idesc_st, ks != 0 ? 1u : 0u);
+          const uint64_t o = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
+          umma_f16_ss(tmem_base + hh * 128 + 64, dV_k + o, od + o, idesc_st, ks != 0 ? 1u : 0u);
         }
         umma_commit(&bars->st_full[hh]);
       };
       // dV += P^T_h dO_h ; dK += dS^T_h Q_h ; dQ^T_h = K^T dS^T_h
-      auto issue_acc = [&](int hh, const uint8_t* stage, bool first) {
-        const uint32_t qa = smem_u32(stage) + hh * 8192;
-        const uint32_t da = smem_u32(stage + TILE_BYTES) + hh * 8192;
-        const uint32_t dsa = smem_u32(sDS + hh * DS_BYTES);
+      auto issue_acc = [&](int hh, int st, bool first) {
+        const uint64_t qd = dQ_mn[st] + hh * kHalfRows, od = dO_mn[st] + hh * kHalfRows;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ts(tmem_base + 256, tmem_base + hh * 128 + ks * 16, make_desc_sw128(da + ks * 2048, HALF_BYTES, 1024),
+          // queries [16 ks, 16 ks + 16) of the half: P^T sits in columns [32 w, 32 w + 16) of softmax warp w = ks / 2
+          umma_f16_ts(tmem_base + 256, tmem_base + hh * 128 + (ks >> 1) * 32 + (ks & 1) * 8, od + ks * (2048 >> 4),
                       idesc_acc, (first && ks == 0) ? 0u : 1u);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ts(tmem_base + 384, tmem_base + hh * 128 + ks * 16 + 8,
-                      make_desc_sw128(qa + ks * 2048, HALF_BYTES, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
-        if (!(a.dbg & 2))
+          umma_f16_ts(tmem_base + 384, tmem_base + hh * 128 + (ks >> 1) * 32 + 16 + (ks & 1) * 8,
+                      qd + ks * (2048 >> 4), idesc_acc, (first && ks == 0) ? 0u : 1u);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 16 rows of K (both 64-wide d halves) and of dS^T
-          umma_f16_ss(tmem_base + hh * 128 + 64, make_desc_sw128(ka + ks * 2048, HALF_BYTES, 1024),
-                      make_desc_sw128(dsa + ks * 2048, HALF_BYTES, 1024), idesc_dq, ks != 0 ? 1u : 0u);
+          umma_f16_ss(tmem_base + hh * 128 + 64, dK_mn + ks * (2048 >> 4), dDS[hh] + ks * (2048 >> 4), idesc_dq,
+                      ks != 0 ? 1u : 0u);
         umma_commit(&bars->dq_full[hh]);
       };
       bool ok = mbar_wait(&bars->kv_full, 0, err, kErrAttnWait) && mbar_wait(&bars->q_full[0], 0, err, kErrAttnWait);
       if (ok) {
         tc_fence_after();
-        issue_s(0, sStage);
-        issue_dp(0, sStage);
-        issue_s(1, sStage);
-        issue_dp(1, sStage);
+        issue_s(0, 0);
+        issue_dp(0, 0);
+        issue_s(1, 0);
+        issue_dp(1, 0);
       }
       for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it % Q_STAGES, sn = (it + 1) % Q_STAGES;
         const uint32_t phn = ((it + 1) / Q_STAGES) & 1;
         const bool more = it + 1 < n_iter;
-        const uint8_t* stage = sStage + s * STAGE_BYTES;
-        const uint8_t* next = sStage + sn * STAGE_BYTES;
         for (int hh = 0; hh < 2 && ok; ++hh) {
           if (!mbar_wait(&bars->pds_ready[hh], it & 1, err, kErrAttnWait)) { ok = false; break; }
           tc_fence_after();
-          issue_acc(hh, stage, it == 0 && hh == 0);
+          issue_acc(hh, s, it == 0 && hh == 0);
           if (hh == 1) umma_commit(&bars->q_empty[s]);
           if (more) {
             if (hh == 0 && !mbar_wait(&bars->q_full[sn], phn, err, kErrAttnWait)) { ok = false; break; }
             tc_fence_after();
-            issue_s(hh, next);       // overwrites P^T_h / dS^T_h: ordered behind the products that read them
+            issue_s(hh, sn);         // overwrites P^T_h / dS^T_h: ordered behind the products that read them
             // the dP^T columns still hold dQ^T_h until the compute warps have read it
             if (!mbar_wait(&bars->dq_drained[hh], it & 1, err, kErrAttnWait)) { ok = false; break; }
             tc_fence_after();
-            issue_dp(hh, next);
+            issue_dp(hh, sn);
           }
         }
       }
@@ -260,28 +291,70 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   } else {
     // ------------------------------------------------ compute warps
     const int quarter = warp & 3;             // TMEM lane quarter this warp may touch
-    const int cg = (warp - 2) >> 2;           // which 16 of a half's 64 query columns
+    const int cg = (warp - 2) >> 2;           // which 32 of a half's 64 query columns
     const int row = quarter * 32 + lane;      // key inside the block (S^T, dP^T) / head-dim index (dQ^T)
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const float2 c2 = make_float2(a.scale_log2, a.scale_log2), sc2 = make_float2(a.scale, a.scale);
+    // byte offsets of this thread's four 16-byte chunks inside its 128-byte dS^T row (128-byte swizzle)
+    uint32_t ds_off[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ds_off[j] = row * 128 + (((4 * cg + j) ^ (row & 7)) << 4);
     bool ok = true;
-    // dQ^T_h of half-step (pit, ph): 16 query columns of this warp, one head-dim index per lane -> fp32 reductions
+    // dQ^T_h of half-step (pit, ph): 32 query columns of this warp, one head-dim index per lane.  The tile leaves TMEM
+    // first (the tensor core may then overwrite it), the 32 fp32 reductions follow; the accumulator is head-major, so
+    // they differ by compile-time offsets.
     auto drain = [&](int pit, int ph) -> bool {
       if (!mbar_wait(&bars->dq_full[ph], pit & 1, err, kErrAttnWait)) return false;
       tc_fence_after();
-      uint32_t v[16];
-      tmem_ld_32x32b_x16(tmem_base + lane_sel + ph * 128 + 64 + cg * 16, v);
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem_base + lane_sel + ph * 128 + 64 + cg * 32, v);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->dq_drained[ph]);
       const int h = kvh * ratio + pit / n_qb;
       const int qb = qb0 + pit % n_qb;
-      float* dst = a.dq_acc + (static_cast<int64_t>(b) * a.Sq + qb * 128 + ph * 64 + cg * 16) * a.ld_dq + h * HD + row;
-      if (!(a.dbg & 1)) {
+      float* dst = a.dq_acc + ((static_cast<int64_t>(b) * a.Hq + h) * a.Sq + qb * 128 + ph * 64 + cg * 32) * HD + row;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) red_add_f32(dst + j * a.ld_dq, __uint_as_float(v[j]));
-      }
+      for (int j = 0; j < 32; ++j) red_add_f32(dst + j * HD, __uint_as_float(v[j]));
       return true;
+    };
+    // P^T_h and dS^T_h of this warp's 32 query columns (one key per lane)
+    auto softmax_half = [&](int hh, const float* sStat, bool diag) {
+      const uint32_t tH = tmem_base + lane_sel + hh * 128;
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32b_x32(tH + cg * 32, sv);
+      tmem_ld_32x32b_x32(tH + 64 + cg * 32, dv);
+      tmem_ld_wait();
+      uint32_t pp[16], pd[16];
+      const int q0 = hh * 64 + cg * 32;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float2 nl = *reinterpret_cast<const float2*>(sStat + q0 + 2 * i);          // -lse2 of the two queries
+        const float2 nd = *reinterpret_cast<const float2*>(sStat + 128 + q0 + 2 * i);    // -delta * scale
+        const float2 t = fma2(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), c2, nl);
+        float2 p = make_float2(ex2(t.x), ex2(t.y));
+        if (diag) {
+          if (q0 + 2 * i < row) p.x = 0.f;       // query before key: masked
+          if (q0 + 2 * i + 1 < row) p.y = 0.f;
+        }
+        const float2 u = fma2(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), sc2, nd);
+        const float2 ds = mul2(p, u);
+        pp[i] = pack_bf16x2(p.x, p.y);
+        pd[i] = pack_bf16x2(ds.x, ds.y);
+      }
+      // both land inside the 32 S^T columns this warp itself consumed, so the warps need no barrier among them
+      tmem_st_32x32b_x16(tH + cg * 32, pp);
+      tmem_st_32x32b_x16(tH + cg * 32 + 16, pd);
+      uint8_t* dsb = sDS + hh * DS_BYTES;     // dS^T row of this key, queries q0..q0+31: four swizzled 16-byte chunks
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(dsb + ds_off[j]) = make_uint4(pd[4 * j], pd[4 * j + 1], pd[4 * j + 2], pd[4 * j + 3]);
+      tmem_st_wait();
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->pds_ready[hh]);
     };
     for (int it = 0; it < n_iter && ok; ++it) {
       const int s = it % Q_STAGES;
@@ -290,40 +363,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       for (int hh = 0; hh < 2; ++hh) {
         if (!mbar_wait(&bars->st_full[hh], it & 1, err, kErrAttnWait)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t tH = tmem_base + lane_sel + hh * 128;
-        uint32_t sv[16], dv[16];
-        tmem_ld_32x32b_x16(tH + cg * 16, sv);
-        tmem_ld_32x32b_x16(tH + 64 + cg * 16, dv);
-        tmem_ld_wait();
-        uint32_t pp[8], pd[8];
-        const int q0 = hh * 64 + cg * 16;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float2 l2 = *reinterpret_cast<const float2*>(sStat + q0 + 2 * i);
-          const float2 dl = *reinterpret_cast<const float2*>(sStat + 128 + q0 + 2 * i);
-          float p0 = ex2(fmaf(__uint_as_float(sv[2 * i]), a.scale_log2, -l2.x));
-          float p1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), a.scale_log2, -l2.y));
-          if (diag) {
-            if (q0 + 2 * i < row) p0 = 0.f;       // query before key: masked
-            if (q0 + 2 * i + 1 < row) p1 = 0.f;
-          }
-          pp[i] = pack_bf16x2(p0, p1);
-          pd[i] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * i]) - dl.x) * a.scale,
-                              p1 * (__uint_as_float(dv[2 * i + 1]) - dl.y) * a.scale);
-        }
-        // both land inside the 16 S^T columns this warp itself consumed, so the warps need no barrier among them
-        tmem_st_32x32b_x8(tH + cg * 16, pp);
-        tmem_st_32x32b_x8(tH + cg * 16 + 8, pd);
-        {   // dS^T row of this key, queries q0..q0+15: two 16-byte chunks of the 128-byte swizzled row
-          uint8_t* rowp = sDS + hh * DS_BYTES + row * 128;
-          *reinterpret_cast<uint4*>(rowp + (((2 * cg) ^ (row & 7)) << 4)) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
-          *reinterpret_cast<uint4*>(rowp + (((2 * cg + 1) ^ (row & 7)) << 4)) = make_uint4(pd[4], pd[5], pd[6], pd[7]);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->pds_ready[hh]);
+        if (diag) softmax_half(hh, sStat, true);
+        else softmax_half(hh, sStat, false);
         // the other half's products of the previous half-step ran meanwhile: take its dQ^T out
         if (hh == 1) {
           if (!drain(it, 0)) { ok = false; break; }
@@ -335,21 +376,24 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (ok && n_iter > 0) ok = drain(n_iter - 1, 1);
     if (ok && mbar_wait(&bars->acc_done, 0, err, kErrAttnWait)) {
       tc_fence_after();
-      // dV and dK: this warp's 32 of the 128 head-dim columns, one key row per lane, written straight to global memory
-      const int kcol = kvh * HD + cg * 32;
+      // dV and dK: this warp's 64 of the 128 head-dim columns, one key row per lane, written straight to global memory
       for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_sel + 256 + which * 128 + cg * 32, v);
-        tmem_ld_wait();
-        __nv_bfloat16* dst = (which == 0 ? a.dv : a.dk) + static_cast<int64_t>(krow0 + row) * a.ld_dkv + kcol;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          const int col = cg * 64 + c * 32;
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_sel + 256 + which * 128 + col, v);
+          tmem_ld_wait();
+          __nv_bfloat16* dst = (which == 0 ? a.dv : a.dk) + static_cast<int64_t>(krow0 + row) * a.ld_dkv + kvh * HD + col;
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          uint4 pk;
-          pk.x = pack_bf16x2(__uint_as_float(v[8 * jj + 0]), __uint_as_float(v[8 * jj + 1]));
-          pk.y = pack_bf16x2(__uint_as_float(v[8 * jj + 2]), __uint_as_float(v[8 * jj + 3]));
-          pk.z = pack_bf16x2(__uint_as_float(v[8 * jj + 4]), __uint_as_float(v[8 * jj + 5]));
-          pk.w = pack_bf16x2(__uint_as_float(v[8 * jj + 6]), __uint_as_float(v[8 * jj + 7]));
-          *reinterpret_cast<uint4*>(dst + 8 * jj) = pk;
+          for (int jj = 0; jj < 4; ++jj) {
+            uint4 pk;
+            pk.x = pack_bf16x2(__uint_as_float(v[8 * jj + 0]), __uint_as_float(v[8 * jj + 1]));
+            pk.y = pack_bf16x2(__uint_as_float(v[8 * jj + 2]), __uint_as_float(v[8 * jj + 3]));
+            pk.z = pack_bf16x2(__uint_as_float(v[8 * jj + 4]), __uint_as_float(v[8 * jj + 5]));
+            pk.w = pack_bf16x2(__uint_as_float(v[8 * jj + 6]), __uint_as_float(v[8 * jj + 7]));
+            *reinterpret_cast<uint4*>(dst + 8 * jj) = pk;
+          }
         }
       }
     }
@@ -367,37 +411,104 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   }
 }
 
-// dst[r, c] (bf16, row stride ld_dst) = src[r, c] (fp32, row stride ld_src), c < cols (a multiple of 8)
+// Row statistics for the single-pass backward, one warp per token row (16 lanes per head, two heads at a time):
+//   nds[b,h,s]   = -rowsum(dO * O) / sqrt(d)        nlse2[b,h,s] = -lse * log2(e)
+// and the token's rows of the head-major dQ accumulator are cleared.
 __global__ void __launch_bounds__(256)
-cast_rows_kernel(const float* __restrict__ src, int64_t ld_src, __nv_bfloat16* __restrict__ dst, int64_t ld_dst,
-                 int64_t rows, int cols) {
+attn_bwd_stats_kernel(const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o,
+                      const float* __restrict__ lse, float* __restrict__ nds, float* __restrict__ nlse2,
+                      float* __restrict__ dq_acc, int B, int S, int Hq, float scale) {
   pdl_wait();
   pdl_launch_dependents();
-  const int per_row = cols / 8;
-  const int64_t total = rows * per_row;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= static_cast<int64_t>(B) * S) return;
+  const int sub = lane & 15, hsel = lane >> 4;
+  const int b = static_cast<int>(row / S), pos = static_cast<int>(row % S);
+  const __nv_bfloat16* pa = d_o + row * Hq * HD + sub * 8;
+  const __nv_bfloat16* pc = o + row * Hq * HD + sub * 8;
+  const int pairs = (Hq + 1) >> 1;
+  constexpr int U = 4;
+  for (int hp = 0; hp < pairs; hp += U) {
+    uint4 x[U], y[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int h = 2 * (hp + k) + hsel;
+      x[k] = y[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (hp + k < pairs && h < Hq) {
+        x[k] = *reinterpret_cast<const uint4*>(pa + h * HD);
+        y[k] = *reinterpret_cast<const uint4*>(pc + h * HD);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int h = 2 * (hp + k) + hsel;
+      const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&x[k]);
+      const __nv_bfloat162* xc = reinterpret_cast<const __nv_bfloat162*>(&y[k]);
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 u = __bfloat1622float2(xa[e]), w = __bfloat1622float2(xc[e]);
+        acc += u.x * w.x + u.y * w.y;
+      }
+#pragma unroll
+      for (int s2 = 8; s2 > 0; s2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s2);
+      if (sub == 0 && hp + k < pairs && h < Hq) {
+        const int64_t idx = (static_cast<int64_t>(b) * Hq + h) * S + pos;
+        nds[idx] = -acc * scale;
+        nlse2[idx] = -lse[idx] * 1.4426950408889634f;
+      }
+    }
+  }
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int h = 0; h < Hq; ++h)
+    reinterpret_cast<float4*>(dq_acc + ((static_cast<int64_t>(b) * Hq + h) * S + pos) * HD)[lane] = zero;
+}
+
+// dst[(b S + s), h 128 + d] (bf16, row stride ld_dst) = acc[b, h, s, d] (fp32): one thread per 8 values
+__global__ void __launch_bounds__(256)
+dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dst, int64_t ld_dst, int B, int S, int Hq) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t total = static_cast<int64_t>(B) * S * Hq * (HD / 8);
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / per_row;
-    const int c = static_cast<int>(i % per_row) * 8;
-    const float4 x = *reinterpret_cast<const float4*>(src + r * ld_src + c);
-    const float4 y = *reinterpret_cast<const float4*>(src + r * ld_src + c + 4);
+    const int c = static_cast<int>(i % (HD / 8)) * 8;
+    int64_t r = i / (HD / 8);              // (b, s, h) with h fastest: consecutive threads write one token row
+    const int h = static_cast<int>(r % Hq);
+    r /= Hq;
+    const int s = static_cast<int>(r % S), b = static_cast<int>(r / S);
+    const float* src = acc + ((static_cast<int64_t>(b) * Hq + h) * S + s) * HD + c;
+    const float4 x = *reinterpret_cast<const float4*>(src);
+    const float4 y = *reinterpret_cast<const float4*>(src + 4);
     uint4 pk;
     pk.x = pack_bf16x2(x.x, x.y);
     pk.y = pack_bf16x2(x.z, x.w);
     pk.z = pack_bf16x2(y.x, y.y);
     pk.w = pack_bf16x2(y.z, y.w);
-    *reinterpret_cast<uint4*>(dst + r * ld_dst + c) = pk;
+    *reinterpret_cast<uint4*>(dst + (static_cast<int64_t>(b) * S + s) * ld_dst + h * HD + c) = pk;
   }
 }
 
 }  // namespace
 
+int attn_bwd_stats(const void* d_o, const void* o, const float* lse, float* nds, float* nlse2, float* dq_acc, int B,
+                   int S, int Hq, cudaStream_t stream) {
+  const int64_t warps = static_cast<int64_t>(B) * S;  // one warp per token row
+  return launch_pdl(attn_bwd_stats_kernel, dim3(static_cast<int>((warps + 7) / 8)), dim3(256), 0, stream,
+                    reinterpret_cast<const __nv_bfloat16*>(d_o), reinterpret_cast<const __nv_bfloat16*>(o), lse, nds,
+                    nlse2, dq_acc, B, S, Hq, 1.f / sqrtf(static_cast<float>(HD))) == cudaSuccess
+             ? 0
+             : -21;
+}
+
 int attn_bwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, const void* d_o, float* dq_acc,
-                   int64_t ld_dq, void* dk, void* dv, int64_t ld_dkv, const float* delta, const float* lse2, int B,
-                   int Sq, int Skv, int Hq, int Hkv, bool causal, int* err, cudaStream_t stream) {
+                   void* dk, void* dv, int64_t ld_dkv, const float* nds, const float* nlse2, int B, int Sq, int Skv,
+                   int Hq, int Hkv, bool causal, int* err, cudaStream_t stream) {
   if (Sq % 128 != 0 || Skv % 128 != 0 || Hq % Hkv != 0 || B <= 0 || Sq <= 0 || Skv <= 0) return -1;
   if (causal && Sq != Skv) return -2;
-  if (ld_dq % 4 != 0 || ld_dkv % 8 != 0 || (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15))
+  if (ld_dkv % 8 != 0 || (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15) ||
+      (reinterpret_cast<uintptr_t>(dq_acc) & 15))
     return -3;
   const uint64_t Mq = static_cast<uint64_t>(B) * Sq, Mk = static_cast<uint64_t>(B) * Skv;
   CUtensorMap tq, tk, tv, tdo;
@@ -412,21 +523,16 @@ int attn_bwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand
   if (!ensure_dynamic_smem(reinterpret_cast<const void*>(attn_bwd_fused_kernel), SMEM_BYTES)) return -20;
   FusedArgs a{};
   a.dq_acc = dq_acc;
-  a.ld_dq = ld_dq;
   a.dk = reinterpret_cast<__nv_bfloat16*>(dk);
   a.dv = reinterpret_cast<__nv_bfloat16*>(dv);
   a.ld_dkv = ld_dkv;
-  a.delta = delta;
-  a.lse2 = lse2;
+  a.nds = nds;
+  a.nlse2 = nlse2;
   a.B = B; a.Sq = Sq; a.Skv = Skv; a.Hq = Hq; a.Hkv = Hkv;
   a.q_col0 = static_cast<int>(q.col0);
   a.k_col0 = static_cast<int>(k.col0);
   a.v_col0 = static_cast<int>(v.col0);
   a.causal = causal ? 1 : 0;
-  {
-    const char* e = std::getenv("TORCHURE_B200_ATTN_DBG");
-    a.dbg = e ? atoi(e) : 0;
-  }
   a.scale = 1.f / sqrtf(static_cast<float>(HD));
   a.scale_log2 = a.scale * 1.4426950408889634f;
   const int grid = (Skv / 128) * B * Hkv;
@@ -436,13 +542,12 @@ int attn_bwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand
   return 0;
 }
 
-int cast_rows_f32_to_bf16(const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int cols,
-                          cudaStream_t stream) {
-  if (cols % 8 != 0 || ld_src % 4 != 0 || ld_dst % 8 != 0) return -1;
-  const int64_t total = rows * (cols / 8);
+int attn_dq_convert(const float* dq_acc, void* dst, int64_t ld_dst, int B, int S, int Hq, cudaStream_t stream) {
+  if (ld_dst % 8 != 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return -1;
+  const int64_t total = static_cast<int64_t>(B) * S * Hq * (HD / 8);
   const int grid = static_cast<int>(total / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  return launch_pdl(cast_rows_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, stream, src, ld_src,
-                    reinterpret_cast<__nv_bfloat16*>(dst), ld_dst, rows, cols) == cudaSuccess
+  return launch_pdl(dq_convert_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, stream, dq_acc,
+                    reinterpret_cast<__nv_bfloat16*>(dst), ld_dst, B, S, Hq) == cudaSuccess
              ? 0
              : -21;
 }

@@ -122,23 +122,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
+      // Descriptors are built once per operand; a K step only adds a constant to the 14-bit address field (16-byte
+      // units; every operand lies below 256 KB, so the sum never carries into the next field).
+      uint64_t dQ[2], dK[KV_STAGES], dV[KV_STAGES];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) dQ[t] = make_desc_sw128(smem_u32(sQ + t * TILE_BYTES), 16, 1024);
+#pragma unroll
+      for (int st = 0; st < KV_STAGES; ++st) {
+        dK[st] = make_desc_sw128(smem_u32(sKV + st * 2 * TILE_BYTES), 16, 1024);
+        dV[st] = make_desc_sw128(smem_u32(sKV + st * 2 * TILE_BYTES + TILE_BYTES), HALF_BYTES, 1024);
+      }
       auto issue_s = [&](int t, int stage) {
-        const uint32_t qa = smem_u32(sQ + t * TILE_BYTES);
-        const uint32_t ka = smem_u32(sKV + stage * 2 * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t o = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_f16_ss(tmem_base + t * 128, make_desc_sw128(qa + o, 16, 1024), make_desc_sw128(ka + o, 16, 1024),
-                      idesc_s, ks != 0 ? 1u : 0u);
+          const uint64_t o = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
+          umma_f16_ss(tmem_base + t * 128, dQ[t] + o, dK[stage] + o, idesc_s, ks != 0 ? 1u : 0u);
         }
         umma_commit(&bars->s_full[t]);
       };
       auto issue_pv = [&](int t, int stage, bool first) {
-        const uint32_t va = smem_u32(sKV + stage * 2 * TILE_BYTES + TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8,
-                      make_desc_sw128(va + ks * 2048, HALF_BYTES, 1024), idesc_pv, (first && ks == 0) ? 0u : 1u);
+          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8, dV[stage] + ks * (2048 >> 4), idesc_pv,
+                      (first && ks == 0) ? 0u : 1u);
         }
         umma_commit(&bars->o_done[t]);
       };

@@ -28,17 +28,19 @@ struct AttnOperand {
 };
 
 // Single-pass backward (attention_bwd_fused_sm100.cu): five tile products per block pair instead of seven.
-//   q [B*Sq rows], k / v [B*Skv rows], d_o [B*Sq, Hq*128] bf16; delta / lse2 [B, Hq, Sq] from attn_bwd_prep
-//   dq_acc  fp32 [B*Sq, ld_dq], head h at column 128 h: every CTA ADDS its partial dQ tiles, so it must hold zeros
-//           (or a running sum to extend) on entry
+//   q [B*Sq rows], k / v [B*Skv rows], d_o [B*Sq, Hq*128] bf16
+//   nds / nlse2  [B, Hq, Sq] fp32 from attn_bwd_stats: -rowsum(dO*O)/sqrt(d) and -lse*log2(e)
+//   dq_acc  fp32 [B, Hq, Sq, 128] (head-major): every CTA ADDS its partial dQ tiles, so it must hold zeros (which
+//           attn_bwd_stats writes) or a running sum to extend on entry; attn_dq_convert turns it into bf16 columns
 //   dk, dv  bf16 destinations of the first row of KV head 0 (row stride ld_dkv elements, 16-byte aligned)
 //   causal  query block qb sees key blocks <= qb (needs Sq == Skv); false = every query sees every key
 // Needs Sq % 128 == 0, Skv % 128 == 0 and Hq % Hkv == 0.
+int attn_bwd_stats(const void* d_o, const void* o, const float* lse, float* nds, float* nlse2, float* dq_acc, int B,
+                   int S, int Hq, cudaStream_t stream);
 int attn_bwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, const void* d_o, float* dq_acc,
-                   int64_t ld_dq, void* dk, void* dv, int64_t ld_dkv, const float* delta, const float* lse2, int B,
-                   int Sq, int Skv, int Hq, int Hkv, bool causal, int* err, cudaStream_t stream);
-// dst[r, c] (bf16, row stride ld_dst) = src[r, c] (fp32, row stride ld_src) for c < cols (a multiple of 8)
-int cast_rows_f32_to_bf16(const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows, int cols,
-                          cudaStream_t stream);
+                   void* dk, void* dv, int64_t ld_dkv, const float* nds, const float* nlse2, int B, int Sq, int Skv,
+                   int Hq, int Hkv, bool causal, int* err, cudaStream_t stream);
+// dst[(b S + s), 128 h + d] (bf16, row stride ld_dst elements) = dq_acc[b, h, s, d]
+int attn_dq_convert(const float* dq_acc, void* dst, int64_t ld_dst, int B, int S, int Hq, cudaStream_t stream);
 
 }  // namespace tb

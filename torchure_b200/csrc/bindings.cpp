@@ -62,7 +62,10 @@ void add_rmsnorm_fwd(c10::optional<torch::Tensor> x, c10::optional<torch::Tensor
                      torch::Tensor& h, torch::Tensor& rstd, double eps) {
   const int M = (int)h.size(0), D = (int)h.size(1);
   TORCH_CHECK(D % 4 == 0, "rmsnorm: D must be a multiple of 4");
-  tb::add_rmsnorm_fwd(opt_ptr<float>(x), opt_ptr<__nv_bfloat16>(y), opt_ptr<int64_t>(ids), opt_ptr<float>(table),
+  const bool bf16_table = table.has_value() && table->defined() && table->scalar_type() == torch::kBFloat16;
+  TORCH_CHECK(!bf16_table || (x_out.has_value() && x_out->defined()), "a bf16 table needs x_out");
+  tb::add_rmsnorm_fwd(opt_ptr<float>(x), opt_ptr<__nv_bfloat16>(y), opt_ptr<int64_t>(ids),
+                      bf16_table ? nullptr : opt_ptr<float>(table), bf16_table ? opt_ptr<__nv_bfloat16>(table) : nullptr,
                       w.data_ptr<float>(), opt_mptr<float>(x_out), bfm(h), rstd.data_ptr<float>(), M, D, (float)eps,
                       cur_stream());
 }
@@ -87,10 +90,16 @@ void qknorm_rope_fwd(const torch::Tensor& qkv, const torch::Tensor& qw, const to
 
 void qknorm_rope_bwd(torch::Tensor& dqkv, const torch::Tensor& qkv, const torch::Tensor& qw, const torch::Tensor& kw,
                      const torch::Tensor& cos, const torch::Tensor& sin, torch::Tensor& dqw, torch::Tensor& dkw,
-                     int64_t S, int64_t Hq, int64_t Hkv, double eps, bool use_norm) {
+                     int64_t S, int64_t Hq, int64_t Hkv, double eps, bool use_norm,
+                     c10::optional<torch::Tensor> dq_acc) {
   TORCH_CHECK(qkv.size(1) == (Hq + 2 * Hkv) * 128, "qknorm_rope: head_dim must be 128");
+  if (dq_acc.has_value() && dq_acc->defined())
+    TORCH_CHECK(dq_acc->scalar_type() == torch::kFloat32 && dq_acc->is_contiguous() &&
+                    dq_acc->numel() == qkv.size(0) * Hq * 128,
+                "qknorm_rope_bwd: dq_acc must be fp32 [B, Hq, S, 128]");
   tb::qknorm_rope_bwd(bfm(dqkv), bf(qkv), qw.data_ptr<float>(), kw.data_ptr<float>(), cos.data_ptr<float>(),
-                      sin.data_ptr<float>(), dqw.data_ptr<float>(), dkw.data_ptr<float>(), (int)qkv.size(0), (int)S,
+                      sin.data_ptr<float>(), dqw.data_ptr<float>(), dkw.data_ptr<float>(), opt_ptr<float>(dq_acc),
+                      (int)qkv.size(0), (int)S,
                       (int)Hq, (int)Hkv, 128, (float)eps, use_norm ? 1 : 0, num_sms(), cur_stream());
 }
 

@@ -319,6 +319,80 @@ broadcast_kernel(CommCtx c, uint64_t off, void* buf, int64_t nvec, int src, int 
   }
 }
 
+// ---- sharded-training collectives on tensors that LIVE in the symmetric allocation (no staging copies) ----------
+// A segment is a matrix of `world` equal row chunks at byte offset off of every rank's allocation (nvec 16-byte
+// vectors per chunk); chunk r is the shard that rank r owns.
+
+// In-place all-gather: every rank pushes its own chunk of every segment into every peer's copy (one multimem.st
+// through the switch above two ranks, posted peer stores at two).  The first handshake says "my consumers of the old
+// contents are done", the second "every chunk has landed".
+__global__ void __launch_bounds__(CT)
+all_gather_inplace_kernel(CommCtx c, CommSegments segs, int use_mc) {
+  if (!block_barrier(c, 0, c.world)) return;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * CT;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x;
+  for (int sgm = 0; sgm < segs.n; ++sgm) {
+    const int64_t nvec = segs.nvec[sgm];
+    const uint64_t base = segs.off[sgm] + static_cast<uint64_t>(c.rank) * nvec * 16;
+    const uint8_t* mine = reinterpret_cast<const uint8_t*>(c.peer_bufs[c.rank] + base);
+    for (int64_t i = first; i < nvec; i += step * UNROLL) {
+      V4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (i + u * step < nvec) v[u] = ld16(mine + (i + u * step) * 16);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int64_t k = i + u * step;
+        if (k >= nvec) continue;
+        if (use_mc) {
+          mc_st(reinterpret_cast<void*>(c.mc_buf + base + k * 16), v[u]);
+        } else {
+          for (int p = 1; p < c.world; ++p)
+            st16(reinterpret_cast<void*>(c.peer_bufs[(c.rank + p) % c.world] + base + k * 16), v[u]);
+        }
+      }
+    }
+  }
+  block_barrier(c, 1, c.world);
+}
+
+// Reduce-scatter out of symmetric memory: out[s] (local fp32) = op over ranks of chunk `rank` of segment s.  The sum
+// of squares of everything this rank wrote is published to every rank's partial table like all_reduce_kernel does.
+// The first handshake says "my contribution is complete", the second "I no longer read your buffer".
+__global__ void __launch_bounds__(CT)
+reduce_scatter_symm_kernel(CommCtx c, CommSegments segs, int op, int use_mc, int sq_slot) {
+  if (!block_barrier(c, 0, c.world)) return;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * CT;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * CT + threadIdx.x;
+  float sq = 0.f;
+  for (int sgm = 0; sgm < segs.n; ++sgm) {
+    const int64_t nvec = segs.nvec[sgm];
+    const uint64_t base = segs.off[sgm] + static_cast<uint64_t>(c.rank) * nvec * 16;
+    uint8_t* out = reinterpret_cast<uint8_t*>(segs.out[sgm]);
+    for (int64_t i = first; i < nvec; i += step * UNROLL) {
+      Acc<kF32> acc[UNROLL];
+      reduce_batch<kF32>(c, base, i, step, nvec, op, use_mc != 0, acc);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int64_t k = i + u * step;
+        if (k < nvec) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) sq += acc[u].f[e] * acc[u].f[e];
+          st16(out + k * 16, acc[u].store());
+        }
+      }
+    }
+  }
+  if (sq_slot >= 0) {
+    sq = block_reduce_sum(sq);
+    if (threadIdx.x < c.world) {
+      float* table = reinterpret_cast<float*>(c.peer_bufs[threadIdx.x] + kFlagBytes);
+      table[(static_cast<int64_t>(sq_slot) * kCommMaxRanks + c.rank) * kCommMaxBlocks + blockIdx.x] = sq;
+    }
+  }
+  block_barrier(c, 1, c.world);
+}
+
 __global__ void __launch_bounds__(CT) barrier_kernel(CommCtx c, int pretend_world) {
   block_barrier(c, 0, pretend_world);
 }
@@ -365,6 +439,15 @@ void comm_all_to_all(const CommCtx& c, uint64_t dst_off, const void* in, void* o
 void comm_broadcast(const CommCtx& c, uint64_t off, void* buf, int64_t n, int dtype, int src, bool use_mc, int blocks,
                     cudaStream_t stream) {
   broadcast_kernel<<<blocks, CT, 0, stream>>>(c, off, buf, vecs(n, dtype), src, use_mc);
+}
+
+void comm_all_gather_inplace(const CommCtx& c, const CommSegments& segs, bool use_mc, int blocks, cudaStream_t stream) {
+  all_gather_inplace_kernel<<<blocks, CT, 0, stream>>>(c, segs, use_mc);
+}
+
+void comm_reduce_scatter_symm(const CommCtx& c, const CommSegments& segs, int op, bool use_mc, int sq_slot, int blocks,
+                              cudaStream_t stream) {
+  reduce_scatter_symm_kernel<<<blocks, CT, 0, stream>>>(c, segs, op, use_mc, sq_slot);
 }
 
 void comm_barrier(const CommCtx& c, uint32_t, int pretend_world, cudaStream_t stream) {

@@ -50,6 +50,22 @@ void comm_all_to_all(const CommCtx& c, uint64_t dst_off, const void* in, void* o
 // broadcast (in place on buf) from rank `src`; staging n elements.
 void comm_broadcast(const CommCtx& c, uint64_t off, void* buf, int64_t n, int dtype, int src, bool use_mc, int blocks,
                     cudaStream_t stream);
+// Segments of the symmetric allocation for the sharded-training collectives: segment s holds `world` equal chunks
+// of nvec[s] 16-byte vectors at byte offset off[s] (chunk r = rank r's shard); out[s] is a local fp32 destination.
+constexpr int kCommMaxSegments = 8;
+struct CommSegments {
+  int n;
+  uint64_t off[kCommMaxSegments];
+  int64_t nvec[kCommMaxSegments];
+  void* out[kCommMaxSegments];
+};
+// In place: every rank's own chunk of every segment is replicated into all peers' copies (no staging, no copy-out).
+void comm_all_gather_inplace(const CommCtx& c, const CommSegments& segs, bool use_mc, int blocks, cudaStream_t stream);
+// fp32: out[s] = op over ranks of chunk `rank` of segment s, read straight from the peers' copies; with sq_slot >= 0
+// the sum of squares of this rank's results goes to every rank's partial table at [sq_slot][rank][block].
+void comm_reduce_scatter_symm(const CommCtx& c, const CommSegments& segs, int op, bool use_mc, int sq_slot, int blocks,
+                              cudaStream_t stream);
+
 // cross-rank barrier only (also the bounded-wait self test: with world == 1 and pretend_world > 1 nothing ever
 // arrives and the kernel records kErrPeerFlagWait).
 void comm_barrier(const CommCtx& c, uint32_t generation, int pretend_world, cudaStream_t stream);

@@ -36,6 +36,7 @@ void register_comm(pybind11::module_& m) {
   m.attr("COMM_PARTIAL_BYTES") = tb::kPartialBytes;
   m.attr("COMM_MAX_BLOCKS") = tb::kCommMaxBlocks;
   m.attr("COMM_MAX_RANKS") = tb::kCommMaxRanks;
+  m.attr("COMM_MAX_SEGMENTS") = tb::kCommMaxSegments;
   m.def("comm_error_word", [] { return comm_err_word(); });
   m.def("comm_all_reduce", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
                               int64_t off, int64_t n, int64_t dtype, int64_t op, bool use_mc, int64_t sq_slot,
@@ -72,6 +73,37 @@ void register_comm(pybind11::module_& m) {
                              int64_t blocks) {
     tb::comm_broadcast(make_ctx(peers, mc, rank, world, limit), off, buf.data_ptr(), n, dt_of(dtype), (int)src, use_mc,
                        (int)blocks, cs());
+  });
+  // segments: (byte offset in the symmetric allocation, elements per chunk); element size from dtype
+  m.def("comm_all_gather_inplace", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                                      std::vector<int64_t> offs, std::vector<int64_t> chunk_bytes, bool use_mc,
+                                      int64_t blocks) {
+    TORCH_CHECK(offs.size() == chunk_bytes.size() && offs.size() <= (size_t)tb::kCommMaxSegments, "too many segments");
+    tb::CommSegments sg{};
+    sg.n = (int)offs.size();
+    for (int i = 0; i < sg.n; ++i) {
+      TORCH_CHECK(offs[i] % 16 == 0 && chunk_bytes[i] % 16 == 0, "segments must be 16-byte aligned");
+      sg.off[i] = (uint64_t)offs[i];
+      sg.nvec[i] = chunk_bytes[i] / 16;
+    }
+    tb::comm_all_gather_inplace(make_ctx(peers, mc, rank, world, limit), sg, use_mc, (int)blocks, cs());
+  });
+  m.def("comm_reduce_scatter_symm", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
+                                       std::vector<int64_t> offs, std::vector<torch::Tensor> outs, int64_t op,
+                                       bool use_mc, int64_t sq_slot, int64_t blocks) {
+    TORCH_CHECK(offs.size() == outs.size() && offs.size() <= (size_t)tb::kCommMaxSegments, "too many segments");
+    tb::CommSegments sg{};
+    sg.n = (int)offs.size();
+    for (int i = 0; i < sg.n; ++i) {
+      TORCH_CHECK(outs[i].scalar_type() == torch::kFloat32 && outs[i].is_contiguous(), "fp32 contiguous shards");
+      const int64_t bytes = outs[i].numel() * 4;
+      TORCH_CHECK(offs[i] % 16 == 0 && bytes % 16 == 0 && ((uintptr_t)outs[i].data_ptr() & 15) == 0, "16-byte alignment");
+      sg.off[i] = (uint64_t)offs[i];
+      sg.nvec[i] = bytes / 16;
+      sg.out[i] = outs[i].data_ptr();
+    }
+    tb::comm_reduce_scatter_symm(make_ctx(peers, mc, rank, world, limit), sg, (int)op, use_mc, (int)sq_slot, (int)blocks,
+                                 cs());
   });
   m.def("ag_gemm", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit, int64_t a_off,
                       int64_t g_off, int64_t epoch, torch::Tensor b, torch::Tensor c, int64_t M, int64_t K, bool b_mn) {

@@ -40,7 +40,8 @@ __device__ __forceinline__ uint32_t f2_to_bf2(float a, float b) {
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 add_rmsnorm_fwd_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ y,
-                       const int64_t* __restrict__ ids, const float* __restrict__ table, const float* __restrict__ w,
+                       const int64_t* __restrict__ ids, const float* __restrict__ table,
+                       const __nv_bfloat16* __restrict__ table_bf16, const float* __restrict__ w,
                        float* __restrict__ x_out, __nv_bfloat16* __restrict__ h, float* __restrict__ rstd, int M,
                        int D, float eps) {
   pdl_wait();
@@ -48,14 +49,23 @@ add_rmsnorm_fwd_kernel(const float* __restrict__ x, const __nv_bfloat16* __restr
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= M) return;
-  const float* xr = ids ? table + ids[row] * static_cast<int64_t>(D) : x + static_cast<int64_t>(row) * D;
+  // the gathered row comes from the fp32 table, or from its bf16 copy when only that exists whole (sharded masters)
+  const __nv_bfloat16* tr = (ids && table_bf16) ? table_bf16 + ids[row] * static_cast<int64_t>(D) : nullptr;
+  const float* xr = tr ? nullptr : (ids ? table + ids[row] * static_cast<int64_t>(D) : x + static_cast<int64_t>(row) * D);
   const __nv_bfloat16* yr = y ? y + static_cast<int64_t>(row) * D : nullptr;
   float* xo = x_out ? x_out + static_cast<int64_t>(row) * D : nullptr;
   __nv_bfloat16* hr = h + static_cast<int64_t>(row) * D;
   const int nvec = D >> 2;
   float ss = 0.f;
   for (int i = lane; i < nvec; i += 32) {
-    float4 v = reinterpret_cast<const float4*>(xr)[i];
+    float4 v;
+    if (tr) {
+      uint2 u = reinterpret_cast<const uint2*>(tr)[i];
+      float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y);
+      v = make_float4(a.x, a.y, b.x, b.y);
+    } else {
+      v = reinterpret_cast<const float4*>(xr)[i];
+    }
     if (yr) {
       uint2 u = reinterpret_cast<const uint2*>(yr)[i];
       float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y);
@@ -364,8 +374,8 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __res
 __global__ void __launch_bounds__(128, 4)
 qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ qkv,
                        const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ cos_t,
-                       const float* __restrict__ sin_t, float* __restrict__ dqw, float* __restrict__ dkw, int M, int S,
-                       int Hq, int Hkv, float eps, int use_norm) {
+                       const float* __restrict__ sin_t, float* __restrict__ dqw, float* __restrict__ dkw,
+                       const float* __restrict__ dq_acc, int M, int S, int Hq, int Hkv, float eps, int use_norm) {
   pdl_wait();
   pdl_launch_dependents();
   const int heads = Hq + Hkv;
@@ -400,14 +410,24 @@ qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __
     load4f(sin_t + static_cast<int64_t>(pos) * 128 + sub * 4, sn);
     __nv_bfloat16* dptr = dqkv + static_cast<int64_t>(row) * ld + sub * 4;
     const __nv_bfloat16* xptr = qkv + static_cast<int64_t>(row) * ld + sub * 4;
+    // dq may still sit in the head-major fp32 accumulator [B, Hq, S, 128] of the single-pass attention backward: it
+    // is rounded to bf16 here, on the way in, instead of by a conversion pass of its own
+    const float* aptr = dq_acc ? dq_acc + (static_cast<int64_t>(row / S) * Hq * S + pos) * 128 + sub * 4 : nullptr;
     // software pipeline: the loads of head pair hp + 1 are in flight while pair hp is processed
     uint2 dl[1], dh[1], xl[1], xh[1], ndl, ndh, nxl, nxh;
     auto fetch = [&](int hp, uint2& a0, uint2& a1, uint2& b0, uint2& b1) {
       const int h = 2 * hp + hsel;
       a0 = a1 = b0 = b1 = make_uint2(0u, 0u);
       if (hp < pairs && h < heads) {
-        a0 = *reinterpret_cast<const uint2*>(dptr + h * 128);
-        a1 = *reinterpret_cast<const uint2*>(dptr + h * 128 + 64);
+        if (aptr != nullptr && h < Hq) {
+          const float4 f0 = *reinterpret_cast<const float4*>(aptr + static_cast<int64_t>(h) * S * 128);
+          const float4 f1 = *reinterpret_cast<const float4*>(aptr + static_cast<int64_t>(h) * S * 128 + 64);
+          a0 = make_uint2(f2_to_bf2(f0.x, f0.y), f2_to_bf2(f0.z, f0.w));
+          a1 = make_uint2(f2_to_bf2(f1.x, f1.y), f2_to_bf2(f1.z, f1.w));
+        } else {
+          a0 = *reinterpret_cast<const uint2*>(dptr + h * 128);
+          a1 = *reinterpret_cast<const uint2*>(dptr + h * 128 + 64);
+        }
         if (use_norm) {
           b0 = *reinterpret_cast<const uint2*>(xptr + h * 128);
           b1 = *reinterpret_cast<const uint2*>(xptr + h * 128 + 64);
@@ -702,9 +722,11 @@ inline int grid_for(int64_t work_items, int threads, int cap) {
 
 }  // namespace
 
-void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids, const float* table, const float* w,
-                     float* x_out, __nv_bfloat16* h, float* rstd, int M, int D, float eps, cudaStream_t stream) {
-  launch_pdl(add_rmsnorm_fwd_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, x, y, ids, table, w, x_out, h, rstd, M, D, eps);
+void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids, const float* table,
+                     const __nv_bfloat16* table_bf16, const float* w, float* x_out, __nv_bfloat16* h, float* rstd, int M,
+                     int D, float eps, cudaStream_t stream) {
+  launch_pdl(add_rmsnorm_fwd_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, x, y, ids, table, table_bf16, w, x_out, h,
+             rstd, M, D, eps);
 }
 
 void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const float* rstd, const float* dx_in,
@@ -732,12 +754,12 @@ void qknorm_rope_fwd(const __nv_bfloat16* qkv, const float* qw, const float* kw,
 }
 
 void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
-                     const float* sin, float* dqw, float* dkw, int M, int S, int Hq, int Hkv, int hd, float eps,
-                     int use_norm, int num_sms, cudaStream_t stream) {
+                     const float* sin, float* dqw, float* dkw, const float* dq_acc, int M, int S, int Hq, int Hkv, int hd,
+                     float eps, int use_norm, int num_sms, cudaStream_t stream) {
   (void)hd;
   const int grid = std::min((M + 3) / 4, num_sms * 4);  // persistent: four 4-warp CTAs per SM, a warp walks rows
-  launch_pdl(qknorm_rope_bwd_kernel, dim3(grid), dim3(128), 0, stream, dqkv, qkv, qw, kw, cos, sin, dqw, dkw, M, S, Hq, Hkv, eps,
-                                                   use_norm);
+  launch_pdl(qknorm_rope_bwd_kernel, dim3(grid), dim3(128), 0, stream, dqkv, qkv, qw, kw, cos, sin, dqw, dkw, dq_acc, M, S,
+             Hq, Hkv, eps, use_norm);
 }
 
 void swiglu_fwd(const __nv_bfloat16* gu, __nv_bfloat16* act, int M, int F, cudaStream_t stream) {

@@ -83,22 +83,28 @@ def attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=True):
     return out.transpose(1, 2).reshape(B * S, Hq * hd), AttnState("sdpa")
 
 
-def attn_bwd(d_o, qk, qkv, state: AttnState, B, S, Hq, Hkv, hd):
-    """Returns dqkv (M, (Hq+2Hkv)*hd) bf16 = [dq (post-rope) | dk (post-rope) | dv]."""
+def attn_bwd(d_o, qk, qkv, state: AttnState, B, S, Hq, Hkv, hd, keep_dq_fp32: bool = False):
+    """Returns dqkv (M, (Hq+2Hkv)*hd) bf16 = [dq (post-rope) | dk (post-rope) | dv].
+
+    With `keep_dq_fp32` the result is ``(dqkv, dq_acc)``: when the single-pass kernel ran, ``dq_acc`` is its head-major
+    fp32 dQ accumulator (B, Hq, S, hd) and the q columns of ``dqkv`` are left unwritten for the consumer that reads
+    the accumulator (``kernels.qknorm_rope_bwd_(..., dq_acc=)``); otherwise ``dq_acc`` is None."""
     M = B * S
     dqkv = new_output("attn_bwd.dqkv", M, (Hq + 2 * Hkv) * hd, dtype=torch.bfloat16, device=d_o.device)
     if state.impl == "sm100":
+        dq_acc = None
         if _BWD == "fused":
-            ops.ext().attn_bwd_fused(d_o, qk, qkv, state.o, state.lse, dqkv, B, S, Hq, Hkv)
-            ops.count_launch(4)  # statistics, accumulator clear, fused kernel, dQ conversion
+            acc = ops.ext().attn_bwd_fused(d_o, qk, qkv, state.o, state.lse, dqkv, B, S, Hq, Hkv, not keep_dq_fp32)
+            ops.count_launch(2 if keep_dq_fp32 else 3)  # statistics (+ accumulator clear), fused kernel, conversion
+            dq_acc = acc if keep_dq_fp32 else None
         else:
             ops.ext().attn_bwd(d_o, qk, qkv, state.o, state.lse, dqkv, B, S, Hq, Hkv)
             ops.count_launch(3)
-        return dqkv
+        return (dqkv, dq_acc) if keep_dq_fp32 else dqkv
     out, ql, kl, vl = state.graph
     g = d_o.view(B, S, Hq, hd).transpose(1, 2)
     dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), g)
     dqkv[:, :Hq * hd].view(B, S, Hq, hd).copy_(dq.transpose(1, 2))
     dqkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, S, Hkv, hd).copy_(dk.transpose(1, 2))
     dqkv[:, (Hq + Hkv) * hd:].view(B, S, Hkv, hd).copy_(dv.transpose(1, 2))
-    return dqkv
+    return (dqkv, None) if keep_dq_fp32 else dqkv

@@ -84,6 +84,12 @@ class Sm100Engine:
         self.expect_tied_grad = False
         _ENGINE_OF_WEIGHT[id(model.lm_head.weight)] = self
         self.dummy = torch.zeros(1, device=dev)
+        # hooks of sharded strategies (parallel/fsdp_engine.py): the shadows are maintained outside (no refresh
+        # from the fp32 masters), tokens are looked up in the bf16 copy of the table, and `pre_block(i)` runs before
+        # block i reads its weights (i = -1: embedding at the bottom, head at the top)
+        self.external_shadows = False
+        self.bf16_embedding = False
+        self.pre_block = None
 
     # -- shadows -----------------------------------------------------------------------------
     def shadow_pairs(self):
@@ -92,6 +98,8 @@ class Sm100Engine:
         return list(self._pairs)
 
     def refresh(self) -> None:
+        if self.external_shadows:
+            return
         for p, shadow in self._pairs:
             v = p._version
             if self._versions.get(id(p)) != v:
@@ -111,7 +119,11 @@ class Sm100Engine:
         cos, sin = m.rope.tables(S, ids.device)
         x, y = None, None
         flat_ids = ids.reshape(-1)
+        if self.pre_block is not None:
+            self.pre_block(-1)
         for i, (block, sh) in enumerate(zip(m.blocks, self.layers)):
+            if self.pre_block is not None:
+                self.pre_block(i)
             g = block.gqa
             qn = g.q_norm.weight if g.qk_norm else self.dummy
             kn = g.k_norm.weight if g.qk_norm else self.dummy
@@ -141,7 +153,8 @@ class _BlockFn(torch.autograd.Function):
         use_norm = cfg["qk_norm"]
         cos, sin = eng.model.rope.tables(S, w1.device)
         if ids is not None:
-            x, h1, rstd1 = K.add_rmsnorm(None, None, w1, eps, ids=ids, table=table)
+            x, h1, rstd1 = K.add_rmsnorm(None, None, w1, eps, ids=ids,
+                                         table=eng.emb_shadow if eng.bf16_embedding else table)
         else:
             x, h1, rstd1 = K.add_rmsnorm(x_in, y_in, w1, eps)
         qkv = K.linear_fwd(h1, sh.wqkv)
@@ -190,14 +203,15 @@ class _BlockFn(torch.autograd.Function):
         # ---- attention
         d_o = K.linear_dgrad(dx1_b, sh.wo)
         out.wgrad((P["wo"],), dx1_b, o)
-        dqkv = attn_ops.attn_bwd(d_o, qk, qkv, ctx.attn_state, B, S, Hq, Hkv, hd)
+        dqkv, dq_acc = attn_ops.attn_bwd(d_o, qk, qkv, ctx.attn_state, B, S, Hq, Hkv, hd, keep_dq_fp32=True)
         ctx.attn_state = None
         del d_o
         if use_norm:
             dqn, dkn = out.small(P["qn"]), out.small(P["kn"])
         else:
             dqn = dkn = eng.dummy
-        K.qknorm_rope_bwd_(dqkv, qkv, qn, kn, cos, sin, dqn, dkn, S, Hq, Hkv, eps, use_norm)
+        K.qknorm_rope_bwd_(dqkv, qkv, qn, kn, cos, sin, dqn, dkn, S, Hq, Hkv, eps, use_norm, dq_acc=dq_acc)
+        del dq_acc
         if use_norm:
             out.done(P["qn"])
             out.done(P["kn"])
@@ -244,8 +258,8 @@ class _GradOut:
 
     def wgrad(self, params: tuple, dy: torch.Tensor, x: torch.Tensor) -> None:
         """dW[N, K] = dy[M, N]^T x[M, K]; `params` are the parameters whose rows make up N, in order."""
-        rows = [p.shape[0] for p in params]
         if self.sink is None:
+            rows = [p.shape[0] for p in params]
             dw = K.linear_wgrad(dy, x, out_dtype=torch.float32)
             at = 0
             for p, r in zip(params, rows):
@@ -253,6 +267,7 @@ class _GradOut:
                 at += r
             return
         dests = [self.sink.grad_dest(p) for p in params]
+        rows = [d[0].shape[0] for d in dests]   # a sharded strategy may have released the parameter's own storage
         contiguous = all(dests[i][0].data_ptr() + dests[i][0].numel() * 4 == dests[i + 1][0].data_ptr()
                          for i in range(len(dests) - 1))
         same_mode = all(d[1] == dests[0][1] for d in dests)

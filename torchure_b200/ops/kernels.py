@@ -113,8 +113,10 @@ def qknorm_rope(qkv, qw, kw, cos, sin, S, Hq, Hkv, eps, use_norm=True):
     return out
 
 
-def qknorm_rope_bwd_(dqkv, qkv, qw, kw, cos, sin, dqw, dkw, S, Hq, Hkv, eps, use_norm=True):
-    _C().qknorm_rope_bwd(dqkv, qkv, qw, kw, cos, sin, dqw, dkw, S, Hq, Hkv, eps, use_norm)
+def qknorm_rope_bwd_(dqkv, qkv, qw, kw, cos, sin, dqw, dkw, S, Hq, Hkv, eps, use_norm=True, dq_acc=None):
+    """In place on the q / k columns of dqkv.  `dq_acc` (fp32 [B, Hq, S, 128]): dq is read from there instead of the
+    q columns (what the single-pass attention backward leaves behind), saving its conversion pass."""
+    _C().qknorm_rope_bwd(dqkv, qkv, qw, kw, cos, sin, dqw, dkw, S, Hq, Hkv, eps, use_norm, dq_acc)
     ops.count_launch()
     return dqkv
 

@@ -16,13 +16,14 @@ OPTIMIZERS = {"adamw": AdamW, "sgd": optim.SGD}
 SCHEDULERS = {"wsd": WarmupStableDecay, "cosine": CosineWithWarmup}
 
 
-def build_optimizer(model: nn.Module, name: str, cfg: dict) -> optim.Optimizer:
+def build_optimizer(model: nn.Module | None, name: str, cfg: dict, params=None) -> optim.Optimizer:
+    """`params` overrides ``model.parameters()``: sharded strategies hand in their shard parameters instead."""
     cfg = dict(cfg)
     weight_decay = cfg.pop("weight_decay", 0.0)
     if name == "sgd":
         cfg.pop("betas", None)
         cfg.pop("fused", None)
-    params = [p for p in model.parameters() if p.requires_grad]
+    params = [p for p in (params if params is not None else model.parameters()) if p.requires_grad]
     groups = [
         {"params": [p for p in params if p.dim() >= 2], "weight_decay": weight_decay},
         {"params": [p for p in params if p.dim() < 2], "weight_decay": 0.0},

@@ -168,6 +168,22 @@ class FSDP:
         """The flat shards: hand these to the optimizer and to ``clip_grad_norm(..., shard_dims=(shard_dim,))``."""
         return [u.shard for u in self.units]
 
+    # the strategy interface shared with DDP and the engine variant (``train/trainer.py``)
+    fused = False
+
+    def optimizer_params(self) -> list[nn.Parameter]:
+        return self.parameters()
+
+    @property
+    def clip_shard_dims(self) -> tuple[str, ...]:
+        return (self.shard_dim,)
+
+    def sync(self) -> None:
+        """Reductions are issued synchronously from the hooks: nothing to wait for."""
+
+    def sq_norm(self):
+        return None
+
     def unshard_all(self) -> None:
         for u in self.units:
             u.unshard(self.mesh, self.shard_dim)

@@ -1,7 +1,11 @@
 """Training orchestration.
 
 Lifecycle (reference ``torchure/train/trainer.py:61-146``): mesh -> model -> init ->
-parallelize (DDP) -> objective -> optimizer -> scheduler -> data -> resume -> prefetcher.
+parallelize -> objective -> optimizer -> scheduler -> data -> resume -> prefetcher.
+The mesh of the config selects the strategy: ``dp`` builds DDP; ``dp_shard`` (optionally after
+``dp_replicate``) builds FSDP2 / HSDP (``parallel/fsdp_engine.py`` on the sm_100a engine,
+``parallel/fsdp.py`` hooks on the PyTorch path); a ``tp`` axis shards every block first
+(``parallel/tensor_parallel.py``).
 One optimizer step (reference ``trainer.py:371-402``): K micro-batches of forward+backward
 with ``requires_sync`` only on the last, ``ddp.sync()``, global grad-norm clip, optimizer,
 ``zero_grad``, scheduler, loss averaged over dp.
@@ -19,7 +23,7 @@ from datetime import datetime
 import torch
 
 from torchure_b200.ckpt import Checkpointer
-from torchure_b200.config import load_config, validate_config
+from torchure_b200.config import DATA_AXES, load_config, validate_config
 from torchure_b200.core.collective import all_reduce, barrier, enable_sm100
 from torchure_b200.core.grad_helper import clip_grad_norm, grad_norm_and_coef
 from torchure_b200.core.mesh import Mesh
@@ -56,13 +60,21 @@ class Trainer:
             torch.backends.cuda.matmul.allow_tf32 = True
             torch.backends.cudnn.allow_tf32 = True
         self.mesh = Mesh(self.config["mesh"])
-        self.dp_size = self.mesh.size("dp")
+        # the data axis: "dp", "dp_shard", or the row-major product of ("dp_replicate", "dp_shard")
+        data_axes = tuple(a for a in self.mesh.axes() if a in DATA_AXES)
+        if len(data_axes) > 1:
+            self.mesh.flatten(data_axes, "data")
+            self.data_axis = "data"
+        else:
+            self.data_axis = data_axes[0]
+        self.dp_size = self.mesh.size(self.data_axis)
         comm_cfg = self.config.get("comm", {})
         if self.on_gpu and comm_cfg.get("backend", "sm100") == "sm100":
             from torchure_b200 import ops
 
             if ops.available():
-                enable_sm100(self.mesh, "dp", comm_cfg.get("max_bytes", 64 << 20))
+                for axis in [self.data_axis] + [a for a in ("tp", "cp") if a in self.mesh.axes()]:
+                    enable_sm100(self.mesh, axis, comm_cfg.get("max_bytes", 64 << 20))
 
         self.ignore_index = self.config["objective"]["config"]["ignore_index"]
         self.tokenizer = None
@@ -76,7 +88,7 @@ class Trainer:
         self.model = self._parallelize(self.model)
         self.objective = build_objective(self.config["objective"]["name"], self.config["objective"]["config"])
         opt_cfg = self.config["optimizer"]
-        self.optimizer = build_optimizer(self.model, opt_cfg["name"], opt_cfg["config"])
+        self.optimizer = build_optimizer(self.model, opt_cfg["name"], opt_cfg["config"], params=self._opt_params)
         self.scheduler = build_scheduler(self.optimizer, opt_cfg["scheduler"])
         self.num_train_steps = opt_cfg["scheduler"]["total_steps"]
         self.max_norm = opt_cfg.get("max_norm")
@@ -120,14 +132,47 @@ class Trainer:
         model.init_weights()
 
     def _parallelize(self, model):
+        """Build the strategy the mesh asks for.  ``self.ddp`` is the data-parallel strategy object whatever its kind
+        (``requires_sync``, ``sync()``, ``sq_norm()``); ``self._opt_params`` is what the optimizer must hold when
+        that is not ``model.parameters()`` (flat or row shards)."""
+        axes = self.mesh.axes()
+        self._opt_params = None
+        self.sharded = "dp_shard" in axes
+        if "tp" in axes and self.mesh.size("tp") > 1:
+            from torchure_b200.parallel.tensor_parallel import parallelize_model
+
+            parallelize_model(model, self.mesh, "tp",
+                              sequence_parallel=self.config.get("tp", {}).get("sequence_parallel", False))
+        if self.sharded:
+            replicate = "dp_replicate" if "dp_replicate" in axes else None
+            engine_path = self.on_gpu and getattr(model, "impl", "torch") != "torch"
+            if engine_path:
+                from torchure_b200 import ops
+
+                engine_path = ops.available() and self.mesh.size("dp_shard") > 1
+            if engine_path:
+                from torchure_b200.parallel.fsdp_engine import EngineFSDP
+
+                self.ddp = EngineFSDP(model, self.mesh, "dp_shard", replicate,
+                                      comm_sms=self.config.get("fsdp", {}).get("comm_sms", 16))
+            else:
+                from torchure_b200.parallel.fsdp import FSDP
+
+                model.impl = "torch"    # the hook-driven units swap parameter storage under plain modules
+                self.ddp = FSDP(model, self.mesh, "dp_shard", replicate)
+            self._opt_params = self.ddp.optimizer_params()
+            return model
         ddp_cfg = self.config.get("ddp", {})
-        self.ddp = DDP(model, self.mesh, dim="dp", bucket_mb=ddp_cfg.get("bucket_mb", 25),
+        self.ddp = DDP(model, self.mesh, dim=self.data_axis, bucket_mb=ddp_cfg.get("bucket_mb", 25),
                        fused=ddp_cfg.get("fused"), merge_small=ddp_cfg.get("merge_small", True),
                        comm_sms=ddp_cfg.get("comm_sms", 16), sm_reserve=ddp_cfg.get("sm_reserve", 0))
         return model
 
     def _wire_engine(self) -> None:
         """Let the AdamW kernel refresh the bf16 shadow weights the sm_100a engine computes with."""
+        if hasattr(self.ddp, "attach_shadows"):
+            self.ddp.attach_shadows(self.optimizer)    # sharded: the shards' shadows are rows of the whole copies
+            return
         if not self.on_gpu or getattr(self.model, "impl", "torch") == "torch":
             return
         from torchure_b200 import ops
@@ -141,7 +186,7 @@ class Trainer:
         data_cfg = dict(self.config["data"])
         data_cfg.setdefault("vocab_size", self.config["model"]["config"]["vocab_size"])
         return build_dataloader(data_cfg, self.tokenizer, self.ignore_index,
-                                self.mesh.coordinate("dp"), self.mesh.size("dp"))
+                                self.mesh.coordinate(self.data_axis), self.mesh.size(self.data_axis))
 
     def _setup_wandb(self) -> None:
         self.wandb_run = None
@@ -176,9 +221,19 @@ class Trainer:
     def checkpoint(self, step: int) -> None:
         """Write the state after `step` completed steps; rank 0 writes replicas, every dp rank its loader."""
         self.check_device_errors()   # never persist the result of a step whose kernels gave up
-        if self.rank == 0:
+        if self.sharded:
+            # model.pt keeps the reference's unsharded keys (gathered; collective), optimizer state stays sharded:
+            # one file per shard coordinate, written by the first replica of that shard
+            full = self.ddp.full_state_dict()
+            if self.rank == 0:
+                self.checkpointer._write(full, step, "model.pt")
+            del full
+            if "dp_replicate" not in self.mesh.axes() or self.mesh.coordinate("dp_replicate") == 0:
+                self.checkpointer.save_optimizer(self.optimizer, step, shard=self.mesh.coordinate("dp_shard"))
+        elif self.rank == 0:
             self.checkpointer.save_model(self.model, step)
             self.checkpointer.save_optimizer(self.optimizer, step)
+        if self.rank == 0:
             self.checkpointer.save_scheduler(self.scheduler, step)
             self.checkpointer.save_trainer({
                 "step": step,
@@ -188,7 +243,7 @@ class Trainer:
                 "wandb_id": self.wandb_run.id if self.wandb_run else None,
             }, step)
         # the prefetcher knows the position of the first batch that was NOT consumed
-        self.checkpointer.save_dataloader(self.prefetcher, step, self.mesh.coordinate("dp"))
+        self.checkpointer.save_dataloader(self.prefetcher, step, self.mesh.coordinate(self.data_axis))
         barrier()
         if self.rank == 0:
             self.checkpointer.mark_complete(step)
@@ -208,13 +263,17 @@ class Trainer:
         state = self.checkpointer.load_trainer(step)
         assert state["config"]["mesh"] == self.config["mesh"], (
             f"cannot resume across a mesh change: checkpoint {state['config']['mesh']}, config {self.config['mesh']}")
-        self.checkpointer.load_model(self.model, step)
-        self.checkpointer.load_optimizer(self.optimizer, step)
+        if self.sharded:
+            self.ddp.load_full_state_dict(self.checkpointer._read(step, "model.pt"))
+            self.checkpointer.load_optimizer(self.optimizer, step, shard=self.mesh.coordinate("dp_shard"))
+        else:
+            self.checkpointer.load_model(self.model, step)
+            self.checkpointer.load_optimizer(self.optimizer, step)
         if self.resume_scheduler:
             self.checkpointer.load_scheduler(self.scheduler, step)
         else:
             self.scheduler.last_epoch = step
-        self.checkpointer.load_dataloader(self.dataloader, step, self.mesh.coordinate("dp"))
+        self.checkpointer.load_dataloader(self.dataloader, step, self.mesh.coordinate(self.data_axis))
         torch.set_rng_state(state["cpu_rng"])
         if self.on_gpu and state.get("cuda_rng") is not None:
             torch.cuda.set_rng_state(state["cuda_rng"], self.device)
@@ -239,6 +298,8 @@ class Trainer:
         AdamW.  `batches` (one dict per micro-batch) are used instead of the prefetcher when given."""
         K = self.microbatches_per_step
         loss = torch.zeros((), device=self.device)
+        if hasattr(self.ddp, "begin_step"):
+            self.ddp.begin_step()      # sharded: all-gather the bf16 weights the last optimizer step rewrote
         self.ddp.requires_sync = False
         for i in range(K - 1):
             loss += self.micro_train_step(batches[i] if batches else None)
@@ -246,14 +307,18 @@ class Trainer:
         loss += self.micro_train_step(batches[K - 1] if batches else None)
         self.ddp.sync()
         sq = self.ddp.sq_norm()
-        params = [p for p in self.model.parameters() if p.requires_grad]
+        params = self._opt_params if self._opt_params is not None else [
+            p for p in self.model.parameters() if p.requires_grad]
         if sq is not None and hasattr(self.optimizer, "set_grad_scale"):
             grad_norm, coef = grad_norm_and_coef(params, self.mesh, self.max_norm, shard_dims=(), presummed_sq=sq)
             if self.max_norm is not None:
                 self.optimizer.set_grad_scale(coef)
         else:
-            grad_norm = clip_grad_norm(params, self.mesh, self.max_norm, shard_dims=())
+            grad_norm = clip_grad_norm(params, self.mesh, self.max_norm,
+                                       shard_dims=getattr(self.ddp, "clip_shard_dims", ()))
         self.optimizer.step()
+        if hasattr(self.ddp, "mark_updated"):
+            self.ddp.mark_updated()
         self.optimizer.zero_grad()
         return loss, grad_norm
 
@@ -264,7 +329,7 @@ class Trainer:
             loss, grad_norm = self._device_step()
         self.scheduler.step()
         if self.dp_size > 1:
-            all_reduce(loss, self.mesh, "dp", "avg")
+            all_reduce(loss, self.mesh, self.data_axis, "avg")
         return {"loss": loss, "grad_norm": grad_norm}
 
     # -- CUDA-graph replay of the device step ----------------------------------------------------
