@@ -262,3 +262,31 @@ def test_poison_and_verify_mode():
             debug.verify()
     finally:
         debug.enable(False)
+
+
+def test_embedding_scatter_is_exact_and_repeatable():
+    """Deterministic multi-source scatter-add against index_add in fp64, with repeated ids inside and across sources;
+    two runs give identical bits, and the per-CTA corrections turn the old sum of squares into the new one."""
+    from torchure_b200.ops import kernels as K
+
+    torch.manual_seed(0)
+    V, D, M = 5000, 1024, 3000
+    srcs = []
+    for p in range(3):
+        ids = torch.randint(0, V, (M,), device="cuda")
+        ids[::7] = 11          # a hot row, hit hundreds of times by every source
+        srcs.append((ids, torch.randn(M, D, device="cuda")))
+    base = torch.randn(V, D, device="cuda")
+    want = base.double()
+    for ids, rows in srcs:
+        want.index_add_(0, ids, rows.double() * 0.25)
+    outs = []
+    for _ in range(2):
+        t = base.clone()
+        delta = torch.zeros(1024, device="cuda")
+        K.embedding_scatter_(srcs, t, M, scale=0.25, sq_delta=delta, blocks=592)
+        outs.append(t)
+        got_sq = base.double().pow(2).sum() + delta.double().sum()
+        assert abs(got_sq.item() - t.double().pow(2).sum().item()) < 1e-4 * t.double().pow(2).sum().item()
+    assert torch.equal(outs[0], outs[1])
+    torch.testing.assert_close(outs[0].double(), want, rtol=1e-5, atol=1e-4)

@@ -74,8 +74,9 @@ def _ddp_parity(rank, world):
     torch.manual_seed(100 + rank)  # different init per rank: the constructor must replicate rank 0
     model = Qwen3(**CFG).cuda()
     model.init_weights()
-    ddp = DDP(model, mesh, "dp", bucket_mb=1)
-    assert ddp.fused
+    # embed_tokens switches on the early reduction of the tied table's bucket plus the exchange of embedding rows
+    ddp = DDP(model, mesh, "dp", bucket_mb=1, embed_tokens=2 * 128)
+    assert ddp.fused and ddp.early_table is model.token_emb.weight
     torch.manual_seed(100)
     single = Qwen3(**CFG).cuda()
     single.init_weights()
@@ -375,3 +376,82 @@ def test_trainer_two_gpus_match_one(tmp_path):
     for x, y in zip(two, one):
         assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)
         assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
+
+
+# ---- long-context strategies on the attention kernels ----------------------------------------------------------------
+def _dense_attention(q, k, v):
+    """fp32 causal attention on (B, S, H, d) tensors."""
+    rep = q.shape[2] // k.shape[2]
+    qf, kf, vf = (t.float().transpose(1, 2) for t in (q, k, v))
+    o = torch.nn.functional.scaled_dot_product_attention(qf, kf.repeat_interleave(rep, 1), vf.repeat_interleave(rep, 1),
+                                                         is_causal=True)
+    return o.transpose(1, 2)
+
+
+def _ring_gpu(rank, world):
+    """Ring attention over zigzag chunks with every block pair on the tcgen05 kernels: forward and all three
+    gradients against dense attention over the whole sequence."""
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.ops import kernels
+    from torchure_b200.parallel.context_parallel import ring_attention_tokens, zigzag_split
+
+    mesh = Mesh({"cp": world})
+    g = torch.Generator(device="cuda").manual_seed(0)
+    B, Hq, Hkv, d = 1, 4, 2, 128
+    S = 2 * world * 256
+    q, k, v = (torch.randn(B, S, h, d, device="cuda", generator=g).bfloat16() for h in (Hq, Hkv, Hkv))
+    do = torch.randn(B, S, Hq, d, device="cuda", generator=g).bfloat16()
+    qf, kf, vf = (t.clone().float().requires_grad_() for t in (q, k, v))
+    ref = _dense_attention(qf, kf, vf)
+    ref.backward(do.float())
+    ql, kl, vl = (zigzag_split(t, world, rank, 1).clone().requires_grad_() for t in (q, k, v))
+    out = ring_attention_tokens(ql, kl, vl, mesh, "cp")
+    assert out.grad_fn is not None and "RingAttentionSm100" in type(out.grad_fn).__name__, type(out.grad_fn)
+    out.backward(zigzag_split(do, world, rank, 1))
+    kernels.check_error()
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+    assert rel(out, zigzag_split(ref.detach(), world, rank, 1)) < 1e-2
+    for name, got, want in (("dq", ql.grad, qf.grad), ("dk", kl.grad, kf.grad), ("dv", vl.grad, vf.grad)):
+        e = rel(got, zigzag_split(want, world, rank, 1))
+        assert e < 2e-2, (name, e)
+
+
+def test_ring_attention_on_kernels():
+    run_on_gpus(_ring_gpu, min(_world(), 4))
+
+
+def _ulysses_gpu(rank, world):
+    from torchure_b200.core import collective as C
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.ops import kernels
+    from torchure_b200.parallel.ulysses import ulysses_attention
+
+    mesh = Mesh({"cp": world})
+    C.enable_sm100(mesh, "cp", 64 << 20)     # the two all-to-alls run on the NVLink kernel
+    g = torch.Generator(device="cuda").manual_seed(0)
+    B, S, d = 1, 1024, 128
+    Hq, Hkv = 4 * world, 2 * world
+    q, k, v = (torch.randn(B, S, h, d, device="cuda", generator=g).bfloat16() for h in (Hq, Hkv, Hkv))
+    do = torch.randn(B, S, Hq, d, device="cuda", generator=g).bfloat16()
+    qf, kf, vf = (t.clone().float().requires_grad_() for t in (q, k, v))
+    ref = _dense_attention(qf, kf, vf)
+    ref.backward(do.float())
+    ql, kl, vl = (t.chunk(world, dim=1)[rank].clone().requires_grad_() for t in (q, k, v))
+    out = ulysses_attention(ql, kl, vl, mesh, "cp")      # default attention: the sm_100a flash_attention op
+    out.backward(do.chunk(world, dim=1)[rank])
+    kernels.check_error()
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+    assert rel(out, ref.detach().chunk(world, dim=1)[rank]) < 1e-2
+    for name, got, want in (("dq", ql.grad, qf.grad), ("dk", kl.grad, kf.grad), ("dv", vl.grad, vf.grad)):
+        e = rel(got, want.chunk(world, dim=1)[rank])
+        assert e < 2e-2, (name, e)
+
+
+def test_ulysses_on_kernels():
+    run_on_gpus(_ulysses_gpu, 2)

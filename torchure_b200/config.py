@@ -14,7 +14,7 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
     data          {name | synthetic, tokenizer, eos_token, pad_token, text_field, shuffle_buffer, seed,
                    num_workers, global_batch_size, micro_batch_size, seq_len, [pack_batch], [packer],
                    synthetic extras: vocab_size, eos_id, mean_doc_len}
-    [ddp]         {bucket_mb, [fused], [merge_small]}
+    [ddp]         {bucket_mb, [fused], [merge_small], [comm_sms], [early_embedding]}
     [fsdp]        {[comm_sms]}
     [tp]          {[sequence_parallel]}
     [comm]        {backend: "sm100" | "torch", [max_bytes]}

@@ -249,6 +249,8 @@ class SymmComm:
             out.view(self.world, n).copy_(dst[:, :n])
         return out
 
-    def barrier(self, pretend_world: int | None = None) -> None:
-        self.ext.comm_barrier(*self._ctx(), pretend_world or self.world)
+    def barrier(self, pretend_world: int | None = None, phase: int = 0) -> None:
+        """Cross-rank barrier on the current stream.  `phase` selects the flag row (0/1: collectives, 4/6: fused GEMMs;
+        2/3 are for barriers that may overlap a collective running on another stream)."""
+        self.ext.comm_barrier(*self._ctx(), pretend_world or self.world, phase)
         ops.count_launch()

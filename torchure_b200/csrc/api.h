@@ -44,6 +44,11 @@ void swiglu_bwd(const __nv_bfloat16* dact, const __nv_bfloat16* gu, __nv_bfloat1
                 cudaStream_t stream);
 // dtable[ids[r]] += dx[r]
 void embedding_bwd(const float* dx, const int64_t* ids, float* dtable, int M, int D, cudaStream_t stream);
+// Deterministic multi-source variant: dtable[id] += scale * sum_p sum_{r: ids_p[r] == id} rows_p[r] with a fixed
+// order of additions and no atomics (sources may be peer GPUs' buffers).  sq_delta (optional, `blocks` floats) receives
+// per-CTA sum(new^2 - old^2) of the touched elements.
+int embedding_scatter(int n_sources, const int64_t* const* ids, const float* const* rows, float* dtable, int M, int D,
+                      float scale, float* sq_delta, int blocks, cudaStream_t stream);
 // logits [C, V] bf16 (row stride ldl) -> per-row loss (0 for ignored rows) and, in place, dlogits scaled by
 // *inv_n_valid.
 void ce_softmax_grad(__nv_bfloat16* logits, int64_t ldl, const int64_t* labels, float* row_loss,

@@ -105,6 +105,9 @@ struct FusedArgs {
   const float* nlse2;  // [B, Hq, Sq]  -lse * log2(e)
   int B, Sq, Skv, Hq, Hkv;
   int q_col0, k_col0, v_col0;
+  // rows of batch b: q / dO at b * q_bstride + q_row0, k / v at b * kv_bstride + kv_row0; the statistics and the dQ
+  // accumulator are [B, Hq, stat_stride(, 128)] with this call's queries starting at stat_row0
+  int q_bstride, q_row0, kv_bstride, kv_row0, stat_stride, stat_row0;
   int causal;
   float scale, scale_log2;
 };
@@ -138,7 +141,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int kblk = static_cast<int>(blockIdx.x) / groups;   // causal: block 0 sees the most query blocks, it goes first
   const int g = static_cast<int>(blockIdx.x) % groups;
   const int kvh = g % a.Hkv, b = g / a.Hkv;
-  const int krow0 = b * a.Skv + kblk * 128;
+  const int krow0 = b * a.Skv + kblk * 128;                          // in the dK / dV outputs
+  const int krow_in = b * a.kv_bstride + a.kv_row0 + kblk * 128;     // in the k / v tensors
   const int qb0 = a.causal ? kblk : 0;       // first visible query block
   const int n_qb = nqb - qb0;
   const int n_iter = n_qb * ratio;           // iteration = (query head of the group, query block)
@@ -176,17 +180,17 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (elect_one()) {
       const int kcol = a.k_col0 + kvh * HD, vcol = a.v_col0 + kvh * HD;
       mbar_expect_tx(&bars->kv_full, 2 * TILE_BYTES);
-      tma_load_2d(sK, &tmK, &bars->kv_full, kcol, krow0);
-      tma_load_2d(sK + HALF_BYTES, &tmK, &bars->kv_full, kcol + 64, krow0);
-      tma_load_2d(sV, &tmV, &bars->kv_full, vcol, krow0);
-      tma_load_2d(sV + HALF_BYTES, &tmV, &bars->kv_full, vcol + 64, krow0);
+      tma_load_2d(sK, &tmK, &bars->kv_full, kcol, krow_in);
+      tma_load_2d(sK + HALF_BYTES, &tmK, &bars->kv_full, kcol + 64, krow_in);
+      tma_load_2d(sV, &tmV, &bars->kv_full, vcol, krow_in);
+      tma_load_2d(sV + HALF_BYTES, &tmV, &bars->kv_full, vcol + 64, krow_in);
       for (int it = 0; it < n_iter; ++it) {
         const int s = it % Q_STAGES;
         const uint32_t ph = (it / Q_STAGES) & 1;
         if (!mbar_wait(&bars->q_empty[s], ph ^ 1, err, kErrAttnWait)) break;
         const int h = kvh * ratio + it / n_qb;
         const int qb = qb0 + it % n_qb;
-        const int qrow = b * a.Sq + qb * 128;
+        const int qrow = b * a.q_bstride + a.q_row0 + qb * 128;
         uint8_t* sQ = sStage + s * STAGE_BYTES;
         uint8_t* sDO = sQ + TILE_BYTES;
         float* sStat = reinterpret_cast<float*>(sDO + TILE_BYTES);
@@ -195,7 +199,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tma_load_2d(sQ + HALF_BYTES, &tmQ, &bars->q_full[s], a.q_col0 + h * HD + 64, qrow);
         tma_load_2d(sDO, &tmDO, &bars->q_full[s], h * HD, qrow);
         tma_load_2d(sDO + HALF_BYTES, &tmDO, &bars->q_full[s], h * HD + 64, qrow);
-        const int64_t stat = (static_cast<int64_t>(b) * a.Hq + h) * a.Sq + qb * 128;
+        const int64_t stat = (static_cast<int64_t>(b) * a.Hq + h) * a.stat_stride + a.stat_row0 + qb * 128;
         bulk_load_1d(sStat, a.nlse2 + stat, 512, &bars->q_full[s]);
         bulk_load_1d(sStat + 128, a.nds + stat, 512, &bars->q_full[s]);
       }
@@ -314,7 +318,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (lane == 0) mbar_arrive(&bars->dq_drained[ph]);
       const int h = kvh * ratio + pit / n_qb;
       const int qb = qb0 + pit % n_qb;
-      float* dst = a.dq_acc + ((static_cast<int64_t>(b) * a.Hq + h) * a.Sq + qb * 128 + ph * 64 + cg * 32) * HD + row;
+      float* dst = a.dq_acc +
+                   ((static_cast<int64_t>(b) * a.Hq + h) * a.stat_stride + a.stat_row0 + qb * 128 + ph * 64 + cg * 32) * HD + row;
 #pragma unroll
       for (int j = 0; j < 32; ++j) red_add_f32(dst + j * HD, __uint_as_float(v[j]));
       return true;
@@ -504,13 +509,15 @@ int attn_bwd_stats(const void* d_o, const void* o, const float* lse, float* nds,
 
 int attn_bwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, const void* d_o, float* dq_acc,
                    void* dk, void* dv, int64_t ld_dkv, const float* nds, const float* nlse2, int B, int Sq, int Skv,
-                   int Hq, int Hkv, bool causal, int* err, cudaStream_t stream) {
+                   int Hq, int Hkv, bool causal, int* err, cudaStream_t stream, const AttnPairLayout* lay) {
   if (Sq % 128 != 0 || Skv % 128 != 0 || Hq % Hkv != 0 || B <= 0 || Sq <= 0 || Skv <= 0) return -1;
+  AttnPairLayout whole{static_cast<int64_t>(B) * Sq, Sq, 0, static_cast<int64_t>(B) * Skv, Skv, 0, Sq, 0};
+  if (lay == nullptr) lay = &whole;
   if (causal && Sq != Skv) return -2;
   if (ld_dkv % 8 != 0 || (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15) ||
       (reinterpret_cast<uintptr_t>(dq_acc) & 15))
     return -3;
-  const uint64_t Mq = static_cast<uint64_t>(B) * Sq, Mk = static_cast<uint64_t>(B) * Skv;
+  const uint64_t Mq = static_cast<uint64_t>(lay->q_rows), Mk = static_cast<uint64_t>(lay->kv_rows);
   CUtensorMap tq, tk, tv, tdo;
   int r = make_tmap_2d(&tq, q.ptr, 2, Mq, q.ld, q.ld, 128, 64);
   if (r) return r;
@@ -533,6 +540,8 @@ int attn_bwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand
   a.k_col0 = static_cast<int>(k.col0);
   a.v_col0 = static_cast<int>(v.col0);
   a.causal = causal ? 1 : 0;
+  a.q_bstride = lay->q_bstride; a.q_row0 = lay->q_row0; a.kv_bstride = lay->kv_bstride; a.kv_row0 = lay->kv_row0;
+  a.stat_stride = lay->stat_stride; a.stat_row0 = lay->stat_row0;
   a.scale = 1.f / sqrtf(static_cast<float>(HD));
   a.scale_log2 = a.scale * 1.4426950408889634f;
   const int grid = (Skv / 128) * B * Hkv;

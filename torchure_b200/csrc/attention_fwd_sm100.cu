@@ -42,10 +42,26 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Shapes and strides of one call.  Query / output rows of batch b start at b * q_bstride + q_row0 in the q tensor and at
+// b * Sq in o and lse; key / value rows at b * kv_bstride + kv_row0.  causal: query block qb sees key blocks <= qb and
+// the last one is masked along its diagonal (Sq == Skv); otherwise every query sees all Skv keys (an off-diagonal
+// block pair of ring attention).
+struct FwdArgs {
+  float* lse;
+  int B, Sq, Skv, Hq, Hkv;
+  int q_col0, k_col0, v_col0;
+  int q_bstride, q_row0, kv_bstride, kv_row0;
+  int causal;
+  float scale_log2;
+};
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
-                const __grid_constant__ CUtensorMap tmO, float* __restrict__ lse, int B, int S, int Hq, int Hkv,
-                float scale_log2, int* err) {
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                const __grid_constant__ FwdArgs a, int* err) {
+  float* __restrict__ lse = a.lse;
+  const int B = a.B, S = a.Sq, Hq = a.Hq, Hkv = a.Hkv;
+  const float scale_log2 = a.scale_log2;
   pdl_wait();
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
@@ -65,11 +81,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
   const int kvh = g % Hkv;
   const int b = g / Hkv;
   const int h0 = kvh * ratio + pair * 2;    // the two query heads of this CTA: h0, h0 + 1
-  const int row0 = b * S + qblk * BQ;       // first token row of the query tile
-  const int n_kv = qblk + 1;                // causal: KV blocks 0..qblk
+  const int row0 = b * a.q_bstride + a.q_row0 + qblk * BQ;   // first token row of the query tile in the q tensor
+  const int orow0 = b * S + qblk * BQ;                       // ... and in the output
+  const int n_kv = a.causal ? qblk + 1 : a.Skv / BKV;        // causal: KV blocks 0..qblk
 
   if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tmQK);
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmO);
     mbar_init(&bars->q_full, 1);
@@ -100,18 +118,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
       mbar_expect_tx(&bars->q_full, 2 * TILE_BYTES);
       for (int t = 0; t < 2; ++t)
         for (int hf = 0; hf < 2; ++hf)
-          tma_load_2d(sQ + t * TILE_BYTES + hf * HALF_BYTES, &tmQK, &bars->q_full, (h0 + t) * HD + hf * 64, row0);
-      const int kcol = (Hq + kvh) * HD, vcol = (Hq + Hkv + kvh) * HD;
+          tma_load_2d(sQ + t * TILE_BYTES + hf * HALF_BYTES, &tmQ, &bars->q_full, a.q_col0 + (h0 + t) * HD + hf * 64, row0);
+      const int kcol = a.k_col0 + kvh * HD, vcol = a.v_col0 + kvh * HD;
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
         if (!mbar_wait(&bars->kv_empty[s], ph ^ 1, err, kErrAttnWait)) break;
         uint8_t* sK = sKV + s * 2 * TILE_BYTES;
         uint8_t* sV = sK + TILE_BYTES;
-        const int krow = b * S + j * BKV;
+        const int krow = b * a.kv_bstride + a.kv_row0 + j * BKV;
         mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
-        tma_load_2d(sK, &tmQK, &bars->k_full[s], kcol, krow);
-        tma_load_2d(sK + HALF_BYTES, &tmQK, &bars->k_full[s], kcol + 64, krow);
+        tma_load_2d(sK, &tmK, &bars->k_full[s], kcol, krow);
+        tma_load_2d(sK + HALF_BYTES, &tmK, &bars->k_full[s], kcol + 64, krow);
         mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
         tma_load_2d(sV, &tmV, &bars->v_full[s], vcol, krow);
         tma_load_2d(sV + HALF_BYTES, &tmV, &bars->v_full[s], vcol + 64, krow);
@@ -188,7 +206,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait(&bars->s_full[t], j & 1, err, kErrAttnWait)) { ok = false; break; }
       tc_fence_after();
-      const bool diag = j == n_kv - 1;
+      const bool diag = a.causal && j == n_kv - 1;
       // the whole score row (128 fp32) comes out of TMEM once: four loads in flight, one wait
       uint32_t sv[128];
       tmem_ld_32x32b_x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
@@ -281,8 +299,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(&tmO, stage, (h0 + t) * HD, row0 + quarter * 32);
-        tma_store_2d(&tmO, stage + 4096, (h0 + t) * HD + 64, row0 + quarter * 32);
+        tma_store_2d(&tmO, stage, (h0 + t) * HD, orow0 + quarter * 32);
+        tma_store_2d(&tmO, stage + 4096, (h0 + t) * HD + 64, orow0 + quarter * 32);
         tma_commit_group();
         tma_wait_group<0>();
       }
@@ -306,22 +324,91 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
 int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_rows, uint32_t box_cols);
 
-int attn_fwd(const void* qk, const void* qkv, void* o, float* lse, int B, int S, int Hq, int Hkv, int* err,
-             cudaStream_t stream) {
-  if (S % 128 != 0 || Hq % Hkv != 0 || (Hq / Hkv) % 2 != 0) return -1;
-  const uint64_t M = static_cast<uint64_t>(B) * S;
-  CUtensorMap tq, tv, to;
-  int r = make_tmap_2d(&tq, qk, 2, M, static_cast<uint64_t>(Hq + Hkv) * HD, static_cast<uint64_t>(Hq + Hkv) * HD, 128, 64);
+namespace {
+// Online-softmax merge of a block pair's partial result into the running one, one warp per (token, head) row:
+//   new = logaddexp(lse_acc, lse_p);  out = out * exp(lse_acc - new) + o_p * exp(lse_p - new);  lse_acc = new
+// out_acc fp32 [B * acc_stride, Hq*128] and lse_acc [B, Hq, acc_stride] cover the whole local sequence, the pair's
+// queries start at acc_row0; o_p bf16 [B*Sq, Hq*128], lse_p [B, Hq, Sq] are compact.
+__global__ void __launch_bounds__(256)
+attn_merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse_acc, const __nv_bfloat16* __restrict__ o_p,
+                  const float* __restrict__ lse_p, int B, int Sq, int Hq, int acc_stride, int acc_row0) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= static_cast<int64_t>(B) * Sq * Hq) return;
+  const int h = static_cast<int>(item % Hq);
+  const int64_t tok = item / Hq;
+  const int s = static_cast<int>(tok % Sq), b = static_cast<int>(tok / Sq);
+  const int64_t li = (static_cast<int64_t>(b) * Hq + h) * acc_stride + acc_row0 + s;
+  const float l1 = lse_acc[li], l2 = lse_p[(static_cast<int64_t>(b) * Hq + h) * Sq + s];
+  const float mx = fmaxf(l1, l2);
+  const float e1 = (l1 == -INFINITY) ? 0.f : __expf(l1 - mx), e2 = (l2 == -INFINITY) ? 0.f : __expf(l2 - mx);
+  const float inv = 1.f / (e1 + e2);
+  const float w1 = e1 * inv, w2 = e2 * inv;
+  float* orow = out_acc + (static_cast<int64_t>(b) * acc_stride + acc_row0 + s) * Hq * HD + h * HD + lane * 4;
+  const __nv_bfloat16* prow = o_p + tok * Hq * HD + h * HD + lane * 4;
+  float4 x = *reinterpret_cast<const float4*>(orow);
+  const uint2 u = *reinterpret_cast<const uint2*>(prow);
+  const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  x.x = x.x * w1 + p0.x * w2;
+  x.y = x.y * w1 + p0.y * w2;
+  x.z = x.z * w1 + p1.x * w2;
+  x.w = x.w * w1 + p1.y * w2;
+  *reinterpret_cast<float4*>(orow) = x;
+  if (lane == 0) lse_acc[li] = mx + __logf(e1 + e2);
+}
+}  // namespace
+
+int attn_merge(float* out_acc, float* lse_acc, const void* o_p, const float* lse_p, int B, int Sq, int Hq, int acc_stride,
+               int acc_row0, cudaStream_t stream) {
+  const int64_t items = static_cast<int64_t>(B) * Sq * Hq;
+  return launch_pdl(attn_merge_kernel, dim3(static_cast<int>((items + 7) / 8)), dim3(256), 0, stream, out_acc, lse_acc,
+                    reinterpret_cast<const __nv_bfloat16*>(o_p), lse_p, B, Sq, Hq, acc_stride, acc_row0) == cudaSuccess
+             ? 0
+             : -21;
+}
+
+int attn_fwd_pair(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, void* o, float* lse, int B, int Sq,
+                  int Skv, int Hq, int Hkv, int64_t q_rows, int q_bstride, int q_row0, int64_t kv_rows, int kv_bstride,
+                  int kv_row0, bool causal, int* err, cudaStream_t stream) {
+  if (Sq % 128 != 0 || Skv % 128 != 0 || Hq % Hkv != 0 || (Hq / Hkv) % 2 != 0 || B <= 0) return -1;
+  if (causal && Sq != Skv) return -2;
+  CUtensorMap tq, tk, tv, to;
+  int r = make_tmap_2d(&tq, q.ptr, 2, static_cast<uint64_t>(q_rows), q.ld, q.ld, 128, 64);
   if (r) return r;
-  r = make_tmap_2d(&tv, qkv, 2, M, static_cast<uint64_t>(Hq + 2 * Hkv) * HD, static_cast<uint64_t>(Hq + 2 * Hkv) * HD, 128, 64);
+  r = make_tmap_2d(&tk, k.ptr, 2, static_cast<uint64_t>(kv_rows), k.ld, k.ld, 128, 64);
   if (r) return r - 100;
-  r = make_tmap_2d(&to, o, 2, M, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(Hq) * HD, 32, 64);
+  r = make_tmap_2d(&tv, v.ptr, 2, static_cast<uint64_t>(kv_rows), v.ld, v.ld, 128, 64);
+  if (r) return r - 150;
+  r = make_tmap_2d(&to, o, 2, static_cast<uint64_t>(B) * Sq, static_cast<uint64_t>(Hq) * HD, static_cast<uint64_t>(Hq) * HD,
+                   32, 64);
   if (r) return r - 200;
   if (!ensure_dynamic_smem(reinterpret_cast<const void*>(attn_fwd_kernel), SMEM_BYTES)) return -20;
-  const int grid = (S / 128) * B * Hkv * ((Hq / Hkv) / 2);
-  const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
-  launch_pdl(attn_fwd_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tv, to, lse, B, S, Hq, Hkv, scale_log2, err);
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  FwdArgs a{};
+  a.lse = lse;
+  a.B = B; a.Sq = Sq; a.Skv = Skv; a.Hq = Hq; a.Hkv = Hkv;
+  a.q_col0 = static_cast<int>(q.col0);
+  a.k_col0 = static_cast<int>(k.col0);
+  a.v_col0 = static_cast<int>(v.col0);
+  a.q_bstride = q_bstride; a.q_row0 = q_row0; a.kv_bstride = kv_bstride; a.kv_row0 = kv_row0;
+  a.causal = causal ? 1 : 0;
+  a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
+  const int grid = (Sq / 128) * B * Hkv * ((Hq / Hkv) / 2);
+  return launch_pdl(attn_fwd_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tq, tk, tv, to, a, err) ==
+                 cudaSuccess
+             ? 0
+             : -21;
+}
+
+int attn_fwd(const void* qk, const void* qkv, void* o, float* lse, int B, int S, int Hq, int Hkv, int* err,
+             cudaStream_t stream) {
+  const int64_t wqk = static_cast<int64_t>(Hq + Hkv) * HD, wqkv = static_cast<int64_t>(Hq + 2 * Hkv) * HD;
+  const int64_t M = static_cast<int64_t>(B) * S;
+  return attn_fwd_pair({qk, wqk, 0}, {qk, wqk, static_cast<int64_t>(Hq) * HD},
+                       {qkv, wqkv, static_cast<int64_t>(Hq + Hkv) * HD}, o, lse, B, S, S, Hq, Hkv, M, S, 0, M, S, 0, true, err,
+                       stream);
 }
 
 }  // namespace tb

@@ -188,6 +188,26 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("embedding_bwd", &embedding_bwd);
+  // ids_ptrs / rows_ptrs: device-visible addresses (ints) of int64 [M] ids and fp32 [M, D] rows, one pair per source
+  m.def("embedding_scatter", [](std::vector<int64_t> ids_ptrs, std::vector<int64_t> rows_ptrs, torch::Tensor& dtable,
+                                int64_t M, double scale, c10::optional<torch::Tensor> sq_delta, int64_t blocks) {
+    TORCH_CHECK(ids_ptrs.size() == rows_ptrs.size() && !ids_ptrs.empty() && ids_ptrs.size() <= 8, "1..8 sources");
+    TORCH_CHECK(dtable.scalar_type() == torch::kFloat32 && dtable.dim() == 2 && dtable.stride(1) == 1 &&
+                dtable.stride(0) == dtable.size(1), "embedding_scatter: dtable must be contiguous fp32 [V, D]");
+    const int64_t* ids[8];
+    const float* rows[8];
+    for (size_t p = 0; p < ids_ptrs.size(); ++p) {
+      TORCH_CHECK(ids_ptrs[p] % 8 == 0 && rows_ptrs[p] % 16 == 0, "embedding_scatter: unaligned source");
+      ids[p] = reinterpret_cast<const int64_t*>(ids_ptrs[p]);
+      rows[p] = reinterpret_cast<const float*>(rows_ptrs[p]);
+    }
+    if (sq_delta.has_value() && sq_delta->defined())
+      TORCH_CHECK(sq_delta->scalar_type() == torch::kFloat32 && sq_delta->numel() >= blocks);
+    const int rc = tb::embedding_scatter((int)ids_ptrs.size(), ids, rows, dtable.data_ptr<float>(), (int)M,
+                                         (int)dtable.size(1), (float)scale, opt_mptr<float>(sq_delta), (int)blocks,
+                                         cur_stream());
+    TORCH_CHECK(rc == 0, "embedding_scatter failed with code ", rc);
+  });
   m.def("ce_softmax_grad", &ce_softmax_grad);
   m.def("cast_to_bf16", &cast_to_bf16);
   m.def("scale_inplace", &scale_inplace);

@@ -393,8 +393,8 @@ reduce_scatter_symm_kernel(CommCtx c, CommSegments segs, int op, int use_mc, int
   block_barrier(c, 1, c.world);
 }
 
-__global__ void __launch_bounds__(CT) barrier_kernel(CommCtx c, int pretend_world) {
-  block_barrier(c, 0, pretend_world);
+__global__ void __launch_bounds__(CT) barrier_kernel(CommCtx c, int pretend_world, int phase) {
+  block_barrier(c, phase, pretend_world);
 }
 
 }  // namespace
@@ -450,8 +450,8 @@ void comm_reduce_scatter_symm(const CommCtx& c, const CommSegments& segs, int op
   reduce_scatter_symm_kernel<<<blocks, CT, 0, stream>>>(c, segs, op, use_mc, sq_slot);
 }
 
-void comm_barrier(const CommCtx& c, uint32_t, int pretend_world, cudaStream_t stream) {
-  barrier_kernel<<<1, CT, 0, stream>>>(c, pretend_world);
+void comm_barrier(const CommCtx& c, int phase, int pretend_world, cudaStream_t stream) {
+  barrier_kernel<<<1, CT, 0, stream>>>(c, pretend_world, phase);
 }
 
 }  // namespace tb

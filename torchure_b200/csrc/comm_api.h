@@ -68,7 +68,9 @@ void comm_reduce_scatter_symm(const CommCtx& c, const CommSegments& segs, int op
 
 // cross-rank barrier only (also the bounded-wait self test: with world == 1 and pretend_world > 1 nothing ever
 // arrives and the kernel records kErrPeerFlagWait).
-void comm_barrier(const CommCtx& c, uint32_t generation, int pretend_world, cudaStream_t stream);
+// `phase` picks the flag row: 0 and 1 belong to the collectives above, 4 and 6 to the fused GEMMs, so a barrier that
+// may run on another stream at the same time as those (the embedding-row exchange of DDP) uses 2 and 3.
+void comm_barrier(const CommCtx& c, int phase, int pretend_world, cudaStream_t stream);
 
 // Fused compute + collective tcgen05 GEMMs (gemm_sm100.cu).
 // ag_gemm: C[M, N] = concat_ranks(A_r)[M, K] * B[N, K]^T.  A_r ([M/world, K] bf16) sits at byte offset a_off of every

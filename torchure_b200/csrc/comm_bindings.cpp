@@ -124,7 +124,9 @@ void register_comm(pybind11::module_& m) {
     TORCH_CHECK(rc == 0, "gemm_rs failed with code ", rc);
   });
   m.def("comm_barrier", [](std::vector<int64_t> peers, int64_t mc, int64_t rank, int64_t world, int64_t limit,
-                           int64_t pretend_world) {
-    tb::comm_barrier(make_ctx(peers, mc, rank, world, limit), 0, (int)pretend_world, cs());
-  });
+                           int64_t pretend_world, int64_t phase) {
+    TORCH_CHECK(phase >= 0 && phase < 8, "barrier phase 0..7");
+    tb::comm_barrier(make_ctx(peers, mc, rank, world, limit), (int)phase, (int)pretend_world, cs());
+  }, pybind11::arg("peers"), pybind11::arg("mc"), pybind11::arg("rank"), pybind11::arg("world"), pybind11::arg("limit"),
+     pybind11::arg("pretend_world"), pybind11::arg("phase") = 0);
 }

@@ -574,6 +574,103 @@ embedding_bwd_kernel(const float* __restrict__ dx, const int64_t* __restrict__ i
   for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dst[i], src[i]);
 }
 
+// Deterministic scatter-add of embedding-row gradients from up to 8 sources (this GPU's rows and, over NVLink, the
+// rows every other data-parallel rank left in its symmetric buffer):
+//     dtable[id] += scale * sum over sources p = 0..n-1 and rows r = 0..M-1 with ids_p[r] == id of rows_p[r]
+// Each destination row belongs to exactly one warp of one CTA (CTA = id mod grid, warp = (id / grid) mod 8), which
+// applies its rows with plain loads and stores in (p, r) order: no atomics, so the result has the same bits on every
+// rank and in every run.  A CTA scans all ids once, 256 at a time, appending its own matches to a list in shared
+// memory by an ordered compaction; the list is applied whenever it fills up.  When sq_delta is given, CTA b stores
+// sum(new^2 - old^2) over everything it touched into sq_delta[b] (the sums telescope over repeated rows), which
+// turns a sum of squares taken before the scatter into the one after it.
+constexpr int EB_THREADS = 256, EB_WARPS = 8, EB_LIST = 1024;
+struct EmbedSources {
+  int n;
+  const int64_t* ids[8];
+  const float* rows[8];
+};
+
+__device__ __forceinline__ float4 ld_sys_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int64_t ld_sys_i64(const int64_t* p) {
+  int64_t v;
+  asm volatile("ld.relaxed.sys.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(EB_THREADS)
+embedding_scatter_kernel(EmbedSources src, float* __restrict__ dtable, int M, int D, float scale,
+                         float* __restrict__ sq_delta) {
+  __shared__ uint32_t list[EB_LIST];        // (source << 27) | row, in application order
+  __shared__ int warp_count[EB_WARPS];
+  __shared__ float warp_delta[EB_WARPS];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nb = gridDim.x;
+  int count = 0;
+  float delta = 0.f;
+  auto apply = [&]() {
+    __syncthreads();
+    for (int e = 0; e < count; ++e) {
+      const uint32_t ent = list[e];
+      const int p = ent >> 27, r = ent & ((1u << 27) - 1);
+      const int64_t id = ld_sys_i64(src.ids[p] + r);
+      if (static_cast<int>((id / nb) % EB_WARPS) != warp) continue;   // another warp of this CTA owns that row
+      const float* s = src.rows[p] + static_cast<int64_t>(r) * D;
+      float* d = dtable + id * static_cast<int64_t>(D);
+      for (int i = lane * 4; i < D; i += 128) {
+        const float4 a = ld_sys_f4(s + i);
+        float4 b = *reinterpret_cast<float4*>(d + i);
+        const float4 o = b;
+        b.x = fmaf(scale, a.x, b.x); b.y = fmaf(scale, a.y, b.y); b.z = fmaf(scale, a.z, b.z); b.w = fmaf(scale, a.w, b.w);
+        *reinterpret_cast<float4*>(d + i) = b;
+        delta += (b.x * b.x - o.x * o.x) + (b.y * b.y - o.y * o.y) + (b.z * b.z - o.z * o.z) + (b.w * b.w - o.w * o.w);
+      }
+      __syncwarp();   // the next entry of this warp may hit the same row
+    }
+    __syncthreads();
+    count = 0;
+  };
+  for (int p = 0; p < src.n; ++p) {
+    for (int base = 0; base < M; base += EB_THREADS) {
+      const int r = base + tid;
+      bool mine = false;
+      if (r < M) {
+        const int64_t id = ld_sys_i64(src.ids[p] + r);
+        mine = static_cast<int>(id % nb) == static_cast<int>(blockIdx.x);
+      }
+      const uint32_t ballot = __ballot_sync(0xffffffffu, mine);
+      if (lane == 0) warp_count[warp] = __popc(ballot);
+      __syncthreads();
+      int before = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < EB_WARPS; ++w) {
+        const int c = warp_count[w];
+        if (w < warp) before += c;
+        total += c;
+      }
+      if (mine) list[count + before + __popc(ballot & ((1u << lane) - 1))] = (static_cast<uint32_t>(p) << 27) | r;
+      count += total;
+      __syncthreads();   // warp_count is rewritten by the next chunk
+      if (count > EB_LIST - EB_THREADS) apply();
+    }
+  }
+  apply();
+  if (sq_delta != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) delta += __shfl_xor_sync(0xffffffffu, delta, o);
+    if (lane == 0) warp_delta[warp] = delta;
+    __syncthreads();
+    if (tid == 0) {
+      float t = 0.f;
+      for (int w = 0; w < EB_WARPS; ++w) t += warp_delta[w];   // fixed order
+      sq_delta[blockIdx.x] = t;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // cross-entropy on one vocabulary row per CTA: online max/sum, target gather, loss, in-place dlogits
 // ---------------------------------------------------------------------------------------------
@@ -777,6 +874,19 @@ void swiglu_bwd(const __nv_bfloat16* dact, const __nv_bfloat16* gu, __nv_bfloat1
 
 void embedding_bwd(const float* dx, const int64_t* ids, float* dtable, int M, int D, cudaStream_t stream) {
   embedding_bwd_kernel<<<M, 256, 0, stream>>>(dx, ids, dtable, M, D);
+}
+
+int embedding_scatter(int n_sources, const int64_t* const* ids, const float* const* rows, float* dtable, int M, int D,
+                      float scale, float* sq_delta, int blocks, cudaStream_t stream) {
+  if (n_sources < 1 || n_sources > 8 || D % 4 != 0 || M <= 0 || M >= (1 << 27) || blocks < 1) return -1;
+  EmbedSources src{};
+  src.n = n_sources;
+  for (int p = 0; p < n_sources; ++p) {
+    src.ids[p] = ids[p];
+    src.rows[p] = rows[p];
+  }
+  embedding_scatter_kernel<<<blocks, EB_THREADS, 0, stream>>>(src, dtable, M, D, scale, sq_delta);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 void ce_softmax_grad(__nv_bfloat16* logits, int64_t ldl, const int64_t* labels, float* row_loss,

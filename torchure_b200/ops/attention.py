@@ -108,3 +108,70 @@ def attn_bwd(d_o, qk, qkv, state: AttnState, B, S, Hq, Hkv, hd, keep_dq_fp32: bo
     dqkv[:, Hq * hd:(Hq + Hkv) * hd].view(B, S, Hkv, hd).copy_(dk.transpose(1, 2))
     dqkv[:, (Hq + Hkv) * hd:].view(B, S, Hkv, hd).copy_(dv.transpose(1, 2))
     return (dqkv, None) if keep_dq_fp32 else dqkv
+
+
+# ---- attention on caller-owned (B, S, H, 128) tensors ---------------------------------------------------------------
+def pair_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """True when the block-pair kernels can take these (B, S, H, d) tensors: CUDA bf16, head_dim 128, sequence
+    lengths in whole 128-token blocks, an even number of query heads per KV head."""
+    ext = ops.ext() if ops.available() else None
+    if ext is None or not hasattr(ext, "attn_fwd_pair"):
+        return False
+    if not (q.is_cuda and q.dtype == k.dtype == v.dtype == torch.bfloat16):
+        return False
+    return (q.shape[-1] == 128 and q.shape[1] % 128 == 0 and k.shape[1] % 128 == 0 and q.shape[2] % k.shape[2] == 0
+            and (q.shape[2] // k.shape[2]) % 2 == 0)
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """(B, S, H, d) -> the token-major 2-D view (B*S, H*d) the kernels index (copy only if not contiguous)."""
+    return t.contiguous().view(t.shape[0] * t.shape[1], t.shape[2] * t.shape[3])
+
+
+class _FlashAttention(torch.autograd.Function):
+    """Full-sequence attention on separate q / k / v tensors through the block-pair entry points of the sm_100a
+    kernels: ``attn_fwd_pair`` forward, ``attn_bwd_stats`` + ``attn_bwd_pair`` + ``attn_dq_convert`` backward."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal):
+        B, Sq, Hq, _ = q.shape
+        Skv, Hkv = k.shape[1], k.shape[2]
+        q2, k2, v2 = _rows(q), _rows(k), _rows(v)
+        o = torch.empty(B * Sq, Hq * 128, dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
+        ops.ext().attn_fwd_pair(q2, 0, k2, 0, v2, 0, o, lse, B, Sq, Skv, Hq, Hkv, Sq, 0, Skv, 0, bool(causal))
+        ops.count_launch()
+        ctx.save_for_backward(q2, k2, v2, o, lse)
+        ctx.dims = (B, Sq, Skv, Hq, Hkv, bool(causal))
+        return o.view(B, Sq, Hq, 128)
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q2, k2, v2, o, lse = ctx.saved_tensors
+        B, Sq, Skv, Hq, Hkv, causal = ctx.dims
+        ext = ops.ext()
+        d_o2 = _rows(d_o.to(torch.bfloat16))
+        dev = q2.device
+        nds = torch.empty(B, Hq, Sq, dtype=torch.float32, device=dev)
+        nlse2 = torch.empty_like(nds)
+        dq_acc = torch.empty(B, Hq, Sq, 128, dtype=torch.float32, device=dev)
+        ext.attn_bwd_stats(d_o2, o, lse, nds, nlse2, dq_acc, B, Sq, Hq)
+        dk = torch.empty(B * Skv, Hkv * 128, dtype=torch.bfloat16, device=dev)
+        dv = torch.empty_like(dk)
+        ext.attn_bwd_pair(q2, 0, k2, 0, v2, 0, d_o2, dq_acc, dk, dv, nds, nlse2, B, Sq, Skv, Hq, Hkv, Sq, 0, Skv, 0, Sq, 0,
+                          causal)
+        dq = torch.empty(B * Sq, Hq * 128, dtype=torch.bfloat16, device=dev)
+        ext.attn_dq_convert(dq_acc, dq, B, Sq, Hq)
+        ops.count_launch(3)
+        return dq.view(B, Sq, Hq, 128), dk.view(B, Skv, Hkv, 128), dv.view(B, Skv, Hkv, 128), None
+
+
+def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    """Attention of q (B, Sq, Hq, 128) over k / v (B, Skv, Hkv, 128), bf16, differentiable.  ``causal`` needs
+    Sq == Skv.  What Ulysses sequence parallelism calls between its two all-to-alls; falls back to SDPA for tensors
+    the kernels do not cover."""
+    if pair_supported(q, k, v):
+        return _FlashAttention.apply(q, k, v, causal)
+    out = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal,
+                                         enable_gqa=q.shape[2] != k.shape[2])
+    return out.transpose(1, 2)

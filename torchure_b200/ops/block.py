@@ -35,6 +35,11 @@ BF16 = torch.bfloat16
 _ENGINE_OF_WEIGHT: "weakref.WeakValueDictionary[int, Sm100Engine]" = weakref.WeakValueDictionary()
 
 
+# value of `engine.pending_tied_grad` when the tied table's bucket was launched by the loss head and the embedding rows
+# are to be exchanged through the gradient sink instead of being added locally
+EARLY_TABLE = object()
+
+
 def engine_for_weight(weight: torch.Tensor):
     return _ENGINE_OF_WEIGHT.get(id(weight))
 
@@ -220,9 +225,15 @@ class _BlockFn(torch.autograd.Function):
         del dqkv
         dw1 = out.small(P["w1"])
         want_prev = not ctx.first
-        dx0, dx0_b = K.rmsnorm_bwd(d_h1, x, w1, rstd1, dx1, dw1, want_bf16=want_prev)
+        early = ctx.first and eng.pending_tied_grad is EARLY_TABLE
+        # with the row exchange, dx0 is written where the other ranks can read it
+        dx_out = out.sink.embed_rows_dest(x.shape[0], x.shape[1]) if early else None
+        dx0, dx0_b = K.rmsnorm_bwd(d_h1, x, w1, rstd1, dx1, dw1, want_bf16=want_prev, dx_out=dx_out)
         out.done(P["w1"])
-        if ctx.first and ctx.needs_input_grad[6]:
+        if early:
+            eng.pending_tied_grad = None
+            out.sink.exchange_embedding(ids, P["table"])
+        elif ctx.first and ctx.needs_input_grad[6]:
             table = P["table"]
             stash = eng.pending_tied_grad
             eng.pending_tied_grad = None
@@ -234,7 +245,10 @@ class _BlockFn(torch.autograd.Function):
                     d_table.zero_()
             else:
                 d_table = torch.zeros(table.shape, dtype=torch.float32, device=x.device)
-            K.embedding_bwd_(dx0, ids, d_table)
+            if d_table.is_contiguous() and d_table.shape[1] % 4 == 0:
+                K.embedding_scatter_([(ids, dx0)], d_table, ids.numel())   # fixed order of additions, no atomics
+            else:
+                K.embedding_bwd_(dx0, ids, d_table)
             if out.sink is not None:
                 out.sink.grad_written(table)
             else:

@@ -97,9 +97,10 @@ def add_rmsnorm(x, y, w, eps, *, ids=None, table=None, need_x_out=True):
     return (x_out if x_out is not None else x), h, rstd
 
 
-def rmsnorm_bwd(dh, x, w, rstd, dx_in, dw, want_bf16=True):
-    """dx = dx_in + d rmsnorm(x)^T dh (fp32), optional bf16 copy; dw += sum_rows(dh * xhat)."""
-    dx = new_output("rmsnorm_bwd.dx", x.shape, dtype=x.dtype, device=x.device)
+def rmsnorm_bwd(dh, x, w, rstd, dx_in, dw, want_bf16=True, dx_out=None):
+    """dx = dx_in + d rmsnorm(x)^T dh (fp32), optional bf16 copy; dw += sum_rows(dh * xhat).  `dx_out`: caller-owned
+    destination of dx (a symmetric buffer the peers will read)."""
+    dx = dx_out if dx_out is not None else new_output("rmsnorm_bwd.dx", x.shape, dtype=x.dtype, device=x.device)
     dxb = new_output("rmsnorm_bwd.dx_bf16", x.shape, dtype=BF16, device=x.device) if want_bf16 else None
     _C().rmsnorm_bwd(dh, x, w, rstd, dx_in, dx, dxb, dw)
     ops.count_launch()
@@ -137,6 +138,16 @@ def swiglu_bwd(dact, gu):
 
 def embedding_bwd_(dx, ids, dtable):
     _C().embedding_bwd(dx, ids, dtable)
+    ops.count_launch()
+    return dtable
+
+
+def embedding_scatter_(sources, dtable, M, scale=1.0, sq_delta=None, blocks=592):
+    """Deterministic dtable[id] += scale * rows, over `sources` = [(ids (M,) int64, rows (M, D) fp32) or
+    (ids address, rows address), ...] in list order; no atomics.  Addresses let a source live on a peer GPU."""
+    ids_ptrs = [s[0] if isinstance(s[0], int) else s[0].data_ptr() for s in sources]
+    rows_ptrs = [s[1] if isinstance(s[1], int) else s[1].data_ptr() for s in sources]
+    _C().embedding_scatter(ids_ptrs, rows_ptrs, dtable, M, float(scale), sq_delta, blocks)
     ops.count_launch()
     return dtable
 

@@ -26,7 +26,7 @@ class _LinearCESm100(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden, weight, labels, ignore_index, chunk_size, w_bf16, engine, loss_scale, sink_dest):
         N, D = hidden.shape
-        V = weight.shape[0]
+        V = w_bf16.shape[0]   # a sharded strategy may have released the fp32 weight's own storage
         dev = hidden.device
         h = hidden if hidden.dtype == BF16 else hidden.to(BF16)
         h = h.contiguous()
@@ -77,9 +77,19 @@ class _LinearCESm100(torch.autograd.Function):
                 K.scale_inplace_(d_weight, scale)
             eng = ctx.engine
             if eng is not None and eng.expect_tied_grad:
-                # tied embedding: hand the buffer to the gather's backward, which adds its rows and returns it
                 eng.expect_tied_grad = False
-                eng.pending_tied_grad = d_weight
+                sink = eng.model._grad_sink
+                head = eng.model.lm_head.weight
+                if ctx.in_sink and hasattr(sink, "early_table") and sink.early_table(head):
+                    # tied embedding under DDP: the dense part of the gradient is complete, reduce it now (under the
+                    # whole block backward); the embedding rows are exchanged when the gather's backward has them
+                    from torchure_b200.ops.block import EARLY_TABLE
+
+                    sink.grad_written(head)
+                    eng.pending_tied_grad = EARLY_TABLE
+                else:
+                    # hand the buffer to the gather's backward, which adds its rows and returns it
+                    eng.pending_tied_grad = d_weight
                 d_weight = None
             elif ctx.in_sink:
                 eng.model._grad_sink.grad_written(eng.model.lm_head.weight)

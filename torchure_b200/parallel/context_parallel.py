@@ -8,8 +8,15 @@ Layout: the sequence is cut into 2n chunks; rank r holds chunks (r, 2n-1-r) conc
 step t a rank holds the K/V of rank (r - t) mod n.  Chunk-level causality decides which (query chunk, key chunk)
 pairs are computed: full, diagonal (causal inside), or skipped.
 
-Each pair is one call of a block attention that returns (out, lse); on GPUs that is the place to call the sm_100a
-kernel (it already emits LSE); the reference implementation below is plain PyTorch so the algorithm is testable on CPU.
+Each pair is one call of a block attention that returns (out, lse).  Two implementations of the same schedule:
+
+``_RingAttention``       plain PyTorch on (B, H, S, d) tensors: the CPU / oracle path.
+``_RingAttentionSm100``  (B, S, H, 128) bf16 tensors on Blackwell: every pair is one launch of the tcgen05 forward
+                         kernel on the tensors where they lie (``attn_fwd_pair``: row offsets select the chunk, a flag
+                         selects diagonal or full visibility) and one merge kernel; backward is one launch of the
+                         single-pass backward kernel per pair, all pairs adding into one fp32 dQ accumulator, with
+                         the dK / dV accumulators travelling around the ring.  The K/V exchange for step t+1 is issued
+                         on a side stream before the pairs of step t are launched, so it runs under them.
 """
 
 from __future__ import annotations
@@ -123,9 +130,121 @@ class _RingAttention(torch.autograd.Function):
         return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), None, None
 
 
+def _ring_next(t: torch.Tensor, mesh, dim, side: torch.cuda.Stream) -> torch.Tensor:
+    """Start sending `t` to the next rank of the ring on the side stream; the caller waits for `side` before use."""
+    cur = torch.cuda.current_stream()
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        out = ring_send_recv(t, mesh, dim)
+    t.record_stream(side)
+    out.record_stream(cur)
+    return out
+
+
+class _RingAttentionSm100(torch.autograd.Function):
+    """q (B, S2, Hq, 128), k / v (B, S2, Hkv, 128) bf16: this rank's two zigzag chunks, token-major."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, mesh, dim):
+        from torchure_b200 import ops
+
+        ext = ops.ext()
+        n, r = mesh.size(dim), mesh.coordinate(dim)
+        B, S2, Hq, hd = q.shape
+        Hkv = k.shape[2]
+        half = S2 // 2
+        dev = q.device
+        q2 = q.contiguous().view(B * S2, Hq * hd)
+        kk, vv = k.contiguous().view(B * S2, Hkv * hd), v.contiguous().view(B * S2, Hkv * hd)
+        out = torch.zeros(B * S2, Hq * hd, dtype=torch.float32, device=dev)
+        lse = torch.full((B, Hq, S2), float("-inf"), dtype=torch.float32, device=dev)
+        o_p = torch.empty(B * half, Hq * hd, dtype=torch.bfloat16, device=dev)
+        l_p = torch.empty(B, Hq, half, dtype=torch.float32, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        for t in range(n):
+            src = (r - t) % n
+            nk = nv = None
+            if t + 1 < n:   # next step's K/V travel while this step's pairs run
+                nk, nv = _ring_next(kk, mesh, dim, side), _ring_next(vv, mesh, dim, side)
+            for qi, ki, causal in _pairs(r, src, n):
+                ext.attn_fwd_pair(q2, 0, kk, 0, vv, 0, o_p, l_p, B, half, half, Hq, Hkv, S2, qi * half, S2, ki * half,
+                                  causal)
+                ext.attn_merge(out, lse, o_p, l_p, B, half, Hq, S2, qi * half)
+                ops.count_launch(2)
+            if nk is not None:
+                torch.cuda.current_stream().wait_stream(side)
+                kk, vv = nk, nv
+        o16 = out.to(torch.bfloat16)
+        ctx.save_for_backward(q2, k.contiguous().view(B * S2, Hkv * hd), v.contiguous().view(B * S2, Hkv * hd), o16, lse)
+        ctx.mesh, ctx.dim, ctx.dims = mesh, dim, (B, S2, Hq, Hkv, hd)
+        return o16.view(B, S2, Hq, hd)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        from torchure_b200 import ops
+
+        ext = ops.ext()
+        q2, k2, v2, o16, lse = ctx.saved_tensors
+        mesh, dim = ctx.mesh, ctx.dim
+        B, S2, Hq, Hkv, hd = ctx.dims
+        n, r = mesh.size(dim), mesh.coordinate(dim)
+        half = S2 // 2
+        dev = q2.device
+        do2 = d_out.to(torch.bfloat16).contiguous().view(B * S2, Hq * hd)
+        nds = torch.empty(B, Hq, S2, dtype=torch.float32, device=dev)
+        nlse2 = torch.empty_like(nds)
+        dq_acc = torch.empty(B, Hq, S2, hd, dtype=torch.float32, device=dev)
+        ext.attn_bwd_stats(do2, o16, lse, nds, nlse2, dq_acc, B, S2, Hq)   # statistics of the MERGED result; clears dq_acc
+        dk_acc = torch.zeros(B, S2, Hkv * hd, dtype=torch.float32, device=dev)
+        dv_acc = torch.zeros_like(dk_acc)
+        dk_p = torch.empty(B * half, Hkv * hd, dtype=torch.bfloat16, device=dev)
+        dv_p = torch.empty_like(dk_p)
+        kk, vv = k2, v2
+        side = torch.cuda.Stream(device=dev)
+        for t in range(n):
+            src = (r - t) % n
+            nk = nv = None
+            if t + 1 < n:
+                nk, nv = _ring_next(kk, mesh, dim, side), _ring_next(vv, mesh, dim, side)
+            for qi, ki, causal in _pairs(r, src, n):
+                ext.attn_bwd_pair(q2, 0, kk, 0, vv, 0, do2, dq_acc, dk_p, dv_p, nds, nlse2, B, half, half, Hq, Hkv,
+                                  S2, qi * half, S2, ki * half, S2, qi * half, causal)
+                ops.count_launch()
+                ks = slice(ki * half, (ki + 1) * half)
+                dk_acc[:, ks] += dk_p.view(B, half, Hkv * hd)
+                dv_acc[:, ks] += dv_p.view(B, half, Hkv * hd)
+            # the gradient accumulators travel with their K/V block; after n hops they are home
+            dk_acc, dv_acc = ring_send_recv(dk_acc, mesh, dim), ring_send_recv(dv_acc, mesh, dim)
+            if nk is not None:
+                torch.cuda.current_stream().wait_stream(side)
+                kk, vv = nk, nv
+        dq = torch.empty(B * S2, Hq * hd, dtype=torch.bfloat16, device=dev)
+        ext.attn_dq_convert(dq_acc, dq, B, S2, Hq)
+        ops.count_launch(2)
+        return (dq.view(B, S2, Hq, hd), dk_acc.to(torch.bfloat16).view(B, S2, Hkv, hd),
+                dv_acc.to(torch.bfloat16).view(B, S2, Hkv, hd), None, None)
+
+
+def ring_attention_tokens(q, k, v, mesh, dim: str = "cp"):
+    """Token-major variant: q (B, 2c, Hq, d), k / v (B, 2c, Hkv, d) are this rank's two zigzag chunks; returns
+    (B, 2c, Hq, d).  On Blackwell with bf16, d = 128 and c a multiple of 128 every block pair runs on the tcgen05
+    attention kernels; anything else goes through the PyTorch implementation."""
+    from torchure_b200.ops.attention import pair_supported
+
+    half_ok = q.shape[1] % 256 == 0
+    if half_ok and pair_supported(q, k, v):
+        return _RingAttentionSm100.apply(q, k, v, mesh, dim)
+    return _RingAttention.apply(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), mesh, dim).transpose(1, 2)
+
+
 def ring_attention(q, k, v, mesh, dim: str = "cp"):
     """Causal attention over a sequence sharded in zigzag order along `dim`.
     q (B, Hq, 2c, d), k/v (B, Hkv, 2c, d) are this rank's two chunks; returns (B, Hq, 2c, d)."""
+    from torchure_b200.ops.attention import pair_supported
+
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if q.is_cuda and qt.shape[1] % 256 == 0 and pair_supported(qt, kt, vt):
+        return _RingAttentionSm100.apply(qt, kt, vt, mesh, dim).transpose(1, 2)
     return _RingAttention.apply(q, k, v, mesh, dim)
 
 

@@ -41,7 +41,7 @@ from torchure_b200.core.collective import MeshLike, all_reduce, broadcast
 
 
 def plan_buckets(params: list[torch.Tensor], cap_bytes: int, merge_small: bool = True,
-                 small_bytes: int | None = None, groups=()) -> list[list[torch.Tensor]]:
+                 small_bytes: int | None = None, groups=(), solo=()) -> list[list[torch.Tensor]]:
     """Group `params` (already in launch order) into buckets of about `cap_bytes`.
 
     A bucket closes when the next tensor would overflow it or has another dtype.  With
@@ -49,7 +49,8 @@ def plan_buckets(params: list[torch.Tensor], cap_bytes: int, merge_small: bool =
     closed by an overflow: the tensor joins it instead.  `groups` lists tuples of parameters
     that must sit next to each other, in the given order, inside one bucket (the rows of a
     fused projection, so one GEMM can write all of their gradients); a group is placed where
-    its first member appears in `params`.
+    its first member appears in `params`.  `solo` lists parameters that get a bucket of their own (one that must be
+    launchable before its neighbours' gradients exist).
     """
     if small_bytes is None:
         small_bytes = cap_bytes // 16
@@ -65,8 +66,15 @@ def plan_buckets(params: list[torch.Tensor], cap_bytes: int, merge_small: bool =
     out: list[list[torch.Tensor]] = []
     run: list[torch.Tensor] = []
     run_bytes = 0
+    solo_ids = {id(p) for p in solo}
     for unit in units:
         nbytes = sum(p.numel() * p.element_size() for p in unit)
+        if any(id(p) in solo_ids for p in unit):
+            if run:
+                out.append(run)
+                run, run_bytes = [], 0
+            out.append(list(unit))
+            continue
         if run:
             dtype_change = unit[0].dtype != run[0].dtype
             overflow = run_bytes + nbytes > cap_bytes
@@ -130,7 +138,12 @@ class TorchReducer:
 
 class DDP:
     def __init__(self, model: nn.Module, mesh: MeshLike, dim: str = "dp", bucket_mb: float = 25,
-                 fused: bool | None = None, merge_small: bool = True, comm_sms: int = 16, sm_reserve: int = 0):
+                 fused: bool | None = None, merge_small: bool = True, comm_sms: int = 16, sm_reserve: int = 0,
+                 embed_tokens: int = 0):
+        """`embed_tokens` (tokens per micro-batch, fused reducer with a tied embedding only): size of the symmetric
+        buffer through which the ranks exchange embedding-row gradients, which lets the tied embedding / head bucket
+        be reduced as soon as the loss head has produced its weight gradient instead of after the last kernel of
+        backward (see ``FusedReducer.exchange_embedding``).  0 keeps the bucket where it is."""
         self.mesh, self.dim = mesh, dim
         self.group_size = mesh.size(dim)
         self.requires_sync = True
@@ -152,8 +165,15 @@ class DDP:
             self._replicate(model)
         params.reverse()
         groups = model.fused_param_groups() if (self.fused and hasattr(model, "fused_param_groups")) else ()
+        self.early_table = None
+        if (self.fused and self.group_size > 1 and embed_tokens > 0 and hasattr(model, "token_emb")
+                and getattr(model, "lm_head", None) is not None and model.lm_head.weight is model.token_emb.weight
+                and model.token_emb.weight.shape[1] % 4 == 0):
+            self.early_table = model.token_emb.weight
+        self.embed_tokens = embed_tokens
         self.buckets = [Bucket(i, ps) for i, ps in
-                        enumerate(plan_buckets(params, int(bucket_mb * 1024 * 1024), merge_small, groups=groups))]
+                        enumerate(plan_buckets(params, int(bucket_mb * 1024 * 1024), merge_small, groups=groups,
+                                               solo=(self.early_table,) if self.early_table is not None else ()))]
         self._bucket_of = {p: b for b in self.buckets for p in b.params}
         if self.fused:
             from torchure_b200.parallel.ddp_fused import FusedReducer

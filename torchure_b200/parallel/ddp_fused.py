@@ -45,16 +45,25 @@ class FusedReducer:
             offs.append(total)
             total += (b.numel + 63) // 64 * 64
         self.comm = None
+        self.embed_rows = self.embed_ids = None
         if self.world > 1:
             from torchure_b200.core.symm import SymmComm
 
+            table = ddp.early_table
+            extra = 0
+            if table is not None:
+                extra = ddp.embed_tokens * (table.shape[1] * 4 + 8) + 1024
             self.comm = SymmComm(ddp.mesh.get_group(ddp.dim), ddp.mesh.coordinate(ddp.dim), self.world,
-                                 staging_bytes=4096, persistent_bytes=total * 4 + 4096)
+                                 staging_bytes=4096, persistent_bytes=total * 4 + 4096 + extra)
             self.comm_sms = comm_sms
             self.flat = self.comm.alloc(total, torch.float32)
             self.flat.zero_()
-            self.partials = self.comm.partials(len(ddp.buckets))
+            # one slot of sum-of-squares partials per bucket, plus one for the embedding-row exchange's correction
+            self.partials = self.comm.partials(len(ddp.buckets) + 1)
             self.partials.zero_()
+            if table is not None:
+                self.embed_rows = self.comm.alloc(ddp.embed_tokens * table.shape[1], torch.float32)
+                self.embed_ids = self.comm.alloc(ddp.embed_tokens, torch.int64)
             self.stream = torch.cuda.Stream(device=dev, priority=-1)
             ops.set_compute_sm_reserve(sm_reserve)
         else:
@@ -69,6 +78,7 @@ class FusedReducer:
             for p, v in zip(b.params, b.views):
                 self._view_of[p] = v
         self._written: set[int] = set()
+        self._table_done: torch.cuda.Event | None = None
 
     # -- sink API: the producer writes into the bucket itself ------------------------------------------------
     def grad_dest(self, p: torch.Tensor) -> tuple[torch.Tensor, bool]:
@@ -80,6 +90,41 @@ class FusedReducer:
         current stream)."""
         self._written.add(id(p))
         self.ddp._count_down(p)
+
+    # -- tied embedding / head bucket: reduce early, exchange the embedding rows afterwards ---------------------
+    # The tied gradient is dW_head (complete when the loss head's backward ends, before any block runs backward)
+    # plus at most one row per token from the embedding lookup (known only after the LAST kernel of backward).  An
+    # all-reduce is linear, so the big dense part is launched at once and hides under the whole backward; the rows
+    # are exchanged at the end: every rank leaves its (ids, rows) in symmetric memory and adds ALL ranks' rows,
+    # scaled by 1/world, into its reduced bucket with the deterministic scatter kernel (same order of additions on
+    # every rank, so the replicas keep identical bits).
+    def early_table(self, p: torch.Tensor) -> bool:
+        """True when `p` is the tied table, the exchange is configured and this micro-batch synchronises."""
+        return self.embed_rows is not None and p is self.ddp.early_table and self.ddp.requires_sync
+
+    def embed_rows_dest(self, M: int, D: int) -> torch.Tensor:
+        assert M * D <= self.embed_rows.numel(), (
+            f"{M} tokens per micro-batch exceed ddp.embed_tokens = {self.ddp.embed_tokens}")
+        return self.embed_rows[: M * D].view(M, D)
+
+    def exchange_embedding(self, ids: torch.Tensor, table: torch.Tensor) -> None:
+        """`embed_rows_dest` holds this rank's embedding-row gradients for tokens `ids`; the table's bucket was
+        launched by ``grad_written(table)`` when the loss head finished."""
+        from torchure_b200.ops import kernels as K
+
+        M = ids.numel()
+        done = self._table_done
+        assert done is not None, "the tied bucket must have been launched before the embedding rows are exchanged"
+        torch.cuda.current_stream().wait_event(done)       # the bucket holds avg(dW_head) now
+        self.embed_ids[:M].copy_(ids.reshape(-1))
+        self.comm.barrier(phase=2)                          # every rank's rows and ids are in place
+        ro, io = self.comm.offset_of(self.embed_rows), self.comm.offset_of(self.embed_ids)
+        sources = [(self.comm.peers[p] + io, self.comm.peers[p] + ro) for p in range(self.world)]
+        K.embedding_scatter_(sources, self._view_of[table], M, scale=1.0 / self.world,
+                             sq_delta=self.partials[len(self.ddp.buckets)], blocks=592)
+        self.comm.barrier(phase=3)                          # nobody reads my rows any more
+        ops.count_launch(2)
+        self._table_done = None
 
     # -- hook path: a gradient arrived through autograd -------------------------------------------------------
     def absorb(self, p: torch.Tensor) -> bool:
@@ -106,14 +151,17 @@ class FusedReducer:
             return _Ready()
         ready = torch.cuda.Event()
         ready.record()
+        early = self.embed_rows is not None and b.params[0] is self.ddp.early_table
         with torch.cuda.stream(self.stream):
             self.stream.wait_event(ready)
             # buckets reduced under the rest of backward share the SMs with it; the last bucket has the GPU to itself
-            last = b.index == len(self.ddp.buckets) - 1
+            last = b.index == len(self.ddp.buckets) - 1 and not early
             self.comm.all_reduce_symmetric_(self.padded[b.index], "avg", sq_slot=b.index,
                                             blocks=self.comm.blocks if last else self.comm_sms)
             done = torch.cuda.Event()
             done.record()
+        if early:
+            self._table_done = done
         return _Ready(done)
 
     def wait(self, works) -> None:

@@ -39,9 +39,15 @@ class _HeadToSeq(torch.autograd.Function):
         return all_to_all(g.contiguous(), ctx.mesh, ctx.dim, split_dim=2, concat_dim=1), None, None
 
 
-def ulysses_attention(q, k, v, mesh, dim: str, attn_fn):
+def ulysses_attention(q, k, v, mesh, dim: str, attn_fn=None):
     """q (B, S/n, Hq, d), k/v (B, S/n, Hkv, d), sequence-sharded in rank order.  `attn_fn(q, k, v)` is any
-    full-sequence attention on (B, S, h, d) tensors (e.g. causal SDPA or the sm_100a kernel wrapper)."""
+    full-sequence attention on (B, S, h, d) tensors; the default is causal ``ops.attention.flash_attention``: the
+    tcgen05 kernels on Blackwell (bf16, d = 128), SDPA elsewhere.  On GPUs the two exchanges are the NVLink
+    all-to-all kernel of ``core.collective``."""
+    if attn_fn is None:
+        from torchure_b200.ops.attention import flash_attention
+
+        attn_fn = flash_attention
     n = mesh.size(dim)
     assert q.shape[2] % n == 0 and k.shape[2] % n == 0, "head counts must be divisible by the Ulysses degree"
     qh, kh, vh = (_SeqToHead.apply(t, mesh, dim) for t in (q, k, v))

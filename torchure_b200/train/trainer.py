@@ -163,9 +163,12 @@ class Trainer:
             self._opt_params = self.ddp.optimizer_params()
             return model
         ddp_cfg = self.config.get("ddp", {})
+        data_cfg = self.config["data"]
+        embed_tokens = data_cfg["micro_batch_size"] * data_cfg["seq_len"] if ddp_cfg.get("early_embedding", True) else 0
         self.ddp = DDP(model, self.mesh, dim=self.data_axis, bucket_mb=ddp_cfg.get("bucket_mb", 25),
                        fused=ddp_cfg.get("fused"), merge_small=ddp_cfg.get("merge_small", True),
-                       comm_sms=ddp_cfg.get("comm_sms", 16), sm_reserve=ddp_cfg.get("sm_reserve", 0))
+                       comm_sms=ddp_cfg.get("comm_sms", 16), sm_reserve=ddp_cfg.get("sm_reserve", 0),
+                       embed_tokens=embed_tokens)
         return model
 
     def _wire_engine(self) -> None:
