@@ -90,6 +90,30 @@ def test_fsdp_and_hsdp_match_single_process(tmp_path):
     _compare(torch.load(tmp_path / "hsdp.pt"), torch.load(tmp_path / "one4.pt"))
 
 
+def _run_hist_only(rank, world, cfg, home, out):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    tr = Trainer(cfg, rank, rank, world, benchmark=True, device="cpu")
+    hist = tr.train_n_step_test(STEPS)
+    if rank == 0:
+        torch.save({"hist": hist}, out)
+
+
+def test_tensor_parallel_trainer_matches_single_process(tmp_path):
+    """mesh {dp: 1, tp: 2}: both ranks see the same batches and hold half of every block; loss and the global
+    gradient norm (sharded tensors summed over tp, replicated ones counted once) must follow the single-process run,
+    which also pins the clip coefficient and therefore every later step."""
+    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
+    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
+    tp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "tp": 2})
+    run_distributed(_run_hist_only, 2, tp_cfg, str(tmp_path), str(tmp_path / "tp.pt"), timeout_s=240)
+    a, b = torch.load(tmp_path / "tp.pt"), torch.load(tmp_path / "one.pt")
+    for x, y in zip(a["hist"], b["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
+
+
 def _run_fsdp_resume(rank, world, home, out):
     os.environ["TORCHURE_B200_HOME"] = home
     from torchure_b200.train.trainer import Trainer

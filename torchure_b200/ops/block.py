@@ -95,6 +95,10 @@ class Sm100Engine:
         self.external_shadows = False
         self.bf16_embedding = False
         self.pre_block = None
+        # tensor parallelism (parallel/tensor_parallel.py::EngineTP): the projections hold this rank's heads / FFN
+        # columns; the partial sums of the row-parallel products and of the column-parallel input gradients are
+        # all-reduced over the axis
+        self.tp = getattr(model, "tp", None)
 
     # -- shadows -----------------------------------------------------------------------------
     def shadow_pairs(self):
@@ -167,10 +171,14 @@ class _BlockFn(torch.autograd.Function):
         need_grad = any(ctx.needs_input_grad)
         o, st = attn_ops.attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=need_grad)
         y_a = K.linear_fwd(o, sh.wo)
+        if eng.tp is not None:
+            eng.tp.all_reduce_(y_a)        # row-parallel: sum the partial products of the ranks' heads
         x2, h2, rstd2 = K.add_rmsnorm(x, y_a, w2, eps)
         gu = K.linear_fwd(h2, sh.wgu)
         act = K.swiglu(gu)
         y_out = K.linear_fwd(act, sh.wd)
+        if eng.tp is not None:
+            eng.tp.all_reduce_(y_out)      # ... and of their FFN columns
         ctx.eng, ctx.sh, ctx.dims = eng, sh, (B, S, Hq, Hkv, hd, eps, use_norm)
         ctx.attn_state = st
         ctx.first = ids is not None
@@ -199,6 +207,8 @@ class _BlockFn(torch.autograd.Function):
         d_gu = K.swiglu_bwd(d_act, gu)
         del d_act
         d_h2 = K.linear_dgrad(d_gu, sh.wgu)
+        if eng.tp is not None:
+            eng.tp.all_reduce_(d_h2)       # column-parallel input gradient: every rank contributes its columns
         out.wgrad((P["wg"], P["wu"]), d_gu, h2)
         del d_gu
         dw2 = out.small(P["w2"])
@@ -215,12 +225,23 @@ class _BlockFn(torch.autograd.Function):
             dqn, dkn = out.small(P["qn"]), out.small(P["kn"])
         else:
             dqn = dkn = eng.dummy
-        K.qknorm_rope_bwd_(dqkv, qkv, qn, kn, cos, sin, dqn, dkn, S, Hq, Hkv, eps, use_norm, dq_acc=dq_acc)
+        if use_norm and eng.tp is not None:
+            # the gains are shared by all heads while each rank sees only its own: this backward's contribution is
+            # summed over the axis before it joins the (possibly running) destination
+            part = torch.zeros(2, dqn.numel(), dtype=torch.float32, device=dqn.device)
+            K.qknorm_rope_bwd_(dqkv, qkv, qn, kn, cos, sin, part[0], part[1], S, Hq, Hkv, eps, use_norm, dq_acc=dq_acc)
+            eng.tp.all_reduce_(part)
+            dqn.add_(part[0])
+            dkn.add_(part[1])
+        else:
+            K.qknorm_rope_bwd_(dqkv, qkv, qn, kn, cos, sin, dqn, dkn, S, Hq, Hkv, eps, use_norm, dq_acc=dq_acc)
         del dq_acc
         if use_norm:
             out.done(P["qn"])
             out.done(P["kn"])
         d_h1 = K.linear_dgrad(dqkv, sh.wqkv)
+        if eng.tp is not None:
+            eng.tp.all_reduce_(d_h1)
         out.wgrad((P["wq"], P["wk"], P["wv"]), dqkv, h1)
         del dqkv
         dw1 = out.small(P["w1"])

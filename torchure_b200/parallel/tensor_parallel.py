@@ -187,6 +187,14 @@ class ColumnParallelLinear(nn.Module):
         self.weight = nn.Parameter(full.weight.detach()[r * per:(r + 1) * per].clone())
         self.mesh, self.dim, self.sp = mesh, dim, sequence_parallel
 
+    @property
+    def in_features(self) -> int:
+        return self.weight.shape[1]
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.shape[0]
+
     def forward(self, x):
         if self.sp:
             comm = _fused_comm(x, self.mesh, self.dim)
@@ -229,18 +237,61 @@ def parallelize_block(block, mesh, dim: str = "tp", sequence_parallel: bool = Fa
     g.o_proj = RowParallelLinear(g.o_proj, mesh, dim, sequence_parallel)
     g.num_heads //= n
     g.num_kv_heads //= n
+    if getattr(g, "qk_norm", False) and n > 1:
+        # the per-head gains are shared by all heads while each rank only sees its own: sum their gradients over the
+        # axis (autograd path; the sm_100a engine does the same inside its block function)
+        def _sum_over_axis(grad):   # on the incoming gradient, so accumulation over micro-batches stays correct
+            grad = grad.contiguous().clone()
+            all_reduce(grad, mesh, dim, "sum")
+            return grad
+
+        for w in (g.q_norm.weight, g.k_norm.weight):
+            w.register_hook(_sum_over_axis)
     f = block.ffn
     f.gate_proj = ColumnParallelLinear(f.gate_proj, mesh, dim, sequence_parallel)
     f.up_proj = ColumnParallelLinear(f.up_proj, mesh, dim, sequence_parallel)
     f.down_proj = RowParallelLinear(f.down_proj, mesh, dim, sequence_parallel)
 
 
-def parallelize_model(model, mesh, dim: str = "tp") -> None:
-    """Tensor-parallel decoder: every block sharded, embedding / norms / head replicated.  Forces the torch path
-    (the sm_100a engine expects unsharded fused projections)."""
+class EngineTP:
+    """What the sm_100a engine needs to run a tensor-parallel block: the partial sums of the two row-parallel GEMMs
+    (attention output, MLP output) and of the two column-parallel input gradients are all-reduced over the axis with
+    the NVLink all-reduce kernel, and the per-head QK-norm gain gradients (each rank sees only its heads) are summed."""
+
+    def __init__(self, mesh, dim: str):
+        self.mesh, self.dim = mesh, dim
+        self.size = mesh.size(dim)
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.size > 1:
+            all_reduce(t, self.mesh, self.dim, "sum")
+        return t
+
+
+def parallelize_model(model, mesh, dim: str = "tp", sequence_parallel: bool = False) -> None:
+    """Tensor-parallel decoder: every block sharded (whole KV heads and FFN columns per rank), embedding / norms /
+    head replicated.
+
+    Without sequence parallelism the model keeps its execution path: on Blackwell the sm_100a engine runs each block
+    on the rank's heads and FFN columns with its own kernels (the fused projections are simply narrower) and
+    all-reduces the four partial sums (``EngineTP``).  With ``sequence_parallel`` the blocks run through the
+    module-level column / row linears, whose sequence-parallel form is ONE fused kernel each on GPUs (``ag_gemm`` /
+    ``gemm_rs``), around the PyTorch attention and norms."""
+    n = mesh.size(dim)
     for b in model.blocks:
-        parallelize_block(b, mesh, dim)
-    model.impl = "torch"
+        parallelize_block(b, mesh, dim, sequence_parallel)
+    for b in model.blocks:
+        for lin in (b.gqa.q_proj, b.gqa.k_proj, b.gqa.v_proj, b.gqa.o_proj, b.ffn.gate_proj, b.ffn.up_proj,
+                    b.ffn.down_proj):
+            lin.weight._tp_sharded = True
+    if sequence_parallel:
+        model.impl = "torch"
+        return
+    # the engine reads head counts and the FFN width from the model's config: make them this rank's
+    model.cfg = dict(model.cfg, num_heads=model.cfg["num_heads"] // n, num_kv_heads=model.cfg["num_kv_heads"] // n,
+                     ffn_dim=model.cfg["ffn_dim"] // n)
+    model._engine = None
+    model.tp = EngineTP(mesh, dim)
 
 
 class _VocabParallelCE(torch.autograd.Function):

@@ -138,6 +138,8 @@ class Trainer:
         axes = self.mesh.axes()
         self._opt_params = None
         self.sharded = "dp_shard" in axes
+        self.tp_size = self.mesh.size("tp") if "tp" in axes else 1
+        assert not (self.sharded and self.tp_size > 1), "dp_shard and tp cannot be combined yet"
         if "tp" in axes and self.mesh.size("tp") > 1:
             from torchure_b200.parallel.tensor_parallel import parallelize_model
 
@@ -233,6 +235,13 @@ class Trainer:
             del full
             if "dp_replicate" not in self.mesh.axes() or self.mesh.coordinate("dp_replicate") == 0:
                 self.checkpointer.save_optimizer(self.optimizer, step, shard=self.mesh.coordinate("dp_shard"))
+        elif self.tp_size > 1:
+            # every tensor-parallel coordinate holds different rows / columns: one file pair per coordinate, written
+            # by the first data-parallel replica
+            if self.mesh.coordinate(self.data_axis) == 0:
+                tp = self.mesh.coordinate("tp")
+                self.checkpointer.save_model(self.model, step, shard=tp)
+                self.checkpointer.save_optimizer(self.optimizer, step, shard=tp)
         elif self.rank == 0:
             self.checkpointer.save_model(self.model, step)
             self.checkpointer.save_optimizer(self.optimizer, step)
@@ -269,6 +278,10 @@ class Trainer:
         if self.sharded:
             self.ddp.load_full_state_dict(self.checkpointer._read(step, "model.pt"))
             self.checkpointer.load_optimizer(self.optimizer, step, shard=self.mesh.coordinate("dp_shard"))
+        elif self.tp_size > 1:
+            tp = self.mesh.coordinate("tp")
+            self.checkpointer.load_model(self.model, step, shard=tp)
+            self.checkpointer.load_optimizer(self.optimizer, step, shard=tp)
         else:
             self.checkpointer.load_model(self.model, step)
             self.checkpointer.load_optimizer(self.optimizer, step)
@@ -312,6 +325,8 @@ class Trainer:
         sq = self.ddp.sq_norm()
         params = self._opt_params if self._opt_params is not None else [
             p for p in self.model.parameters() if p.requires_grad]
+        if self.tp_size > 1:
+            sq = self._tp_sq_norm(params)
         if sq is not None and hasattr(self.optimizer, "set_grad_scale"):
             grad_norm, coef = grad_norm_and_coef(params, self.mesh, self.max_norm, shard_dims=(), presummed_sq=sq)
             if self.max_norm is not None:
@@ -324,6 +339,17 @@ class Trainer:
             self.ddp.mark_updated()
         self.optimizer.zero_grad()
         return loss, grad_norm
+
+    def _tp_sq_norm(self, params) -> torch.Tensor:
+        """Global sum of squared gradients under tensor parallelism: the sharded matrices contribute their own rows /
+        columns on every rank (summed over the axis), the replicated tensors are counted once."""
+        from torchure_b200.core.grad_helper import _local_sq_norm
+
+        sharded = [p.grad for p in params if p.grad is not None and getattr(p, "_tp_sharded", False)]
+        whole = [p.grad for p in params if p.grad is not None and not getattr(p, "_tp_sharded", False)]
+        sq = _local_sq_norm(sharded).reshape(1).clone()
+        all_reduce(sq, self.mesh, "tp", "sum")
+        return (sq + _local_sq_norm(whole).reshape(1)).reshape(())
 
     def train_step_untimed(self) -> dict[str, torch.Tensor]:
         if self.use_cuda_graph:
