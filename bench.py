@@ -55,11 +55,25 @@ SEQ_LEN = 4096
 PUBLISHED_TPS_1GPU_H100 = 54_500.0
 
 
-def bench_config(model: str, n_gpus: int, total_steps: int, micro_batch: int | None = None, chunk: int = 4096) -> dict:
+def bench_mesh(parallel: str, n_gpus: int) -> dict:
+    """dp: DDP (the headline).  fsdp / hsdp2 / tp2: the other strategies the mesh can select, for comparison rows."""
+    if parallel == "fsdp":
+        return {"dp_shard": n_gpus}
+    if parallel == "hsdp2":
+        return {"dp_replicate": 2, "dp_shard": n_gpus // 2}
+    if parallel == "tp2":
+        return {"dp": n_gpus // 2, "tp": 2}
+    return {"dp": n_gpus}
+
+
+def bench_config(model: str, n_gpus: int, total_steps: int, micro_batch: int | None = None, chunk: int = 4096,
+                 parallel: str = "dp") -> dict:
     mbs = micro_batch or MICRO_BATCH[model]
+    mesh = bench_mesh(parallel, n_gpus)
+    replicas = n_gpus // mesh.get("tp", 1)      # ranks that see different data
     return {
         "model": {"name": "qwen3_dense", "config": dict(MODELS[model])},
-        "mesh": {"dp": n_gpus},
+        "mesh": mesh,
         "optimizer": {"name": "adamw",
                       "config": {"lr": 3e-4, "weight_decay": 0.1, "betas": [0.9, 0.95], "fused": True},
                       "max_norm": 1.0,
@@ -68,7 +82,7 @@ def bench_config(model: str, n_gpus: int, total_steps: int, micro_batch: int | N
         "objective": {"name": "AR", "config": {"ignore_index": -100, "fused_linear_ce": True, "ce_chunk_size": chunk}},
         "data": {"name": "synthetic", "synthetic": True, "seed": 42, "mean_doc_len": 1024, "eos_id": 151643,
                  "tokenizer": "synthetic", "eos_token": "<eos>", "pad_token": "<pad>", "text_field": "text",
-                 "shuffle_buffer": 0, "num_workers": 0, "global_batch_size": mbs * n_gpus, "micro_batch_size": mbs,
+                 "shuffle_buffer": 0, "num_workers": 0, "global_batch_size": mbs * replicas, "micro_batch_size": mbs,
                  "seq_len": SEQ_LEN},
         "ddp": {"bucket_mb": 25},
         "checkpointing": {"save_steps": 10 ** 9, "resume": None},
@@ -181,8 +195,11 @@ def timed_steps(step_fn, k: int, read_loss: bool):
 def shared_config(model: str, cfg: dict, world: int, ce_chunk: int) -> dict:
     """The `config` object both arms print: identical keys and values for identical work."""
     mbs = cfg["data"]["micro_batch_size"]
-    return {"model": f"qwen3-{model}", "ffn_dim": cfg["model"]["config"]["ffn_dim"], "global_batch": mbs * world,
-            "micro_batch": mbs, "seq_len": cfg["data"]["seq_len"], "parallelism": f"dp{world}", "ce_chunk": ce_chunk,
+    mesh = cfg["mesh"]
+    par = f"dp{world}" if list(mesh) == ["dp"] else "x".join(f"{k}{v}" for k, v in mesh.items())
+    return {"model": f"qwen3-{model}", "ffn_dim": cfg["model"]["config"]["ffn_dim"],
+            "global_batch": cfg["data"]["global_batch_size"],
+            "micro_batch": mbs, "seq_len": cfg["data"]["seq_len"], "parallelism": par, "ce_chunk": ce_chunk,
             "grad_clip": 1.0, "ddp_bucket_mb": cfg["ddp"]["bucket_mb"], "sync_per_step": False,
             "l2": "per-step working set (>10 GB) exceeds the 126 MB L2; no explicit flush"}
 
@@ -245,7 +262,8 @@ def run_ours(args) -> None:
 
     rank, local_rank, world = init_distributed()
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    cfg = bench_config(args.model, world, args.steps * 2 + args.warmup + 8, args.micro_batch, args.ce_chunk)
+    cfg = bench_config(args.model, world, args.steps * 2 + args.warmup + 8, args.micro_batch, args.ce_chunk,
+                       args.parallel)
     if args.torch_path:
         cfg["compile"] = False
     cfg["cuda_graph"] = bool(args.graph) and not args.torch_path
@@ -311,6 +329,8 @@ def main() -> None:
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--torch-path", action="store_true", help="ours: run the PyTorch oracle path (A/B)")
     ap.add_argument("--graph", type=int, default=1, help="ours: replay the device step from one CUDA graph (1) or launch eagerly (0)")
+    ap.add_argument("--parallel", choices=["dp", "fsdp", "hsdp2", "tp2"], default="dp",
+                    help="ours: strategy selected through the mesh (dp = DDP is the headline configuration)")
     ap.add_argument("--census", type=int, default=1, help="one extra untimed step under torch.profiler: kernel census")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:

@@ -33,7 +33,7 @@ def _entry(rank, world, port, fn, args, errq, env, store_path):
             dist.destroy_process_group()
 
 
-def run_on_gpus(fn, world: int, *args, timeout_s: int = 300, env: dict | None = None):
+def run_on_gpus(fn, world: int, *args, timeout_s: int = 150, env: dict | None = None):
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
     port = free_port()

@@ -142,3 +142,50 @@ def test_fused_linear_ce_sm100(shape):
     assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, ref.item())
     assert relerr(h.grad, h2.grad) < 3e-2
     assert relerr(w.grad, w2.grad) < 3e-2
+
+
+def test_llama3_runs_on_the_engine_and_matches_oracle():
+    """The Llama-3 variant (no QK-norm, theta 5e5, eps 1e-5) on the same kernels, at a head_dim they cover."""
+    from torchure_b200 import ops
+    from torchure_b200.models import Llama3
+    from torchure_b200.objectives import ARObjective
+    from torchure_b200.ops import kernels
+
+    cfg = dict(num_layers=2, num_heads=4, num_kv_heads=2, emb_dim=512, vocab_size=4096, ffn_dim=1024)   # head_dim 128
+    torch.manual_seed(5)
+    fast = Llama3(**cfg).cuda()
+    fast.init_weights()
+    slow = Llama3(**cfg, impl="torch").cuda()
+    slow.load_state_dict(fast.state_dict())
+    ids = torch.randint(0, cfg["vocab_size"], (2, 256), device="cuda")
+    batch = {"input_ids": ids, "labels": ids}
+    before = ops.launches()
+    loss = ARObjective(fused_linear_ce=True, ce_chunk_size=256).compute_loss(fast, batch)
+    loss.backward()
+    assert ops.launches() - before > 40
+    ops.force_fallback(True)
+    try:
+        ref = ARObjective(fused_linear_ce=False).compute_loss(slow, batch)
+        ref.backward()
+    finally:
+        ops.force_fallback(False)
+    kernels.check_error()
+    assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, abs(ref.item()))
+    for (n, p), (_, q) in zip(fast.named_parameters(), slow.named_parameters()):
+        assert relerr(p.grad, q.grad) < 3e-2, (n, relerr(p.grad, q.grad))
+
+
+def test_uncovered_shapes_are_loud():
+    """A sequence length the attention kernels do not cover raises; a head_dim they do not cover runs the PyTorch
+    path with a warning: never a silent library kernel on the hot path."""
+    from torchure_b200.models import Qwen3
+
+    m = Qwen3(**CFG).cuda()
+    m.init_weights()
+    with pytest.raises(RuntimeError, match="multiples of 128"):
+        m(torch.randint(0, CFG["vocab_size"], (1, 100), device="cuda"))
+    small = Qwen3(num_layers=1, num_heads=4, num_kv_heads=2, emb_dim=256, head_dim=64, vocab_size=512, ffn_dim=512).cuda()
+    small.init_weights()
+    with pytest.warns(UserWarning, match="PyTorch path"):
+        out = small(torch.randint(0, 512, (1, 100), device="cuda"))
+    assert out.shape == (1, 100, 512)

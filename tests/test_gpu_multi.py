@@ -362,7 +362,7 @@ def _trainer_strategies(rank, world, home, out):
 
 
 def test_trainer_ddp_and_fsdp_on_gpus(tmp_path):
-    run_on_gpus(_trainer_strategies, min(_world(), 4), str(tmp_path), str(tmp_path / "h.pt"), timeout_s=600)
+    run_on_gpus(_trainer_strategies, min(_world(), 4), str(tmp_path), str(tmp_path / "h.pt"), timeout_s=240)
     got = torch.load(tmp_path / "h.pt")
     assert got["ddp"][-1]["loss"] < got["ddp"][0]["loss"]
 
@@ -377,7 +377,9 @@ def _trainer_vs_single(rank, world, home, out, emulate):
     cfg = _trainer_cfg({"dp": world}, f"t_par_{world}", 4 * max(world, emulate), graph=True)
     tr = Trainer(cfg, rank, rank, world, benchmark=True)
     if emulate:
-        tr.prefetcher = _Interleaved(cfg, emulate)
+        from torchure_b200.data import CUDAPrefetcher
+
+        tr.prefetcher = CUDAPrefetcher(_Interleaved(cfg, emulate), tr.device)
     hist = tr.train_n_step_test(6)
     if rank == 0:
         torch.save(hist, out)
@@ -385,8 +387,8 @@ def _trainer_vs_single(rank, world, home, out, emulate):
 
 def test_trainer_two_gpus_match_one(tmp_path):
     """2-GPU DDP through the Trainer (graph replay, fused reducer) against ONE GPU fed the same rows."""
-    run_on_gpus(_trainer_vs_single, 2, str(tmp_path), str(tmp_path / "two.pt"), 0, timeout_s=600)
-    run_on_gpus(_trainer_vs_single, 1, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=600)
+    run_on_gpus(_trainer_vs_single, 2, str(tmp_path), str(tmp_path / "two.pt"), 0, timeout_s=240)
+    run_on_gpus(_trainer_vs_single, 1, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=240)
     two, one = torch.load(tmp_path / "two.pt"), torch.load(tmp_path / "one.pt")
     for x, y in zip(two, one):
         assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)
@@ -496,8 +498,8 @@ def _trainer_tp(rank, world, home, out):
 
 
 def test_trainer_tensor_parallel_on_engine(tmp_path):
-    run_on_gpus(_trainer_tp, 2, str(tmp_path), str(tmp_path / "tp.pt"), timeout_s=600)
-    run_on_gpus(_trainer_vs_single_cfg, 1, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=600)
+    run_on_gpus(_trainer_tp, 2, str(tmp_path), str(tmp_path / "tp.pt"), timeout_s=240)
+    run_on_gpus(_trainer_vs_single_cfg, 1, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
     tp, one = torch.load(tmp_path / "tp.pt"), torch.load(tmp_path / "one.pt")
     for x, y in zip(tp, one):
         assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)

@@ -120,3 +120,71 @@ def test_matches_reference_model_cpu_fp32():
     ref(ids).sum().backward()
     for (n, p), (_, q) in zip(ours.named_parameters(), ref.named_parameters()):
         torch.testing.assert_close(p.grad, q.grad, rtol=1e-3, atol=1e-5, msg=lambda m: f"{n}: {m}")
+
+
+def _hf_pair(kind):
+    """(our model, the Hugging Face implementation of the same architecture with our weights), tiny, fp32, CPU."""
+    transformers = pytest.importorskip("transformers")
+    from torchure_b200.models import Llama3, Qwen3
+
+    torch.manual_seed(0)
+    common = dict(num_layers=2, num_heads=4, num_kv_heads=2, emb_dim=64, vocab_size=97, ffn_dim=160)
+    if kind == "llama3":
+        ours = Llama3(**common)           # head_dim = emb / heads = 16, no QK-norm, theta 5e5, eps 1e-5
+        hf_cfg = transformers.LlamaConfig(
+            vocab_size=97, hidden_size=64, intermediate_size=160, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=True,
+            attention_bias=False, mlp_bias=False, max_position_embeddings=128)
+        hf = transformers.LlamaForCausalLM(hf_cfg)
+    else:
+        ours = Qwen3(**common, head_dim=32)   # head_dim independent of emb / heads, QK-norm, theta 1e6, eps 1e-6
+        hf_cfg = transformers.Qwen3Config(
+            vocab_size=97, hidden_size=64, intermediate_size=160, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True,
+            attention_bias=False, max_position_embeddings=128, use_sliding_window=False)
+        hf = transformers.Qwen3ForCausalLM(hf_cfg)
+    ours.init_weights()
+    with torch.no_grad():
+        for p in ours.parameters():   # non-trivial norm gains
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = {"model.embed_tokens.weight": ours.token_emb.weight, "model.norm.weight": ours.norm.weight,
+          "lm_head.weight": ours.lm_head.weight}
+    for i, b in enumerate(ours.blocks):
+        pre = f"model.layers.{i}."
+        sd.update({pre + "self_attn.q_proj.weight": b.gqa.q_proj.weight, pre + "self_attn.k_proj.weight": b.gqa.k_proj.weight,
+                   pre + "self_attn.v_proj.weight": b.gqa.v_proj.weight, pre + "self_attn.o_proj.weight": b.gqa.o_proj.weight,
+                   pre + "mlp.gate_proj.weight": b.ffn.gate_proj.weight, pre + "mlp.up_proj.weight": b.ffn.up_proj.weight,
+                   pre + "mlp.down_proj.weight": b.ffn.down_proj.weight, pre + "input_layernorm.weight": b.norm1.weight,
+                   pre + "post_attention_layernorm.weight": b.norm2.weight})
+        if kind != "llama3":
+            sd[pre + "self_attn.q_norm.weight"] = b.gqa.q_norm.weight
+            sd[pre + "self_attn.k_norm.weight"] = b.gqa.k_norm.weight
+    missing, unexpected = hf.load_state_dict({k: v.detach().clone() for k, v in sd.items()}, strict=False)
+    assert not unexpected and all("rotary" in m or "inv_freq" in m for m in missing), (missing, unexpected)
+    return ours.eval(), hf.eval()
+
+
+@pytest.mark.parametrize("kind", ["llama3", "qwen3"])
+def test_models_match_the_hugging_face_implementations(kind):
+    """Independent oracle for both model families: logits and input-embedding gradients of the Hugging Face
+    implementation (random init, no download) loaded with our weights."""
+    ours, hf = _hf_pair(kind)
+    ids = torch.randint(0, 97, (2, 24), generator=torch.Generator().manual_seed(1))
+    got = ours(ids)
+    want = hf(input_ids=ids).logits
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    got.float().pow(2).mean().backward()
+    want.float().pow(2).mean().backward()
+    torch.testing.assert_close(ours.token_emb.weight.grad, hf.model.embed_tokens.weight.grad, rtol=1e-3, atol=1e-6)
+    torch.testing.assert_close(ours.blocks[0].gqa.q_proj.weight.grad, hf.model.layers[0].self_attn.q_proj.weight.grad,
+                               rtol=1e-3, atol=1e-6)
+
+
+def test_llama3_registry_and_defaults():
+    from torchure_b200.models import build_model
+
+    m = build_model("llama3_2", dict(num_layers=1, num_heads=4, num_kv_heads=2, emb_dim=64, vocab_size=50))
+    assert m.cfg["head_dim"] == 16 and m.cfg["qk_norm"] is False and m.cfg["rope_theta"] == 500_000.0
+    assert not hasattr(m.blocks[0].gqa, "q_norm")
+    assert m.lm_head.weight is m.token_emb.weight

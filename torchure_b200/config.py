@@ -22,6 +22,7 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
     run_name      str
     [wandb]       {enabled, project, entity}
     [compile]     bool   per-block fused execution (hand-written kernels) on/off
+    [torch_compile] bool, [compile_mode] str   with compile=false: torch.compile every block of the PyTorch path
     [log_every]   int
 """
 

@@ -160,7 +160,9 @@ class SymmComm:
         return all(t.data_ptr() % 16 == 0 and (t.numel() * t.element_size()) % 16 == 0 for t in ts)
 
     def _grid(self, nbytes: int) -> int:
-        return max(1, min(self.blocks, (nbytes + 65535) // 65536))
+        """CTAs for a message: one per 8 KiB (a 512-thread CTA moves 8 KiB per pass of 16-byte accesses), so that a
+        64 KiB - 512 KiB one-shot all-reduce is spread over 8 - 64 CTAs instead of crawling through one."""
+        return max(1, min(self.blocks, (nbytes + 8191) // 8192))
 
     def all_reduce_(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
         nbytes = t.numel() * t.element_size()

@@ -77,6 +77,9 @@ constexpr int kChunkElems = 16384;
 void adamw_multi(const TensorList& t, float lr, float beta1, float beta2, float eps, float weight_decay,
                  float bias1, float bias2, const float* grad_scale, int maximize, const float* hyper,
                  cudaStream_t stream);
+// out[0] = sqrt(sum(partials[0..n))), out[1] = min(1, max_norm / (out[0] + eps)) (1 when max_norm <= 0); one launch,
+// fixed summation order
+void finalize_norm(const float* partials, int n, float max_norm, float eps, float* out, cudaStream_t stream);
 // out[0] += sum over all tensors of x^2 (flag bit0 = bf16)
 void sqnorm_multi(const TensorList& t, float* out, cudaStream_t stream);
 void scale_multi(const TensorList& t, const float* scale, cudaStream_t stream);

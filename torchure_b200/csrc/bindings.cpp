@@ -213,6 +213,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scale_inplace", &scale_inplace);
   m.def("adamw_multi", &adamw_multi);
   m.def("sqnorm_multi", &sqnorm_multi);
+  m.def("finalize_norm", [](const torch::Tensor& partials, double max_norm, double eps, torch::Tensor& out) {
+    TORCH_CHECK(partials.scalar_type() == torch::kFloat32 && partials.is_contiguous() && out.numel() >= 2 &&
+                out.scalar_type() == torch::kFloat32);
+    tb::finalize_norm(partials.data_ptr<float>(), (int)partials.numel(), (float)max_norm, (float)eps,
+                      out.data_ptr<float>(), cur_stream());
+  });
   m.def("scale_multi", &scale_multi);
   m.def("bucket_pack_multi", &bucket_pack_multi);
   register_comm(m);

@@ -202,14 +202,16 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
   for (int j = 0; j < MAX_VEC; ++j) dw_acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int row = lo + wid; row < hi; row += WARPS) {
     const int64_t off = static_cast<int64_t>(row) * D;
-    float4 xv[MAX_VEC];
+    float4 xv[MAX_VEC], pv[MAX_VEC];
     uint2 dv[MAX_VEC];
+    // all three input streams of the row are requested before anything is consumed
 #pragma unroll
     for (int j = 0; j < MAX_VEC; ++j) {
       const int i = lane + j * 32;
       if (i < nvec) {
         xv[j] = reinterpret_cast<const float4*>(x + off)[i];
         dv[j] = reinterpret_cast<const uint2*>(dh + off)[i];
+        pv[j] = dx_in ? reinterpret_cast<const float4*>(dx_in + off)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
     const float r = rstd[row];
@@ -236,10 +238,7 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
         o.y = r * (a.y * g.y - xv[j].y * dot);
         o.z = r * (b.x * g.z - xv[j].z * dot);
         o.w = r * (b.y * g.w - xv[j].w * dot);
-        if (dx_in) {
-          const float4 p = reinterpret_cast<const float4*>(dx_in + off)[i];
-          o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-        }
+        o.x += pv[j].x; o.y += pv[j].y; o.z += pv[j].z; o.w += pv[j].w;
         reinterpret_cast<float4*>(dx + off)[i] = o;
         if (dx_bf16) {
           uint2 ob;
@@ -674,7 +673,9 @@ embedding_scatter_kernel(EmbedSources src, float* __restrict__ dtable, int M, in
 // ---------------------------------------------------------------------------------------------
 // cross-entropy on one vocabulary row per CTA: online max/sum, target gather, loss, in-place dlogits
 // ---------------------------------------------------------------------------------------------
-constexpr int CE_THREADS = 512;
+// 1024 threads per row: at most two rows per SM are in flight (296 rows = 90 MB of bf16 logits), so the second pass
+// over a row finds it in the 126 MB L2 instead of going back to HBM
+constexpr int CE_THREADS = 1024;
 
 __global__ void __launch_bounds__(CE_THREADS)
 ce_softmax_grad_kernel(__nv_bfloat16* __restrict__ logits, int64_t ldl, const int64_t* __restrict__ labels,
@@ -698,6 +699,7 @@ ce_softmax_grad_kernel(__nv_bfloat16* __restrict__ logits, int64_t ldl, const in
     if (v > m) { s = s * __expf(m - v) + 1.f; m = v; }
     else s += __expf(v - m);
   };
+#pragma unroll 4
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
     uint4 u = reinterpret_cast<const uint4*>(lr)[i];
     const uint32_t us[4] = {u.x, u.y, u.z, u.w};
@@ -735,6 +737,7 @@ ce_softmax_grad_kernel(__nv_bfloat16* __restrict__ logits, int64_t ldl, const in
   const float scale = *inv_n_valid;
   const float inv_s = 1.f / s_stats[1];
   const int lvec = static_cast<int>(label >> 3), lsub = static_cast<int>(label & 7);
+#pragma unroll 4
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
     uint4 u = reinterpret_cast<const uint4*>(lr)[i];
     const uint32_t us[4] = {u.x, u.y, u.z, u.w};

@@ -169,6 +169,31 @@ void adamw_multi(const TensorList& t, float lr, float beta1, float beta2, float 
                                                       grad_scale, maximize, hyper);
 }
 
+// Gradient-norm finalisation in one launch: out[0] = sqrt(sum of `n` partial sums of squares), out[1] = the clip
+// coefficient min(1, max_norm / (norm + eps)) (1 when max_norm <= 0).  The sum runs in a fixed order (strided per
+// thread, then a shared-memory tree), so ranks holding the same partials derive the same bits.
+__global__ void __launch_bounds__(256)
+finalize_norm_kernel(const float* __restrict__ partials, int n, float max_norm, float eps, float* __restrict__ out) {
+  __shared__ float s[256];
+  float a = 0.f;
+  for (int i = threadIdx.x; i < n; i += 256) a += partials[i];
+  s[threadIdx.x] = a;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) s[threadIdx.x] += s[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const float norm = sqrtf(s[0]);
+    out[0] = norm;
+    out[1] = max_norm > 0.f ? fminf(1.f, max_norm / (norm + eps)) : 1.f;
+  }
+}
+
+void finalize_norm(const float* partials, int n, float max_norm, float eps, float* out, cudaStream_t stream) {
+  finalize_norm_kernel<<<1, 256, 0, stream>>>(partials, n, max_norm, eps, out);
+}
+
 void sqnorm_multi(const TensorList& t, float* out, cudaStream_t stream) {
   if (t.n_blocks <= 0) return;
   sqnorm_kernel<<<t.n_blocks, MT_THREADS, 0, stream>>>(t, out);

@@ -207,7 +207,17 @@ class Qwen3(nn.Module):
             return False
         from torchure_b200 import ops
 
-        return ops.available()
+        if not ops.available():
+            return False
+        if self.cfg["head_dim"] != 128:
+            if not getattr(self, "_warned_head_dim", False):
+                import warnings
+
+                warnings.warn(f"head_dim {self.cfg['head_dim']} is not covered by the sm_100a kernels (128 only): this "
+                              "model runs on the PyTorch path", stacklevel=3)
+                self._warned_head_dim = True
+            return False
+        return True
 
     def fused_param_groups(self):
         """Parameters whose gradients one fused GEMM produces (rows of Wqkv, rows of [Wgate; Wup]).  A gradient

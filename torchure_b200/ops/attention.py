@@ -14,8 +14,10 @@ backward, either the single-pass kernel ``csrc/attention_bwd_fused_sm100.cu`` (d
 block pair, dQ partial tiles added into an fp32 accumulator, so dQ is not bitwise repeatable) or the two-kernel
 path ``csrc/attention_bwd_dq_sm100.cu`` + ``csrc/attention_bwd_dkv_sm100.cu`` (seven products, no atomics, bitwise
 repeatable; ``set_backward("split")`` or ``TORCHURE_B200_ATTN_BWD=split``).
-``impl="sdpa"`` routes through ``torch.nn.functional.scaled_dot_product_attention`` and exists for
-A/B comparison and for shapes the kernel does not cover (head_dim != 128, S % 128 != 0, odd GQA ratio).
+``impl="sdpa"`` routes through ``torch.nn.functional.scaled_dot_product_attention``.  It exists for A/B comparison
+only and must be asked for (``TORCHURE_B200_ATTN=sdpa``): a shape the kernels do not cover (S % 128 != 0, an odd
+number of query heads per KV head) raises instead of silently running the library kernel on the hot path.  Models
+whose head_dim is not 128 never reach this module: they run on the PyTorch path (``models/qwen3.py::_use_sm100``).
 """
 
 from __future__ import annotations
@@ -65,6 +67,11 @@ class AttnState:
 
 def attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=True):
     """Returns (o (M, Hq*hd) bf16, state)."""
+    if _FORCE != "sdpa" and not kernel_supported(S, Hq, Hkv, hd):
+        raise RuntimeError(
+            f"the sm_100a attention kernels cover head_dim 128, sequence lengths in multiples of 128 and an even "
+            f"number of query heads per KV head; got head_dim {hd}, S {S}, {Hq}/{Hkv} heads.  Pad the sequence, or run "
+            f"the model with impl='torch', or set TORCHURE_B200_ATTN=sdpa to use the library kernel on purpose")
     if kernel_supported(S, Hq, Hkv, hd):
         ext = ops.ext()
         o = new_output("attn_fwd.o", B * S, Hq * hd, dtype=torch.bfloat16, device=qk.device)

@@ -83,6 +83,15 @@ def sq_norm(tensors: list[torch.Tensor]) -> torch.Tensor:
     return out
 
 
+def finalize_norm(partials: torch.Tensor, max_norm: float | None, eps: float = 1e-6) -> tuple[torch.Tensor, torch.Tensor]:
+    """(norm, clip coefficient) as 0-d device tensors from partial sums of squares, in ONE launch with a fixed
+    summation order: sqrt(sum(partials)) and min(1, max_norm / (norm + eps)) (1 without a max_norm)."""
+    out = torch.empty(2, dtype=torch.float32, device=partials.device)
+    ops.ext().finalize_norm(partials.reshape(-1), float(max_norm) if max_norm is not None else -1.0, eps, out)
+    ops.count_launch()
+    return out[0], out[1]
+
+
 def scale_(tensors: list[torch.Tensor], scale: torch.Tensor) -> None:
     tab = _table("scale", [tensors], _bf16_flags(tensors))
     ops.ext().scale_multi(*tab.args(), scale.to(torch.float32))

@@ -219,6 +219,19 @@ class DDP:
         self._works.clear()
 
     # -- fused extras ------------------------------------------------------------------------
+    def norm_and_coef(self, max_norm):
+        """(gradient norm, clip coefficient) from ONE finalisation kernel over the fused reducer's partials; None
+        on the library path."""
+        if self.active and self.fused:
+            return self.reducer.norm_and_coef(max_norm)
+        return None
+
+    def loss_slot(self):
+        """Symmetric 4-float tensor for the step's loss (fused reducer with more than one rank), else None."""
+        if self.active and self.fused:
+            return self.reducer.loss_slot()
+        return None
+
     def sq_norm(self) -> torch.Tensor | None:
         """Sum of squares of the reduced gradients, from the fused kernels' per-bucket partials
         (identical bits on every rank).  None on the library path."""

@@ -58,6 +58,8 @@ class FusedReducer:
             self.comm_sms = comm_sms
             self.flat = self.comm.alloc(total, torch.float32)
             self.flat.zero_()
+            self.flat_tail = self.comm.alloc(4, torch.float32)     # the step's loss, averaged in place over the ranks
+            self.flat_tail.zero_()
             # one slot of sum-of-squares partials per bucket, plus one for the embedding-row exchange's correction
             self.partials = self.comm.partials(len(ddp.buckets) + 1)
             self.partials.zero_()
@@ -173,6 +175,21 @@ class FusedReducer:
         if self.world == 1:
             return multi_tensor.sq_norm([self.flat])
         return self.partials.sum()
+
+    def norm_and_coef(self, max_norm: float | None) -> tuple[torch.Tensor, torch.Tensor]:
+        """(global gradient norm, clip coefficient) on the device, one finalisation launch over the per-bucket
+        partials the all-reduce kernels published (identical bits on every rank)."""
+        src = self.partials if self.world > 1 else multi_tensor.sq_norm([self.flat]).reshape(1)
+        return multi_tensor.finalize_norm(src, max_norm)
+
+    def loss_slot(self) -> torch.Tensor | None:
+        """A 4-float tensor inside the symmetric region: accumulating the step's loss there lets the data-parallel
+        average run as an in-place symmetric all-reduce (no padding copy, capturable in the step's graph)."""
+        if self.comm is None:
+            return None
+        if getattr(self, "_loss_slot", None) is None:
+            self._loss_slot = self.flat_tail
+        return self._loss_slot
 
 
 class _Ready:

@@ -287,9 +287,9 @@ class EngineFSDP:
             sq = multi_tensor.sq_norm([m.shard_grad for u in self.units for m in u.mats])
             all_reduce(sq, self.mesh, self.shard_dim, "sum")
             return sq + multi_tensor.sq_norm([self.gain_flat])
-        per = self.partials.view(len(self.units) + 1, self.comm.ext.COMM_MAX_RANKS, -1)
-        # the gains are replicated: every rank published the same value for them, count it once
-        return per[:-1].sum() + per[-1, 0].sum()
+        # every rank published the sum of squares of the rows (units) or of the slice (gains) IT reduced: the whole
+        # table adds up to the global norm, in the same order on every rank
+        return self.partials.sum()
 
     @property
     def clip_shard_dims(self) -> tuple[str, ...]:

@@ -241,6 +241,8 @@ def parallelize_block(block, mesh, dim: str = "tp", sequence_parallel: bool = Fa
         # the per-head gains are shared by all heads while each rank only sees its own: sum their gradients over the
         # axis (autograd path; the sm_100a engine does the same inside its block function)
         def _sum_over_axis(grad):   # on the incoming gradient, so accumulation over micro-batches stays correct
+            if grad is None:          # the sm_100a engine delivers these gradients through its sink, already summed
+                return None
             grad = grad.contiguous().clone()
             all_reduce(grad, mesh, dim, "sum")
             return grad

@@ -20,7 +20,8 @@ import json
 import os
 
 COMM_PATTERNS = ("nccl", "all_reduce_kernel", "all_gather_kernel", "reduce_scatter_kernel", "all_to_all_kernel",
-                 "broadcast_kernel", "barrier_kernel", "ag_gemm", "gemm_rs")
+                 "broadcast_kernel", "barrier_kernel", "ag_gemm", "gemm_rs", "all_gather_inplace_kernel",
+                 "reduce_scatter_symm_kernel", "embedding_scatter_kernel")
 GPU_CATS = ("kernel", "gpu_memcpy", "gpu_memset")
 
 

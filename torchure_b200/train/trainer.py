@@ -119,10 +119,19 @@ class Trainer:
 
     # -- construction --------------------------------------------------------------------------
     def _build_model(self):
+        """``compile: false`` selects the PyTorch path (the oracle) instead of the sm_100a engine.  On that path
+        ``torch_compile: true`` compiles every transformer block and the final norm in place, one region per block as
+        the reference does (``torchure/train/trainer.py:223-244``), with the reference's ``compile_mode`` key."""
         mc = dict(self.config["model"]["config"])
         if not self.config.get("compile", True):
             mc["impl"] = "torch"
-        return build_model(self.config["model"]["name"], mc)
+        model = build_model(self.config["model"]["name"], mc)
+        if self.config.get("torch_compile", False) and mc.get("impl") == "torch":
+            mode = self.config.get("compile_mode", "default")
+            for block in model.blocks:
+                block.compile(mode=mode)
+            model.norm.compile(mode=mode)
+        return model
 
     def _init_weights(self, model) -> None:
         model.to(self.device)
@@ -313,7 +322,13 @@ class Trainer:
         """Everything of one optimizer step that runs on the device: micro-batches, gradient reduction, clipping,
         AdamW.  `batches` (one dict per micro-batch) are used instead of the prefetcher when given."""
         K = self.microbatches_per_step
-        loss = torch.zeros((), device=self.device)
+        slot = self.ddp.loss_slot() if hasattr(self.ddp, "loss_slot") else None
+        if slot is not None:
+            slot.zero_()
+            loss = slot[0]          # accumulates inside symmetric memory: averaged over the ranks in place below
+        else:
+            loss = torch.zeros((), device=self.device)
+        self._loss_averaged = slot is not None
         if hasattr(self.ddp, "begin_step"):
             self.ddp.begin_step()      # sharded: all-gather the bf16 weights the last optimizer step rewrote
         self.ddp.requires_sync = False
@@ -322,12 +337,18 @@ class Trainer:
         self.ddp.requires_sync = True
         loss += self.micro_train_step(batches[K - 1] if batches else None)
         self.ddp.sync()
-        sq = self.ddp.sq_norm()
         params = self._opt_params if self._opt_params is not None else [
             p for p in self.model.parameters() if p.requires_grad]
-        if self.tp_size > 1:
-            sq = self._tp_sq_norm(params)
-        if sq is not None and hasattr(self.optimizer, "set_grad_scale"):
+        fused_norm = sq = None
+        if self.tp_size == 1 and hasattr(self.ddp, "norm_and_coef") and hasattr(self.optimizer, "set_grad_scale"):
+            fused_norm = self.ddp.norm_and_coef(self.max_norm)     # one kernel: partials -> norm and coefficient
+        if fused_norm is None:
+            sq = self._tp_sq_norm(params) if self.tp_size > 1 else self.ddp.sq_norm()
+        if fused_norm is not None:
+            grad_norm, coef = fused_norm
+            if self.max_norm is not None:
+                self.optimizer.set_grad_scale(coef)
+        elif sq is not None and hasattr(self.optimizer, "set_grad_scale"):
             grad_norm, coef = grad_norm_and_coef(params, self.mesh, self.max_norm, shard_dims=(), presummed_sq=sq)
             if self.max_norm is not None:
                 self.optimizer.set_grad_scale(coef)
@@ -338,6 +359,9 @@ class Trainer:
         if hasattr(self.ddp, "mark_updated"):
             self.ddp.mark_updated()
         self.optimizer.zero_grad()
+        if slot is not None:
+            self.ddp.reducer.comm.all_reduce_symmetric_(slot, "avg", blocks=1)
+            loss = slot[0].clone()
         return loss, grad_norm
 
     def _tp_sq_norm(self, params) -> torch.Tensor:
@@ -357,7 +381,7 @@ class Trainer:
         else:
             loss, grad_norm = self._device_step()
         self.scheduler.step()
-        if self.dp_size > 1:
+        if self.dp_size > 1 and not getattr(self, "_loss_averaged", False):
             all_reduce(loss, self.mesh, self.data_axis, "avg")
         return {"loss": loss, "grad_norm": grad_norm}
 
