@@ -290,3 +290,49 @@ def test_embedding_scatter_is_exact_and_repeatable():
         assert abs(got_sq.item() - t.double().pow(2).sum().item()) < 1e-4 * t.double().pow(2).sum().item()
     assert torch.equal(outs[0], outs[1])
     torch.testing.assert_close(outs[0].double(), want, rtol=1e-5, atol=1e-4)
+
+
+def test_repeat_runs_are_bitwise_stable_under_poison():
+    """Race detection for the compute kernels: the deterministic ones (GEMMs with their TMA rings and TMEM double
+    buffering, the attention forward, the two-kernel attention backward, norms, RoPE, SwiGLU) must give identical bits
+    on every one of many back-to-back launches while every output buffer is pre-filled with NaN; a consumer that
+    outruns its producer, a stage recycled too early or a tile left unwritten shows up as a differing or NaN element."""
+    from torchure_b200 import ops
+    from torchure_b200.models.qwen3 import RotaryEmbedding
+    from torchure_b200.ops import debug
+    from torchure_b200.ops import kernels as K
+
+    torch.manual_seed(0)
+    M, D, F_, Hq, Hkv, hd, S, B = 1024, 512, 1024, 4, 2, 128, 512, 2
+    x, y = torch.randn(M, D, device="cuda"), torch.randn(M, D, device="cuda").bfloat16()
+    w = torch.rand(D, device="cuda") + 0.5
+    h = torch.randn(M, D, device="cuda").bfloat16()
+    wqkv = (torch.randn((Hq + 2 * Hkv) * hd, D, device="cuda") * 0.05).bfloat16()
+    cos, sin = RotaryEmbedding(hd).tables(S, "cuda")
+    gains = torch.rand(hd, device="cuda") + 0.5
+    d_o = torch.randn(M, Hq * hd, device="cuda").bfloat16()
+
+    def once():
+        outs = list(K.add_rmsnorm(x, y, w, 1e-6))
+        qkv = K.linear_fwd(h, wqkv)
+        qk = K.qknorm_rope(qkv, gains, gains, cos, sin, S, Hq, Hkv, 1e-6, True)
+        o = debug.new_output("o", M, Hq * hd, dtype=torch.bfloat16, device="cuda")
+        lse = debug.new_output("lse", B, Hq, S, dtype=torch.float32, device="cuda")
+        ops.ext().attn_fwd(qk, qkv, o, lse, B, S, Hq, Hkv)
+        dqkv = debug.new_output("dqkv", M, (Hq + 2 * Hkv) * hd, dtype=torch.bfloat16, device="cuda")
+        ops.ext().attn_bwd(d_o, qk, qkv, o, lse, dqkv, B, S, Hq, Hkv)      # the deterministic two-kernel backward
+        gu = K.linear_fwd(h, torch.cat([wqkv, wqkv])[: 2 * F_])
+        outs += [qkv, qk, o, lse, dqkv, K.swiglu(gu), K.linear_dgrad(qkv, wqkv),
+                 K.linear_wgrad(qkv, h)]
+        return outs
+
+    debug.enable(True)
+    try:
+        ref = [t.clone() for t in once()]
+        for rep in range(40):
+            for i, (a, b) in enumerate(zip(once(), ref)):
+                assert torch.equal(a, b), (rep, i)
+            assert debug.verify() > 0
+    finally:
+        debug.enable(False)
+    K.check_error()

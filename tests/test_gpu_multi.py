@@ -261,13 +261,13 @@ def _fsdp_parity(rank, world):
                 lo = rank * m.per
                 err = ((m.shard.grad - want[lo:lo + m.per]).norm() / want[lo:lo + m.per].norm().clamp_min(1e-12)).item()
                 # after the first optimizer step the two models differ by Adam's sign flips on noise-level gradients
-                assert err < (2e-2 if cycle == 0 else 1e-1), (m.name, cycle, err)
+                assert err < (4e-2 if cycle == 0 else 1e-1), (m.name, cycle, err)
                 total += want.double().pow(2).sum().item()
         names = {p: n for n, p in model.named_parameters()}
         for p in fsdp.gains:
             want = ref_names[names[p]].grad
             err = ((p.grad - want).norm() / want.norm().clamp_min(1e-12)).item()
-            assert err < (3e-2 if cycle == 0 else 1.5e-1), (names[p], cycle, err)
+            assert err < (5e-2 if cycle == 0 else 1.5e-1), (names[p], cycle, err)
             total += want.double().pow(2).sum().item()
         sq = fsdp.sq_norm().item()
         if cycle == 0:
@@ -516,3 +516,72 @@ def _trainer_vs_single_cfg(rank, world, home, out):
     hist = tr.train_n_step_test(6)
     if rank == 0:
         torch.save(hist, out)
+
+
+def _collective_stress(rank, world):
+    """Race detection without a sanitizer: many collectives of random kind, size (odd sizes included), dtype and
+    reduction, issued in a random order that is the same on every rank and alternating between two streams (ordered
+    by events, as training orders its communication and compute streams), each checked against its closed form.
+    The self-resetting flags must never let a late rank see an early rank's next handshake; the launchers run with
+    their debug range checks on."""
+    import random
+
+    from torchure_b200.core import collective as C
+    from torchure_b200.core.mesh import Mesh
+
+    mesh = Mesh({"dp": world})
+    comm = C.enable_sm100(mesh, "dp", 32 << 20)
+    rng = random.Random(1234)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    prev = torch.cuda.Event()
+    prev.record()
+    checks = []
+    tri = world * (world + 1) / 2
+    for it in range(150):
+        kind = rng.choice(["all_reduce", "all_gather", "reduce_scatter", "all_to_all", "broadcast"])
+        dtype = rng.choice([torch.float32, torch.bfloat16])
+        n = rng.choice([1, 3, 17, 1000, 4097, 65536, 300_001, 1 << 20])
+        st = streams[it % 2] if rng.random() < 0.7 else streams[rng.randrange(2)]
+        with torch.cuda.stream(st):
+            st.wait_event(prev)
+            base = ((torch.arange(n, device="cuda") + it) % 13).float()
+            if kind == "all_reduce":
+                op = rng.choice(["sum", "avg", "max"])
+                x = (base * (rank + 1)).to(dtype)
+                C.all_reduce(x, mesh, "dp", op)
+                want = base * {"sum": tri, "avg": tri / world, "max": world}[op]
+                checks.append((kind, it, x.float(), want.to(dtype).float() if op == "max" else want, 2e-2 if dtype == torch.bfloat16 else 1e-5))
+            elif kind == "all_gather":
+                x = (base + rank).to(dtype)
+                g = C.all_gather(x, mesh, "dp", 0)
+                want = torch.cat([(base + r).to(dtype) for r in range(world)]).float()
+                checks.append((kind, it, g.float(), want, 0.0))
+            elif kind == "reduce_scatter":
+                full = ((torch.arange(n * world, device="cuda") + it) % 13).float()
+                x = (full * (rank + 1)).to(dtype)
+                rs = C.reduce_scatter(x, mesh, "dp", "sum")
+                checks.append((kind, it, rs.float(), full[rank * n:(rank + 1) * n] * tri, 2e-2 if dtype == torch.bfloat16 else 1e-5))
+            elif kind == "all_to_all":
+                m = max(1, n // world)
+                x = torch.stack([torch.full((m,), rank * 100.0 + j, device="cuda") for j in range(world)]).to(dtype)
+                a = C.all_to_all(x, mesh, "dp", 0, 0)
+                want = torch.stack([torch.full((m,), s * 100.0 + rank, device="cuda") for s in range(world)]).to(dtype).float()
+                checks.append((kind, it, a.float(), want, 0.0))
+            else:
+                src = rng.randrange(world)
+                x = torch.full((n,), float(rank), device="cuda", dtype=dtype)
+                C.broadcast(x, mesh, "dp", src=src)
+                checks.append((kind, it, x.float(), torch.full((n,), float(src), device="cuda"), 0.0))
+            prev = torch.cuda.Event()
+            prev.record(st)
+    torch.cuda.synchronize()
+    for kind, it, got, want, tol in checks:
+        if tol == 0.0:
+            assert torch.equal(got, want), (kind, it)
+        else:
+            torch.testing.assert_close(got, want, rtol=tol, atol=tol * float(want.abs().max().item() + 1), msg=lambda m: f"{kind} #{it}: {m}")
+    comm.check()
+
+
+def test_collectives_random_order_stress():
+    run_on_gpus(_collective_stress, _world(), env={"TORCHURE_B200_DEBUG": "1"})

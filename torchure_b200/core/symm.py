@@ -26,6 +26,7 @@ import torch.distributed as dist
 
 from torchure_b200 import ops
 
+_DEBUG = os.environ.get("TORCHURE_B200_DEBUG", "0") == "1"
 _OPS = {"sum": 0, "avg": 1, "max": 2, "min": 3}
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 ONESHOT_BYTES = 256 * 1024
@@ -68,6 +69,17 @@ class SymmComm:
     def _ctx(self):
         return self.peers, self.mc, self.rank, self.world, self.limit_ns
 
+    def _check_range(self, off: int, nbytes: int, what: str) -> None:
+        """Debug build of the launchers (``TORCHURE_B200_DEBUG=1``): every byte range a kernel will touch in the
+        symmetric allocation must lie inside it, past the flag and partial tables, and start on a 16-byte boundary.
+        A bad range is refused here instead of becoming a stray store into a peer's memory."""
+        if not _DEBUG:
+            return
+        total = self.buf.numel()
+        if off % 16 != 0 or nbytes < 0 or off < self.header or off + nbytes > total:
+            raise AssertionError(f"{what}: bytes [{off}, {off + nbytes}) outside the data area [{self.header}, {total}) "
+                                 f"of the symmetric allocation, or misaligned (rank {self.rank})")
+
     def supports(self, t: torch.Tensor, copies: int = 1) -> bool:
         """True when `t` can go through the kernels; `copies` = staging bytes needed per byte of `t`."""
         ok = t.is_cuda and t.dtype in _DT and t.is_contiguous() and t.numel() > 0
@@ -82,6 +94,7 @@ class SymmComm:
 
     def _staging(self, nbytes: int, dtype, at: int = 0) -> torch.Tensor:
         lo = self.staging_off + at
+        self._check_range(lo, nbytes, "staging area")
         assert at + nbytes <= self.staging_bytes, (
             f"message of {nbytes} bytes exceeds the {self.staging_bytes}-byte staging area of this communicator")
         return self.buf[lo:lo + nbytes].view(dtype)
@@ -120,6 +133,7 @@ class SymmComm:
         """In-place two-shot all-reduce of a tensor that lives in the symmetric region."""
         off = self.offset_of(t)
         assert off is not None and off % 16 == 0 and (t.numel() * t.element_size()) % 16 == 0
+        self._check_range(off, t.numel() * t.element_size(), "all_reduce_symmetric_")
         use_mc = bool(self.mc) and op in ("sum", "avg")
         self.ext.comm_all_reduce(*self._ctx(), off, t.numel(), _DT[t.dtype], _OPS[op], use_mc, sq_slot,
                                  blocks or self.blocks)
@@ -133,6 +147,7 @@ class SymmComm:
             off = self.offset_of(t)
             nbytes = t.numel() * t.element_size()
             assert off is not None and t.is_contiguous() and nbytes % (16 * self.world) == 0 and off % 16 == 0
+            self._check_range(off, nbytes, "all_gather_inplace_")
             offs.append(off)
             sizes.append(nbytes // self.world)
         for lo in range(0, len(offs), self.ext.COMM_MAX_SEGMENTS):
@@ -150,6 +165,7 @@ class SymmComm:
         for t, o in zip(fulls, outs):
             off = self.offset_of(t)
             assert off is not None and t.dtype == torch.float32 and t.numel() == o.numel() * self.world
+            self._check_range(off, t.numel() * 4, "reduce_scatter_symmetric")
             offs.append(off)
         use_mc = bool(self.mc) and op in ("sum", "avg")
         self.ext.comm_reduce_scatter_symm(*self._ctx(), offs, outs, _OPS[op], use_mc, sq_slot, blocks or self.blocks)
