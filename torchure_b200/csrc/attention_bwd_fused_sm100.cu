@@ -11,20 +11,20 @@
 //     S^T_h  = K Q_h^T          (SS, 128x64x128)   columns [0, 64)
 //     dP^T_h = V dO_h^T         (SS, 128x64x128)   columns [64, 128)
 //     P^T_h  = exp2(S^T_h c - lse2[q]);  dS^T_h = P^T_h o (dP^T_h - delta[q]) / sqrt(d)
-//                               bf16 P^T_h / dS^T_h -> 16 + 16 columns inside each warp's own 32 S^T columns; dS^T_h
-//                               also goes to shared memory
+//                               bf16 P^T_h / dS^T_h -> 8 + 8 columns in place of every 16 S^T columns; dS^T_h also
+//                               goes to shared memory
 //     dV    += P^T_h  dO_h      (TS, 128x128x64)   columns 256..383
 //     dK    += dS^T_h Q_h       (TS, 128x128x64)   columns 384..511
 //     dQ^T_h = K^T dS^T_h       (SS, 128x64x128, both operands MN-major)   columns [64, 128) of the half's buffer
-// 320 threads: TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter, 32 query columns each).  While the
-// compute warps work on one half the tensor core runs the other half's products; after each half they drain the
-// previous half's dQ^T tile with fp32 reductions to global memory.  Measured on B200 the kernel is bound by the
-// L2's fp32 reduction rate (64 KB of partial dQ per block pair, about 2.5 TB/s over the whole GPU): neither halving
-// the instruction count, nor dedicated drain warps, nor 16-byte vector reductions moved its time, so the simplest
-// of those variants is kept.  The element-wise part runs on packed fp32 pairs
-// (fma.rn.f32x2) with every constant folded into the row statistics (-lse*log2e and -delta/sqrt(d), written by the
-// statistics kernel below, which also clears the dQ accumulator).  The accumulator is head-major
-// ([B, Hq, Sq, 128] fp32) so that the 32 reductions of a thread differ by compile-time offsets.
+// 576 threads: TMA warp, MMA warp and two groups of 8 compute warps, one group per half (two warps per TMEM lane
+// quarter, 32 query columns each).  The tensor core alternates between the halves, dQ^T first, and so do the groups:
+// while one waits for its products, moves tiles between TMEM and registers or issues its burst of reductions, the
+// other runs its exp2 / multiply pass.  A group takes its dQ^T tile out of TMEM as soon as the product has completed
+// (which releases the columns for the next block's dP^T) and adds it to the global accumulator with 32 fp32
+// reductions per thread.  The element-wise part runs on packed fp32 pairs (fma.rn.f32x2), 16 columns at a time, with
+// every constant folded into the row statistics (-lse*log2e and -delta/sqrt(d), written by the statistics kernel
+// below, which also clears the dQ accumulator).  The accumulator is head-major ([B, Hq, Sq, 128] fp32) so that the
+// 32 reductions of a thread differ by compile-time offsets.
 //
 // `causal`: query block qb sees key blocks <= qb (Sq == Skv); otherwise every query sees every key (the off-diagonal
 // steps of ring attention).  Because partial dQ tiles are added in whatever order CTAs finish, dQ is not bitwise
@@ -50,8 +50,8 @@ constexpr int BAR_BYTES = 256;
 constexpr int SMEM_USED = 2 * TILE_BYTES + Q_STAGES * STAGE_BYTES + 2 * DS_BYTES + BAR_BYTES;
 constexpr int SMEM_BYTES = 232448;        // the whole 227 KB: SMEM_USED plus alignment slack
 static_assert(SMEM_USED <= SMEM_BYTES, "shared-memory plan exceeds the per-CTA limit");
-constexpr int COMPUTE_WARPS = 8;
-constexpr int NUM_THREADS = (2 + COMPUTE_WARPS) * 32;
+constexpr int COMPUTE_WARPS = 8;           // per half of a query block
+constexpr int NUM_THREADS = (2 + 2 * COMPUTE_WARPS) * 32;
 
 struct Bars {
   uint64_t kv_full;
@@ -68,8 +68,14 @@ static_assert(sizeof(Bars) <= BAR_BYTES, "barrier block");
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// A reduction nobody in this kernel reads back: no "memory" clobber, so that the compiler may keep scheduling
+// shared-memory loads and arithmetic of later loop iterations across it.
+__device__ __forceinline__ void red_add_unordered(float* p, float x) {
+  asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(x));
 }
 
 // two fp32 lanes per instruction (Blackwell FFMA2 / FMUL2)
@@ -244,23 +250,26 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         umma_commit(&bars->st_full[hh]);
       };
-      // dV += P^T_h dO_h ; dK += dS^T_h Q_h ; dQ^T_h = K^T dS^T_h
+      // dQ^T_h = K^T dS^T_h goes first and is committed on its own: the compute warps take it out of TMEM in the
+      // middle of the other half's element-wise pass, so the columns are free again before dP^T of the next block
+      // wants them.  Then dV += P^T_h dO_h and dK += dS^T_h Q_h.
       auto issue_acc = [&](int hh, int st, bool first) {
         const uint64_t qd = dQ_mn[st] + hh * kHalfRows, od = dO_mn[st] + hh * kHalfRows;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          // queries [16 ks, 16 ks + 16) of the half: P^T sits in columns [32 w, 32 w + 16) of softmax warp w = ks / 2
-          umma_f16_ts(tmem_base + 256, tmem_base + hh * 128 + (ks >> 1) * 32 + (ks & 1) * 8, od + ks * (2048 >> 4),
-                      idesc_acc, (first && ks == 0) ? 0u : 1u);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ts(tmem_base + 384, tmem_base + hh * 128 + (ks >> 1) * 32 + 16 + (ks & 1) * 8,
-                      qd + ks * (2048 >> 4), idesc_acc, (first && ks == 0) ? 0u : 1u);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 16 rows of K (both 64-wide d halves) and of dS^T
           umma_f16_ss(tmem_base + hh * 128 + 64, dK_mn + ks * (2048 >> 4), dDS[hh] + ks * (2048 >> 4), idesc_dq,
                       ks != 0 ? 1u : 0u);
         umma_commit(&bars->dq_full[hh]);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          // queries [16 ks, 16 ks + 16) of the half: their P^T sits in columns [16 ks, 16 ks + 8), their dS^T in
+          // [16 ks + 8, 16 ks + 16) (each group of 16 S^T columns is replaced by its own two products)
+          umma_f16_ts(tmem_base + 256, tmem_base + hh * 128 + ks * 16, od + ks * (2048 >> 4), idesc_acc,
+                      (first && ks == 0) ? 0u : 1u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ts(tmem_base + 384, tmem_base + hh * 128 + ks * 16 + 8, qd + ks * (2048 >> 4), idesc_acc,
+                      (first && ks == 0) ? 0u : 1u);
       };
       bool ok = mbar_wait(&bars->kv_full, 0, err, kErrAttnWait) && mbar_wait(&bars->q_full[0], 0, err, kErrAttnWait);
       if (ok) {
@@ -294,8 +303,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
   } else {
     // ------------------------------------------------ compute warps
+    // Two groups of eight warps: group g owns half g of every query block (two warps per TMEM lane quarter, 32 of
+    // the half's 64 query columns each).  The groups run out of phase, like the tensor core's work on the two halves,
+    // so the waits, TMEM round trips and reduction bursts of one group are covered by the arithmetic of the other.
+    const int grp = (warp - 2) >> 3;
     const int quarter = warp & 3;             // TMEM lane quarter this warp may touch
-    const int cg = (warp - 2) >> 2;           // which 32 of a half's 64 query columns
+    const int cg = ((warp - 2) >> 2) & 1;     // which 32 of the half's 64 query columns
     const int row = quarter * 32 + lane;      // key inside the block (S^T, dP^T) / head-dim index (dQ^T)
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const float2 c2 = make_float2(a.scale_log2, a.scale_log2), sc2 = make_float2(a.scale, a.scale);
@@ -303,86 +316,81 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint32_t ds_off[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) ds_off[j] = row * 128 + (((4 * cg + j) ^ (row & 7)) << 4);
+    const uint32_t tH = tmem_base + lane_sel + grp * 128 + cg * 32;
+    uint8_t* dsb = sDS + grp * DS_BYTES;      // dS^T row of this key: queries q0..q0+31 are four swizzled 16-byte chunks
     bool ok = true;
-    // dQ^T_h of half-step (pit, ph): 32 query columns of this warp, one head-dim index per lane.  The tile leaves TMEM
-    // first (the tensor core may then overwrite it), the 32 fp32 reductions follow; the accumulator is head-major, so
-    // they differ by compile-time offsets.
-    auto drain = [&](int pit, int ph) -> bool {
-      if (!mbar_wait(&bars->dq_full[ph], pit & 1, err, kErrAttnWait)) return false;
-      tc_fence_after();
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_sel + ph * 128 + 64 + cg * 32, v);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->dq_drained[ph]);
-      const int h = kvh * ratio + pit / n_qb;
-      const int qb = qb0 + pit % n_qb;
-      float* dst = a.dq_acc +
-                   ((static_cast<int64_t>(b) * a.Hq + h) * a.stat_stride + a.stat_row0 + qb * 128 + ph * 64 + cg * 32) * HD + row;
+    // P^T and dS^T of this warp's 32 query columns (one key per lane), 16 columns at a time.  Each group of 16 S^T
+    // columns is overwritten by its own P^T (8 columns of bf16 pairs) and dS^T (8 columns), so the warps need no
+    // barrier among them and the second group's scores are still intact when the first group's results are stored.
+    auto softmax_half = [&](const float* sStat, bool diag) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) red_add_f32(dst + j * HD, __uint_as_float(v[j]));
-      return true;
-    };
-    // P^T_h and dS^T_h of this warp's 32 query columns (one key per lane)
-    auto softmax_half = [&](int hh, const float* sStat, bool diag) {
-      const uint32_t tH = tmem_base + lane_sel + hh * 128;
-      uint32_t sv[32], dv[32];
-      tmem_ld_32x32b_x32(tH + cg * 32, sv);
-      tmem_ld_32x32b_x32(tH + 64 + cg * 32, dv);
-      tmem_ld_wait();
-      uint32_t pp[16], pd[16];
-      const int q0 = hh * 64 + cg * 32;
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[16], dv[16];
+        tmem_ld_32x32b_x16(tH + c * 16, sv);
+        tmem_ld_32x32b_x16(tH + 64 + c * 16, dv);
+        tmem_ld_wait();
+        uint32_t pp[8], pd[8];
+        const int q0 = grp * 64 + cg * 32 + c * 16;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float2 nl = *reinterpret_cast<const float2*>(sStat + q0 + 2 * i);          // -lse2 of the two queries
-        const float2 nd = *reinterpret_cast<const float2*>(sStat + 128 + q0 + 2 * i);    // -delta * scale
-        const float2 t = fma2(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), c2, nl);
-        float2 p = make_float2(ex2(t.x), ex2(t.y));
-        if (diag) {
-          if (q0 + 2 * i < row) p.x = 0.f;       // query before key: masked
-          if (q0 + 2 * i + 1 < row) p.y = 0.f;
+        for (int i = 0; i < 8; ++i) {
+          const float2 nl = *reinterpret_cast<const float2*>(sStat + q0 + 2 * i);          // -lse2 of the two queries
+          const float2 nd = *reinterpret_cast<const float2*>(sStat + 128 + q0 + 2 * i);    // -delta * scale
+          const float2 t = fma2(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), c2, nl);
+          float2 p = make_float2(ex2(t.x), ex2(t.y));
+          if (diag) {
+            if (q0 + 2 * i < row) p.x = 0.f;       // query before key: masked
+            if (q0 + 2 * i + 1 < row) p.y = 0.f;
+          }
+          const float2 u = fma2(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), sc2, nd);
+          const float2 ds = mul2(p, u);
+          pp[i] = pack_bf16x2(p.x, p.y);
+          pd[i] = pack_bf16x2(ds.x, ds.y);
         }
-        const float2 u = fma2(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), sc2, nd);
-        const float2 ds = mul2(p, u);
-        pp[i] = pack_bf16x2(p.x, p.y);
-        pd[i] = pack_bf16x2(ds.x, ds.y);
-      }
-      // both land inside the 32 S^T columns this warp itself consumed, so the warps need no barrier among them
-      tmem_st_32x32b_x16(tH + cg * 32, pp);
-      tmem_st_32x32b_x16(tH + cg * 32 + 16, pd);
-      uint8_t* dsb = sDS + hh * DS_BYTES;     // dS^T row of this key, queries q0..q0+31: four swizzled 16-byte chunks
+        tmem_st_32x32b_x8(tH + c * 16, pp);
+        tmem_st_32x32b_x8(tH + c * 16 + 8, pd);
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        *reinterpret_cast<uint4*>(dsb + ds_off[j]) = make_uint4(pd[4 * j], pd[4 * j + 1], pd[4 * j + 2], pd[4 * j + 3]);
+        for (int j = 0; j < 2; ++j)
+          *reinterpret_cast<uint4*>(dsb + ds_off[2 * c + j]) =
+              make_uint4(pd[4 * j], pd[4 * j + 1], pd[4 * j + 2], pd[4 * j + 3]);
+      }
       tmem_st_wait();
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->pds_ready[hh]);
+      if (lane == 0) mbar_arrive(&bars->pds_ready[grp]);
     };
     for (int it = 0; it < n_iter && ok; ++it) {
       const int s = it % Q_STAGES;
       const bool diag = a.causal && (it % n_qb) == 0;     // query block == key block
       const float* sStat = reinterpret_cast<const float*>(sStage + s * STAGE_BYTES + 2 * TILE_BYTES);
-      for (int hh = 0; hh < 2; ++hh) {
-        if (!mbar_wait(&bars->st_full[hh], it & 1, err, kErrAttnWait)) { ok = false; break; }
-        tc_fence_after();
-        if (diag) softmax_half(hh, sStat, true);
-        else softmax_half(hh, sStat, false);
-        // the other half's products of the previous half-step ran meanwhile: take its dQ^T out
-        if (hh == 1) {
-          if (!drain(it, 0)) { ok = false; break; }
-        } else if (it > 0) {
-          if (!drain(it - 1, 1)) { ok = false; break; }
-        }
-      }
+      if (!mbar_wait(&bars->st_full[grp], it & 1, err, kErrAttnWait)) { ok = false; break; }
+      tc_fence_after();
+      if (diag) softmax_half(sStat, true);
+      else softmax_half(sStat, false);
+      // dQ^T of this half (the first product the tensor core runs on it): 32 query columns of this warp, one head-dim
+      // index per lane.  The tile leaves TMEM first, which releases its columns for the next block's dP^T; the 32
+      // fp32 reductions follow.  The accumulator is head-major, so they differ by compile-time offsets.
+      if (!mbar_wait(&bars->dq_full[grp], it & 1, err, kErrAttnWait)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tH + 64, v);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->dq_drained[grp]);
+      const int h = kvh * ratio + it / n_qb;
+      const int qb = qb0 + it % n_qb;
+      float* dst = a.dq_acc +
+                   ((static_cast<int64_t>(b) * a.Hq + h) * a.stat_stride + a.stat_row0 + qb * 128 + grp * 64 + cg * 32) * HD + row;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) red_add_unordered(dst + j * HD, __uint_as_float(v[j]));
     }
-    if (ok && n_iter > 0) ok = drain(n_iter - 1, 1);
     if (ok && mbar_wait(&bars->acc_done, 0, err, kErrAttnWait)) {
       tc_fence_after();
-      // dV and dK: this warp's 64 of the 128 head-dim columns, one key row per lane, written straight to global memory
-      for (int which = 0; which < 2; ++which) {   // 0: dV, 1: dK
+      // group 0 writes dV, group 1 dK: this warp's 64 of the 128 head-dim columns, one key row per lane, straight to
+      // global memory
+      {
+        const int which = grp;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
           const int col = cg * 64 + c * 32;
