@@ -3,7 +3,7 @@
     python -m benchmarks.profile_case <case> [--iters N]
 
 Cases: gemm_fwd, gemm_dgrad, gemm_wgrad, attn_fwd, attn_bwd (single pass), attn_bwd_split, attn_prep, rmsnorm, rmsnorm_bwd, qknorm_rope,
-qknorm_rope_bwd, swiglu, swiglu_bwd, ce, adamw.  Each case builds inputs
+qknorm_rope_bwd, qknorm_rope_bwd_acc, swiglu, swiglu_bwd, ce, adamw.  Each case builds inputs
 larger than the 126 MB L2 but well under a few GB, launches the kernel `iters` times (default 4) and prints the
 CUDA-event time of the last launch with the achieved FLOP/s or bytes/s, so the same command serves a plain timing run
 and an `ncu -k regex:<kernel> -s 2 -c 1` capture.
@@ -75,14 +75,18 @@ def main(argv=None) -> None:
         w = torch.ones(hd, device=dev)
         fn = lambda: K.qknorm_rope(qkv, w, w, cos, sin, S, Hq, Hkv, 1e-6, True)
         bytes_ = 2 * M * (Hq + Hkv) * hd * 2
-    elif args.case == "qknorm_rope_bwd":
+    elif args.case in ("qknorm_rope_bwd", "qknorm_rope_bwd_acc"):
         qkv = torch.randn(M, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
         dqkv = torch.randn(M, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
         cos, sin = RotaryEmbedding(hd).tables(S, dev)
         w = torch.ones(hd, device=dev)
         dqw, dkw = torch.zeros(hd, device=dev), torch.zeros(hd, device=dev)
-        fn = lambda: K.qknorm_rope_bwd_(dqkv, qkv, w, w, cos, sin, dqw, dkw, S, Hq, Hkv, 1e-6, True)
+        # _acc: dq comes from the head-major fp32 accumulator of the single-pass attention backward (the engine's path)
+        acc = torch.randn(M // S, Hq, S, hd, device=dev) if args.case.endswith("_acc") else None
+        fn = lambda: K.qknorm_rope_bwd_(dqkv, qkv, w, w, cos, sin, dqw, dkw, S, Hq, Hkv, 1e-6, True, dq_acc=acc)
         bytes_ = 3 * M * (Hq + Hkv) * hd * 2   # read dqkv and qkv (q, k columns), write dqkv
+        if acc is not None:
+            bytes_ += M * Hq * hd * 2          # dq is read as fp32 instead of bf16
     elif args.case == "rmsnorm_bwd":
         rows = 4 * M
         x, dh = torch.randn(rows, D, device=dev), torch.randn(rows, D, device=dev).bfloat16()

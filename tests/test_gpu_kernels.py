@@ -146,6 +146,37 @@ def test_qknorm_rope_fwd_bwd(use_norm):
         assert relerr(dqw, qwa.grad) < 5e-3 and relerr(dkw, kwa.grad) < 5e-3
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(4, 2), (16, 8), (6, 3)])
+def test_qknorm_rope_bwd_reads_dq_from_the_fp32_accumulator(Hq, Hkv):
+    """dq taken from the head-major fp32 accumulator gives what the q columns of dqkv give when both hold the same
+    values, on both row-buffer plans of the kernel; an odd number of k heads leaves half a warp idle in the last pass."""
+    from torchure_b200 import ops
+    from torchure_b200.models.qwen3 import RotaryEmbedding
+    from torchure_b200.ops import kernels
+
+    torch.manual_seed(1)
+    B, S, hd = 2, 384, 128
+    M = B * S
+    qkv = torch.randn(M, (Hq + 2 * Hkv) * hd, device="cuda").bfloat16()
+    g = torch.randn(M, (Hq + 2 * Hkv) * hd, device="cuda").bfloat16()
+    qw, kw = torch.rand(hd, device="cuda") + 0.5, torch.rand(hd, device="cuda") + 0.5
+    cos, sin = RotaryEmbedding(hd).tables(S, "cuda")
+    acc = g[:, :Hq * hd].float().view(B, S, Hq, hd).permute(0, 2, 1, 3).contiguous()
+    outs = []
+    for dq_acc, stages in ((None, 1), (None, 2), (acc, 1), (acc, 2)):
+        d = g.clone()
+        if dq_acc is not None:
+            d[:, :Hq * hd] = 0          # must not be read
+        dqw, dkw = torch.zeros(hd, device="cuda"), torch.zeros(hd, device="cuda")
+        ops.ext().qknorm_rope_bwd(d, qkv, qw, kw, cos, sin, dqw, dkw, S, Hq, Hkv, 1e-6, True, dq_acc, stages)
+        outs.append((d, dqw, dkw))
+    kernels.check_error()
+    for d, dqw, dkw in outs[1:]:
+        assert torch.equal(d, outs[0][0])
+        torch.testing.assert_close(dqw, outs[0][1], rtol=1e-4, atol=1e-3)
+        torch.testing.assert_close(dkw, outs[0][2], rtol=1e-4, atol=1e-3)
+
+
 def test_swiglu_fwd_bwd():
     from torchure_b200.ops import kernels, oracle
 

@@ -36,9 +36,12 @@ void qknorm_rope_fwd(const __nv_bfloat16* qkv, const float* qw, const float* kw,
                      cudaStream_t stream);
 // in place on the q/k column ranges of dqkv [M, (Hq+2Hkv)*hd]; dqw/dkw fp32 [hd] accumulate.  dq_acc (optional):
 // head-major fp32 [B, Hq, S, hd] holding dq instead of the q columns of dqkv (they are only written then).
-void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
-                     const float* sin, float* dqw, float* dkw, const float* dq_acc, int M, int S, int Hq, int Hkv, int hd,
-                     float eps, int use_norm, int num_sms, cudaStream_t stream);
+// Returns 0, or a negative code when the row buffers do not fit / the launch failed.  `err`: device error word, set
+// when a staged row never arrives.
+int qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
+                    const float* sin, float* dqw, float* dkw, const float* dq_acc, int M, int S, int Hq, int Hkv, int hd,
+                    float eps, int use_norm, int num_sms, int* err, cudaStream_t stream, int force_stages = 0,
+                    int force_warps = 0);
 void swiglu_fwd(const __nv_bfloat16* gu, __nv_bfloat16* act, int M, int F, cudaStream_t stream);
 void swiglu_bwd(const __nv_bfloat16* dact, const __nv_bfloat16* gu, __nv_bfloat16* dgu, int M, int F,
                 cudaStream_t stream);

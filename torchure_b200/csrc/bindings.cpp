@@ -91,16 +91,26 @@ void qknorm_rope_fwd(const torch::Tensor& qkv, const torch::Tensor& qw, const to
 void qknorm_rope_bwd(torch::Tensor& dqkv, const torch::Tensor& qkv, const torch::Tensor& qw, const torch::Tensor& kw,
                      const torch::Tensor& cos, const torch::Tensor& sin, torch::Tensor& dqw, torch::Tensor& dkw,
                      int64_t S, int64_t Hq, int64_t Hkv, double eps, bool use_norm,
-                     c10::optional<torch::Tensor> dq_acc) {
+                     c10::optional<torch::Tensor> dq_acc, int64_t stages, int64_t warps) {
   TORCH_CHECK(qkv.size(1) == (Hq + 2 * Hkv) * 128, "qknorm_rope: head_dim must be 128");
   if (dq_acc.has_value() && dq_acc->defined())
     TORCH_CHECK(dq_acc->scalar_type() == torch::kFloat32 && dq_acc->is_contiguous() &&
                     dq_acc->numel() == qkv.size(0) * Hq * 128,
                 "qknorm_rope_bwd: dq_acc must be fp32 [B, Hq, S, 128]");
-  tb::qknorm_rope_bwd(bfm(dqkv), bf(qkv), qw.data_ptr<float>(), kw.data_ptr<float>(), cos.data_ptr<float>(),
-                      sin.data_ptr<float>(), dqw.data_ptr<float>(), dkw.data_ptr<float>(), opt_ptr<float>(dq_acc),
-                      (int)qkv.size(0), (int)S,
-                      (int)Hq, (int)Hkv, 128, (float)eps, use_norm ? 1 : 0, num_sms(), cur_stream());
+  TORCH_CHECK(cos.stride(0) == 128 && sin.stride(0) == 128 && cos.is_contiguous() && sin.is_contiguous(),
+              "qknorm_rope_bwd: cos / sin tables must be contiguous [S, 128]");
+  // rows are staged by bulk copies: 16-byte aligned bases (row and head offsets are multiples of 256 bytes)
+  TORCH_CHECK(dqkv.is_contiguous() && qkv.is_contiguous() && (reinterpret_cast<uintptr_t>(dqkv.data_ptr()) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(qkv.data_ptr()) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(cos.data_ptr()) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(sin.data_ptr()) & 15) == 0,
+              "qknorm_rope_bwd: operands must be contiguous and 16-byte aligned");
+  const int rc = tb::qknorm_rope_bwd(bfm(dqkv), bf(qkv), qw.data_ptr<float>(), kw.data_ptr<float>(),
+                                     cos.data_ptr<float>(), sin.data_ptr<float>(), dqw.data_ptr<float>(),
+                                     dkw.data_ptr<float>(), opt_ptr<float>(dq_acc), (int)qkv.size(0), (int)S, (int)Hq,
+                                     (int)Hkv, 128, (float)eps, use_norm ? 1 : 0, num_sms(), err_word().data_ptr<int>(),
+                                     cur_stream(), (int)stages, (int)warps);
+  TORCH_CHECK(rc == 0, "qknorm_rope_bwd failed with code ", rc);
 }
 
 void swiglu_fwd(const torch::Tensor& gu, torch::Tensor& act) {
@@ -184,7 +194,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("qknorm_rope_fwd", &qknorm_rope_fwd);
-  m.def("qknorm_rope_bwd", &qknorm_rope_bwd);
+  m.def("qknorm_rope_bwd", &qknorm_rope_bwd, pybind11::arg("dqkv"), pybind11::arg("qkv"), pybind11::arg("qw"),
+        pybind11::arg("kw"), pybind11::arg("cos"), pybind11::arg("sin"), pybind11::arg("dqw"), pybind11::arg("dkw"),
+        pybind11::arg("S"), pybind11::arg("Hq"), pybind11::arg("Hkv"), pybind11::arg("eps"), pybind11::arg("use_norm"),
+        pybind11::arg("dq_acc") = c10::nullopt, pybind11::arg("stages") = 0, pybind11::arg("warps") = 0);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("embedding_bwd", &embedding_bwd);

@@ -50,18 +50,19 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
-// The opt-in to more than 48 KB of dynamic shared memory is an attribute of (kernel, device): set it once for each
-// pair, with that device current.  Returns false if the device cannot be queried or the attribute is refused.
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of (kernel, device): set it for each pair,
+// with that device current, and again whenever a launch needs more than was granted before.  Returns false if the device cannot be queried or the attribute is refused.
 inline bool ensure_dynamic_smem(const void* kernel, int bytes) {
   static std::mutex mu;
-  static std::map<std::pair<const void*, int>, bool> done;
+  static std::map<std::pair<const void*, int>, int> done;   // largest size granted so far
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) return false;
   std::lock_guard<std::mutex> lock(mu);
   auto key = std::make_pair(kernel, dev);
-  if (done.count(key)) return true;
+  auto it = done.find(key);
+  if (it != done.end() && it->second >= bytes) return true;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
-  done[key] = true;
+  done[key] = bytes;
   return true;
 }
 
@@ -76,6 +77,7 @@ enum ErrCode : int {
   kErrEpilogueTmemFullWait = 4,
   kErrPeerFlagWait = 5,
   kErrAttnWait = 6,
+  kErrStagedRowWait = 7,   // a row staged into shared memory by a bulk copy never arrived
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -142,6 +144,14 @@ __device__ __forceinline__ void fence_barrier_init() {
 }
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- bulk copy (untiled): 16-byte aligned addresses, size a multiple of 16 bytes ------------
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // ---- TMA (tiled, no multicast) ------------------------------------------------------------
@@ -300,6 +310,23 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_m
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// two fp32 lanes per instruction (Blackwell FFMA2 / FMUL2)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)),
+        "l"(reinterpret_cast<const uint64_t&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return d;
 }
 
 }  // namespace tb

@@ -11,6 +11,7 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <type_traits>
 
 namespace tb {
 
@@ -279,7 +280,8 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
 // the row and both gain vectors are loaded once per row and reused by all heads.
 // ---------------------------------------------------------------------------------------------
 constexpr int QK_UNROLL = 4;      // forward: head pairs in flight per warp
-constexpr int QK_BWD_UNROLL = 1;  // backward: one head pair per iteration, the next pair's loads prefetched
+constexpr int QKB_U = 2;         // backward: head pairs whose reductions are interleaved
+constexpr int QKB_MAX_WARPS = 8;  // backward: warps of the one persistent CTA per SM (see the kernel)
 
 __device__ __forceinline__ void unpack4(const uint2& u, float (&f)[4]) {
   float2 a = bf2_to_f2(u.x), b = bf2_to_f2(u.y);
@@ -371,141 +373,221 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __res
   }
 }
 
-// 4-warp CTAs (14 K registers): they fit next to a CTA of a gradient all-reduce kernel on the same SM
-template <bool ACC>   // ACC: dq is read from the head-major fp32 accumulator instead of the q columns of dqkv
-__global__ void __launch_bounds__(128, 4)
+// Backward of QK-norm + RoPE, one warp per token row, rows staged through shared memory by the TMA unit.
+//
+// A row needs dq (from the q columns of dqkv, or, ACC, from the head-major fp32 accumulator [B, Hq, S, 128] of the
+// single-pass attention backward, which is rounded to bf16 here on the way in instead of by a conversion pass of its
+// own), dk, the forward inputs x of the same heads and 64 cos / sin values: 16 KB for 16 + 8 heads.  Loaded straight
+// into registers, the bytes a warp keeps in flight are bounded by its register budget and the kernel ran at about a
+// third of the copy bandwidth.  Here every warp owns two row buffers; while it works on one row, up to 32 bulk
+// copies (one per lane: a head of the accumulator, the dk columns, the x columns, cos, sin) fill the other and
+// signal an mbarrier, so that a persistent CTA of eight warps keeps 100 KB and more in flight at no register cost.
+// Results are written to dqkv with 8-byte stores (16 lanes cover the 128 contiguous bytes of half a head).
+// Eight warps of 128 registers use half of the SM's register file: the CTA also fits on an SM that hosts a 512-thread
+// CTA of a gradient all-reduce kernel, so a launch during a data-parallel backward pass does not wait for those SMs.
+// Measured on B200, 8192 rows of 16 + 8 heads: 39 us with bf16 dq (two buffers per warp), 52 us with the fp32
+// accumulator (16.9 KB rows: one buffer per warp); twelve warps would gain 3 us but fill the register file.
+struct QkBwdPlan {
+  int dq_bytes;      // Hq * 512 (ACC) or Hq * 256
+  int off_dk, off_x, off_cs, stage_bytes;
+  int stages;        // row buffers per warp: 2 (the next row loads during this one's arithmetic) or 1
+};
+
+template <bool ACC>
+__global__ void __launch_bounds__(QKB_MAX_WARPS * 32, 2)   // <= 128 registers
 qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ qkv,
                        const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ cos_t,
                        const float* __restrict__ sin_t, float* __restrict__ dqw, float* __restrict__ dkw,
-                       const float* __restrict__ dq_acc, int M, int S, int Hq, int Hkv, float eps, int use_norm) {
+                       const float* __restrict__ dq_acc, int M, int S, int Hq, int Hkv, float eps, int use_norm,
+                       QkBwdPlan plan, int* err) {
   pdl_wait();
   pdl_launch_dependents();
+  extern __shared__ __align__(128) uint8_t qk_smem[];
+  __shared__ uint64_t bars[QKB_MAX_WARPS][2];
+  __shared__ __align__(16) float red[2][128];
   const int heads = Hq + Hkv;
   const int lane = threadIdx.x & 31;
-  const int wid = threadIdx.x >> 5;
+  const int wid = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int sub = lane & 15, hsel = lane >> 4;
   const int ld = (Hq + 2 * Hkv) * 128;
   const int pairs = (heads + 1) >> 1;
-  // gains and this lane's gain-gradient partials: [0..3] elements 4*sub.., [4..7] elements 64+4*sub..
-  float gq[8], gk[8], aq[8], ak[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) { gq[e] = gk[e] = 1.f; aq[e] = ak[e] = 0.f; }
-  if (use_norm) {
-    float t[4];
-    load4f(qw + sub * 4, t);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) gq[e] = t[e];
-    load4f(qw + 64 + sub * 4, t);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) gq[4 + e] = t[e];
-    load4f(kw + sub * 4, t);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) gk[e] = t[e];
-    load4f(kw + 64 + sub * 4, t);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) gk[4 + e] = t[e];
+  uint8_t* buf = qk_smem + static_cast<size_t>(wid) * plan.stages * plan.stage_bytes;
+  if (lane == 0) {
+    mbar_init(&bars[wid][0], 1);
+    mbar_init(&bars[wid][1], 1);
+    fence_barrier_init();
   }
-  for (int row = blockIdx.x * 4 + wid; row < M; row += gridDim.x * 4) {
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) (&red[0][0])[i] = 0.f;
+  __syncthreads();
+  // gains and this lane's gain-gradient partials as fp32 pairs: [0], [1] elements 4*sub.., [2], [3] elements 64+4*sub..
+  float2 gq[4], gk[4], aq[4], ak[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    gq[e] = gk[e] = make_float2(1.f, 1.f);
+    aq[e] = ak[e] = make_float2(0.f, 0.f);
+  }
+  if (use_norm) {
+    const float4 q0 = *reinterpret_cast<const float4*>(qw + sub * 4), q1 = *reinterpret_cast<const float4*>(qw + 64 + sub * 4);
+    const float4 k0 = *reinterpret_cast<const float4*>(kw + sub * 4), k1 = *reinterpret_cast<const float4*>(kw + 64 + sub * 4);
+    gq[0] = make_float2(q0.x, q0.y); gq[1] = make_float2(q0.z, q0.w); gq[2] = make_float2(q1.x, q1.y); gq[3] = make_float2(q1.z, q1.w);
+    gk[0] = make_float2(k0.x, k0.y); gk[1] = make_float2(k0.z, k0.w); gk[2] = make_float2(k1.x, k1.y); gk[3] = make_float2(k1.z, k1.w);
+  }
+  const uint32_t tx_bytes = static_cast<uint32_t>(plan.dq_bytes + Hkv * 256 + (use_norm ? heads * 256 : 0) + 512);
+  // every lane issues the copies whose index it owns: [0, n_dq) accumulator heads (or one copy of the q columns),
+  // then dk, x, cos, sin
+  auto issue = [&](int row, int stage) {
+    uint8_t* dst = buf + stage * plan.stage_bytes;
+    uint64_t* bar = &bars[wid][stage];
+    if (lane == 0) mbar_expect_tx(bar, tx_bytes);
+    __syncwarp();
     const int pos = row % S;
-    float c[4], sn[4];
-    load4f(cos_t + static_cast<int64_t>(pos) * 128 + sub * 4, c);
-    load4f(sin_t + static_cast<int64_t>(pos) * 128 + sub * 4, sn);
-    __nv_bfloat16* dptr = dqkv + static_cast<int64_t>(row) * ld + sub * 4;
-    const __nv_bfloat16* xptr = qkv + static_cast<int64_t>(row) * ld + sub * 4;
-    // dq may still sit in the head-major fp32 accumulator [B, Hq, S, 128] of the single-pass attention backward: it
-    // is rounded to bf16 here, on the way in, instead of by a conversion pass of its own
-    const float* aptr = ACC ? dq_acc + (static_cast<int64_t>(row / S) * Hq * S + pos) * 128 + sub * 4 : nullptr;
-    // software pipeline: the loads of head pair hp + 1 are in flight while pair hp is processed
-    uint2 dl[1], dh[1], xl[1], xh[1], ndl, ndh, nxl, nxh;
-    auto fetch = [&](int hp, uint2& a0, uint2& a1, uint2& b0, uint2& b1) {
-      const int h = 2 * hp + hsel;
-      a0 = a1 = b0 = b1 = make_uint2(0u, 0u);
-      if (hp < pairs && h < heads) {
-        if (ACC && h < Hq) {
-          const float4 f0 = *reinterpret_cast<const float4*>(aptr + static_cast<int64_t>(h) * S * 128);
-          const float4 f1 = *reinterpret_cast<const float4*>(aptr + static_cast<int64_t>(h) * S * 128 + 64);
-          a0 = make_uint2(f2_to_bf2(f0.x, f0.y), f2_to_bf2(f0.z, f0.w));
-          a1 = make_uint2(f2_to_bf2(f1.x, f1.y), f2_to_bf2(f1.z, f1.w));
-        } else {
-          a0 = *reinterpret_cast<const uint2*>(dptr + h * 128);
-          a1 = *reinterpret_cast<const uint2*>(dptr + h * 128 + 64);
-        }
-        if (use_norm) {
-          b0 = *reinterpret_cast<const uint2*>(xptr + h * 128);
-          b1 = *reinterpret_cast<const uint2*>(xptr + h * 128 + 64);
-        }
+    const __nv_bfloat16* drow = dqkv + static_cast<int64_t>(row) * ld;
+    const int n_dq = ACC ? Hq : 1;
+    for (int i = lane; i < n_dq + 4; i += 32) {
+      if (i < n_dq) {
+        if (ACC)
+          bulk_load_1d(dst + i * 512, dq_acc + ((static_cast<int64_t>(row / S) * Hq + i) * S + pos) * 128, 512, bar);
+        else
+          bulk_load_1d(dst, drow, static_cast<uint32_t>(Hq * 256), bar);
+      } else if (i == n_dq) {
+        bulk_load_1d(dst + plan.off_dk, drow + Hq * 128, static_cast<uint32_t>(Hkv * 256), bar);
+      } else if (i == n_dq + 1) {
+        if (use_norm)
+          bulk_load_1d(dst + plan.off_x, qkv + static_cast<int64_t>(row) * ld, static_cast<uint32_t>(heads * 256), bar);
+      } else if (i == n_dq + 2) {
+        bulk_load_1d(dst + plan.off_cs, cos_t + static_cast<int64_t>(pos) * 128, 256, bar);   // cos[i] == cos[i + 64]
+      } else {
+        bulk_load_1d(dst + plan.off_cs + 256, sin_t + static_cast<int64_t>(pos) * 128, 256, bar);
       }
-    };
-    fetch(0, ndl, ndh, nxl, nxh);
-    for (int hp = 0; hp < pairs; hp += QK_BWD_UNROLL) {
-      dl[0] = ndl; dh[0] = ndh; xl[0] = nxl; xh[0] = nxh;
-      fetch(hp + 1, ndl, ndh, nxl, nxh);
+    }
+  };
+  const int row0 = blockIdx.x * warps + wid, row_step = gridDim.x * warps;
+  bool ok = true;
+  const bool two = plan.stages == 2;
+  if (two && row0 < M) issue(row0, 0);
+  int k = 0;
+  for (int row = row0; row < M; row += row_step, ++k) {
+    const int stage = two ? (k & 1) : 0;
+    if (!two) issue(row, 0);
+    else if (row + row_step < M) issue(row + row_step, stage ^ 1);
+    if (!mbar_wait(&bars[wid][stage], (two ? (k >> 1) : k) & 1, err, kErrStagedRowWait)) { ok = false; break; }
+    const uint8_t* st = buf + stage * plan.stage_bytes;
+    float2 c[2], sn[2], nsn[2];
+    {
+      const float4 cv = *reinterpret_cast<const float4*>(st + plan.off_cs + sub * 16);
+      const float4 sv = *reinterpret_cast<const float4*>(st + plan.off_cs + 256 + sub * 16);
+      c[0] = make_float2(cv.x, cv.y); c[1] = make_float2(cv.z, cv.w);
+      sn[0] = make_float2(sv.x, sv.y); sn[1] = make_float2(sv.z, sv.w);
+      nsn[0] = make_float2(-sv.x, -sv.y); nsn[1] = make_float2(-sv.z, -sv.w);
+    }
+    __nv_bfloat16* dptr = dqkv + static_cast<int64_t>(row) * ld + sub * 4;
+    // One call handles the head pairs [first, first + count) of one kind (q or k, so the gains are not selected per
+    // element), QKB_U pairs at a time with every step written across the group: their shuffle chains, the only long
+    // dependency of a pass, then overlap.  All arithmetic is on fp32 pairs.  With xh = x r the normalised input,
+    // t = n g and d = mean(t xh):  dx = r (t - xh d) = r (g n - (r d) x),  dgain += n xh = (n x) r.
+    auto run = [&](auto is_q_tag, int first, int count, const float2 (&g)[4], float2 (&acc)[4]) {
+      constexpr bool IS_Q = decltype(is_q_tag)::value;
+      for (int p0 = 0; p0 < count; p0 += QKB_U) {
+        float2 n[QKB_U][4], x[QKB_U][4], ssd[QKB_U][2];   // ssd: partial sums of x^2 and of g n x
+        bool live[QKB_U];
+        int hh[QKB_U];
 #pragma unroll
-      for (int k = 0; k < QK_BWD_UNROLL; ++k) {
-        const int h = 2 * (hp + k) + hsel;
-        float dlo[4], dhi[4], n[8];
-        unpack4(dl[k], dlo);
-        unpack4(dh[k], dhi);
-        // transpose of the rotation
+        for (int u = 0; u < QKB_U; ++u) {
+          const int h = first + 2 * (p0 + u) + hsel;
+          live[u] = p0 + u < count && h < (IS_Q ? Hq : heads);   // an idle pass still takes part in the shuffles
+          hh[u] = h;
+          const int hs = live[u] ? h : first;
+          float2 d[4];
+          if (ACC && IS_Q) {
+            const float4 lo = *reinterpret_cast<const float4*>(st + hs * 512 + sub * 16);
+            const float4 hi = *reinterpret_cast<const float4*>(st + hs * 512 + 256 + sub * 16);
+            d[0] = make_float2(lo.x, lo.y); d[1] = make_float2(lo.z, lo.w);
+            d[2] = make_float2(hi.x, hi.y); d[3] = make_float2(hi.z, hi.w);
+          } else {
+            const uint8_t* src = IS_Q ? st + hs * 256 : st + plan.off_dk + (hs - Hq) * 256;
+            const uint2 lo = *reinterpret_cast<const uint2*>(src + sub * 8), hi = *reinterpret_cast<const uint2*>(src + 128 + sub * 8);
+            d[0] = bf2_to_f2(lo.x); d[1] = bf2_to_f2(lo.y); d[2] = bf2_to_f2(hi.x); d[3] = bf2_to_f2(hi.y);
+          }
+          // transpose of the rotation: n_lo = d_lo c + d_hi s, n_hi = d_hi c - d_lo s
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          n[e] = dlo[e] * c[e] + dhi[e] * sn[e];
-          n[4 + e] = dhi[e] * c[e] - dlo[e] * sn[e];
+          for (int e = 0; e < 2; ++e) {
+            n[u][e] = fma2(d[2 + e], sn[e], mul2(d[e], c[e]));
+            n[u][2 + e] = fma2(d[e], nsn[e], mul2(d[2 + e], c[e]));
+          }
+          if (use_norm) {
+            const uint8_t* xs = st + plan.off_x + hs * 256;
+            const uint2 lo = *reinterpret_cast<const uint2*>(xs + sub * 8), hi = *reinterpret_cast<const uint2*>(xs + 128 + sub * 8);
+            x[u][0] = bf2_to_f2(lo.x); x[u][1] = bf2_to_f2(lo.y); x[u][2] = bf2_to_f2(hi.x); x[u][3] = bf2_to_f2(hi.y);
+            ssd[u][0] = ssd[u][1] = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              ssd[u][0] = fma2(x[u][e], x[u][e], ssd[u][0]);
+              ssd[u][1] = fma2(mul2(n[u][e], x[u][e]), g[e], ssd[u][1]);
+            }
+          }
         }
         if (use_norm) {
-          float x[8];
-          {
-            float t0[4], t1[4];
-            unpack4(xl[k], t0);
-            unpack4(xh[k], t1);
+          float ss[QKB_U], dot[QKB_U];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { x[e] = t0[e]; x[4 + e] = t1[e]; }
+          for (int u = 0; u < QKB_U; ++u) {
+            ss[u] = ssd[u][0].x + ssd[u][0].y;
+            dot[u] = ssd[u][1].x + ssd[u][1].y;
           }
-          float ss = 0.f;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
-          ss = group16_sum(ss);
-          const float r = rsqrtf(ss * (1.f / 128.f) + eps);
-          const bool is_q = h < Hq;
-          float dot = 0.f;
+          for (int o = 8; o > 0; o >>= 1) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            x[e] *= r;  // normalised value
-            dot += n[e] * (is_q ? gq[e] : gk[e]) * x[e];
-          }
-          dot = group16_sum(dot) * (1.f / 128.f);
-          if (h < heads) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              if (is_q) aq[e] += n[e] * x[e]; else ak[e] += n[e] * x[e];
+            for (int u = 0; u < QKB_U; ++u) {
+              ss[u] += __shfl_xor_sync(0xffffffffu, ss[u], o);
+              dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
             }
           }
 #pragma unroll
-          for (int e = 0; e < 8; ++e) n[e] = r * (n[e] * (is_q ? gq[e] : gk[e]) - x[e] * dot);
-        }
-        if (h < heads) {
-          float o0[4], o1[4];
+          for (int u = 0; u < QKB_U; ++u) {
+            const float r = rsqrtf(ss[u] * (1.f / 128.f) + eps);
+            const float nrd = -r * r * dot[u] * (1.f / 128.f);      // -(r d)
+            const float2 r2 = make_float2(r, r), nrd2 = make_float2(nrd, nrd);
+            const float2 ra = live[u] ? r2 : make_float2(0.f, 0.f);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) { o0[e] = n[e]; o1[e] = n[4 + e]; }
-          *reinterpret_cast<uint2*>(dptr + h * 128) = pack4(o0);
-          *reinterpret_cast<uint2*>(dptr + h * 128 + 64) = pack4(o1);
+            for (int e = 0; e < 4; ++e) {
+              acc[e] = fma2(mul2(n[u][e], x[u][e]), ra, acc[e]);
+              n[u][e] = mul2(fma2(x[u][e], nrd2, mul2(n[u][e], g[e])), r2);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < QKB_U; ++u) {
+          if (live[u]) {
+            *reinterpret_cast<uint2*>(dptr + hh[u] * 128) =
+                make_uint2(f2_to_bf2(n[u][0].x, n[u][0].y), f2_to_bf2(n[u][1].x, n[u][1].y));
+            *reinterpret_cast<uint2*>(dptr + hh[u] * 128 + 64) =
+                make_uint2(f2_to_bf2(n[u][2].x, n[u][2].y), f2_to_bf2(n[u][3].x, n[u][3].y));
+          }
         }
       }
-    }
+    };
+    run(std::true_type{}, 0, (Hq + 1) >> 1, gq, aq);
+    run(std::false_type{}, Hq, (Hkv + 1) >> 1, gk, ak);
+    __syncwarp();   // every lane is done with this buffer before the next iteration's copies overwrite it
+  }
+  if (!ok) {
+    // a copy may still be landing in this CTA's shared memory: give it time before the CTA retires
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
   if (use_norm) {
-    __shared__ __align__(16) float red[2][128];
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) (&red[0][0])[i] = 0.f;
-    __syncthreads();
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      atomicAdd(&red[0][sub * 4 + e], aq[e]);
-      atomicAdd(&red[0][64 + sub * 4 + e], aq[4 + e]);
-      atomicAdd(&red[1][sub * 4 + e], ak[e]);
-      atomicAdd(&red[1][64 + sub * 4 + e], ak[4 + e]);
+    for (int e = 0; e < 2; ++e) {
+      atomicAdd(&red[0][sub * 4 + 2 * e], aq[e].x);
+      atomicAdd(&red[0][sub * 4 + 2 * e + 1], aq[e].y);
+      atomicAdd(&red[0][64 + sub * 4 + 2 * e], aq[2 + e].x);
+      atomicAdd(&red[0][64 + sub * 4 + 2 * e + 1], aq[2 + e].y);
+      atomicAdd(&red[1][sub * 4 + 2 * e], ak[e].x);
+      atomicAdd(&red[1][sub * 4 + 2 * e + 1], ak[e].y);
+      atomicAdd(&red[1][64 + sub * 4 + 2 * e], ak[2 + e].x);
+      atomicAdd(&red[1][64 + sub * 4 + 2 * e + 1], ak[2 + e].y);
     }
     __syncthreads();
-    // one 16-byte reduction per four columns per CTA; the grid is two CTAs per SM, so few of them meet in L2
+    // one 16-byte reduction per four columns per CTA
     if (threadIdx.x < 64) {
       const int which = threadIdx.x >> 5, i = threadIdx.x & 31;
       const float4 v = *reinterpret_cast<const float4*>(&red[which][4 * i]);
@@ -856,17 +938,35 @@ void qknorm_rope_fwd(const __nv_bfloat16* qkv, const float* qw, const float* kw,
   launch_pdl(qknorm_rope_fwd_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, qkv, qw, kw, cos, sin, out, M, S, Hq, Hkv, eps, use_norm);
 }
 
-void qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
-                     const float* sin, float* dqw, float* dkw, const float* dq_acc, int M, int S, int Hq, int Hkv, int hd,
-                     float eps, int use_norm, int num_sms, cudaStream_t stream) {
+int qknorm_rope_bwd(__nv_bfloat16* dqkv, const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos,
+                    const float* sin, float* dqw, float* dkw, const float* dq_acc, int M, int S, int Hq, int Hkv, int hd,
+                    float eps, int use_norm, int num_sms, int* err, cudaStream_t stream, int force_stages, int force_warps) {
   (void)hd;
-  const int grid = std::min((M + 3) / 4, num_sms * 4);  // persistent: four 4-warp CTAs per SM, a warp walks rows
-  if (dq_acc != nullptr)
-    launch_pdl(qknorm_rope_bwd_kernel<true>, dim3(grid), dim3(128), 0, stream, dqkv, qkv, qw, kw, cos, sin, dqw, dkw, dq_acc,
-               M, S, Hq, Hkv, eps, use_norm);
-  else
-    launch_pdl(qknorm_rope_bwd_kernel<false>, dim3(grid), dim3(128), 0, stream, dqkv, qkv, qw, kw, cos, sin, dqw, dkw,
-               dq_acc, M, S, Hq, Hkv, eps, use_norm);
+  const bool acc = dq_acc != nullptr;
+  QkBwdPlan plan;
+  plan.dq_bytes = Hq * (acc ? 512 : 256);
+  plan.off_dk = plan.dq_bytes;
+  plan.off_x = plan.off_dk + Hkv * 256;
+  plan.off_cs = plan.off_x + (Hq + Hkv) * 256;
+  plan.stage_bytes = plan.off_cs + 512;
+  // as many warps (two row buffers each) as fit into the shared memory of one persistent CTA per SM
+  const int budget = 220 * 1024;
+  // two buffers per warp when all warps can have them, else one (more warps beat deeper buffers)
+  plan.stages = force_stages > 0 ? force_stages : (2 * plan.stage_bytes * QKB_MAX_WARPS <= budget ? 2 : 1);
+  int warps = std::min(force_warps > 0 ? std::min(force_warps, QKB_MAX_WARPS) : QKB_MAX_WARPS,
+                       budget / (plan.stages * plan.stage_bytes));
+  if (warps < 1) return -1;
+  const int smem = warps * plan.stages * plan.stage_bytes;
+  const void* fn = acc ? reinterpret_cast<const void*>(qknorm_rope_bwd_kernel<true>)
+                       : reinterpret_cast<const void*>(qknorm_rope_bwd_kernel<false>);
+  if (!ensure_dynamic_smem(fn, smem)) return -2;
+  const int grid = std::max(1, std::min((M + warps - 1) / warps, num_sms));
+  const cudaError_t rc =
+      acc ? launch_pdl(qknorm_rope_bwd_kernel<true>, dim3(grid), dim3(warps * 32), smem, stream, dqkv, qkv, qw, kw, cos,
+                       sin, dqw, dkw, dq_acc, M, S, Hq, Hkv, eps, use_norm, plan, err)
+          : launch_pdl(qknorm_rope_bwd_kernel<false>, dim3(grid), dim3(warps * 32), smem, stream, dqkv, qkv, qw, kw, cos,
+                       sin, dqw, dkw, dq_acc, M, S, Hq, Hkv, eps, use_norm, plan, err);
+  return rc == cudaSuccess ? 0 : -3;
 }
 
 void swiglu_fwd(const __nv_bfloat16* gu, __nv_bfloat16* act, int M, int F, cudaStream_t stream) {

@@ -29,7 +29,8 @@ def check_error() -> None:
         word.zero_()
         names = {1: "GEMM producer waited for a free stage", 2: "GEMM MMA warp waited for a full stage",
                  3: "GEMM MMA warp waited for a free accumulator", 4: "GEMM epilogue waited for an accumulator",
-                 5: "a collective waited for a peer flag", 6: "attention pipeline wait"}
+                 5: "a collective waited for a peer flag", 6: "attention pipeline wait",
+                 7: "a row staged into shared memory by a bulk copy never arrived"}
         raise RuntimeError(f"sm_100a kernel reported an expired wait: code {code} ({names.get(code, 'unknown')})")
 
 
