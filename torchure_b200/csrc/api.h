@@ -19,6 +19,11 @@ namespace tb {
 // one of its bounded waits expires.
 int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
               bool a_mn, bool b_mn, int out_mode, int* err, int num_sms, cudaStream_t stream, int force_splits = 0);
+// CTA pairs the device holds at once (0 before the first pair launch of this process).
+int gemm_pair_capacity();
+// The CTA-pair kernel behind gemm_bf16 (tiles of 256 x 256 on two SMs); `splits` as chosen by gemm_bf16.
+int gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+               bool a_mn, bool b_mn, int out_mode, int splits, int* err, int num_sms, cudaStream_t stream);
 
 // ---- elementwise / normalisation -------------------------------------------------------------
 // h = rmsnorm(x_new) * w with x_new = x (+ y); optional gather x = table[ids].  Writes x_new when y or ids

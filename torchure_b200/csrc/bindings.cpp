@@ -190,6 +190,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("b"), pybind11::arg("out"), pybind11::arg("a_mn"), pybind11::arg("b_mn"), pybind11::arg("out_mode"),
         pybind11::arg("splits") = 0);
   m.def("set_sm_reserve", [](int64_t n) { g_sm_reserve = (int)n; }, "persistent kernels use (SM count - n) CTAs");
+  m.def("gemm_pair_capacity", &tb::gemm_pair_capacity, "CTA pairs (2-SM clusters) resident at once; 0 before the first launch");
   m.def("error_word", &error_word, "device int32[4]; [0] is set when a bounded wait of a kernel expired");
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

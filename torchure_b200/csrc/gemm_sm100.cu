@@ -18,6 +18,7 @@
 #include "comm_device.cuh"
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -486,11 +487,22 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorM
              : -21;
 }
 
+// Problems with more than 128 rows run on CTA pairs (gemm2_sm100.cu) unless TORCHURE_B200_GEMM_PAIR=0.
+static bool pair_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("TORCHURE_B200_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
               bool a_mn, bool b_mn, int out_mode, int* err, int num_sms, cudaStream_t stream, int force_splits) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const bool pair = pair_enabled() && M > BM && num_sms >= 2;
   CUtensorMap ta, tb_, tc;
   int r;
+  if (!pair) {
   // K-major operand [R, K]: box 64 (k) x tile rows.  MN-major operand stored [K, R]: box 64 (r) x 64 (k rows).
   r = a_mn ? make_tmap_2d(&ta, A, 2, K, M, lda, 64, 64) : make_tmap_2d(&ta, A, 2, M, K, lda, BM, 64);
   if (r) return r;
@@ -498,16 +510,19 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_
   if (r) return r - 100;
   r = out_mode == 0 ? make_tmap_2d(&tc, C, 2, M, N, ldc, 32, 64) : make_tmap_2d(&tc, C, 4, M, N, ldc, 32, 32);
   if (r) return r - 200;
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  }
+  // work units and workers: 128 x 256 tiles on SMs, or 256 x 256 tiles on SM pairs
+  const int tiles = ((M + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM)) * ((N + BN - 1) / BN);
+  const int workers = pair ? (gemm_pair_capacity() > 0 ? gemm_pair_capacity() : num_sms / 2) : num_sms;
   // split-K for fp32 outputs (wgrad: few output tiles, long K): pick the slice count with the least wave time
   int splits = 1;
   const int num_kb = (K + BK - 1) / BK;
   if (force_splits > 0) {
     splits = force_splits;
-  } else if (out_mode != 0 && num_kb >= 32 && tiles < 2 * num_sms) {
+  } else if (out_mode != 0 && num_kb >= 32 && tiles < 2 * workers) {
     float best = 1e30f;
     for (int s = 1; s <= 8 && s * 8 <= num_kb; ++s) {
-      const int waves = (tiles * s + num_sms - 1) / num_sms;
+      const int waves = (tiles * s + workers - 1) / workers;
       const float cost = static_cast<float>(waves) / s + 0.02f * (s - 1);
       if (cost < best - 1e-6f) { best = cost; splits = s; }
     }
@@ -517,6 +532,8 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_
     if (cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, stream) != cudaSuccess) return -22;
     out_mode = 2;
   }
+  if (pair)
+    return gemm2_bf16(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_mode, splits, err, num_sms, stream);
   const int units = tiles * splits;
   const int grid = units < num_sms ? units : num_sms;
 #define TB_GEMM_CASE(AM, BMN, O) \
