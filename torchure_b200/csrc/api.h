@@ -33,8 +33,10 @@ void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids,
                      const __nv_bfloat16* table_bf16, const float* w, float* x_out, __nv_bfloat16* h, float* rstd, int M,
                      int D, float eps, cudaStream_t stream);
 // dx = dx_in + d rmsnorm; dw += sum_rows(dh * xhat).  dx_bf16 (optional) receives a bf16 copy of dx.
+// variant 0: rows staged through shared memory when the shape allows (D <= 1024); 1: the register-resident kernels
 void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const float* rstd, const float* dx_in,
-                 float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, cudaStream_t stream);
+                 float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, int* err, cudaStream_t stream,
+                 int variant = 0);
 // per-head RMSNorm + RoPE on the q and k column ranges of qkv [M, (Hq+2Hkv)*hd]; out [M, (Hq+Hkv)*hd]
 void qknorm_rope_fwd(const __nv_bfloat16* qkv, const float* qw, const float* kw, const float* cos, const float* sin,
                      __nv_bfloat16* out, int M, int S, int Hq, int Hkv, int hd, float eps, int use_norm,

@@ -72,11 +72,12 @@ void add_rmsnorm_fwd(c10::optional<torch::Tensor> x, c10::optional<torch::Tensor
 
 void rmsnorm_bwd(const torch::Tensor& dh, const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& rstd,
                  c10::optional<torch::Tensor> dx_in, torch::Tensor& dx, c10::optional<torch::Tensor> dx_bf16,
-                 torch::Tensor& dw) {
+                 torch::Tensor& dw, int64_t variant) {
   const int M = (int)x.size(0), D = (int)x.size(1);
+  TORCH_CHECK(dh.is_contiguous() && x.is_contiguous() && dx.is_contiguous(), "rmsnorm_bwd: operands must be contiguous");
   tb::rmsnorm_bwd(bf(dh), x.data_ptr<float>(), w.data_ptr<float>(), rstd.data_ptr<float>(), opt_ptr<float>(dx_in),
                   dx.data_ptr<float>(), opt_mptr<__nv_bfloat16>(dx_bf16), dw.data_ptr<float>(), M, D, num_sms(),
-                  cur_stream());
+                  err_word().data_ptr<int>(), cur_stream(), (int)variant);
 }
 
 void qknorm_rope_fwd(const torch::Tensor& qkv, const torch::Tensor& qw, const torch::Tensor& kw,
@@ -193,7 +194,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_pair_capacity", &tb::gemm_pair_capacity, "CTA pairs (2-SM clusters) resident at once; 0 before the first launch");
   m.def("error_word", &error_word, "device int32[4]; [0] is set when a bounded wait of a kernel expired");
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, pybind11::arg("dh"), pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("rstd"),
+        pybind11::arg("dx_in"), pybind11::arg("dx"), pybind11::arg("dx_bf16"), pybind11::arg("dw"),
+        pybind11::arg("variant") = 0);
   m.def("qknorm_rope_fwd", &qknorm_rope_fwd);
   m.def("qknorm_rope_bwd", &qknorm_rope_bwd, pybind11::arg("dqkv"), pybind11::arg("qkv"), pybind11::arg("qw"),
         pybind11::arg("kw"), pybind11::arg("cos"), pybind11::arg("sin"), pybind11::arg("dqw"), pybind11::arg("dkw"),

@@ -274,6 +274,133 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dh, const float* __res
 }
 
 // ---------------------------------------------------------------------------------------------
+// rmsnorm backward for D <= 1024, rows staged through shared memory by bulk copies (the scheme of the QK-norm / RoPE
+// backward further down): every warp of one persistent CTA per SM owns one or two row buffers [x fp32 | dh bf16 |
+// dx_in fp32]; while it works on a row the next one is in flight, at no register cost, and the second pass (outputs
+// and gain gradient) re-reads the row from shared memory instead of holding it in registers.  Eight warps of at most
+// 128 registers: the CTA fits beside a 512-thread CTA of a gradient all-reduce kernel.
+// ---------------------------------------------------------------------------------------------
+constexpr int RNB_MAX_WARPS = 8;
+
+__global__ void __launch_bounds__(RNB_MAX_WARPS * 32, 2)
+rmsnorm_bwd_staged_kernel(const __nv_bfloat16* __restrict__ dh, const float* __restrict__ x, const float* __restrict__ w,
+                          const float* __restrict__ rstd, const float* __restrict__ dx_in, float* __restrict__ dx,
+                          __nv_bfloat16* __restrict__ dx_bf16, float* __restrict__ dw, int M, int D, int stage_bytes,
+                          int stages, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int MAX_VEC = 8;
+  extern __shared__ __align__(128) uint8_t rn_smem[];
+  __shared__ uint64_t bars[RNB_MAX_WARPS][2];
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int nvec = D >> 2;
+  uint8_t* buf = rn_smem + static_cast<size_t>(wid) * stages * stage_bytes;
+  const int off_dh = D * 4, off_in = D * 6;
+  if (lane == 0) {
+    mbar_init(&bars[wid][0], 1);
+    mbar_init(&bars[wid][1], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  float4 wv[MAX_VEC], dw_acc[MAX_VEC];
+#pragma unroll
+  for (int j = 0; j < MAX_VEC; ++j) {
+    const int i = lane + j * 32;
+    wv[j] = i < nvec ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    dw_acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const uint32_t tx_bytes = static_cast<uint32_t>(D * (dx_in ? 10 : 6));
+  auto issue = [&](int row, int stage) {
+    uint8_t* dst = buf + stage * stage_bytes;
+    uint64_t* bar = &bars[wid][stage];
+    if (lane == 0) mbar_expect_tx(bar, tx_bytes);
+    __syncwarp();
+    const int64_t off = static_cast<int64_t>(row) * D;
+    if (lane == 0) bulk_load_1d(dst, x + off, static_cast<uint32_t>(D * 4), bar);
+    else if (lane == 1) bulk_load_1d(dst + off_dh, dh + off, static_cast<uint32_t>(D * 2), bar);
+    else if (lane == 2 && dx_in) bulk_load_1d(dst + off_in, dx_in + off, static_cast<uint32_t>(D * 4), bar);
+  };
+  const int row0 = blockIdx.x * warps + wid, row_step = gridDim.x * warps;
+  const bool two = stages == 2;
+  bool ok = true;
+  if (two && row0 < M) issue(row0, 0);
+  float r_next = row0 < M ? rstd[row0] : 0.f;
+  int k = 0;
+  for (int row = row0; row < M; row += row_step, ++k) {
+    const int stage = two ? (k & 1) : 0;
+    if (!two) issue(row, 0);
+    else if (row + row_step < M) issue(row + row_step, stage ^ 1);
+    const float r = r_next;
+    if (row + row_step < M) r_next = rstd[row + row_step];
+    if (!mbar_wait(&bars[wid][stage], (two ? (k >> 1) : k) & 1, err, kErrStagedRowWait)) { ok = false; break; }
+    const uint8_t* st = buf + stage * stage_bytes;
+    const float2 r2 = make_float2(r, r);
+    // pass 1: dot = mean(dh w xhat)
+    float2 dot2 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < MAX_VEC; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        const float4 xv = reinterpret_cast<const float4*>(st)[i];
+        const uint2 dv = reinterpret_cast<const uint2*>(st + off_dh)[i];
+        const float2 a = bf2_to_f2(dv.x), b = bf2_to_f2(dv.y);
+        dot2 = fma2(mul2(a, make_float2(wv[j].x, wv[j].y)), make_float2(xv.x, xv.y), dot2);
+        dot2 = fma2(mul2(b, make_float2(wv[j].z, wv[j].w)), make_float2(xv.z, xv.w), dot2);
+      }
+    }
+    const float dot = warp_sum(dot2.x + dot2.y) * r / D;
+    const float2 nd2 = make_float2(-dot, -dot);
+    // pass 2: dx = r (dh w - xhat dot) (+ dx_in), dw += dh xhat
+    const int64_t off = static_cast<int64_t>(row) * D;
+#pragma unroll
+    for (int j = 0; j < MAX_VEC; ++j) {
+      const int i = lane + j * 32;
+      if (i < nvec) {
+        const float4 xv = reinterpret_cast<const float4*>(st)[i];
+        const uint2 dv = reinterpret_cast<const uint2*>(st + off_dh)[i];
+        const float2 a = bf2_to_f2(dv.x), b = bf2_to_f2(dv.y);
+        const float2 xh0 = mul2(make_float2(xv.x, xv.y), r2), xh1 = mul2(make_float2(xv.z, xv.w), r2);
+        float2 o0 = mul2(fma2(xh0, nd2, mul2(a, make_float2(wv[j].x, wv[j].y))), r2);
+        float2 o1 = mul2(fma2(xh1, nd2, mul2(b, make_float2(wv[j].z, wv[j].w))), r2);
+        if (dx_in) {
+          const float4 p = reinterpret_cast<const float4*>(st + off_in)[i];
+          o0.x += p.x; o0.y += p.y; o1.x += p.z; o1.y += p.w;
+        }
+        reinterpret_cast<float4*>(dx + off)[i] = make_float4(o0.x, o0.y, o1.x, o1.y);
+        if (dx_bf16) reinterpret_cast<uint2*>(dx_bf16 + off)[i] = make_uint2(f2_to_bf2(o0.x, o0.y), f2_to_bf2(o1.x, o1.y));
+        const float2 d0 = fma2(a, xh0, make_float2(dw_acc[j].x, dw_acc[j].y));
+        const float2 d1 = fma2(b, xh1, make_float2(dw_acc[j].z, dw_acc[j].w));
+        dw_acc[j] = make_float4(d0.x, d0.y, d1.x, d1.y);
+      }
+    }
+    __syncwarp();   // every lane is done with this buffer before the next iteration's copies overwrite it
+  }
+  if (!ok) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  // warps -> one partial per column in shared memory (the row buffers are free now) -> one vector reduction per four
+  // columns per CTA
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(rn_smem);
+#pragma unroll
+  for (int j = 0; j < MAX_VEC; ++j) {
+    const int i = lane + j * 32;
+    if (i < nvec) reinterpret_cast<float4*>(red + wid * D)[i] = dw_acc[j];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int kk = 0; kk < warps; ++kk) {
+      const float4 v = reinterpret_cast<const float4*>(red + kk * D)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    red_add_v4(dw + 4 * i, acc);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // QK-norm + RoPE, hd == 128.  One warp per token row; 16 lanes per head, so a warp instruction covers two heads.
 // Lane sub = lane & 15 holds elements 4*sub .. 4*sub+3 AND 64+4*sub .. 64+4*sub+3 of its head (two 8-byte accesses):
 // the rotation pairs element i with i + 64, so both partners sit in the same lane and need no shuffle.  cos/sin of
@@ -915,7 +1042,23 @@ void add_rmsnorm_fwd(const float* x, const __nv_bfloat16* y, const int64_t* ids,
 }
 
 void rmsnorm_bwd(const __nv_bfloat16* dh, const float* x, const float* w, const float* rstd, const float* dx_in,
-                 float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, cudaStream_t stream) {
+                 float* dx, __nv_bfloat16* dx_bf16, float* dw, int M, int D, int num_sms, int* err, cudaStream_t stream,
+                 int variant) {
+  const bool aligned = D % 8 == 0 && ((reinterpret_cast<uintptr_t>(dh) | reinterpret_cast<uintptr_t>(x) |
+                                       reinterpret_cast<uintptr_t>(dx_in)) & 15) == 0;
+  if (variant != 1 && D <= 128 * 8 && M >= 4 * num_sms && aligned && err != nullptr) {
+    const int stage_bytes = D * (dx_in ? 10 : 6);
+    const int budget = 200 * 1024;
+    const int stages = 2 * stage_bytes * RNB_MAX_WARPS <= budget ? 2 : 1;
+    const int warps = std::min(RNB_MAX_WARPS, budget / (stages * stage_bytes));
+    const int smem = std::max(warps * stages * stage_bytes, warps * D * 4);
+    if (warps >= 1 && ensure_dynamic_smem(reinterpret_cast<const void*>(rmsnorm_bwd_staged_kernel), smem)) {
+      const int grid = std::max(1, std::min((M + warps - 1) / warps, num_sms));
+      launch_pdl(rmsnorm_bwd_staged_kernel, dim3(grid), dim3(warps * 32), smem, stream, dh, x, w, rstd, dx_in, dx,
+                 dx_bf16, dw, M, D, stage_bytes, stages, err);
+      return;
+    }
+  }
   // two rows per warp keeps every warp equally loaded and the per-CTA atomics on dw few
   if (D <= 128 * 8 && M >= 4 * num_sms) {
     constexpr int W = 4;
