@@ -58,7 +58,7 @@ void embedding_bwd(const float* dx, const int64_t* ids, float* dtable, int M, in
 // order of additions and no atomics (sources may be peer GPUs' buffers).  sq_delta (optional, `blocks` floats) receives
 // per-CTA sum(new^2 - old^2) of the touched elements.
 int embedding_scatter(int n_sources, const int64_t* const* ids, const float* const* rows, float* dtable, int M, int D,
-                      float scale, float* sq_delta, int blocks, cudaStream_t stream);
+                      float scale, float* sq_delta, int blocks, cudaStream_t stream, int64_t* ids_scratch = nullptr);
 // logits [C, V] bf16 (row stride ldl) -> per-row loss (0 for ignored rows) and, in place, dlogits scaled by
 // *inv_n_valid.
 void ce_softmax_grad(__nv_bfloat16* logits, int64_t ldl, const int64_t* labels, float* row_loss,

@@ -207,7 +207,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_bwd", &embedding_bwd);
   // ids_ptrs / rows_ptrs: device-visible addresses (ints) of int64 [M] ids and fp32 [M, D] rows, one pair per source
   m.def("embedding_scatter", [](std::vector<int64_t> ids_ptrs, std::vector<int64_t> rows_ptrs, torch::Tensor& dtable,
-                                int64_t M, double scale, c10::optional<torch::Tensor> sq_delta, int64_t blocks) {
+                                int64_t M, double scale, c10::optional<torch::Tensor> sq_delta, int64_t blocks,
+                                c10::optional<torch::Tensor> ids_scratch) {
     TORCH_CHECK(ids_ptrs.size() == rows_ptrs.size() && !ids_ptrs.empty() && ids_ptrs.size() <= 8, "1..8 sources");
     TORCH_CHECK(dtable.scalar_type() == torch::kFloat32 && dtable.dim() == 2 && dtable.stride(1) == 1 &&
                 dtable.stride(0) == dtable.size(1), "embedding_scatter: dtable must be contiguous fp32 [V, D]");
@@ -220,11 +221,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }
     if (sq_delta.has_value() && sq_delta->defined())
       TORCH_CHECK(sq_delta->scalar_type() == torch::kFloat32 && sq_delta->numel() >= blocks);
+    int64_t* scratch = nullptr;
+    if (ids_scratch.has_value() && ids_scratch->defined()) {
+      TORCH_CHECK(ids_scratch->scalar_type() == torch::kInt64 && ids_scratch->is_contiguous() &&
+                      ids_scratch->numel() >= (int64_t)ids_ptrs.size() * M,
+                  "embedding_scatter: ids_scratch must be int64 with room for every source's ids");
+      scratch = ids_scratch->data_ptr<int64_t>();
+    }
     const int rc = tb::embedding_scatter((int)ids_ptrs.size(), ids, rows, dtable.data_ptr<float>(), (int)M,
                                          (int)dtable.size(1), (float)scale, opt_mptr<float>(sq_delta), (int)blocks,
-                                         cur_stream());
+                                         cur_stream(), scratch);
     TORCH_CHECK(rc == 0, "embedding_scatter failed with code ", rc);
-  });
+  }, pybind11::arg("ids_ptrs"), pybind11::arg("rows_ptrs"), pybind11::arg("dtable"), pybind11::arg("M"),
+     pybind11::arg("scale"), pybind11::arg("sq_delta"), pybind11::arg("blocks"),
+     pybind11::arg("ids_scratch") = c10::nullopt);
   m.def("ce_softmax_grad", &ce_softmax_grad);
   m.def("cast_to_bf16", &cast_to_bf16);
   m.def("scale_inplace", &scale_inplace);

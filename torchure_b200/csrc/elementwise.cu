@@ -794,7 +794,7 @@ embedding_bwd_kernel(const float* __restrict__ dx, const int64_t* __restrict__ i
 // memory by an ordered compaction; the list is applied whenever it fills up.  When sq_delta is given, CTA b stores
 // sum(new^2 - old^2) over everything it touched into sq_delta[b] (the sums telescope over repeated rows), which
 // turns a sum of squares taken before the scatter into the one after it.
-constexpr int EB_THREADS = 256, EB_WARPS = 8, EB_LIST = 1024;
+constexpr int EB_THREADS = 256, EB_WARPS = 8, EB_SCAN = 4, EB_LIST = 4096;
 struct EmbedSources {
   int n;
   const int64_t* ids[8];
@@ -812,11 +812,31 @@ __device__ __forceinline__ int64_t ld_sys_i64(const int64_t* p) {
   return v;
 }
 
+// ids of every source -> one local array [n, M]: the scatter kernel below makes every CTA scan all ids, which must
+// not be remote reads (at eight ranks that would be 300 MB over NVLink for 512 KB of ids)
+__global__ void __launch_bounds__(256)
+embedding_gather_ids_kernel(EmbedSources src, int64_t* __restrict__ out, int M) {
+  const int total = src.n * M;
+  constexpr int U = 4;
+  for (int base = (blockIdx.x * 256 + threadIdx.x) * U; base < total; base += gridDim.x * 256 * U) {
+    int64_t v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u;
+      if (i < total) v[u] = ld_sys_i64(src.ids[i / M] + i % M);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (base + u < total) out[base + u] = v[u];
+  }
+}
+
 __global__ void __launch_bounds__(EB_THREADS)
 embedding_scatter_kernel(EmbedSources src, float* __restrict__ dtable, int M, int D, float scale,
                          float* __restrict__ sq_delta) {
   __shared__ uint32_t list[EB_LIST];        // (source << 27) | row, in application order
-  __shared__ int warp_count[EB_WARPS];
+  __shared__ int list_id[EB_LIST];          // the row's token id
+  __shared__ int warp_count[EB_SCAN][EB_WARPS];
   __shared__ float warp_delta[EB_WARPS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nb = gridDim.x;
@@ -825,10 +845,10 @@ embedding_scatter_kernel(EmbedSources src, float* __restrict__ dtable, int M, in
   auto apply = [&]() {
     __syncthreads();
     for (int e = 0; e < count; ++e) {
+      const int id = list_id[e];
+      if ((id / nb) % EB_WARPS != warp) continue;   // another warp of this CTA owns that row
       const uint32_t ent = list[e];
       const int p = ent >> 27, r = ent & ((1u << 27) - 1);
-      const int64_t id = ld_sys_i64(src.ids[p] + r);
-      if (static_cast<int>((id / nb) % EB_WARPS) != warp) continue;   // another warp of this CTA owns that row
       const float* s = src.rows[p] + static_cast<int64_t>(r) * D;
       float* d = dtable + id * static_cast<int64_t>(D);
       for (int i = lane * 4; i < D; i += 128) {
@@ -844,28 +864,45 @@ embedding_scatter_kernel(EmbedSources src, float* __restrict__ dtable, int M, in
     __syncthreads();
     count = 0;
   };
+  // scan: EB_SCAN ids per thread and round, all loads issued before the first is used; entries are appended in
+  // (source, round, slot, warp, lane) order, the same on every rank
   for (int p = 0; p < src.n; ++p) {
-    for (int base = 0; base < M; base += EB_THREADS) {
-      const int r = base + tid;
-      bool mine = false;
-      if (r < M) {
-        const int64_t id = ld_sys_i64(src.ids[p] + r);
-        mine = static_cast<int>(id % nb) == static_cast<int>(blockIdx.x);
-      }
-      const uint32_t ballot = __ballot_sync(0xffffffffu, mine);
-      if (lane == 0) warp_count[warp] = __popc(ballot);
-      __syncthreads();
-      int before = 0, total = 0;
+    for (int base = 0; base < M; base += EB_THREADS * EB_SCAN) {
+      int64_t id[EB_SCAN];
+      uint32_t ballot[EB_SCAN];
 #pragma unroll
-      for (int w = 0; w < EB_WARPS; ++w) {
-        const int c = warp_count[w];
-        if (w < warp) before += c;
-        total += c;
+      for (int u = 0; u < EB_SCAN; ++u) {
+        const int r = base + u * EB_THREADS + tid;
+        id[u] = r < M ? ld_sys_i64(src.ids[p] + r) : -1;
       }
-      if (mine) list[count + before + __popc(ballot & ((1u << lane) - 1))] = (static_cast<uint32_t>(p) << 27) | r;
+#pragma unroll
+      for (int u = 0; u < EB_SCAN; ++u) {
+        const bool mine = id[u] >= 0 && static_cast<int>(id[u]) % nb == static_cast<int>(blockIdx.x);
+        ballot[u] = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_count[u][warp] = __popc(ballot[u]);
+      }
+      __syncthreads();
+      int at = count, total = 0;
+#pragma unroll
+      for (int u = 0; u < EB_SCAN; ++u) {
+        int before = 0, slot_total = 0;
+#pragma unroll
+        for (int w = 0; w < EB_WARPS; ++w) {
+          const int c = warp_count[u][w];
+          if (w < warp) before += c;
+          slot_total += c;
+        }
+        if (ballot[u] & (1u << lane)) {
+          const int pos = at + before + __popc(ballot[u] & ((1u << lane) - 1));
+          list[pos] = (static_cast<uint32_t>(p) << 27) | static_cast<uint32_t>(base + u * EB_THREADS + tid);
+          list_id[pos] = static_cast<int>(id[u]);
+        }
+        at += slot_total;
+        total += slot_total;
+      }
       count += total;
-      __syncthreads();   // warp_count is rewritten by the next chunk
-      if (count > EB_LIST - EB_THREADS) apply();
+      __syncthreads();   // warp_count is rewritten by the next round
+      if (count > EB_LIST - EB_THREADS * EB_SCAN) apply();
     }
   }
   apply();
@@ -1130,13 +1167,19 @@ void embedding_bwd(const float* dx, const int64_t* ids, float* dtable, int M, in
 }
 
 int embedding_scatter(int n_sources, const int64_t* const* ids, const float* const* rows, float* dtable, int M, int D,
-                      float scale, float* sq_delta, int blocks, cudaStream_t stream) {
+                      float scale, float* sq_delta, int blocks, cudaStream_t stream, int64_t* ids_scratch) {
   if (n_sources < 1 || n_sources > 8 || D % 4 != 0 || M <= 0 || M >= (1 << 27) || blocks < 1) return -1;
   EmbedSources src{};
   src.n = n_sources;
   for (int p = 0; p < n_sources; ++p) {
     src.ids[p] = ids[p];
     src.rows[p] = rows[p];
+  }
+  if (ids_scratch != nullptr) {
+    // sources may live on peer GPUs: bring the ids here once, then scan the local copy
+    const int total = n_sources * M;
+    embedding_gather_ids_kernel<<<std::max(1, std::min(148, (total + 1023) / 1024)), 256, 0, stream>>>(src, ids_scratch, M);
+    for (int p = 0; p < n_sources; ++p) src.ids[p] = ids_scratch + static_cast<int64_t>(p) * M;
   }
   embedding_scatter_kernel<<<blocks, EB_THREADS, 0, stream>>>(src, dtable, M, D, scale, sq_delta);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

@@ -143,13 +143,15 @@ def embedding_bwd_(dx, ids, dtable):
     return dtable
 
 
-def embedding_scatter_(sources, dtable, M, scale=1.0, sq_delta=None, blocks=592):
+def embedding_scatter_(sources, dtable, M, scale=1.0, sq_delta=None, blocks=592, ids_scratch=None):
     """Deterministic dtable[id] += scale * rows, over `sources` = [(ids (M,) int64, rows (M, D) fp32) or
-    (ids address, rows address), ...] in list order; no atomics.  Addresses let a source live on a peer GPU."""
+    (ids address, rows address), ...] in list order; no atomics.  Addresses let a source live on a peer GPU; then pass
+    `ids_scratch` (local int64, len(sources) * M): a first kernel copies every source's ids there, because every CTA
+    of the scatter scans all of them."""
     ids_ptrs = [s[0] if isinstance(s[0], int) else s[0].data_ptr() for s in sources]
     rows_ptrs = [s[1] if isinstance(s[1], int) else s[1].data_ptr() for s in sources]
-    _C().embedding_scatter(ids_ptrs, rows_ptrs, dtable, M, float(scale), sq_delta, blocks)
-    ops.count_launch()
+    _C().embedding_scatter(ids_ptrs, rows_ptrs, dtable, M, float(scale), sq_delta, blocks, ids_scratch)
+    ops.count_launch(2 if ids_scratch is not None else 1)
     return dtable
 
 

@@ -66,6 +66,7 @@ class FusedReducer:
             if table is not None:
                 self.embed_rows = self.comm.alloc(ddp.embed_tokens * table.shape[1], torch.float32)
                 self.embed_ids = self.comm.alloc(ddp.embed_tokens, torch.int64)
+                self.embed_ids_all = torch.empty(self.world * ddp.embed_tokens, dtype=torch.int64, device=dev)
             self.stream = torch.cuda.Stream(device=dev, priority=-1)
             ops.set_compute_sm_reserve(sm_reserve)
         else:
@@ -123,7 +124,7 @@ class FusedReducer:
         ro, io = self.comm.offset_of(self.embed_rows), self.comm.offset_of(self.embed_ids)
         sources = [(self.comm.peers[p] + io, self.comm.peers[p] + ro) for p in range(self.world)]
         K.embedding_scatter_(sources, self._view_of[table], M, scale=1.0 / self.world,
-                             sq_delta=self.partials[len(self.ddp.buckets)], blocks=592)
+                             sq_delta=self.partials[len(self.ddp.buckets)], blocks=592, ids_scratch=self.embed_ids_all)
         self.comm.barrier(phase=3)                          # nobody reads my rows any more
         ops.count_launch(2)
         self._table_done = None
