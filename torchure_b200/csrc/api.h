@@ -93,6 +93,7 @@ void finalize_norm(const float* partials, int n, float max_norm, float eps, floa
 // out[0] += sum over all tensors of x^2 (flag bit0 = bf16)
 void sqnorm_multi(const TensorList& t, float* out, cudaStream_t stream);
 void scale_multi(const TensorList& t, const float* scale, cudaStream_t stream);
+void zero_multi(const TensorList& t, cudaStream_t stream);
 // bucket[off_i ...] (=|+=) cast(grad_i); sq (optional) receives the sum of squares of the result
 void bucket_pack_multi(const TensorList& t, int accumulate, float post_scale, float* sq, cudaStream_t stream);
 

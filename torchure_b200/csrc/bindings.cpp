@@ -170,6 +170,10 @@ void scale_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const to
                  const torch::Tensor& bt, const torch::Tensor& bc, const torch::Tensor& scale) {
   tb::scale_multi(as_list(ptrs, numel, flags, bt, bc), scale.data_ptr<float>(), cur_stream());
 }
+void zero_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
+                const torch::Tensor& bt, const torch::Tensor& bc) {
+  tb::zero_multi(as_list(ptrs, numel, flags, bt, bc), cur_stream());
+}
 void bucket_pack_multi(const torch::Tensor& ptrs, const torch::Tensor& numel, const torch::Tensor& flags,
                        const torch::Tensor& bt, const torch::Tensor& bc, bool accumulate, double post_scale,
                        c10::optional<torch::Tensor> sq) {
@@ -247,6 +251,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                       out.data_ptr<float>(), cur_stream());
   });
   m.def("scale_multi", &scale_multi);
+  m.def("zero_multi", &zero_multi);
   m.def("bucket_pack_multi", &bucket_pack_multi);
   register_comm(m);
   register_attn(m);

@@ -6,6 +6,7 @@
 //                      clip coefficient, optional bf16 shadow write
 //   sqnorm_multi       sum of squares over all tensors (grad norm)
 //   scale_multi        x *= *scale (skipped when the scale is 1)
+//   zero_multi         x = 0 for a list of fp32 tensors
 //   bucket_pack_multi  DDP bucket fill: bucket (= | +=) fp32(grad), optional post-scale, optional sum
 //                      of squares of the result
 #include "api.h"
@@ -136,6 +137,17 @@ scale_kernel(TensorList t, const float* __restrict__ scale) {
   }
 }
 
+// fp32 tensors := 0 (the many small gain-gradient slices of a step, in one launch)
+__global__ void __launch_bounds__(MT_THREADS)
+zero_kernel(TensorList t) {
+  const int ti = t.block_tensor[blockIdx.x];
+  const int64_t n = t.numel[ti];
+  const int64_t lo = static_cast<int64_t>(t.block_chunk[blockIdx.x]) * kChunkElems;
+  const int64_t hi = lo + kChunkElems < n ? lo + kChunkElems : n;
+  float* x = reinterpret_cast<float*>(t.ptrs_a[ti]);
+  for (int64_t i = lo + threadIdx.x; i < hi; i += MT_THREADS) x[i] = 0.f;
+}
+
 // ptrs_a: source grad (bf16 or fp32), ptrs_b: destination slice inside the fp32 bucket
 __global__ void __launch_bounds__(MT_THREADS)
 bucket_pack_kernel(TensorList t, int accumulate, float post_scale, float* __restrict__ sq) {
@@ -202,6 +214,11 @@ void sqnorm_multi(const TensorList& t, float* out, cudaStream_t stream) {
 void scale_multi(const TensorList& t, const float* scale, cudaStream_t stream) {
   if (t.n_blocks <= 0) return;
   scale_kernel<<<t.n_blocks, MT_THREADS, 0, stream>>>(t, scale);
+}
+
+void zero_multi(const TensorList& t, cudaStream_t stream) {
+  if (t.n_blocks <= 0) return;
+  zero_kernel<<<t.n_blocks, MT_THREADS, 0, stream>>>(t);
 }
 
 void bucket_pack_multi(const TensorList& t, int accumulate, float post_scale, float* sq, cudaStream_t stream) {

@@ -99,6 +99,27 @@ class Sm100Engine:
         # columns; the partial sums of the row-parallel products and of the column-parallel input gradients are
         # all-reduced over the axis
         self.tp = getattr(model, "tp", None)
+        # gain gradients are accumulated by kernels with reductions, into destinations that must start at zero: the
+        # backward pass clears all of them with one launch (`prezero_gains`) instead of one fill per gain
+        self.gain_params = [p for p in model.parameters() if p.ndim == 1]
+        self._prezeroed: set[int] = set()
+
+    def prezero_gains(self, sink) -> None:
+        """Called by the first backward function of a pass: zero every gain-gradient destination that starts a new
+        sum in this pass (those that continue a running sum are left alone)."""
+        from torchure_b200.ops import multi_tensor as MT
+
+        self._prezeroed.clear()
+        if sink is None or not MT.available():
+            return
+        dests = []
+        for p in self.gain_params:
+            dst, acc = sink.grad_dest(p)
+            if not acc:
+                dests.append(dst)
+                self._prezeroed.add(id(p))
+        if dests:
+            MT.zero_(dests)
 
     # -- shadows -----------------------------------------------------------------------------
     def shadow_pairs(self):
@@ -193,7 +214,7 @@ class _BlockFn(torch.autograd.Function):
         P = dict(sh.params)  # the nn.Parameter objects, which is what a gradient sink is keyed by
         if ctx.first:
             P["table"] = eng.model.token_emb.weight
-        out = _GradOut(eng.model._grad_sink, x.device)
+        out = _GradOut(eng.model._grad_sink, x.device, eng)
         nq, nkv = Hq * hd, Hkv * hd
         # the consumer computed x2 + y_out, so both incoming grads carry the same values
         if dy is None:
@@ -286,9 +307,10 @@ class _GradOut:
     """Where a block's weight gradients go: into the gradient sink (fused DDP buckets) when one is installed,
     otherwise into fresh fp32 tensors handed back to autograd."""
 
-    def __init__(self, sink, device):
+    def __init__(self, sink, device, eng=None):
         self.sink = sink
         self.device = device
+        self.eng = eng
         self.grads: dict = {}
 
     def wgrad(self, params: tuple, dy: torch.Tensor, x: torch.Tensor) -> None:
@@ -326,7 +348,10 @@ class _GradOut:
             return t
         dst, acc = self.sink.grad_dest(p)
         if not acc:
-            dst.zero_()
+            if self.eng is not None and id(p) in self.eng._prezeroed:
+                self.eng._prezeroed.discard(id(p))     # cleared with all the others at the start of this pass
+            else:
+                dst.zero_()
         return dst
 
     def done(self, p: torch.Tensor) -> None:
@@ -346,7 +371,8 @@ class _FinalNormFn(torch.autograd.Function):
     def backward(ctx, dh):
         x2, rstd = ctx.saved_tensors
         w = ctx.eng.model.norm.weight
-        out = _GradOut(ctx.eng.model._grad_sink, x2.device)
+        ctx.eng.prezero_gains(ctx.eng.model._grad_sink)      # this is the first engine function of a backward pass
+        out = _GradOut(ctx.eng.model._grad_sink, x2.device, ctx.eng)
         dw = out.small(w)
         dx, dxb = K.rmsnorm_bwd(dh.contiguous().view(x2.shape).to(BF16), x2, w.detach(), rstd, None, dw)
         out.done(w)

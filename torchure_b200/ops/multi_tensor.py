@@ -98,6 +98,14 @@ def scale_(tensors: list[torch.Tensor], scale: torch.Tensor) -> None:
     ops.count_launch()
 
 
+def zero_(tensors: list[torch.Tensor]) -> None:
+    """fp32 tensors := 0 in one launch."""
+    assert all(t.dtype == torch.float32 for t in tensors)
+    tab = _table("zero", [tensors])
+    ops.ext().zero_multi(*tab.args())
+    ops.count_launch()
+
+
 def adamw_step(params, grads, exp_avgs, exp_avg_sqs, shadows, lr, beta1, beta2, eps, weight_decay, step,
                grad_scale=None, maximize=False, hyper=None) -> None:
     """`hyper`: optional device tensor {lr, 1 - beta1^t, 1 - beta2^t} that overrides lr/step at run time (graph replay)."""
