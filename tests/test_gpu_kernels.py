@@ -192,7 +192,7 @@ def test_swiglu_fwd_bwd():
     assert relerr(kernels.swiglu_bwd(d, gu), ga.grad) < 5e-3
 
 
-@pytest.mark.parametrize("C,V", [(64, 1000), (300, 5000), (512, 151936)])
+@pytest.mark.parametrize("C,V", [(64, 1000), (300, 5000), (512, 151936), (600, 50264), (130, 32000)])
 def test_ce_softmax_grad(C, V):
     from torchure_b200.ops import kernels
 
@@ -312,14 +312,15 @@ def test_embedding_scatter_is_exact_and_repeatable():
     for ids, rows in srcs:
         want.index_add_(0, ids, rows.double() * 0.25)
     outs = []
-    for _ in range(2):
+    scratch = torch.empty(3 * M, dtype=torch.int64, device="cuda")
+    for use_scratch in (None, None, scratch):      # the third run scans a gathered copy of the ids
         t = base.clone()
         delta = torch.zeros(1024, device="cuda")
-        K.embedding_scatter_(srcs, t, M, scale=0.25, sq_delta=delta, blocks=592)
+        K.embedding_scatter_(srcs, t, M, scale=0.25, sq_delta=delta, blocks=592, ids_scratch=use_scratch)
         outs.append(t)
         got_sq = base.double().pow(2).sum() + delta.double().sum()
         assert abs(got_sq.item() - t.double().pow(2).sum().item()) < 1e-4 * t.double().pow(2).sum().item()
-    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     torch.testing.assert_close(outs[0].double(), want, rtol=1e-5, atol=1e-4)
 
 

@@ -730,19 +730,33 @@ __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int64_t total_vec, int Fv) {
   pdl_wait();
   pdl_launch_dependents();
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = i / Fv, col = i % Fv;
-    const uint4 g = reinterpret_cast<const uint4*>(gu)[row * 2 * Fv + col];
-    const uint4 u = reinterpret_cast<const uint4*>(gu)[row * 2 * Fv + Fv + col];
-    const uint32_t gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
-    uint32_t o[4];
+  // two 16-byte vectors of gate and of up per thread and round: four loads in flight; the quotient is the
+  // approximate division (the result is rounded to bf16 anyway)
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total_vec; i0 += 2 * stride) {
+    uint4 g[2], u[2];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float2 a = bf2_to_f2(gs[k]), b = bf2_to_f2(us[k]);
-      o[k] = f2_to_bf2(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+    for (int v = 0; v < 2; ++v) {
+      const int64_t i = i0 + v * stride;
+      if (i < total_vec) {
+        const int64_t row = i / Fv, col = i % Fv;
+        g[v] = reinterpret_cast<const uint4*>(gu)[row * 2 * Fv + col];
+        u[v] = reinterpret_cast<const uint4*>(gu)[row * 2 * Fv + Fv + col];
+      }
     }
-    reinterpret_cast<uint4*>(act)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+      const int64_t i = i0 + v * stride;
+      if (i >= total_vec) break;
+      const uint32_t gs[4] = {g[v].x, g[v].y, g[v].z, g[v].w}, us[4] = {u[v].x, u[v].y, u[v].z, u[v].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = bf2_to_f2(gs[k]), b = bf2_to_f2(us[k]);
+        o[k] = f2_to_bf2(__fdividef(a.x, 1.f + __expf(-a.x)) * b.x, __fdividef(a.y, 1.f + __expf(-a.y)) * b.y);
+      }
+      reinterpret_cast<uint4*>(act)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
   }
 }
 
@@ -923,7 +937,10 @@ embedding_scatter_kernel(EmbedSources src, float* __restrict__ dtable, int M, in
 // cross-entropy on one vocabulary row per CTA: online max/sum, target gather, loss, in-place dlogits
 // ---------------------------------------------------------------------------------------------
 // 1024 threads per row: at most two rows per SM are in flight (296 rows = 90 MB of bf16 logits), so the second pass
-// over a row finds it in the 126 MB L2 instead of going back to HBM
+// over a row has a chance to find it in the 126 MB L2.  Measured 537 us per 4096 x 151936 chunk (2.5 GB read + written
+// once = 4.6 TB/s; three passes' worth of traffic would be the copy bandwidth, so part of the second pass still comes
+// from HBM).  A variant that kept the row on chip (a cluster of two 512-thread CTAs, half a row each in shared memory,
+// partials exchanged through distributed shared memory) measured 804 us: 74 rows in flight are too few.
 constexpr int CE_THREADS = 1024;
 
 __global__ void __launch_bounds__(CE_THREADS)
