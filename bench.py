@@ -61,7 +61,7 @@ def bench_mesh(parallel: str, n_gpus: int) -> dict:
         return {"dp_shard": n_gpus}
     if parallel == "hsdp2":
         return {"dp_replicate": 2, "dp_shard": n_gpus // 2}
-    if parallel == "tp2":
+    if parallel in ("tp2", "tp2sp"):
         return {"dp": n_gpus // 2, "tp": 2}
     return {"dp": n_gpus}
 
@@ -266,7 +266,10 @@ def run_ours(args) -> None:
                        args.parallel)
     if args.torch_path:
         cfg["compile"] = False
-    cfg["cuda_graph"] = bool(args.graph) and not args.torch_path
+    if args.parallel == "tp2sp":
+        # sequence parallelism: the block linears run as the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels
+        cfg["tp"] = {"sequence_parallel": True}
+    cfg["cuda_graph"] = bool(args.graph) and not args.torch_path and args.parallel != "tp2sp"
     trainer = Trainer(cfg, rank, local_rank, world, benchmark=True)
     step = trainer.train_step_untimed
     for _ in range(max(5, args.warmup)):
@@ -329,7 +332,7 @@ def main() -> None:
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--torch-path", action="store_true", help="ours: run the PyTorch oracle path (A/B)")
     ap.add_argument("--graph", type=int, default=1, help="ours: replay the device step from one CUDA graph (1) or launch eagerly (0)")
-    ap.add_argument("--parallel", choices=["dp", "fsdp", "hsdp2", "tp2"], default="dp",
+    ap.add_argument("--parallel", choices=["dp", "fsdp", "hsdp2", "tp2", "tp2sp"], default="dp",
                     help="ours: strategy selected through the mesh (dp = DDP is the headline configuration)")
     ap.add_argument("--census", type=int, default=1, help="one extra untimed step under torch.profiler: kernel census")
     args = ap.parse_args()

@@ -114,6 +114,22 @@ def test_tensor_parallel_trainer_matches_single_process(tmp_path):
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
 
 
+def test_sequence_parallel_trainer_matches_single_process(tmp_path):
+    """mesh {dp: 1, tp: 2} with `tp.sequence_parallel`: the activations between the column / row linears are sharded
+    along the sequence, the embedding output is sliced on entry and the hidden state gathered before the final norm;
+    the norm gains inside the blocks see half of the tokens each and their gradients are summed over the axis.  Loss
+    and global gradient norm must follow the single-process run."""
+    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
+    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
+    sp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "tp": 2})
+    sp_cfg["tp"] = {"sequence_parallel": True}
+    run_distributed(_run_hist_only, 2, sp_cfg, str(tmp_path), str(tmp_path / "sp.pt"), timeout_s=240)
+    a, b = torch.load(tmp_path / "sp.pt"), torch.load(tmp_path / "one.pt")
+    for x, y in zip(a["hist"], b["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
+
+
 def _run_fsdp_resume(rank, world, home, out):
     os.environ["TORCHURE_B200_HOME"] = home
     from torchure_b200.train.trainer import Trainer

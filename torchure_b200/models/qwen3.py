@@ -110,9 +110,12 @@ class GroupQueryAttention(nn.Module):
             self.q_norm = RMSNorm(self.head_dim, norm_eps)
             self.k_norm = RMSNorm(self.head_dim, norm_eps)
 
-    def forward(self, x, cos, sin, attention_mask=None):
-        B, S, _ = x.shape
-        q = self.q_proj(x).view(B, S, self.num_heads, self.head_dim).transpose(1, 2)
+    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None):
+        # `batch_shape` = (B, S) under sequence parallelism: x is then this rank's slice of the B * S tokens laid out
+        # as one row sequence [1, B * S / n, D], which the column-parallel projections gather
+        q = self.q_proj(x)
+        B, S = batch_shape if batch_shape is not None else (x.shape[0], q.shape[1])
+        q = q.view(B, S, self.num_heads, self.head_dim).transpose(1, 2)
         k = self.k_proj(x).view(B, S, self.num_kv_heads, self.head_dim).transpose(1, 2)
         v = self.v_proj(x).view(B, S, self.num_kv_heads, self.head_dim).transpose(1, 2)
         if self.qk_norm:
@@ -131,6 +134,8 @@ class GroupQueryAttention(nn.Module):
             mask = mask | torch.eye(S, dtype=torch.bool, device=x.device)[None, None]
             o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
         o = o.transpose(1, 2).reshape(B, S, self.num_heads * self.head_dim)
+        if batch_shape is not None:
+            o = o.reshape(1, B * S, -1)
         return self.o_proj(o)
 
 
@@ -154,8 +159,8 @@ class TransformerBlock(nn.Module):
         self.norm2 = RMSNorm(emb_dim, norm_eps)
         self.ffn = SwiGLU(emb_dim, ffn_dim if ffn_dim is not None else default_ffn_dim(emb_dim))
 
-    def forward(self, x, cos, sin, attention_mask=None):
-        x = x + self.gqa(self.norm1(x), cos, sin, attention_mask)
+    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None):
+        x = x + self.gqa(self.norm1(x), cos, sin, attention_mask, batch_shape)
         return x + self.ffn(self.norm2(x))
 
 
@@ -257,11 +262,20 @@ class Qwen3(nn.Module):
             pos = (attention_mask.long().cumsum(dim=1) - 1).masked_fill(~attention_mask, 0)
             cos, sin = self.rope(pos)
         h = self.token_emb(x)
+        sp = getattr(self, "sp", None)      # (mesh, axis) under tensor parallelism with sequence parallelism
+        if sp is not None:
+            from torchure_b200.parallel.tensor_parallel import shard_sequence, unshard_sequence
+
+            assert attention_mask is None and not return_hidden_states, "sequence parallelism: causal path only"
+            # all B * S tokens as one row sequence, of which every rank of the axis keeps a contiguous slice
+            h = shard_sequence(h.reshape(1, B * S, -1), *sp)
         hidden_states = [h] if return_hidden_states else []
         for block in self.blocks:
-            h = block(h, cos, sin, attention_mask)
+            h = block(h, cos, sin, attention_mask, (B, S)) if sp is not None else block(h, cos, sin, attention_mask)
             if return_hidden_states:
                 hidden_states.append(h)
+        if sp is not None:
+            h = unshard_sequence(h, *sp).reshape(B, S, -1)
         h = self.norm(h)
         if return_final_hidden:
             return h

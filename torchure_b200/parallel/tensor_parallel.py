@@ -85,6 +85,54 @@ class _ScatterSeq(torch.autograd.Function):
         return all_gather(g.contiguous(), ctx.mesh, ctx.dim, gather_dim=1), None, None
 
 
+class _ShardSeq(torch.autograd.Function):
+    """Entry of a sequence-parallel region whose input is REPLICATED over the axis (the embedding output): keep this
+    rank's slice of dim 1 forward; backward all-gathers the slices, so the replicated producer sees the full gradient
+    on every rank (its weight gradient then needs no sum over the axis)."""
+
+    @staticmethod
+    def forward(ctx, x, mesh, dim):
+        ctx.mesh, ctx.dim = mesh, dim
+        n, r = mesh.size(dim), mesh.coordinate(dim)
+        assert x.shape[1] % n == 0, f"sequence length {x.shape[1]} is not divisible by tp={n}"
+        return x.chunk(n, dim=1)[r].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return all_gather(g.contiguous(), ctx.mesh, ctx.dim, gather_dim=1), None, None
+
+
+class _UnshardSeq(torch.autograd.Function):
+    """Exit of a sequence-parallel region into REPLICATED computation (final norm, head, loss run identically on every
+    rank of the axis): all-gather dim 1 forward; every rank then holds the same full gradient, of which backward keeps
+    this rank's slice (no sum: the replicas compute one loss, not n of them)."""
+
+    @staticmethod
+    def forward(ctx, x, mesh, dim):
+        ctx.mesh, ctx.dim = mesh, dim
+        return all_gather(x.contiguous(), mesh, dim, gather_dim=1)
+
+    @staticmethod
+    def backward(ctx, g):
+        n, r = ctx.mesh.size(ctx.dim), ctx.mesh.coordinate(ctx.dim)
+        return g.chunk(n, dim=1)[r].contiguous(), None, None
+
+
+def shard_sequence(x: torch.Tensor, mesh, dim: str = "tp") -> torch.Tensor:
+    return _ShardSeq.apply(x, mesh, dim)
+
+
+def unshard_sequence(x: torch.Tensor, mesh, dim: str = "tp") -> torch.Tensor:
+    return _UnshardSeq.apply(x, mesh, dim)
+
+
+def _autocast_input(x: torch.Tensor) -> torch.Tensor:
+    """What F.linear would do to its input under autocast, done up front so that the fused kernels see bf16 rows."""
+    if x.is_cuda and torch.is_autocast_enabled() and x.is_floating_point():
+        return x.to(torch.get_autocast_gpu_dtype())
+    return x
+
+
 def _fused_comm(x: torch.Tensor, mesh, dim: str):
     """The axis' sm_100a communicator if the fused GEMM+collective kernels can take `x` (tokens of ONE sequence shard
     as rows), else None."""
@@ -197,6 +245,7 @@ class ColumnParallelLinear(nn.Module):
 
     def forward(self, x):
         if self.sp:
+            x = _autocast_input(x)
             comm = _fused_comm(x, self.mesh, self.dim)
             if comm is not None:
                 y = _ColumnSPFused.apply(x.reshape(-1, x.shape[-1]), self.weight, comm, self.mesh, self.dim)
@@ -218,6 +267,7 @@ class RowParallelLinear(nn.Module):
     def forward(self, x):
         if self.sp:
             n = self.mesh.size(self.dim)
+            x = _autocast_input(x)
             comm = _fused_comm(x, self.mesh, self.dim)
             if comm is not None and (x.numel() // x.shape[-1]) % (128 * n) == 0:
                 y = _RowSPFused.apply(x.reshape(-1, x.shape[-1]), self.weight, comm, self.mesh, self.dim)
@@ -287,7 +337,23 @@ def parallelize_model(model, mesh, dim: str = "tp", sequence_parallel: bool = Fa
                     b.ffn.down_proj):
             lin.weight._tp_sharded = True
     if sequence_parallel:
+        # The module path runs with the activations between the linears sharded along the sequence: the model slices
+        # the embedding output (`shard_sequence`) and gathers before its final norm (`unshard_sequence`); the norms
+        # inside the blocks see 1/n of the tokens each, so their gain gradients are summed over the axis.
         model.impl = "torch"
+        model.sp = (mesh, dim)
+
+        def _sum_partial(grad):
+            if grad is None:
+                return None
+            grad = grad.contiguous().clone()
+            all_reduce(grad, mesh, dim, "sum")
+            return grad
+
+        if n > 1:
+            for b in model.blocks:
+                for norm in (b.norm1, b.norm2):
+                    norm.weight.register_hook(_sum_partial)
         return
     # the engine reads head counts and the FFN width from the model's config: make them this rank's
     model.cfg = dict(model.cfg, num_heads=model.cfg["num_heads"] // n, num_kv_heads=model.cfg["num_kv_heads"] // n,

@@ -74,7 +74,17 @@ class Trainer:
 
             if ops.available():
                 for axis in [self.data_axis] + [a for a in ("tp", "cp") if a in self.mesh.axes()]:
-                    enable_sm100(self.mesh, axis, comm_cfg.get("max_bytes", 64 << 20))
+                    persistent = 0
+                    if axis == "tp" and self.config.get("tp", {}).get("sequence_parallel", False):
+                        # operands of the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels live in the axis'
+                        # symmetric region: the shard and the gathered copy of the widest activation (bf16) and one
+                        # fp32 reduce-scatter target, each kept per shape
+                        d = self.config["data"]
+                        mc = self.config["model"]["config"]
+                        tokens = d["micro_batch_size"] * d["seq_len"]
+                        widest = max(mc["emb_dim"], mc.get("ffn_dim") or 0, mc["num_heads"] * (mc.get("head_dim") or 128))
+                        persistent = tokens * widest * 24 + (8 << 20)
+                    enable_sm100(self.mesh, axis, comm_cfg.get("max_bytes", 64 << 20), persistent)
 
         self.ignore_index = self.config["objective"]["config"]["ignore_index"]
         self.tokenizer = None
