@@ -56,13 +56,15 @@ PUBLISHED_TPS_1GPU_H100 = 54_500.0
 
 
 def bench_mesh(parallel: str, n_gpus: int) -> dict:
-    """dp: DDP (the headline).  fsdp / hsdp2 / tp2: the other strategies the mesh can select, for comparison rows."""
+    """dp: DDP (the headline).  fsdp / hsdp2 / tp2 / cp2: the other strategies the mesh can select, for comparison rows."""
     if parallel == "fsdp":
         return {"dp_shard": n_gpus}
     if parallel == "hsdp2":
         return {"dp_replicate": 2, "dp_shard": n_gpus // 2}
     if parallel in ("tp2", "tp2sp"):
         return {"dp": n_gpus // 2, "tp": 2}
+    if parallel == "cp2":
+        return {"dp": n_gpus // 2, "cp": 2}
     return {"dp": n_gpus}
 
 
@@ -70,7 +72,7 @@ def bench_config(model: str, n_gpus: int, total_steps: int, micro_batch: int | N
                  parallel: str = "dp") -> dict:
     mbs = micro_batch or MICRO_BATCH[model]
     mesh = bench_mesh(parallel, n_gpus)
-    replicas = n_gpus // mesh.get("tp", 1)      # ranks that see different data
+    replicas = n_gpus // (mesh.get("tp", 1) * mesh.get("cp", 1))      # ranks that see different data
     return {
         "model": {"name": "qwen3_dense", "config": dict(MODELS[model])},
         "mesh": mesh,
@@ -269,7 +271,7 @@ def run_ours(args) -> None:
     if args.parallel == "tp2sp":
         # sequence parallelism: the block linears run as the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels
         cfg["tp"] = {"sequence_parallel": True}
-    cfg["cuda_graph"] = bool(args.graph) and not args.torch_path and args.parallel != "tp2sp"
+    cfg["cuda_graph"] = bool(args.graph) and not args.torch_path and args.parallel not in ("tp2sp", "cp2")
     trainer = Trainer(cfg, rank, local_rank, world, benchmark=True)
     step = trainer.train_step_untimed
     for _ in range(max(5, args.warmup)):
@@ -332,7 +334,7 @@ def main() -> None:
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--torch-path", action="store_true", help="ours: run the PyTorch oracle path (A/B)")
     ap.add_argument("--graph", type=int, default=1, help="ours: replay the device step from one CUDA graph (1) or launch eagerly (0)")
-    ap.add_argument("--parallel", choices=["dp", "fsdp", "hsdp2", "tp2", "tp2sp"], default="dp",
+    ap.add_argument("--parallel", choices=["dp", "fsdp", "hsdp2", "tp2", "tp2sp", "cp2"], default="dp",
                     help="ours: strategy selected through the mesh (dp = DDP is the headline configuration)")
     ap.add_argument("--census", type=int, default=1, help="one extra untimed step under torch.profiler: kernel census")
     args = ap.parse_args()

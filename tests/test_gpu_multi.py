@@ -506,6 +506,40 @@ def test_trainer_tensor_parallel_on_engine(tmp_path):
         assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
 
 
+def _trainer_cp(rank, world, home, out):
+    """Context parallelism on the sm_100a engine through the Trainer (mesh {dp: 1, cp: world}, or one GPU for the
+    comparison): sequences of 512 tokens, so every zigzag chunk is one 128-token block of the pair kernels."""
+    import os
+
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    mesh = {"dp": 1, "cp": world} if world > 1 else {"dp": 1}
+    cfg = _trainer_cfg(mesh, f"t_cp{world}", 4, graph=False)
+    cfg["data"]["seq_len"] = 128 * 2 * 2
+    tr = Trainer(cfg, rank, rank, world, benchmark=True)
+    assert tr.model.impl != "torch"
+    if world > 1:
+        assert tr.model.cp is not None and tr.model.engine().cp is not None
+        seen = []
+        tr.model.register_forward_pre_hook(lambda mod, args: seen.append(tuple(args[0].shape)))
+    hist = tr.train_n_step_test(6)
+    if world > 1:
+        assert set(seen) == {(2, 512 // world)}, set(seen)
+    tr.check_device_errors()
+    if rank == 0:
+        torch.save(hist, out)
+
+
+def test_trainer_context_parallel_on_engine(tmp_path):
+    run_on_gpus(_trainer_cp, 2, str(tmp_path), str(tmp_path / "cp.pt"), timeout_s=240)
+    run_on_gpus(_trainer_cp, 1, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
+    cp, one = torch.load(tmp_path / "cp.pt"), torch.load(tmp_path / "one.pt")
+    for x, y in zip(cp, one):
+        assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
+
+
 def _trainer_vs_single_cfg(rank, world, home, out):
     import os
 

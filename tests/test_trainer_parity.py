@@ -95,9 +95,11 @@ def _run_hist_only(rank, world, cfg, home, out):
     from torchure_b200.train.trainer import Trainer
 
     tr = Trainer(cfg, rank, rank, world, benchmark=True, device="cpu")
+    seen = []
+    tr.model.register_forward_pre_hook(lambda mod, args: seen.append(tuple(args[0].shape)))
     hist = tr.train_n_step_test(STEPS)
     if rank == 0:
-        torch.save({"hist": hist}, out)
+        torch.save({"hist": hist, "input_shapes": sorted(set(seen))}, out)
 
 
 def test_tensor_parallel_trainer_matches_single_process(tmp_path):
@@ -125,6 +127,22 @@ def test_sequence_parallel_trainer_matches_single_process(tmp_path):
     sp_cfg["tp"] = {"sequence_parallel": True}
     run_distributed(_run_hist_only, 2, sp_cfg, str(tmp_path), str(tmp_path / "sp.pt"), timeout_s=240)
     a, b = torch.load(tmp_path / "sp.pt"), torch.load(tmp_path / "one.pt")
+    for x, y in zip(a["hist"], b["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
+
+
+def test_context_parallel_trainer_matches_single_process(tmp_path):
+    """mesh {dp: 1, cp: 2}: both ranks read the same rows, keep two zigzag chunks of every sequence, rotate by the
+    chunks' global positions and run attention as a ring; each divides its summed loss by half of the global target
+    count and the gradients are averaged over dp x cp.  Loss and gradient norm must follow the single-process run."""
+    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
+    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
+    cp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "cp": 2})
+    run_distributed(_run_hist_only, 2, cp_cfg, str(tmp_path), str(tmp_path / "cp.pt"), timeout_s=240)
+    a, b = torch.load(tmp_path / "cp.pt"), torch.load(tmp_path / "one.pt")
+    d = cp_cfg["data"]
+    assert a["input_shapes"] == [(d["micro_batch_size"], d["seq_len"] // 2)], a["input_shapes"]   # half of every row
     for x, y in zip(a["hist"], b["hist"]):
         assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)

@@ -7,7 +7,8 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
                    [ffn_dim], [norm_eps], [rope_theta], [impl]}}
     mesh          {axis: size, ...}   product == WORLD_SIZE.  Data axes: "dp" (DDP), or "dp_shard" (FSDP2) with an
                   optional "dp_replicate" in front of it (HSDP); "tp" shards every block (Megatron column/row split);
-                  "cp" splits the sequence (ring attention).  At least one data axis is required.
+                  "cp" (after "dp") splits every sequence into zigzag chunks and runs attention as a ring.  At least one
+                  data axis is required.
     optimizer     {name, config{lr, weight_decay, betas, fused}, [max_norm],
                    scheduler{type, warmup_ratio, decay_ratio, total_steps}}
     objective     {name, config{ignore_index, fused_linear_ce, ce_chunk_size}}
@@ -63,6 +64,11 @@ def validate_config(cfg: dict, world_size: int | None = None) -> dict:
         raise ConfigError('"dp_replicate" needs a "dp_shard" axis (HSDP); use "dp" for plain replication')
     if "dp_replicate" in mesh and list(mesh).index("dp_replicate") > list(mesh).index("dp_shard"):
         raise ConfigError('"dp_replicate" must come before "dp_shard" in the mesh')
+    if mesh.get("cp", 1) > 1:
+        if list(mesh)[: 2] != ["dp", "cp"] or len(mesh) != 2:
+            raise ConfigError('context parallelism is selected by mesh {"dp": D, "cp": C} (in this order, no other axis)')
+        if cfg.get("data", {}).get("seq_len", 0) % (2 * mesh["cp"]) != 0:
+            raise ConfigError(f"seq_len must be a multiple of 2 x cp = {2 * mesh['cp']} (zigzag chunks)")
     if world_size is not None and math.prod(mesh.values()) != world_size:
         raise ConfigError(f"mesh {mesh} does not cover world size {world_size}")
     opt = cfg["optimizer"]

@@ -32,7 +32,7 @@ def _chunk_torch(h: torch.Tensor, w: torch.Tensor, y: torch.Tensor, ignore_index
 
 class _LinearCE(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden, weight, labels, ignore_index, chunk_size):
+    def forward(ctx, hidden, weight, labels, ignore_index, chunk_size, normalizer=None):
         n = hidden.shape[0]
         w = weight.to(hidden.dtype)
         loss_sum = torch.zeros((), dtype=torch.float32, device=hidden.device)
@@ -45,7 +45,7 @@ class _LinearCE(torch.autograd.Function):
             d_hidden[lo:hi] = dh
             if d_weight is not None:
                 d_weight += dw
-        n_valid = (labels != ignore_index).sum().clamp_min(1)
+        n_valid = (labels != ignore_index).sum().clamp_min(1) if normalizer is None else normalizer
         ctx.stash = (d_hidden, d_weight, n_valid)
         ctx.weight_dtype = weight.dtype
         return loss_sum / n_valid
@@ -61,13 +61,16 @@ class _LinearCE(torch.autograd.Function):
         if d_weight is not None:
             d_weight.mul_(scale)
             d_weight = d_weight.to(ctx.weight_dtype)
-        return d_hidden, d_weight, None, None, None
+        return d_hidden, d_weight, None, None, None, None
 
 
 def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
-                               ignore_index: int = -100, chunk_size: int = 1024, loss_scale: float = 1.0) -> torch.Tensor:
+                               ignore_index: int = -100, chunk_size: int = 1024, loss_scale: float = 1.0,
+                               normalizer: torch.Tensor | None = None) -> torch.Tensor:
     """hidden (B,S,D) or (N,D); weight (V,D); labels already shifted, (B,S) or (N,).  Returns mean CE * loss_scale
-    (the scale is folded into the gradients that are computed during the forward pass)."""
+    (the scale is folded into the gradients that are computed during the forward pass).  `normalizer` (a 0-d device
+    tensor) replaces the count of valid labels as the divisor: a rank that holds only part of every sequence divides
+    by its share of the global count, so that averaging the ranks' losses and gradients gives the global mean."""
     if hidden.dim() == 3:
         hidden = hidden.reshape(-1, hidden.shape[-1])
         labels = labels.reshape(-1)
@@ -77,6 +80,6 @@ def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, label
         if ops.available():
             from torchure_b200.ops.linear_ce import linear_ce_sm100
 
-            return linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size, loss_scale)
-    loss = _LinearCE.apply(hidden, weight, labels, ignore_index, chunk_size)
+            return linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size, loss_scale, normalizer)
+    loss = _LinearCE.apply(hidden, weight, labels, ignore_index, chunk_size, normalizer)
     return loss if loss_scale == 1.0 else loss * loss_scale

@@ -70,7 +70,7 @@ class RotaryEmbedding(nn.Module):
         self.base = float(base)
         inv_freq = 1.0 / (self.base ** (torch.arange(0, head_dim, 2).float() / head_dim))
         self.register_buffer("inv_freq", inv_freq, persistent=False)
-        self._cache: dict[tuple[int, torch.device], tuple[torch.Tensor, torch.Tensor]] = {}
+        self._cache: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
     def tables(self, seq_len: int, device) -> tuple[torch.Tensor, torch.Tensor]:
         """(S, hd) fp32 cos/sin for positions 0..S-1, cached per (seq_len, device)."""
@@ -81,6 +81,20 @@ class RotaryEmbedding(nn.Module):
             ang = pos.float()[:, None] * self.inv_freq.to(device)[None, :]
             ang = torch.cat([ang, ang], dim=-1)
             hit = (ang.cos().contiguous(), ang.sin().contiguous())
+            self._cache[key] = hit
+        return hit
+
+    def zigzag_tables(self, local_len: int, n: int, r: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+        """(local_len, hd) fp32 cos/sin of the global positions that rank r of n holds under context parallelism:
+        chunks r and 2n-1-r of a sequence of n * local_len tokens cut into 2n chunks."""
+        key = ("zigzag", local_len, n, r, torch.device(device))
+        hit = self._cache.get(key)
+        if hit is None:
+            cos, sin = self.tables(local_len * n, device)
+            c = local_len // 2
+            pos = torch.cat([torch.arange(r * c, (r + 1) * c, device=device),
+                             torch.arange((2 * n - 1 - r) * c, (2 * n - r) * c, device=device)])
+            hit = (cos[pos].contiguous(), sin[pos].contiguous())
             self._cache[key] = hit
         return hit
 
@@ -110,9 +124,11 @@ class GroupQueryAttention(nn.Module):
             self.q_norm = RMSNorm(self.head_dim, norm_eps)
             self.k_norm = RMSNorm(self.head_dim, norm_eps)
 
-    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None):
+    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None, cp=None):
         # `batch_shape` = (B, S) under sequence parallelism: x is then this rank's slice of the B * S tokens laid out
-        # as one row sequence [1, B * S / n, D], which the column-parallel projections gather
+        # as one row sequence [1, B * S / n, D], which the column-parallel projections gather.
+        # `cp` = (mesh, axis) under context parallelism: x holds this rank's two zigzag chunks of every sequence and
+        # cos / sin their global positions; attention runs as a ring over the axis.
         q = self.q_proj(x)
         B, S = batch_shape if batch_shape is not None else (x.shape[0], q.shape[1])
         q = q.view(B, S, self.num_heads, self.head_dim).transpose(1, 2)
@@ -121,6 +137,12 @@ class GroupQueryAttention(nn.Module):
         if self.qk_norm:
             q, k = self.q_norm(q), self.k_norm(k)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        if cp is not None:
+            from torchure_b200.parallel.context_parallel import ring_attention
+
+            assert attention_mask is None, "context parallelism: causal path only"
+            o = ring_attention(q, k, v, *cp).to(v.dtype)
+            return self.o_proj(o.transpose(1, 2).reshape(B, S, self.num_heads * self.head_dim))
         rep = self.num_heads // self.num_kv_heads
         if rep > 1:
             k = k.repeat_interleave(rep, dim=1)
@@ -159,8 +181,8 @@ class TransformerBlock(nn.Module):
         self.norm2 = RMSNorm(emb_dim, norm_eps)
         self.ffn = SwiGLU(emb_dim, ffn_dim if ffn_dim is not None else default_ffn_dim(emb_dim))
 
-    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None):
-        x = x + self.gqa(self.norm1(x), cos, sin, attention_mask, batch_shape)
+    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None, cp=None):
+        x = x + self.gqa(self.norm1(x), cos, sin, attention_mask, batch_shape, cp)
         return x + self.ffn(self.norm2(x))
 
 
@@ -254,7 +276,12 @@ class Qwen3(nn.Module):
                 return h
             return self.engine().lm_head(h)
         B, S = x.shape
-        if attention_mask is None:
+        cp = getattr(self, "cp", None)      # (mesh, axis): x holds this rank's zigzag chunks of sequences n times longer
+        if cp is not None:
+            assert attention_mask is None and not return_hidden_states, "context parallelism: causal path only"
+            cos, sin = self.rope.zigzag_tables(S, cp[0].size(cp[1]), cp[0].coordinate(cp[1]), x.device)
+            cos, sin = cos[None, None], sin[None, None]
+        elif attention_mask is None:
             cos, sin = self.rope.tables(S, x.device)
             cos, sin = cos[None, None], sin[None, None]
         else:
@@ -271,7 +298,12 @@ class Qwen3(nn.Module):
             h = shard_sequence(h.reshape(1, B * S, -1), *sp)
         hidden_states = [h] if return_hidden_states else []
         for block in self.blocks:
-            h = block(h, cos, sin, attention_mask, (B, S)) if sp is not None else block(h, cos, sin, attention_mask)
+            if sp is not None:
+                h = block(h, cos, sin, attention_mask, (B, S))
+            elif cp is not None:
+                h = block(h, cos, sin, None, None, cp)
+            else:
+                h = block(h, cos, sin, attention_mask)
             if return_hidden_states:
                 hidden_states.append(h)
         if sp is not None:

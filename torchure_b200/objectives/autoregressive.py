@@ -16,6 +16,9 @@ class ARObjective:
     def compute_loss(self, model, batch: dict[str, torch.Tensor], loss_scale: float = 1.0) -> torch.Tensor:
         """Mean next-token CE times `loss_scale` (1/micro-batches under gradient accumulation: folding it here
         keeps the loss the root of backward, which the fused gradient paths rely on)."""
+        cp = getattr(model, "cp", None)
+        if cp is not None:
+            return self._compute_loss_cp(model, batch, loss_scale, *cp)
         if self.fused_linear_ce:
             hidden = model(batch["input_ids"], return_final_hidden=True)
             labels = shift_labels(batch["labels"], self.ignore_index)
@@ -24,3 +27,26 @@ class ARObjective:
         logits = model(batch["input_ids"])
         loss = cross_entropy_loss(batch["labels"], logits, self.ignore_index)
         return loss if loss_scale == 1.0 else loss * loss_scale
+
+    def _compute_loss_cp(self, model, batch, loss_scale, mesh, dim) -> torch.Tensor:
+        """Context parallelism: every rank of the axis receives the whole batch, keeps its two zigzag chunks of every
+        sequence (tokens and the already shifted targets) and divides its summed loss by 1/n of the GLOBAL target
+        count, so that the average over the axis (which the gradient reduction takes anyway) is the mean over all
+        targets whatever the chunks' own counts are."""
+        import torch.nn.functional as F
+
+        from torchure_b200.parallel.context_parallel import zigzag_split
+
+        n, r = mesh.size(dim), mesh.coordinate(dim)
+        full = shift_labels(batch["labels"], self.ignore_index)
+        normalizer = (full != self.ignore_index).sum().clamp_min(1).float() / n
+        ids = zigzag_split(batch["input_ids"], n, r).contiguous()
+        labels = zigzag_split(full, n, r).contiguous()
+        if self.fused_linear_ce:
+            hidden = model(ids, return_final_hidden=True)
+            return fused_linear_cross_entropy(hidden, model.lm_head.weight, labels, self.ignore_index,
+                                              self.ce_chunk_size, loss_scale, normalizer)
+        logits = model(ids)
+        total = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), labels.reshape(-1),
+                                ignore_index=self.ignore_index, reduction="sum")
+        return total * (loss_scale / normalizer)

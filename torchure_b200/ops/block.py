@@ -141,12 +141,23 @@ class Sm100Engine:
         for p, _ in self._pairs:
             self._versions[id(p)] = p._version
 
+    @property
+    def cp(self):
+        """(mesh, axis) when the model runs under context parallelism: the engine then sees this rank's two zigzag
+        chunks of every sequence, rotates by their global positions and runs attention as a ring over the axis."""
+        return getattr(self.model, "cp", None)
+
+    def rope_tables(self, S: int, device):
+        cp = self.cp
+        if cp is None:
+            return self.model.rope.tables(S, device)
+        return self.model.rope.zigzag_tables(S, cp[0].size(cp[1]), cp[0].coordinate(cp[1]), device)
+
     # -- forward -----------------------------------------------------------------------------
     def forward_hidden(self, ids: torch.Tensor) -> torch.Tensor:
         m = self.model
         self.refresh()
         B, S = ids.shape
-        cos, sin = m.rope.tables(S, ids.device)
         x, y = None, None
         flat_ids = ids.reshape(-1)
         if self.pre_block is not None:
@@ -181,7 +192,7 @@ class _BlockFn(torch.autograd.Function):
         cfg = eng.cfg
         Hq, Hkv, hd, eps = cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["norm_eps"]
         use_norm = cfg["qk_norm"]
-        cos, sin = eng.model.rope.tables(S, w1.device)
+        cos, sin = eng.rope_tables(S, w1.device)
         if ids is not None:
             x, h1, rstd1 = K.add_rmsnorm(None, None, w1, eps, ids=ids,
                                          table=eng.emb_shadow if eng.bf16_embedding else table)
@@ -190,7 +201,15 @@ class _BlockFn(torch.autograd.Function):
         qkv = K.linear_fwd(h1, sh.wqkv)
         qk = K.qknorm_rope(qkv, qn, kn, cos, sin, S, Hq, Hkv, eps, use_norm)
         need_grad = any(ctx.needs_input_grad)
-        o, st = attn_ops.attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=need_grad)
+        if eng.cp is not None:
+            from torchure_b200.parallel.context_parallel import ring_fwd_sm100
+
+            # q is used where it lies in `qk`; K and V travel around the ring, so they get buffers of their own
+            k2, v2 = qk[:, Hq * hd:].contiguous(), qkv[:, (Hq + Hkv) * hd:].contiguous()
+            o, lse = ring_fwd_sm100(qk, 0, k2, v2, B, S, Hq, Hkv, *eng.cp)
+            st = (k2, v2, lse)
+        else:
+            o, st = attn_ops.attn_fwd(qk, qkv, B, S, Hq, Hkv, hd, need_grad=need_grad)
         y_a = K.linear_fwd(o, sh.wo)
         if eng.tp is not None:
             eng.tp.all_reduce_(y_a)        # row-parallel: sum the partial products of the ranks' heads
@@ -239,7 +258,17 @@ class _BlockFn(torch.autograd.Function):
         # ---- attention
         d_o = K.linear_dgrad(dx1_b, sh.wo)
         out.wgrad((P["wo"],), dx1_b, o)
-        dqkv, dq_acc = attn_ops.attn_bwd(d_o, qk, qkv, ctx.attn_state, B, S, Hq, Hkv, hd, keep_dq_fp32=True)
+        if eng.cp is not None:
+            from torchure_b200.parallel.context_parallel import ring_bwd_sm100
+
+            k2, v2, lse = ctx.attn_state
+            dq_acc, dk, dv = ring_bwd_sm100(qk, 0, k2, v2, o, lse, d_o, B, S, Hq, Hkv, *eng.cp)
+            dqkv = torch.empty(B * S, nq + 2 * nkv, dtype=BF16, device=d_o.device)   # q columns: read from dq_acc
+            dqkv[:, nq:nq + nkv].copy_(dk.view(B * S, nkv))
+            dqkv[:, nq + nkv:].copy_(dv.view(B * S, nkv))
+            del k2, v2, lse, dk, dv
+        else:
+            dqkv, dq_acc = attn_ops.attn_bwd(d_o, qk, qkv, ctx.attn_state, B, S, Hq, Hkv, hd, keep_dq_fp32=True)
         ctx.attn_state = None
         del d_o
         if use_norm:

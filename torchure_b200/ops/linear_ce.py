@@ -24,13 +24,14 @@ BF16 = torch.bfloat16
 
 class _LinearCESm100(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden, weight, labels, ignore_index, chunk_size, w_bf16, engine, loss_scale, sink_dest):
+    def forward(ctx, hidden, weight, labels, ignore_index, chunk_size, w_bf16, engine, loss_scale, sink_dest,
+                normalizer=None):
         N, D = hidden.shape
         V = w_bf16.shape[0]   # a sharded strategy may have released the fp32 weight's own storage
         dev = hidden.device
         h = hidden if hidden.dtype == BF16 else hidden.to(BF16)
         h = h.contiguous()
-        n_valid = (labels != ignore_index).sum().clamp_min(1)
+        n_valid = (labels != ignore_index).sum().clamp_min(1) if normalizer is None else normalizer
         inv_n = (loss_scale / n_valid.float()).reshape(1)
         row_loss = torch.empty(N, dtype=torch.float32, device=dev)
         need_dh = ctx.needs_input_grad[0]
@@ -94,10 +95,10 @@ class _LinearCESm100(torch.autograd.Function):
             elif ctx.in_sink:
                 eng.model._grad_sink.grad_written(eng.model.lm_head.weight)
                 d_weight = None
-        return d_hidden, d_weight, None, None, None, None, None, None, None
+        return d_hidden, d_weight, None, None, None, None, None, None, None, None
 
 
-def linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size, loss_scale=1.0):
+def linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size, loss_scale=1.0, normalizer=None):
     from torchure_b200.ops.block import engine_for_weight
 
     eng = engine_for_weight(weight)
@@ -111,4 +112,4 @@ def linear_ce_sm100(hidden, weight, labels, ignore_index, chunk_size, loss_scale
     else:
         w_bf16 = K.cast_to_bf16(weight.detach().contiguous()) if weight.dtype != BF16 else weight.detach()
     return _LinearCESm100.apply(hidden, weight, labels, ignore_index, chunk_size, w_bf16, eng, float(loss_scale),
-                                sink_dest)
+                                sink_dest, normalizer)

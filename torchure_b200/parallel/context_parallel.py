@@ -141,41 +141,91 @@ def _ring_next(t: torch.Tensor, mesh, dim, side: torch.cuda.Stream) -> torch.Ten
     return out
 
 
+def ring_fwd_sm100(q2, q_col0, k2, v2, B, S2, Hq, Hkv, mesh, dim):
+    """Forward ring on the tcgen05 block-pair kernels.  q2: bf16 [B * S2, ld] whose head h sits at columns
+    [q_col0 + 128 h, ...) (any row stride: the q columns of a fused projection are used where they lie); k2 / v2:
+    contiguous bf16 [B * S2, Hkv * 128], this rank's chunks, which travel around the ring.  Returns the merged
+    output (bf16 [B * S2, Hq * 128]) and its log-sum-exp (fp32 [B, Hq, S2])."""
+    from torchure_b200 import ops
+
+    ext = ops.ext()
+    n, r = mesh.size(dim), mesh.coordinate(dim)
+    half = S2 // 2
+    dev = q2.device
+    out = torch.zeros(B * S2, Hq * 128, dtype=torch.float32, device=dev)
+    lse = torch.full((B, Hq, S2), float("-inf"), dtype=torch.float32, device=dev)
+    o_p = torch.empty(B * half, Hq * 128, dtype=torch.bfloat16, device=dev)
+    l_p = torch.empty(B, Hq, half, dtype=torch.float32, device=dev)
+    side = torch.cuda.Stream(device=dev)
+    kk, vv = k2, v2
+    for t in range(n):
+        src = (r - t) % n
+        nk = nv = None
+        if t + 1 < n:   # next step's K/V travel while this step's pairs run
+            nk, nv = _ring_next(kk, mesh, dim, side), _ring_next(vv, mesh, dim, side)
+        for qi, ki, causal in _pairs(r, src, n):
+            ext.attn_fwd_pair(q2, q_col0, kk, 0, vv, 0, o_p, l_p, B, half, half, Hq, Hkv, S2, qi * half, S2, ki * half,
+                              causal)
+            ext.attn_merge(out, lse, o_p, l_p, B, half, Hq, S2, qi * half)
+            ops.count_launch(2)
+        if nk is not None:
+            torch.cuda.current_stream().wait_stream(side)
+            kk, vv = nk, nv
+    return out.to(torch.bfloat16), lse
+
+
+def ring_bwd_sm100(q2, q_col0, k2, v2, o16, lse, do2, B, S2, Hq, Hkv, mesh, dim):
+    """Backward ring: one single-pass backward launch per block pair, all pairs adding into one head-major fp32 dQ
+    accumulator; the fp32 dK / dV accumulators travel with their K/V block and are home after n hops.  Returns
+    (dq_acc fp32 [B, Hq, S2, 128], dk fp32 [B, S2, Hkv * 128], dv likewise)."""
+    from torchure_b200 import ops
+
+    ext = ops.ext()
+    n, r = mesh.size(dim), mesh.coordinate(dim)
+    half = S2 // 2
+    dev = q2.device
+    nds = torch.empty(B, Hq, S2, dtype=torch.float32, device=dev)
+    nlse2 = torch.empty_like(nds)
+    dq_acc = torch.empty(B, Hq, S2, 128, dtype=torch.float32, device=dev)
+    ext.attn_bwd_stats(do2, o16, lse, nds, nlse2, dq_acc, B, S2, Hq)   # statistics of the MERGED result; clears dq_acc
+    ops.count_launch()
+    dk_acc = torch.zeros(B, S2, Hkv * 128, dtype=torch.float32, device=dev)
+    dv_acc = torch.zeros_like(dk_acc)
+    dk_p = torch.empty(B * half, Hkv * 128, dtype=torch.bfloat16, device=dev)
+    dv_p = torch.empty_like(dk_p)
+    kk, vv = k2, v2
+    side = torch.cuda.Stream(device=dev)
+    for t in range(n):
+        src = (r - t) % n
+        nk = nv = None
+        if t + 1 < n:
+            nk, nv = _ring_next(kk, mesh, dim, side), _ring_next(vv, mesh, dim, side)
+        for qi, ki, causal in _pairs(r, src, n):
+            ext.attn_bwd_pair(q2, q_col0, kk, 0, vv, 0, do2, dq_acc, dk_p, dv_p, nds, nlse2, B, half, half, Hq, Hkv,
+                              S2, qi * half, S2, ki * half, S2, qi * half, causal)
+            ops.count_launch()
+            ks = slice(ki * half, (ki + 1) * half)
+            dk_acc[:, ks] += dk_p.view(B, half, Hkv * 128)
+            dv_acc[:, ks] += dv_p.view(B, half, Hkv * 128)
+        # the gradient accumulators travel with their K/V block; after n hops they are home
+        dk_acc, dv_acc = ring_send_recv(dk_acc, mesh, dim), ring_send_recv(dv_acc, mesh, dim)
+        if nk is not None:
+            torch.cuda.current_stream().wait_stream(side)
+            kk, vv = nk, nv
+    return dq_acc, dk_acc, dv_acc
+
+
 class _RingAttentionSm100(torch.autograd.Function):
     """q (B, S2, Hq, 128), k / v (B, S2, Hkv, 128) bf16: this rank's two zigzag chunks, token-major."""
 
     @staticmethod
     def forward(ctx, q, k, v, mesh, dim):
-        from torchure_b200 import ops
-
-        ext = ops.ext()
-        n, r = mesh.size(dim), mesh.coordinate(dim)
         B, S2, Hq, hd = q.shape
         Hkv = k.shape[2]
-        half = S2 // 2
-        dev = q.device
         q2 = q.contiguous().view(B * S2, Hq * hd)
-        kk, vv = k.contiguous().view(B * S2, Hkv * hd), v.contiguous().view(B * S2, Hkv * hd)
-        out = torch.zeros(B * S2, Hq * hd, dtype=torch.float32, device=dev)
-        lse = torch.full((B, Hq, S2), float("-inf"), dtype=torch.float32, device=dev)
-        o_p = torch.empty(B * half, Hq * hd, dtype=torch.bfloat16, device=dev)
-        l_p = torch.empty(B, Hq, half, dtype=torch.float32, device=dev)
-        side = torch.cuda.Stream(device=dev)
-        for t in range(n):
-            src = (r - t) % n
-            nk = nv = None
-            if t + 1 < n:   # next step's K/V travel while this step's pairs run
-                nk, nv = _ring_next(kk, mesh, dim, side), _ring_next(vv, mesh, dim, side)
-            for qi, ki, causal in _pairs(r, src, n):
-                ext.attn_fwd_pair(q2, 0, kk, 0, vv, 0, o_p, l_p, B, half, half, Hq, Hkv, S2, qi * half, S2, ki * half,
-                                  causal)
-                ext.attn_merge(out, lse, o_p, l_p, B, half, Hq, S2, qi * half)
-                ops.count_launch(2)
-            if nk is not None:
-                torch.cuda.current_stream().wait_stream(side)
-                kk, vv = nk, nv
-        o16 = out.to(torch.bfloat16)
-        ctx.save_for_backward(q2, k.contiguous().view(B * S2, Hkv * hd), v.contiguous().view(B * S2, Hkv * hd), o16, lse)
+        k2, v2 = k.contiguous().view(B * S2, Hkv * hd), v.contiguous().view(B * S2, Hkv * hd)
+        o16, lse = ring_fwd_sm100(q2, 0, k2, v2, B, S2, Hq, Hkv, mesh, dim)
+        ctx.save_for_backward(q2, k2, v2, o16, lse)
         ctx.mesh, ctx.dim, ctx.dims = mesh, dim, (B, S2, Hq, Hkv, hd)
         return o16.view(B, S2, Hq, hd)
 
@@ -183,44 +233,13 @@ class _RingAttentionSm100(torch.autograd.Function):
     def backward(ctx, d_out):
         from torchure_b200 import ops
 
-        ext = ops.ext()
         q2, k2, v2, o16, lse = ctx.saved_tensors
-        mesh, dim = ctx.mesh, ctx.dim
         B, S2, Hq, Hkv, hd = ctx.dims
-        n, r = mesh.size(dim), mesh.coordinate(dim)
-        half = S2 // 2
-        dev = q2.device
         do2 = d_out.to(torch.bfloat16).contiguous().view(B * S2, Hq * hd)
-        nds = torch.empty(B, Hq, S2, dtype=torch.float32, device=dev)
-        nlse2 = torch.empty_like(nds)
-        dq_acc = torch.empty(B, Hq, S2, hd, dtype=torch.float32, device=dev)
-        ext.attn_bwd_stats(do2, o16, lse, nds, nlse2, dq_acc, B, S2, Hq)   # statistics of the MERGED result; clears dq_acc
-        dk_acc = torch.zeros(B, S2, Hkv * hd, dtype=torch.float32, device=dev)
-        dv_acc = torch.zeros_like(dk_acc)
-        dk_p = torch.empty(B * half, Hkv * hd, dtype=torch.bfloat16, device=dev)
-        dv_p = torch.empty_like(dk_p)
-        kk, vv = k2, v2
-        side = torch.cuda.Stream(device=dev)
-        for t in range(n):
-            src = (r - t) % n
-            nk = nv = None
-            if t + 1 < n:
-                nk, nv = _ring_next(kk, mesh, dim, side), _ring_next(vv, mesh, dim, side)
-            for qi, ki, causal in _pairs(r, src, n):
-                ext.attn_bwd_pair(q2, 0, kk, 0, vv, 0, do2, dq_acc, dk_p, dv_p, nds, nlse2, B, half, half, Hq, Hkv,
-                                  S2, qi * half, S2, ki * half, S2, qi * half, causal)
-                ops.count_launch()
-                ks = slice(ki * half, (ki + 1) * half)
-                dk_acc[:, ks] += dk_p.view(B, half, Hkv * hd)
-                dv_acc[:, ks] += dv_p.view(B, half, Hkv * hd)
-            # the gradient accumulators travel with their K/V block; after n hops they are home
-            dk_acc, dv_acc = ring_send_recv(dk_acc, mesh, dim), ring_send_recv(dv_acc, mesh, dim)
-            if nk is not None:
-                torch.cuda.current_stream().wait_stream(side)
-                kk, vv = nk, nv
-        dq = torch.empty(B * S2, Hq * hd, dtype=torch.bfloat16, device=dev)
-        ext.attn_dq_convert(dq_acc, dq, B, S2, Hq)
-        ops.count_launch(2)
+        dq_acc, dk_acc, dv_acc = ring_bwd_sm100(q2, 0, k2, v2, o16, lse, do2, B, S2, Hq, Hkv, ctx.mesh, ctx.dim)
+        dq = torch.empty(B * S2, Hq * hd, dtype=torch.bfloat16, device=q2.device)
+        ops.ext().attn_dq_convert(dq_acc, dq, B, S2, Hq)
+        ops.count_launch()
         return (dq.view(B, S2, Hq, hd), dk_acc.to(torch.bfloat16).view(B, S2, Hkv, hd),
                 dv_acc.to(torch.bfloat16).view(B, S2, Hkv, hd), None, None)
 

@@ -68,12 +68,20 @@ class Trainer:
         else:
             self.data_axis = data_axes[0]
         self.dp_size = self.mesh.size(self.data_axis)
+        # gradients (and the reported loss) are averaged over every replica of the parameters: the data axis and,
+        # under context parallelism, the ranks that hold the other chunks of the same sequences
+        self.cp_size = self.mesh.size("cp") if "cp" in self.mesh.axes() else 1
+        self.grad_axis = self.data_axis
+        if self.cp_size > 1:
+            assert data_axes == ("dp",) and "tp" not in self.mesh.axes(), "cp combines with plain dp only"
+            self.mesh.flatten(("dp", "cp"), "dp_cp")
+            self.grad_axis = "dp_cp"
         comm_cfg = self.config.get("comm", {})
         if self.on_gpu and comm_cfg.get("backend", "sm100") == "sm100":
             from torchure_b200 import ops
 
             if ops.available():
-                for axis in [self.data_axis] + [a for a in ("tp", "cp") if a in self.mesh.axes()]:
+                for axis in [self.grad_axis] + [a for a in ("tp",) if a in self.mesh.axes()]:
                     persistent = 0
                     if axis == "tp" and self.config.get("tp", {}).get("sequence_parallel", False):
                         # operands of the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels live in the axis'
@@ -103,7 +111,8 @@ class Trainer:
         self.num_train_steps = opt_cfg["scheduler"]["total_steps"]
         self.max_norm = opt_cfg.get("max_norm")
         self._wire_engine()
-        self.use_cuda_graph = bool(self.config.get("cuda_graph", False)) and self.on_gpu
+        # the ring exchange of context parallelism goes through library p2p calls on a side stream: not captured
+        self.use_cuda_graph = bool(self.config.get("cuda_graph", False)) and self.on_gpu and self.cp_size == 1
         self._graph = None
         self._graph_eager_left = int(self.config.get("cuda_graph_warmup", 3))
 
@@ -185,8 +194,16 @@ class Trainer:
             return model
         ddp_cfg = self.config.get("ddp", {})
         data_cfg = self.config["data"]
-        embed_tokens = data_cfg["micro_batch_size"] * data_cfg["seq_len"] if ddp_cfg.get("early_embedding", True) else 0
-        self.ddp = DDP(model, self.mesh, dim=self.data_axis, bucket_mb=ddp_cfg.get("bucket_mb", 25),
+        local_tokens = data_cfg["micro_batch_size"] * data_cfg["seq_len"] // self.cp_size
+        if self.cp_size > 1:
+            # every rank of the axis holds two zigzag chunks of each sequence; attention runs as a ring over the axis
+            # (on the tcgen05 block-pair kernels when a chunk is a multiple of 128 tokens and head_dim is 128)
+            model.cp = (self.mesh, "cp")
+            chunk = data_cfg["seq_len"] // (2 * self.cp_size)
+            if chunk % 128 != 0:
+                model.impl = "torch"
+        embed_tokens = local_tokens if ddp_cfg.get("early_embedding", True) else 0
+        self.ddp = DDP(model, self.mesh, dim=self.grad_axis, bucket_mb=ddp_cfg.get("bucket_mb", 25),
                        fused=ddp_cfg.get("fused"), merge_small=ddp_cfg.get("merge_small", True),
                        comm_sms=ddp_cfg.get("comm_sms", 16), sm_reserve=ddp_cfg.get("sm_reserve", 0),
                        embed_tokens=embed_tokens)
@@ -274,7 +291,8 @@ class Trainer:
                 "wandb_id": self.wandb_run.id if self.wandb_run else None,
             }, step)
         # the prefetcher knows the position of the first batch that was NOT consumed
-        self.checkpointer.save_dataloader(self.prefetcher, step, self.mesh.coordinate(self.data_axis))
+        if self.cp_size == 1 or self.mesh.coordinate("cp") == 0:    # the ranks of a cp group read the same rows
+            self.checkpointer.save_dataloader(self.prefetcher, step, self.mesh.coordinate(self.data_axis))
         barrier()
         if self.rank == 0:
             self.checkpointer.mark_complete(step)
@@ -391,8 +409,8 @@ class Trainer:
         else:
             loss, grad_norm = self._device_step()
         self.scheduler.step()
-        if self.dp_size > 1 and not getattr(self, "_loss_averaged", False):
-            all_reduce(loss, self.mesh, self.data_axis, "avg")
+        if self.mesh.size(self.grad_axis) > 1 and not getattr(self, "_loss_averaged", False):
+            all_reduce(loss, self.mesh, self.grad_axis, "avg")
         return {"loss": loss, "grad_norm": grad_norm}
 
     # -- CUDA-graph replay of the device step ----------------------------------------------------
