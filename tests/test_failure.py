@@ -92,6 +92,23 @@ def test_config_errors_are_loud():
     bad["mesh"]["tp"] = 2
     with pytest.raises(ConfigError):
         validate_config(bad, 2)
+    # context and pipeline parallelism: {"dp", "cp"} / {"dp", "pp"} in this order, chunks and stages that divide
+    validate_config(parity_config(1, mesh={"dp": 1, "cp": 2}), 2)
+    validate_config(parity_config(1, mesh={"dp": 1, "pp": 2}), 2)
+    for mesh in ({"cp": 2, "dp": 1}, {"dp": 1, "tp": 1, "cp": 2}, {"pp": 2, "dp": 1}):
+        with pytest.raises(ConfigError):
+            validate_config(parity_config(1, mesh=mesh), 2)
+    bad = parity_config(1, mesh={"dp": 1, "cp": 3})
+    bad["data"]["seq_len"] = 256            # not a multiple of 2 x 3 chunks
+    with pytest.raises(ConfigError):
+        validate_config(bad, 3)
+    bad = parity_config(1, mesh={"dp": 1, "pp": 8})     # four blocks
+    with pytest.raises(ConfigError):
+        validate_config(bad, 8)
+    bad = parity_config(1, mesh={"dp": 1, "pp": 2})
+    bad["pp"] = {"schedule": "zero-bubble"}
+    with pytest.raises(ConfigError):
+        validate_config(bad, 2)
 
 
 @pytest.mark.gpu

@@ -148,6 +148,84 @@ def test_context_parallel_trainer_matches_single_process(tmp_path):
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
 
 
+def _run_pp(rank, world, cfg, home, out, emulate_world):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    tr = Trainer(cfg, rank, rank, world, benchmark=True, device="cpu")
+    assert type(tr.model).__name__ == "PipelineStage" and tr.model.stages == cfg["mesh"]["pp"]
+    hist = tr.train_n_step_test(STEPS)
+    params = _weights(tr)          # the stage's tensors under the keys of the whole model
+    torch.save({"hist": hist, "params": params}, f"{out}.{rank}")
+
+
+def test_pipeline_trainer_matches_single_process(tmp_path, schedule="1f1b"):
+    """mesh {dp: 1, pp: 2}: two stages of two blocks, the tied embedding / head held by both (gradients summed,
+    values equal), four micro-batches per step through the schedule, the clip norm taken over both stages.  Loss,
+    gradient norm and the final weights of BOTH stages must follow the single-process run."""
+    one_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
+    run_distributed(_run, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), 0, timeout_s=240)
+    pp_cfg = parity_config(world=1, steps=STEPS, accumulation=4, mesh={"dp": 1, "pp": 2})
+    pp_cfg["pp"] = {"schedule": schedule}
+    run_distributed(_run_pp, 2, pp_cfg, str(tmp_path), str(tmp_path / "pp.pt"), 0, timeout_s=240)
+    one = torch.load(tmp_path / "one.pt")
+    parts = [torch.load(f"{tmp_path}/pp.pt.{r}") for r in range(2)]
+    assert "token_emb.weight" in parts[0]["params"] and "lm_head.weight" in parts[1]["params"]
+    assert "blocks.0.norm1.weight" in parts[0]["params"] and "blocks.3.norm1.weight" in parts[1]["params"]
+    merged = {**parts[0]["params"], **parts[1]["params"]}
+    # the whole model lists its tied tensor once, as the embedding; the last stage holds it as the head
+    assert torch.equal(parts[0]["params"]["token_emb.weight"], merged.pop("lm_head.weight"))
+    assert set(merged) == set(one["params"])
+    for part in parts:      # every stage reports the same loss and norm
+        assert [h["loss"] for h in part["hist"]] == [h["loss"] for h in parts[0]["hist"]]
+    _compare({"hist": parts[0]["hist"], "params": merged}, one)
+
+
+def test_pipeline_with_data_parallel_replicas(tmp_path):
+    """mesh {dp: 2, pp: 2} on four ranks (GPipe order) against one process fed the rows of both replicas."""
+    one_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
+    run_distributed(_run, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=240)
+    pp_cfg = parity_config(world=2, steps=STEPS, accumulation=2, mesh={"dp": 2, "pp": 2})
+    pp_cfg["pp"] = {"schedule": "gpipe"}
+    run_distributed(_run_pp, 4, pp_cfg, str(tmp_path), str(tmp_path / "pp.pt"), 0, timeout_s=300)
+    one = torch.load(tmp_path / "one.pt")
+    parts = [torch.load(f"{tmp_path}/pp.pt.{r}") for r in range(4)]    # ranks 0 / 1: stages 0 / 1 of replica 0
+    merged = {**parts[0]["params"], **parts[1]["params"]}
+    merged.pop("lm_head.weight")
+    _compare({"hist": parts[0]["hist"], "params": merged}, one)
+    for n, v in parts[2]["params"].items():
+        assert torch.equal(v, parts[0]["params"][n]), n      # the replicas stay identical
+
+
+def _run_pp_resume(rank, world, home, out):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    mesh = {"dp": 1, "pp": 2}
+    straight = Trainer(parity_config(1, steps=5, run_name="pp_straight", accumulation=2, mesh=mesh), rank, rank, world,
+                       device="cpu")
+    straight.train()
+    first = Trainer(parity_config(1, steps=5, run_name="pp_resumed", accumulation=2, save_steps=3, mesh=mesh), rank,
+                    rank, world, device="cpu")
+    first.num_train_steps = 3
+    first.train()
+    second = Trainer(parity_config(1, steps=5, run_name="pp_resumed", accumulation=2, resume="auto", save_steps=1000,
+                                   mesh=mesh), rank, rank, world, device="cpu")
+    assert second.start_step == 3
+    second.train()
+    torch.save({"a": _weights(straight), "b": _weights(second)}, f"{out}.{rank}")
+
+
+def test_pipeline_resume_is_exact(tmp_path):
+    run_distributed(_run_pp_resume, 2, str(tmp_path), str(tmp_path / "r.pt"), timeout_s=240)
+    for r in range(2):
+        got = torch.load(f"{tmp_path}/r.pt.{r}")
+        for n in got["a"]:
+            assert torch.equal(got["a"][n], got["b"][n]), n
+    files = sorted(os.listdir(tmp_path / "checkpoints" / "pp_resumed" / "3"))
+    assert "model_shard0.pt" in files and "model_shard1.pt" in files and "optimizer_shard1.pt" in files, files
+
+
 def _run_fsdp_resume(rank, world, home, out):
     os.environ["TORCHURE_B200_HOME"] = home
     from torchure_b200.train.trainer import Trainer

@@ -18,6 +18,7 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
     [ddp]         {bucket_mb, [fused], [merge_small], [comm_sms], [early_embedding]}
     [fsdp]        {[comm_sms]}
     [tp]          {[sequence_parallel]}
+    [pp]          {[schedule]: "1f1b" | "gpipe"}   with mesh {"dp": D, "pp": P}: contiguous stages of blocks
     [comm]        {backend: "sm100" | "torch", [max_bytes]}
     checkpointing {save_steps, resume: null|"auto"|int, [resume_scheduler]}
     run_name      str
@@ -69,6 +70,13 @@ def validate_config(cfg: dict, world_size: int | None = None) -> dict:
             raise ConfigError('context parallelism is selected by mesh {"dp": D, "cp": C} (in this order, no other axis)')
         if cfg.get("data", {}).get("seq_len", 0) % (2 * mesh["cp"]) != 0:
             raise ConfigError(f"seq_len must be a multiple of 2 x cp = {2 * mesh['cp']} (zigzag chunks)")
+    if mesh.get("pp", 1) > 1:
+        if list(mesh)[: 2] != ["dp", "pp"] or len(mesh) != 2:
+            raise ConfigError('pipeline parallelism is selected by mesh {"dp": D, "pp": P} (in this order, no other axis)')
+        if cfg["model"]["config"].get("num_layers", mesh["pp"]) < mesh["pp"]:
+            raise ConfigError("more pipeline stages than transformer blocks")
+        if cfg.get("pp", {}).get("schedule", "1f1b") not in ("1f1b", "gpipe"):
+            raise ConfigError('pp.schedule must be "1f1b" or "gpipe"')
     if world_size is not None and math.prod(mesh.values()) != world_size:
         raise ConfigError(f"mesh {mesh} does not cover world size {world_size}")
     opt = cfg["optimizer"]

@@ -28,6 +28,14 @@ class ARObjective:
         loss = cross_entropy_loss(batch["labels"], logits, self.ignore_index)
         return loss if loss_scale == 1.0 else loss * loss_scale
 
+    def loss_from_output(self, out: torch.Tensor, head_weight: torch.Tensor, label_ids: torch.Tensor) -> torch.Tensor:
+        """Mean next-token CE from what the last pipeline stage produced: the normalised hidden state when the head
+        is fused into the loss (``fused_linear_ce``), logits otherwise."""
+        if self.fused_linear_ce:
+            labels = shift_labels(label_ids, self.ignore_index)
+            return fused_linear_cross_entropy(out, head_weight, labels, self.ignore_index, self.ce_chunk_size)
+        return cross_entropy_loss(label_ids, out, self.ignore_index)
+
     def _compute_loss_cp(self, model, batch, loss_scale, mesh, dim) -> torch.Tensor:
         """Context parallelism: every rank of the axis receives the whole batch, keeps its two zigzag chunks of every
         sequence (tokens and the already shifted targets) and divides its summed loss by 1/n of the GLOBAL target

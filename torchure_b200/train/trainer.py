@@ -71,6 +71,7 @@ class Trainer:
         # gradients (and the reported loss) are averaged over every replica of the parameters: the data axis and,
         # under context parallelism, the ranks that hold the other chunks of the same sequences
         self.cp_size = self.mesh.size("cp") if "cp" in self.mesh.axes() else 1
+        self.pp_size = self.mesh.size("pp") if "pp" in self.mesh.axes() else 1
         self.grad_axis = self.data_axis
         if self.cp_size > 1:
             assert data_axes == ("dp",) and "tp" not in self.mesh.axes(), "cp combines with plain dp only"
@@ -112,7 +113,8 @@ class Trainer:
         self.max_norm = opt_cfg.get("max_norm")
         self._wire_engine()
         # the ring exchange of context parallelism goes through library p2p calls on a side stream: not captured
-        self.use_cuda_graph = bool(self.config.get("cuda_graph", False)) and self.on_gpu and self.cp_size == 1
+        self.use_cuda_graph = (bool(self.config.get("cuda_graph", False)) and self.on_gpu and self.cp_size == 1
+                               and self.pp_size == 1)
         self._graph = None
         self._graph_eager_left = int(self.config.get("cuda_graph_warmup", 3))
 
@@ -167,6 +169,20 @@ class Trainer:
         self._opt_params = None
         self.sharded = "dp_shard" in axes
         self.tp_size = self.mesh.size("tp") if "tp" in axes else 1
+        if self.pp_size > 1:
+            # every rank built the whole model from the same seed and keeps its stage: contiguous blocks, the first
+            # stage also the embedding, the last the final norm and the head.  Stages run the PyTorch blocks; their
+            # replicas along "dp" are averaged by the bucketed reducer
+            from torchure_b200.parallel.pipeline import PipelineStage
+
+            assert not self.sharded and self.tp_size == 1 and self.cp_size == 1, "pp combines with plain dp only"
+            model.impl = "torch"
+            stage = PipelineStage(model, self.mesh, "pp")
+            stage.sync_tied_weight()
+            ddp_cfg = self.config.get("ddp", {})
+            self.ddp = DDP(stage, self.mesh, dim=self.data_axis, bucket_mb=ddp_cfg.get("bucket_mb", 25), fused=False,
+                           merge_small=ddp_cfg.get("merge_small", True))
+            return stage
         assert not (self.sharded and self.tp_size > 1), "dp_shard and tp cannot be combined yet"
         if "tp" in axes and self.mesh.size("tp") > 1:
             from torchure_b200.parallel.tensor_parallel import parallelize_model
@@ -271,13 +287,14 @@ class Trainer:
             del full
             if "dp_replicate" not in self.mesh.axes() or self.mesh.coordinate("dp_replicate") == 0:
                 self.checkpointer.save_optimizer(self.optimizer, step, shard=self.mesh.coordinate("dp_shard"))
-        elif self.tp_size > 1:
-            # every tensor-parallel coordinate holds different rows / columns: one file pair per coordinate, written
-            # by the first data-parallel replica
+        elif self.tp_size > 1 or self.pp_size > 1:
+            # every tensor-parallel coordinate holds different rows / columns, every pipeline stage different blocks
+            # (under the keys of the whole model): one file pair per coordinate, written by the first data-parallel
+            # replica
             if self.mesh.coordinate(self.data_axis) == 0:
-                tp = self.mesh.coordinate("tp")
-                self.checkpointer.save_model(self.model, step, shard=tp)
-                self.checkpointer.save_optimizer(self.optimizer, step, shard=tp)
+                shard = self.mesh.coordinate("tp" if self.tp_size > 1 else "pp")
+                self.checkpointer.save_model(self.model, step, shard=shard)
+                self.checkpointer.save_optimizer(self.optimizer, step, shard=shard)
         elif self.rank == 0:
             self.checkpointer.save_model(self.model, step)
             self.checkpointer.save_optimizer(self.optimizer, step)
@@ -291,7 +308,8 @@ class Trainer:
                 "wandb_id": self.wandb_run.id if self.wandb_run else None,
             }, step)
         # the prefetcher knows the position of the first batch that was NOT consumed
-        if self.cp_size == 1 or self.mesh.coordinate("cp") == 0:    # the ranks of a cp group read the same rows
+        if all(self.mesh.coordinate(a) == 0 for a in ("cp", "pp") if a in self.mesh.axes()):
+            # (the ranks of a cp group, and the stages of a pipeline, read the same rows)
             self.checkpointer.save_dataloader(self.prefetcher, step, self.mesh.coordinate(self.data_axis))
         barrier()
         if self.rank == 0:
@@ -315,10 +333,10 @@ class Trainer:
         if self.sharded:
             self.ddp.load_full_state_dict(self.checkpointer._read(step, "model.pt"))
             self.checkpointer.load_optimizer(self.optimizer, step, shard=self.mesh.coordinate("dp_shard"))
-        elif self.tp_size > 1:
-            tp = self.mesh.coordinate("tp")
-            self.checkpointer.load_model(self.model, step, shard=tp)
-            self.checkpointer.load_optimizer(self.optimizer, step, shard=tp)
+        elif self.tp_size > 1 or self.pp_size > 1:
+            shard = self.mesh.coordinate("tp" if self.tp_size > 1 else "pp")
+            self.checkpointer.load_model(self.model, step, shard=shard)
+            self.checkpointer.load_optimizer(self.optimizer, step, shard=shard)
         else:
             self.checkpointer.load_model(self.model, step)
             self.checkpointer.load_optimizer(self.optimizer, step)
@@ -349,6 +367,8 @@ class Trainer:
     def _device_step(self, batches=None) -> tuple[torch.Tensor, torch.Tensor]:
         """Everything of one optimizer step that runs on the device: micro-batches, gradient reduction, clipping,
         AdamW.  `batches` (one dict per micro-batch) are used instead of the prefetcher when given."""
+        if self.pp_size > 1:
+            return self._pipeline_step(batches)
         K = self.microbatches_per_step
         slot = self.ddp.loss_slot() if hasattr(self.ddp, "loss_slot") else None
         if slot is not None:
@@ -390,6 +410,49 @@ class Trainer:
         if slot is not None:
             self.ddp.reducer.comm.all_reduce_symmetric_(slot, "avg", blocks=1)
             loss = slot[0].clone()
+        return loss, grad_norm
+
+    def _pipeline_step(self, batches=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """One optimizer step of a pipeline stage: the step's micro-batches run through the schedule
+        (``pp.schedule``: "1f1b" or "gpipe"), activations and their gradients moving between neighbouring stages;
+        the stage's replicas along "dp" reduce their gradients during the last micro-batch's backward; the two
+        holders of a tied embedding / head sum their gradients; the clip norm is taken over all stages."""
+        from contextlib import nullcontext
+
+        from torchure_b200.core.grad_helper import _collect, _total_norm
+        from torchure_b200.parallel.pipeline import run_schedule
+
+        K = self.microbatches_per_step
+        fetched = batches if batches else [next(self.prefetcher) for _ in range(K)]
+        micro = [(b["input_ids"], b["labels"]) for b in fetched]
+        stage, obj = self.model, self.objective
+        fused_ce = getattr(obj, "fused_linear_ce", False)
+
+        def loss_fn(out, label_ids):
+            return obj.loss_from_output(out, stage.lm_head.weight, label_ids)
+
+        def last_backward():
+            self.ddp.requires_sync = True
+
+        self.ddp.requires_sync = K == 1
+        cast = torch.autocast(device_type="cuda", dtype=torch.bfloat16) if self.on_gpu else nullcontext()
+        with cast:
+            loss = run_schedule(stage, micro, loss_fn, self.config.get("pp", {}).get("schedule", "1f1b"),
+                                before_last_backward=last_backward, final_hidden=fused_ce)
+        self.ddp.requires_sync = True
+        self.ddp.sync()
+        stage.sync_tied_grad()
+        if loss is None:
+            loss = torch.zeros((), device=self.device)
+        loss = loss.float().reshape(())
+        all_reduce(loss, self.mesh, "pp", "sum")       # the last stage has it; every stage reports it
+        grads = _collect(stage.parameters())
+        grad_norm = _total_norm(_collect(stage.norm_params()), self.mesh, ("pp",))
+        if self.max_norm is not None:
+            torch._foreach_mul_(grads, torch.clamp(self.max_norm / (grad_norm + 1e-6), max=1.0))
+        self.optimizer.step()
+        self.optimizer.zero_grad()
+        self._loss_averaged = False
         return loss, grad_norm
 
     def _tp_sq_norm(self, params) -> torch.Tensor:
