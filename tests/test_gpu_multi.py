@@ -540,6 +540,31 @@ def test_trainer_context_parallel_on_engine(tmp_path):
         assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
 
 
+def _trainer_pp(rank, world, home, out):
+    """Pipeline parallelism through the Trainer on GPUs (mesh {dp: 1, pp: world}): stages of PyTorch blocks under
+    autocast, activations and their gradients over library p2p, two micro-batches per step through 1F1B."""
+    import os
+
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    cfg = _trainer_cfg({"dp": 1, "pp": world}, "t_pp", 4, graph=False)
+    tr = Trainer(cfg, rank, rank, world, benchmark=True)
+    assert type(tr.model).__name__ == "PipelineStage" and tr.microbatches_per_step == 2
+    hist = tr.train_n_step_test(6)
+    if rank == 0:
+        torch.save(hist, out)
+
+
+def test_trainer_pipeline_on_gpus(tmp_path):
+    run_on_gpus(_trainer_pp, 2, str(tmp_path), str(tmp_path / "pp.pt"), timeout_s=240)
+    run_on_gpus(_trainer_vs_single_cfg, 1, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
+    pp, one = torch.load(tmp_path / "pp.pt"), torch.load(tmp_path / "one.pt")
+    for x, y in zip(pp, one):
+        assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
+
+
 def _trainer_vs_single_cfg(rank, world, home, out):
     import os
 
