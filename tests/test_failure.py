@@ -102,6 +102,10 @@ def test_config_errors_are_loud():
     bad["data"]["seq_len"] = 256            # not a multiple of 2 x 3 chunks
     with pytest.raises(ConfigError):
         validate_config(bad, 3)
+    bad = parity_config(1, mesh={"dp": 1, "cp": 4})     # two KV heads cannot be split four ways
+    bad["cp"] = {"kind": "ulysses"}
+    with pytest.raises(ConfigError):
+        validate_config(bad, 4)
     bad = parity_config(1, mesh={"dp": 1, "pp": 8})     # four blocks
     with pytest.raises(ConfigError):
         validate_config(bad, 8)

@@ -506,7 +506,7 @@ def test_trainer_tensor_parallel_on_engine(tmp_path):
         assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
 
 
-def _trainer_cp(rank, world, home, out):
+def _trainer_cp(rank, world, home, out, kind="ring"):
     """Context parallelism on the sm_100a engine through the Trainer (mesh {dp: 1, cp: world}, or one GPU for the
     comparison): sequences of 512 tokens, so every zigzag chunk is one 128-token block of the pair kernels."""
     import os
@@ -515,12 +515,14 @@ def _trainer_cp(rank, world, home, out):
     from torchure_b200.train.trainer import Trainer
 
     mesh = {"dp": 1, "cp": world} if world > 1 else {"dp": 1}
-    cfg = _trainer_cfg(mesh, f"t_cp{world}", 4, graph=False)
+    cfg = _trainer_cfg(mesh, f"t_cp{world}{kind}", 4, graph=False)
     cfg["data"]["seq_len"] = 128 * 2 * 2
+    cfg["cp"] = {"kind": kind}
     tr = Trainer(cfg, rank, rank, world, benchmark=True)
-    assert tr.model.impl != "torch"
     if world > 1:
-        assert tr.model.cp is not None and tr.model.engine().cp is not None
+        assert tr.model.cp is not None
+        if kind == "ring":
+            assert tr.model.impl != "torch" and tr.model.engine().cp is not None
         seen = []
         tr.model.register_forward_pre_hook(lambda mod, args: seen.append(tuple(args[0].shape)))
     hist = tr.train_n_step_test(6)
@@ -532,12 +534,16 @@ def _trainer_cp(rank, world, home, out):
 
 
 def test_trainer_context_parallel_on_engine(tmp_path):
+    """Ring attention inside the engine, and Ulysses (`cp.kind`) on the module path with the attention kernels
+    between its all-to-alls, against one GPU."""
     run_on_gpus(_trainer_cp, 2, str(tmp_path), str(tmp_path / "cp.pt"), timeout_s=240)
+    run_on_gpus(_trainer_cp, 2, str(tmp_path), str(tmp_path / "ul.pt"), "ulysses", timeout_s=240)
     run_on_gpus(_trainer_cp, 1, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
-    cp, one = torch.load(tmp_path / "cp.pt"), torch.load(tmp_path / "one.pt")
-    for x, y in zip(cp, one):
-        assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)
-        assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
+    one = torch.load(tmp_path / "one.pt")
+    for got in (torch.load(tmp_path / "cp.pt"), torch.load(tmp_path / "ul.pt")):
+        for x, y in zip(got, one):
+            assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)
+            assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
 
 
 def _trainer_pp(rank, world, home, out):

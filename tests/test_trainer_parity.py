@@ -148,6 +148,22 @@ def test_context_parallel_trainer_matches_single_process(tmp_path):
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
 
 
+def test_ulysses_trainer_matches_single_process(tmp_path):
+    """mesh {dp: 1, cp: 2} with `cp.kind: "ulysses"`: contiguous halves of every sequence, all heads of the half
+    exchanged for half of the heads of the whole sequence around attention."""
+    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
+    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
+    u_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "cp": 2})
+    u_cfg["cp"] = {"kind": "ulysses"}
+    run_distributed(_run_hist_only, 2, u_cfg, str(tmp_path), str(tmp_path / "u.pt"), timeout_s=240)
+    a, b = torch.load(tmp_path / "u.pt"), torch.load(tmp_path / "one.pt")
+    d = u_cfg["data"]
+    assert a["input_shapes"] == [(d["micro_batch_size"], d["seq_len"] // 2)], a["input_shapes"]
+    for x, y in zip(a["hist"], b["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
+
+
 def _run_pp(rank, world, cfg, home, out, emulate_world):
     os.environ["TORCHURE_B200_HOME"] = home
     from torchure_b200.train.trainer import Trainer

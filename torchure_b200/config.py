@@ -18,6 +18,8 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
     [ddp]         {bucket_mb, [fused], [merge_small], [comm_sms], [early_embedding]}
     [fsdp]        {[comm_sms]}
     [tp]          {[sequence_parallel]}
+    [cp]          {[kind]: "ring" | "ulysses"}     with mesh {"dp": D, "cp": C}: zigzag ring attention, or heads <->
+                  sequence all-to-alls around whole-sequence attention
     [pp]          {[schedule]: "1f1b" | "gpipe"}   with mesh {"dp": D, "pp": P}: contiguous stages of blocks
     [comm]        {backend: "sm100" | "torch", [max_bytes]}
     checkpointing {save_steps, resume: null|"auto"|int, [resume_scheduler]}
@@ -70,6 +72,11 @@ def validate_config(cfg: dict, world_size: int | None = None) -> dict:
             raise ConfigError('context parallelism is selected by mesh {"dp": D, "cp": C} (in this order, no other axis)')
         if cfg.get("data", {}).get("seq_len", 0) % (2 * mesh["cp"]) != 0:
             raise ConfigError(f"seq_len must be a multiple of 2 x cp = {2 * mesh['cp']} (zigzag chunks)")
+        kind = cfg.get("cp", {}).get("kind", "ring")
+        if kind not in ("ring", "ulysses"):
+            raise ConfigError('cp.kind must be "ring" or "ulysses"')
+        if kind == "ulysses" and cfg["model"]["config"].get("num_kv_heads", mesh["cp"]) % mesh["cp"] != 0:
+            raise ConfigError("Ulysses needs the number of KV heads to be a multiple of cp")
     if mesh.get("pp", 1) > 1:
         if list(mesh)[: 2] != ["dp", "pp"] or len(mesh) != 2:
             raise ConfigError('pipeline parallelism is selected by mesh {"dp": D, "pp": P} (in this order, no other axis)')

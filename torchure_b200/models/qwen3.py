@@ -124,11 +124,12 @@ class GroupQueryAttention(nn.Module):
             self.q_norm = RMSNorm(self.head_dim, norm_eps)
             self.k_norm = RMSNorm(self.head_dim, norm_eps)
 
-    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None, cp=None):
+    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None, cp=None, cp_kind="ring"):
         # `batch_shape` = (B, S) under sequence parallelism: x is then this rank's slice of the B * S tokens laid out
         # as one row sequence [1, B * S / n, D], which the column-parallel projections gather.
-        # `cp` = (mesh, axis) under context parallelism: x holds this rank's two zigzag chunks of every sequence and
-        # cos / sin their global positions; attention runs as a ring over the axis.
+        # `cp` = (mesh, axis) under context parallelism: x holds this rank's part of every sequence and cos / sin its
+        # global positions; attention runs as a ring over the axis (two zigzag chunks per rank), or, `cp_kind`
+        # "ulysses", on whole sequences of 1/n of the heads between two all-to-alls (one contiguous chunk per rank).
         q = self.q_proj(x)
         B, S = batch_shape if batch_shape is not None else (x.shape[0], q.shape[1])
         q = q.view(B, S, self.num_heads, self.head_dim).transpose(1, 2)
@@ -141,6 +142,11 @@ class GroupQueryAttention(nn.Module):
             from torchure_b200.parallel.context_parallel import ring_attention
 
             assert attention_mask is None, "context parallelism: causal path only"
+            if cp_kind == "ulysses":
+                from torchure_b200.parallel.ulysses import ulysses_attention
+
+                o = ulysses_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), *cp).to(v.dtype)
+                return self.o_proj(o.reshape(B, S, self.num_heads * self.head_dim))
             o = ring_attention(q, k, v, *cp).to(v.dtype)
             return self.o_proj(o.transpose(1, 2).reshape(B, S, self.num_heads * self.head_dim))
         rep = self.num_heads // self.num_kv_heads
@@ -181,8 +187,8 @@ class TransformerBlock(nn.Module):
         self.norm2 = RMSNorm(emb_dim, norm_eps)
         self.ffn = SwiGLU(emb_dim, ffn_dim if ffn_dim is not None else default_ffn_dim(emb_dim))
 
-    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None, cp=None):
-        x = x + self.gqa(self.norm1(x), cos, sin, attention_mask, batch_shape, cp)
+    def forward(self, x, cos, sin, attention_mask=None, batch_shape=None, cp=None, cp_kind="ring"):
+        x = x + self.gqa(self.norm1(x), cos, sin, attention_mask, batch_shape, cp, cp_kind)
         return x + self.ffn(self.norm2(x))
 
 
@@ -279,7 +285,11 @@ class Qwen3(nn.Module):
         cp = getattr(self, "cp", None)      # (mesh, axis): x holds this rank's zigzag chunks of sequences n times longer
         if cp is not None:
             assert attention_mask is None and not return_hidden_states, "context parallelism: causal path only"
-            cos, sin = self.rope.zigzag_tables(S, cp[0].size(cp[1]), cp[0].coordinate(cp[1]), x.device)
+            n, r = cp[0].size(cp[1]), cp[0].coordinate(cp[1])
+            if getattr(self, "cp_kind", "ring") == "ulysses":
+                cos, sin = (t[r * S:(r + 1) * S] for t in self.rope.tables(S * n, x.device))
+            else:
+                cos, sin = self.rope.zigzag_tables(S, n, r, x.device)
             cos, sin = cos[None, None], sin[None, None]
         elif attention_mask is None:
             cos, sin = self.rope.tables(S, x.device)
@@ -301,7 +311,7 @@ class Qwen3(nn.Module):
             if sp is not None:
                 h = block(h, cos, sin, attention_mask, (B, S))
             elif cp is not None:
-                h = block(h, cos, sin, None, None, cp)
+                h = block(h, cos, sin, None, None, cp, getattr(self, "cp_kind", "ring"))
             else:
                 h = block(h, cos, sin, attention_mask)
             if return_hidden_states:

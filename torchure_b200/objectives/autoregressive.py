@@ -37,8 +37,9 @@ class ARObjective:
         return cross_entropy_loss(label_ids, out, self.ignore_index)
 
     def _compute_loss_cp(self, model, batch, loss_scale, mesh, dim) -> torch.Tensor:
-        """Context parallelism: every rank of the axis receives the whole batch, keeps its two zigzag chunks of every
-        sequence (tokens and the already shifted targets) and divides its summed loss by 1/n of the GLOBAL target
+        """Context parallelism: every rank of the axis receives the whole batch, keeps its part of every sequence
+        (two zigzag chunks for ring attention, one contiguous chunk for Ulysses; tokens and the already shifted
+        targets alike) and divides its summed loss by 1/n of the GLOBAL target
         count, so that the average over the axis (which the gradient reduction takes anyway) is the mean over all
         targets whatever the chunks' own counts are."""
         import torch.nn.functional as F
@@ -48,8 +49,10 @@ class ARObjective:
         n, r = mesh.size(dim), mesh.coordinate(dim)
         full = shift_labels(batch["labels"], self.ignore_index)
         normalizer = (full != self.ignore_index).sum().clamp_min(1).float() / n
-        ids = zigzag_split(batch["input_ids"], n, r).contiguous()
-        labels = zigzag_split(full, n, r).contiguous()
+        if getattr(model, "cp_kind", "ring") == "ulysses":
+            ids, labels = batch["input_ids"].chunk(n, dim=1)[r].contiguous(), full.chunk(n, dim=1)[r].contiguous()
+        else:
+            ids, labels = zigzag_split(batch["input_ids"], n, r).contiguous(), zigzag_split(full, n, r).contiguous()
         if self.fused_linear_ce:
             hidden = model(ids, return_final_hidden=True)
             return fused_linear_cross_entropy(hidden, model.lm_head.weight, labels, self.ignore_index,

@@ -82,7 +82,10 @@ class Trainer:
             from torchure_b200 import ops
 
             if ops.available():
-                for axis in [self.grad_axis] + [a for a in ("tp",) if a in self.mesh.axes()]:
+                axes = [self.grad_axis] + [a for a in ("tp",) if a in self.mesh.axes()]
+                if self.cp_size > 1 and self.config.get("cp", {}).get("kind", "ring") == "ulysses":
+                    axes.append("cp")       # the two all-to-alls around attention run on the NVLink kernel
+                for axis in axes:
                     persistent = 0
                     if axis == "tp" and self.config.get("tp", {}).get("sequence_parallel", False):
                         # operands of the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels live in the axis'
@@ -215,8 +218,11 @@ class Trainer:
             # every rank of the axis holds two zigzag chunks of each sequence; attention runs as a ring over the axis
             # (on the tcgen05 block-pair kernels when a chunk is a multiple of 128 tokens and head_dim is 128)
             model.cp = (self.mesh, "cp")
+            model.cp_kind = self.config.get("cp", {}).get("kind", "ring")
             chunk = data_cfg["seq_len"] // (2 * self.cp_size)
-            if chunk % 128 != 0:
+            if chunk % 128 != 0 or model.cp_kind == "ulysses":
+                # Ulysses (`cp.kind`: one contiguous chunk per rank, heads exchanged for sequence around attention)
+                # runs the module path: its attention between the two all-to-alls is still the tcgen05 kernel
                 model.impl = "torch"
         embed_tokens = local_tokens if ddp_cfg.get("early_embedding", True) else 0
         self.ddp = DDP(model, self.mesh, dim=self.grad_axis, bucket_mb=ddp_cfg.get("bucket_mb", 25),
