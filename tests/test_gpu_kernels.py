@@ -213,6 +213,43 @@ def test_ce_softmax_grad(C, V):
     assert work[labels == -100].abs().sum() == 0
 
 
+@pytest.mark.parametrize("C,V,shards", [(64, 1024, 2), (300, 5000, 2), (256, 151936, 4)])
+def test_ce_vocabulary_sharded_passes(C, V, shards):
+    """The two passes of the loss-parallel CE on column shards of one logits matrix (what the ranks of a
+    tensor-parallel axis hold): row statistics per shard, combined as the ranks' all-reduces would, must give the
+    log-sum-exp and target logit of the whole row; the gradient pass must give (softmax - onehot) / n."""
+    from torchure_b200.ops import kernels
+
+    torch.manual_seed(0)
+    logits = (torch.randn(C, V, device="cuda") * 2).bfloat16()
+    labels = torch.randint(0, V, (C,), device="cuda")
+    labels[torch.rand(C, device="cuda") < 0.1] = -100
+    keep = labels != -100
+    inv = (1.0 / keep.sum().clamp_min(1)).float().reshape(1)
+    la = logits.float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(la, labels, ignore_index=-100, reduction="sum")
+    ref.backward()
+    per = V // shards
+    parts = [logits[:, r * per:(r + 1) * per].contiguous() for r in range(shards)]
+    stats = [torch.empty(3, C, device="cuda") for _ in range(shards)]
+    for r in range(shards):
+        kernels.ce_row_stats_(parts[r], labels, stats[r], r * per, -100)
+    mx = torch.stack([s[0] for s in stats]).max(dim=0).values
+    sumexp = sum(s[1] * torch.exp(s[0] - mx) for s in stats)
+    tgt = sum(s[2] for s in stats)
+    lse = mx + torch.log(sumexp)
+    torch.testing.assert_close(lse, torch.logsumexp(logits.float(), dim=-1), rtol=1e-5, atol=1e-4)
+    want_tgt = logits.float().gather(1, labels.clamp_min(0)[:, None]).squeeze(1) * keep
+    torch.testing.assert_close(tgt, want_tgt, rtol=0, atol=0)
+    torch.testing.assert_close(((lse - tgt) * keep).sum(), ref.detach(), rtol=1e-4, atol=1e-3)
+    for r in range(shards):
+        kernels.ce_grad_from_lse_(parts[r], labels, lse, inv, r * per, -100)
+        want = la.grad[:, r * per:(r + 1) * per] * inv
+        assert relerr(parts[r], want) < 8e-3, r
+        assert parts[r][~keep].abs().sum() == 0
+    kernels.check_error()
+
+
 def test_multi_tensor_adamw_norm_scale():
     from torchure_b200.ops import multi_tensor, oracle
 

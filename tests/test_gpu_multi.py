@@ -546,6 +546,64 @@ def test_trainer_context_parallel_on_engine(tmp_path):
             assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
 
 
+def _loss_parallel(rank, world, home, out):
+    """The loss-parallel fused linear + CE on the kernels (each rank: V / world rows of the head, statistics ->
+    two all-reduces -> gradient per chunk) against the unsharded kernel path on the same inputs, then through the
+    Trainer (mesh {dp: 1, tp: world}, `tp.loss_parallel`)."""
+    import os
+
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.core import collective as C
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.loss import fused_linear_cross_entropy
+    from torchure_b200.ops import kernels
+    from torchure_b200.train.trainer import Trainer
+
+    mesh = Mesh({"tp": world})
+    C.enable_sm100(mesh, "tp", 64 << 20)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    N, D, V = 700, 512, 4096
+    h = torch.randn(N, D, device="cuda", generator=g).bfloat16()
+    w = torch.randn(V, D, device="cuda", generator=g) * 0.05
+    y = torch.randint(0, V, (N,), device="cuda", generator=g)
+    y[::7] = -100
+    h1, w1 = h.clone().requires_grad_(), w.clone().requires_grad_()
+    want = fused_linear_cross_entropy(h1, w1, y, -100, 256)
+    want.backward()
+    h2, w2 = h.clone().requires_grad_(), w.clone().requires_grad_()
+    got = fused_linear_cross_entropy(h2, w2, y, -100, 256, vocab_parallel=(mesh, "tp"))
+    got.backward()
+    kernels.check_error()
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+    assert abs(got.item() - want.item()) < 1e-3 * abs(want.item()), (got.item(), want.item())
+    assert rel(h2.grad, h1.grad) < 1e-2
+    lo, hi = rank * V // world, (rank + 1) * V // world
+    assert rel(w2.grad[lo:hi], w1.grad[lo:hi]) < 1e-2
+    assert w2.grad[:lo].abs().sum() == 0 and w2.grad[hi:].abs().sum() == 0
+    del mesh
+
+    cfg = _trainer_cfg({"dp": 1, "tp": world}, "t_lp", 4, graph=False)
+    cfg["tp"] = {"loss_parallel": True}
+    tr = Trainer(cfg, rank, rank, world, benchmark=True)
+    assert tr.model.vocab_parallel is not None and tr.model.impl != "torch"
+    hist = tr.train_n_step_test(6)
+    tr.check_device_errors()
+    if rank == 0:
+        torch.save(hist, out)
+
+
+def test_loss_parallel_on_engine(tmp_path):
+    run_on_gpus(_loss_parallel, 2, str(tmp_path), str(tmp_path / "lp.pt"), timeout_s=240)
+    run_on_gpus(_trainer_vs_single_cfg, 1, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
+    lp, one = torch.load(tmp_path / "lp.pt"), torch.load(tmp_path / "one.pt")
+    for x, y in zip(lp, one):
+        assert abs(x["loss"] - y["loss"]) < 5e-3 * abs(y["loss"]), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 3e-2 * abs(y["grad_norm"]), (x, y)
+
+
 def _trainer_pp(rank, world, home, out):
     """Pipeline parallelism through the Trainer on GPUs (mesh {dp: 1, pp: world}): stages of PyTorch blocks under
     autocast, activations and their gradients over library p2p, two micro-batches per step through 1F1B."""

@@ -108,6 +108,26 @@ def _tp(rank, world):
     want.backward()
     torch.testing.assert_close(loss, want.detach(), rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(local.grad, logits.grad[:, rank * V // world:(rank + 1) * V // world], rtol=1e-5, atol=1e-7)
+    # the same inside the chunked fused linear + CE: every rank computes its V / tp rows of the head, two small
+    # all-reduces per chunk; loss and dL/dhidden complete everywhere, dL/dweight complete in the rank's rows
+    from torchure_b200.loss import fused_linear_cross_entropy
+
+    g = torch.Generator().manual_seed(5)
+    h = torch.randn(37, 16, generator=g)
+    w = torch.randn(V, 16, generator=g) * 0.3
+    y = torch.randint(0, V, (37,), generator=g)
+    y[::5] = -100
+    h1, w1 = h.clone().requires_grad_(), w.clone().requires_grad_()
+    want = fused_linear_cross_entropy(h1, w1, y, -100, 8)
+    want.backward()
+    h2, w2 = h.clone().requires_grad_(), w.clone().requires_grad_()
+    got = fused_linear_cross_entropy(h2, w2, y, -100, 8, vocab_parallel=(mesh, "tp"))
+    got.backward()
+    torch.testing.assert_close(got, want.detach(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(h2.grad, h1.grad, rtol=1e-5, atol=1e-7)
+    lo, hi = rank * V // world, (rank + 1) * V // world
+    torch.testing.assert_close(w2.grad[lo:hi], w1.grad[lo:hi], rtol=1e-5, atol=1e-7)
+    assert w2.grad[:lo].abs().sum() == 0 and w2.grad[hi:].abs().sum() == 0
 
 
 def test_tensor_parallel_and_vocab_parallel_ce():

@@ -95,6 +95,7 @@ def _run_hist_only(rank, world, cfg, home, out):
     from torchure_b200.train.trainer import Trainer
 
     tr = Trainer(cfg, rank, rank, world, benchmark=True, device="cpu")
+    assert (getattr(tr.model, "vocab_parallel", None) is not None) == bool(cfg.get("tp", {}).get("loss_parallel"))
     seen = []
     tr.model.register_forward_pre_hook(lambda mod, args: seen.append(tuple(args[0].shape)))
     hist = tr.train_n_step_test(STEPS)
@@ -111,6 +112,20 @@ def test_tensor_parallel_trainer_matches_single_process(tmp_path):
     tp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "tp": 2})
     run_distributed(_run_hist_only, 2, tp_cfg, str(tmp_path), str(tmp_path / "tp.pt"), timeout_s=240)
     a, b = torch.load(tmp_path / "tp.pt"), torch.load(tmp_path / "one.pt")
+    for x, y in zip(a["hist"], b["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
+
+
+def test_loss_parallel_trainer_matches_single_process(tmp_path):
+    """mesh {dp: 1, tp: 2} with `tp.loss_parallel`: each rank computes half of the vocabulary's logits inside the
+    chunked CE, the row slices of the tied embedding / head gradient are gathered before the clip norm."""
+    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
+    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
+    lp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "tp": 2})
+    lp_cfg["tp"] = {"loss_parallel": True}
+    run_distributed(_run_hist_only, 2, lp_cfg, str(tmp_path), str(tmp_path / "lp.pt"), timeout_s=240)
+    a, b = torch.load(tmp_path / "lp.pt"), torch.load(tmp_path / "one.pt")
     for x, y in zip(a["hist"], b["hist"]):
         assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)

@@ -17,7 +17,7 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
                    synthetic extras: vocab_size, eos_id, mean_doc_len}
     [ddp]         {bucket_mb, [fused], [merge_small], [comm_sms], [early_embedding]}
     [fsdp]        {[comm_sms]}
-    [tp]          {[sequence_parallel]}
+    [tp]          {[sequence_parallel], [loss_parallel]: the fused CE computes V / tp rows of the head per rank}
     [cp]          {[kind]: "ring" | "ulysses"}     with mesh {"dp": D, "cp": C}: zigzag ring attention, or heads <->
                   sequence all-to-alls around whole-sequence attention
     [pp]          {[schedule]: "1f1b" | "gpipe"}   with mesh {"dp": D, "pp": P}: contiguous stages of blocks

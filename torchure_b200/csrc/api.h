@@ -63,6 +63,14 @@ int embedding_scatter(int n_sources, const int64_t* const* ids, const float* con
 // *inv_n_valid.
 void ce_softmax_grad(__nv_bfloat16* logits, int64_t ldl, const int64_t* labels, float* row_loss,
                      const float* inv_n_valid, int C, int V, int ignore_index, cudaStream_t stream);
+// The same for a vocabulary sharded over ranks (this rank's logits hold columns [vocab_lo, vocab_lo + V)):
+// ce_row_stats writes each row's maximum, sum of exponentials relative to it and target logit (0 when the target is
+// another rank's) to stats[0 / 1 / 2][C]; ce_grad_from_lse, given the log-sum-exp over ALL ranks' columns, overwrites
+// the logits with (softmax - onehot) * *inv_n_valid (zeros for ignored rows).
+void ce_row_stats(const __nv_bfloat16* logits, int64_t ldl, const int64_t* labels, float* stats, int C, int V,
+                  int64_t vocab_lo, int ignore_index, cudaStream_t stream);
+void ce_grad_from_lse(__nv_bfloat16* logits, int64_t ldl, const int64_t* labels, const float* lse,
+                      const float* inv_n_valid, int C, int V, int64_t vocab_lo, int ignore_index, cudaStream_t stream);
 void cast_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t stream);
 // x *= *scale unless *scale == 1
 void scale_inplace_f32(float* x, const float* scale, int64_t n, cudaStream_t stream);

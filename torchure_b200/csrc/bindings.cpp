@@ -132,6 +132,24 @@ void ce_softmax_grad(torch::Tensor& logits, const torch::Tensor& labels, torch::
                       inv_n_valid.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)ignore_index,
                       cur_stream());
 }
+void ce_row_stats(const torch::Tensor& logits, const torch::Tensor& labels, torch::Tensor& stats, int64_t vocab_lo,
+                  int64_t ignore_index) {
+  TORCH_CHECK(logits.stride(1) == 1 && logits.stride(0) % 8 == 0, "ce: logits rows must be 16-byte aligned");
+  TORCH_CHECK(stats.is_contiguous() && stats.scalar_type() == torch::kFloat32 && stats.numel() == 3 * logits.size(0) &&
+              labels.numel() == logits.size(0), "ce_row_stats: stats must be fp32 [3, rows]");
+  tb::ce_row_stats(bf(logits), logits.stride(0), labels.data_ptr<int64_t>(),
+                   stats.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), vocab_lo, (int)ignore_index,
+                   cur_stream());
+}
+void ce_grad_from_lse(torch::Tensor& logits, const torch::Tensor& labels, const torch::Tensor& lse,
+                      const torch::Tensor& inv_n_valid, int64_t vocab_lo, int64_t ignore_index) {
+  TORCH_CHECK(logits.stride(1) == 1 && logits.stride(0) % 8 == 0, "ce: logits rows must be 16-byte aligned");
+  TORCH_CHECK(lse.is_contiguous() && lse.scalar_type() == torch::kFloat32 && lse.numel() == logits.size(0) &&
+              labels.numel() == logits.size(0), "ce_grad_from_lse: lse must be fp32 [rows]");
+  tb::ce_grad_from_lse(bfm(logits), logits.stride(0), labels.data_ptr<int64_t>(), lse.data_ptr<float>(),
+                       inv_n_valid.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), vocab_lo,
+                       (int)ignore_index, cur_stream());
+}
 void cast_to_bf16(const torch::Tensor& src, torch::Tensor& dst) {
   tb::cast_f32_to_bf16(src.data_ptr<float>(), bfm(dst), src.numel(), cur_stream());
 }
@@ -240,6 +258,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      pybind11::arg("scale"), pybind11::arg("sq_delta"), pybind11::arg("blocks"),
      pybind11::arg("ids_scratch") = c10::nullopt);
   m.def("ce_softmax_grad", &ce_softmax_grad);
+  m.def("ce_row_stats", &ce_row_stats);
+  m.def("ce_grad_from_lse", &ce_grad_from_lse);
   m.def("cast_to_bf16", &cast_to_bf16);
   m.def("scale_inplace", &scale_inplace);
   m.def("adamw_multi", &adamw_multi);

@@ -943,66 +943,89 @@ embedding_scatter_kernel(EmbedSources src, float* __restrict__ dtable, int M, in
 // partials exchanged through distributed shared memory) measured 804 us: 74 rows in flight are too few.
 constexpr int CE_THREADS = 1024;
 
+//
+// Three forms of one kernel.  CE_FUSED: the whole vocabulary is in the row (statistics, loss and gradient in one
+// launch).  The other two split it for a vocabulary sharded over ranks, where a row's log-sum-exp needs every rank's
+// columns: CE_STATS reads the rank's columns [vocab_lo, vocab_lo + V) once and writes the row's maximum, the sum of
+// exponentials relative to it and the target's logit (0 when another rank holds the target) to stats[0 / 1 / 2][row];
+// after the ranks have combined these, CE_GRAD overwrites the columns with (exp(logit - lse[row]) - [target]) *
+// *inv_n_valid.
+enum { CE_FUSED = 0, CE_STATS = 1, CE_GRAD = 2 };
+
+template <int MODE>
 __global__ void __launch_bounds__(CE_THREADS)
 ce_softmax_grad_kernel(__nv_bfloat16* __restrict__ logits, int64_t ldl, const int64_t* __restrict__ labels,
                        float* __restrict__ row_loss, const float* __restrict__ inv_n_valid, int V,
-                       int ignore_index) {
+                       int ignore_index, int64_t vocab_lo, float* __restrict__ stats,
+                       const float* __restrict__ lse) {
   const int row = blockIdx.x;
   __nv_bfloat16* lr = logits + static_cast<int64_t>(row) * ldl;
-  const int64_t label = labels[row];
-  const bool valid = label != ignore_index;
+  const int64_t global_label = labels[row];
+  const bool valid = global_label != ignore_index;
+  // the target's column among this rank's, -1 when it is ignored or lies in another rank's shard
+  const int64_t label = (valid && global_label >= vocab_lo && global_label < vocab_lo + V) ? global_label - vocab_lo : -1;
   const int nvec = V >> 3;  // 8 bf16 per 16 B
   __shared__ float s_m[CE_THREADS / 32], s_s[CE_THREADS / 32];
   __shared__ float s_stats[2];
-  if (!valid) {  // ignored rows contribute neither loss nor gradient
+  if (MODE != CE_STATS && !valid) {  // ignored rows contribute neither loss nor gradient
     for (int i = threadIdx.x; i < nvec; i += CE_THREADS) reinterpret_cast<uint4*>(lr)[i] = make_uint4(0, 0, 0, 0);
     for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) lr[i] = __float2bfloat16(0.f);
-    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    if (MODE == CE_FUSED && threadIdx.x == 0) row_loss[row] = 0.f;
     return;
   }
-  float m = -INFINITY, s = 0.f;
-  auto push = [&](float v) {
-    if (v > m) { s = s * __expf(m - v) + 1.f; m = v; }
-    else s += __expf(v - m);
-  };
+  if constexpr (MODE != CE_GRAD) {
+    float m = -INFINITY, s = 0.f;
+    auto push = [&](float v) {
+      if (v > m) { s = s * __expf(m - v) + 1.f; m = v; }
+      else s += __expf(v - m);
+    };
 #pragma unroll 4
-  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
-    uint4 u = reinterpret_cast<const uint4*>(lr)[i];
-    const uint32_t us[4] = {u.x, u.y, u.z, u.w};
-    float vals[8];
-    float lm = -INFINITY;
+    for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+      uint4 u = reinterpret_cast<const uint4*>(lr)[i];
+      const uint32_t us[4] = {u.x, u.y, u.z, u.w};
+      float vals[8];
+      float lm = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float2 f = bf2_to_f2(us[k]);
-      vals[2 * k] = f.x; vals[2 * k + 1] = f.y;
-      lm = fmaxf(lm, fmaxf(f.x, f.y));
-    }
-    if (lm > m) { s *= __expf(m - lm); m = lm; }
+      for (int k = 0; k < 4; ++k) {
+        float2 f = bf2_to_f2(us[k]);
+        vals[2 * k] = f.x; vals[2 * k + 1] = f.y;
+        lm = fmaxf(lm, fmaxf(f.x, f.y));
+      }
+      if (lm > m) { s *= __expf(m - lm); m = lm; }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) s += __expf(vals[k] - m);
-  }
-  for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) push(__bfloat162float(lr[i]));
-  // combine (m, s) across the CTA
-  float wm = warp_max(m);
-  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));
-  if ((threadIdx.x & 31) == 0) { s_m[threadIdx.x >> 5] = wm; s_s[threadIdx.x >> 5] = s; }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    float mm = threadIdx.x < CE_THREADS / 32 ? s_m[threadIdx.x] : -INFINITY;
-    float sv = threadIdx.x < CE_THREADS / 32 ? s_s[threadIdx.x] : 0.f;
-    float gm = warp_max(mm);
-    float gs = warp_sum(mm == -INFINITY ? 0.f : sv * __expf(mm - gm));
-    if (threadIdx.x == 0) {
-      s_stats[0] = gm;
-      s_stats[1] = gs;
-      row_loss[row] = gm + __logf(gs) - __bfloat162float(lr[label]);
+      for (int k = 0; k < 8; ++k) s += __expf(vals[k] - m);
     }
+    for (int i = (nvec << 3) + threadIdx.x; i < V; i += CE_THREADS) push(__bfloat162float(lr[i]));
+    // combine (m, s) across the CTA
+    float wm = warp_max(m);
+    s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));
+    if ((threadIdx.x & 31) == 0) { s_m[threadIdx.x >> 5] = wm; s_s[threadIdx.x >> 5] = s; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float mm = threadIdx.x < CE_THREADS / 32 ? s_m[threadIdx.x] : -INFINITY;
+      float sv = threadIdx.x < CE_THREADS / 32 ? s_s[threadIdx.x] : 0.f;
+      float gm = warp_max(mm);
+      float gs = warp_sum(mm == -INFINITY ? 0.f : sv * __expf(mm - gm));
+      if (threadIdx.x == 0) {
+        s_stats[0] = gm;
+        s_stats[1] = gs;
+        if constexpr (MODE == CE_FUSED) {
+          row_loss[row] = gm + __logf(gs) - (label >= 0 ? __bfloat162float(lr[label]) : 0.f);
+        } else {
+          const int64_t n_rows = gridDim.x;
+          stats[row] = gm;
+          stats[n_rows + row] = gs;
+          stats[2 * n_rows + row] = label >= 0 ? __bfloat162float(lr[label]) : 0.f;
+        }
+      }
+    }
+    if constexpr (MODE == CE_STATS) return;
+    __syncthreads();
   }
-  __syncthreads();
-  const float gm = s_stats[0];
+  const float gm = MODE == CE_GRAD ? lse[row] : s_stats[0];
   const float scale = *inv_n_valid;
-  const float inv_s = 1.f / s_stats[1];
-  const int lvec = static_cast<int>(label >> 3), lsub = static_cast<int>(label & 7);
+  const float inv_s = MODE == CE_GRAD ? 1.f : 1.f / s_stats[1];
+  const int lvec = label >= 0 ? static_cast<int>(label >> 3) : -1, lsub = static_cast<int>(label & 7);
 #pragma unroll 4
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
     uint4 u = reinterpret_cast<const uint4*>(lr)[i];
@@ -1204,7 +1227,20 @@ int embedding_scatter(int n_sources, const int64_t* const* ids, const float* con
 
 void ce_softmax_grad(__nv_bfloat16* logits, int64_t ldl, const int64_t* labels, float* row_loss,
                      const float* inv_n_valid, int C, int V, int ignore_index, cudaStream_t stream) {
-  ce_softmax_grad_kernel<<<C, CE_THREADS, 0, stream>>>(logits, ldl, labels, row_loss, inv_n_valid, V, ignore_index);
+  ce_softmax_grad_kernel<CE_FUSED><<<C, CE_THREADS, 0, stream>>>(logits, ldl, labels, row_loss, inv_n_valid, V,
+                                                                 ignore_index, 0, nullptr, nullptr);
+}
+
+void ce_row_stats(const __nv_bfloat16* logits, int64_t ldl, const int64_t* labels, float* stats, int C, int V,
+                  int64_t vocab_lo, int ignore_index, cudaStream_t stream) {
+  ce_softmax_grad_kernel<CE_STATS><<<C, CE_THREADS, 0, stream>>>(const_cast<__nv_bfloat16*>(logits), ldl, labels, nullptr,
+                                                                 nullptr, V, ignore_index, vocab_lo, stats, nullptr);
+}
+
+void ce_grad_from_lse(__nv_bfloat16* logits, int64_t ldl, const int64_t* labels, const float* lse,
+                      const float* inv_n_valid, int C, int V, int64_t vocab_lo, int ignore_index, cudaStream_t stream) {
+  ce_softmax_grad_kernel<CE_GRAD><<<C, CE_THREADS, 0, stream>>>(logits, ldl, labels, nullptr, inv_n_valid, V, ignore_index,
+                                                                vocab_lo, nullptr, lse);
 }
 
 void cast_f32_to_bf16(const float* src, __nv_bfloat16* dst, int64_t n, cudaStream_t stream) {

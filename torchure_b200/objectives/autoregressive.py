@@ -22,8 +22,10 @@ class ARObjective:
         if self.fused_linear_ce:
             hidden = model(batch["input_ids"], return_final_hidden=True)
             labels = shift_labels(batch["labels"], self.ignore_index)
+            # (mesh, axis) when the run asked for a loss-parallel head over its tensor-parallel axis
             return fused_linear_cross_entropy(hidden, model.lm_head.weight, labels, self.ignore_index,
-                                              self.ce_chunk_size, loss_scale)
+                                              self.ce_chunk_size, loss_scale,
+                                              vocab_parallel=getattr(model, "vocab_parallel", None))
         logits = model(batch["input_ids"])
         loss = cross_entropy_loss(batch["labels"], logits, self.ignore_index)
         return loss if loss_scale == 1.0 else loss * loss_scale

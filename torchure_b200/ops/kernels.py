@@ -160,6 +160,19 @@ def ce_softmax_grad_(logits, labels, row_loss, inv_n_valid, ignore_index):
     ops.count_launch()
 
 
+def ce_row_stats_(logits, labels, stats, vocab_lo, ignore_index):
+    """Vocabulary-sharded CE, first pass: stats (fp32 [3, rows]) <- row maximum, sum of exponentials relative to it,
+    target logit (0 when the target lies outside columns [vocab_lo, vocab_lo + V))."""
+    _C().ce_row_stats(logits, labels, stats, vocab_lo, ignore_index)
+    ops.count_launch()
+
+
+def ce_grad_from_lse_(logits, labels, lse, inv_n_valid, vocab_lo, ignore_index):
+    """Second pass: logits <- (exp(logits - lse[row]) - onehot) * inv_n_valid in place, zeros for ignored rows."""
+    _C().ce_grad_from_lse(logits, labels, lse, inv_n_valid, vocab_lo, ignore_index)
+    ops.count_launch()
+
+
 def cast_to_bf16(src, dst=None):
     if dst is None:
         dst = torch.empty(src.shape, dtype=BF16, device=src.device)

@@ -192,6 +192,12 @@ class Trainer:
 
             parallelize_model(model, self.mesh, "tp",
                               sequence_parallel=self.config.get("tp", {}).get("sequence_parallel", False))
+            if self.config.get("tp", {}).get("loss_parallel", False):
+                # the fused linear + CE computes only this rank's V / tp rows of the head (`vocab_parallel`); the
+                # head's weight gradient is then complete in those rows only, and `_gather_head_rows` completes it
+                assert self.config["objective"]["config"].get("fused_linear_ce", True), "loss_parallel needs the fused CE"
+                assert model.cfg["vocab_size"] % self.tp_size == 0, "loss_parallel: vocabulary not divisible by tp"
+                model.vocab_parallel = (self.mesh, "tp")
         if self.sharded:
             replicate = "dp_replicate" if "dp_replicate" in axes else None
             engine_path = self.on_gpu and getattr(model, "impl", "torch") != "torch"
@@ -391,6 +397,8 @@ class Trainer:
         self.ddp.requires_sync = True
         loss += self.micro_train_step(batches[K - 1] if batches else None)
         self.ddp.sync()
+        if getattr(self.model, "vocab_parallel", None) is not None:
+            self._gather_head_rows()
         params = self._opt_params if self._opt_params is not None else [
             p for p in self.model.parameters() if p.requires_grad]
         fused_norm = sq = None
@@ -460,6 +468,18 @@ class Trainer:
         self.optimizer.zero_grad()
         self._loss_averaged = False
         return loss, grad_norm
+
+    def _gather_head_rows(self) -> None:
+        """Loss-parallel head: every rank of the tp axis computed the head's weight gradient for its own V / tp rows
+        (to which the replicated embedding lookup, when the tensor is tied, added the same rows on every rank), so
+        the rank's row slice is complete and the other rows are not: each rank's slice replaces those rows
+        everywhere."""
+        from torchure_b200.core.collective import all_gather
+        from torchure_b200.loss.fused_linear_ce import vocab_slice
+
+        grad = self.model.lm_head.weight.grad
+        v0, rows = vocab_slice(grad.shape[0], self.mesh, "tp")
+        all_gather(grad[v0:v0 + rows].clone(), self.mesh, "tp", output_tensor=grad)
 
     def _tp_sq_norm(self, params) -> torch.Tensor:
         """Global sum of squared gradients under tensor parallelism: the sharded matrices contribute their own rows /
