@@ -61,7 +61,7 @@ def bench_mesh(parallel: str, n_gpus: int) -> dict:
         return {"dp_shard": n_gpus}
     if parallel == "hsdp2":
         return {"dp_replicate": 2, "dp_shard": n_gpus // 2}
-    if parallel in ("tp2", "tp2sp"):
+    if parallel in ("tp2", "tp2sp", "tp2lp"):
         return {"dp": n_gpus // 2, "tp": 2}
     if parallel == "cp2":
         return {"dp": n_gpus // 2, "cp": 2}
@@ -271,6 +271,10 @@ def run_ours(args) -> None:
     if args.parallel == "tp2sp":
         # sequence parallelism: the block linears run as the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels
         cfg["tp"] = {"sequence_parallel": True}
+    if args.parallel == "tp2lp":
+        # loss-parallel head: every rank computes V / tp rows of the logits inside the chunked CE
+        cfg["tp"] = {"loss_parallel": True}
+        cfg["comm"] = {"max_bytes": 1 << 30}    # room for the gather of the head-gradient row slices (311 MB per rank)
     cfg["cuda_graph"] = bool(args.graph) and not args.torch_path and args.parallel not in ("tp2sp", "cp2")
     trainer = Trainer(cfg, rank, local_rank, world, benchmark=True)
     step = trainer.train_step_untimed
@@ -334,7 +338,7 @@ def main() -> None:
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--torch-path", action="store_true", help="ours: run the PyTorch oracle path (A/B)")
     ap.add_argument("--graph", type=int, default=1, help="ours: replay the device step from one CUDA graph (1) or launch eagerly (0)")
-    ap.add_argument("--parallel", choices=["dp", "fsdp", "hsdp2", "tp2", "tp2sp", "cp2"], default="dp",
+    ap.add_argument("--parallel", choices=["dp", "fsdp", "hsdp2", "tp2", "tp2sp", "tp2lp", "cp2"], default="dp",
                     help="ours: strategy selected through the mesh (dp = DDP is the headline configuration)")
     ap.add_argument("--census", type=int, default=1, help="one extra untimed step under torch.profiler: kernel census")
     args = ap.parse_args()
