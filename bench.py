@@ -199,6 +199,7 @@ def shared_config(model: str, cfg: dict, world: int, ce_chunk: int) -> dict:
     mbs = cfg["data"]["micro_batch_size"]
     mesh = cfg["mesh"]
     par = f"dp{world}" if list(mesh) == ["dp"] else "x".join(f"{k}{v}" for k, v in mesh.items())
+    par += "".join(f"+{k}" for k, v in sorted(cfg.get("tp", {}).items()) if v)    # sequence_parallel / loss_parallel
     return {"model": f"qwen3-{model}", "ffn_dim": cfg["model"]["config"]["ffn_dim"],
             "global_batch": cfg["data"]["global_batch_size"],
             "micro_batch": mbs, "seq_len": cfg["data"]["seq_len"], "parallelism": par, "ce_chunk": ce_chunk,

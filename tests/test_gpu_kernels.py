@@ -213,7 +213,7 @@ def test_ce_softmax_grad(C, V):
     assert work[labels == -100].abs().sum() == 0
 
 
-@pytest.mark.parametrize("C,V,shards", [(64, 1024, 2), (300, 5000, 2), (256, 151936, 4)])
+@pytest.mark.parametrize("C,V,shards", [(64, 1024, 2), (300, 5008, 2), (256, 151936, 4)])   # shard rows stay 16-byte aligned
 def test_ce_vocabulary_sharded_passes(C, V, shards):
     """The two passes of the loss-parallel CE on column shards of one logits matrix (what the ranks of a
     tensor-parallel axis hold): row statistics per shard, combined as the ranks' all-reduces would, must give the
