@@ -25,6 +25,11 @@ def _entry(rank, world, port, fn, args, errq, timeout_s):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), LOCAL_RANK=str(rank),
                       WORLD_SIZE=str(world))
     try:
+        import torch
+
+        # the ranks share this host's cores: without a cap every rank starts one thread per core and they fight.  The
+        # same count for every world size, so that a single-process reference sums its products in the same order
+        torch.set_num_threads(2)
         dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=timeout_s))
         fn(rank, world, *args)
         dist.barrier()

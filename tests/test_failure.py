@@ -92,6 +92,9 @@ def test_config_errors_are_loud():
     bad["mesh"]["tp"] = 2
     with pytest.raises(ConfigError):
         validate_config(bad, 2)
+    for mesh in ({"dp": 1, "ep": 2}, {"dp_shard": 1, "tp": 2}):      # nothing to select / not combinable
+        with pytest.raises(ConfigError):
+            validate_config(parity_config(1, mesh=mesh), 2)
     # context and pipeline parallelism: {"dp", "cp"} / {"dp", "pp"} in this order, chunks and stages that divide
     validate_config(parity_config(1, mesh={"dp": 1, "cp": 2}), 2)
     validate_config(parity_config(1, mesh={"dp": 1, "pp": 2}), 2)

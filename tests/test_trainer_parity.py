@@ -53,6 +53,26 @@ def _run(rank, world, cfg, home, out, emulate_world):
         torch.save({"hist": hist, "params": params}, out)
 
 
+_REFERENCE: dict = {}
+
+
+def _single_process(tmp_path, accumulation: int, emulate_world: int | None = None) -> dict:
+    """What ONE process does with the same global batch (computed once per test session and kind): with
+    `emulate_world` the run is fed the rows that many data-parallel ranks would read and returns the loss / norm
+    history and the final weights; without it, the history only."""
+    key = (accumulation, emulate_world)
+    if key not in _REFERENCE:
+        cfg = parity_config(world=1, steps=STEPS, accumulation=accumulation)
+        out = str(tmp_path / f"single_{accumulation}_{emulate_world}.pt")
+        if emulate_world is None:
+            run_distributed(_run_hist_only, 1, cfg, str(tmp_path), out, timeout_s=240)
+        else:
+            run_distributed(_run, 1, cfg, str(tmp_path), out, emulate_world, timeout_s=240)
+        _REFERENCE[key] = torch.load(out)
+    return _REFERENCE[key]
+
+
+
 def _weights(tr):
     """Unsharded fp32 weights under the model's keys (a collective when the strategy shards them)."""
     if getattr(tr, "sharded", False):
@@ -78,16 +98,12 @@ def _compare(a, b):
 
 def test_fsdp_and_hsdp_match_single_process(tmp_path):
     """The mesh alone selects the strategy: dp_shard -> FSDP2 units, dp_replicate x dp_shard -> HSDP."""
-    one_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
-    run_distributed(_run, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=240)
     fsdp_cfg = parity_config(world=2, steps=STEPS, accumulation=2, mesh={"dp_shard": 2})
     run_distributed(_run, 2, fsdp_cfg, str(tmp_path), str(tmp_path / "fsdp.pt"), 0, timeout_s=240)
-    _compare(torch.load(tmp_path / "fsdp.pt"), torch.load(tmp_path / "one.pt"))
-    one4_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
-    run_distributed(_run, 1, one4_cfg, str(tmp_path), str(tmp_path / "one4.pt"), 4, timeout_s=240)
+    _compare(torch.load(tmp_path / "fsdp.pt"), _single_process(tmp_path, 4, 2))
     hsdp_cfg = parity_config(world=4, steps=STEPS, accumulation=1, mesh={"dp_replicate": 2, "dp_shard": 2})
     run_distributed(_run, 4, hsdp_cfg, str(tmp_path), str(tmp_path / "hsdp.pt"), 0, timeout_s=240)
-    _compare(torch.load(tmp_path / "hsdp.pt"), torch.load(tmp_path / "one4.pt"))
+    _compare(torch.load(tmp_path / "hsdp.pt"), _single_process(tmp_path, 4, 4))
 
 
 def _run_hist_only(rank, world, cfg, home, out):
@@ -107,11 +123,9 @@ def test_tensor_parallel_trainer_matches_single_process(tmp_path):
     """mesh {dp: 1, tp: 2}: both ranks see the same batches and hold half of every block; loss and the global
     gradient norm (sharded tensors summed over tp, replicated ones counted once) must follow the single-process run,
     which also pins the clip coefficient and therefore every later step."""
-    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
-    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
     tp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "tp": 2})
     run_distributed(_run_hist_only, 2, tp_cfg, str(tmp_path), str(tmp_path / "tp.pt"), timeout_s=240)
-    a, b = torch.load(tmp_path / "tp.pt"), torch.load(tmp_path / "one.pt")
+    a, b = torch.load(tmp_path / "tp.pt"), _single_process(tmp_path, 2)
     for x, y in zip(a["hist"], b["hist"]):
         assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
@@ -120,12 +134,10 @@ def test_tensor_parallel_trainer_matches_single_process(tmp_path):
 def test_loss_parallel_trainer_matches_single_process(tmp_path):
     """mesh {dp: 1, tp: 2} with `tp.loss_parallel`: each rank computes half of the vocabulary's logits inside the
     chunked CE, the row slices of the tied embedding / head gradient are gathered before the clip norm."""
-    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
-    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
     lp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "tp": 2})
     lp_cfg["tp"] = {"loss_parallel": True}
     run_distributed(_run_hist_only, 2, lp_cfg, str(tmp_path), str(tmp_path / "lp.pt"), timeout_s=240)
-    a, b = torch.load(tmp_path / "lp.pt"), torch.load(tmp_path / "one.pt")
+    a, b = torch.load(tmp_path / "lp.pt"), _single_process(tmp_path, 2)
     for x, y in zip(a["hist"], b["hist"]):
         assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
@@ -136,12 +148,10 @@ def test_sequence_parallel_trainer_matches_single_process(tmp_path):
     along the sequence, the embedding output is sliced on entry and the hidden state gathered before the final norm;
     the norm gains inside the blocks see half of the tokens each and their gradients are summed over the axis.  Loss
     and global gradient norm must follow the single-process run."""
-    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
-    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
     sp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "tp": 2})
     sp_cfg["tp"] = {"sequence_parallel": True}
     run_distributed(_run_hist_only, 2, sp_cfg, str(tmp_path), str(tmp_path / "sp.pt"), timeout_s=240)
-    a, b = torch.load(tmp_path / "sp.pt"), torch.load(tmp_path / "one.pt")
+    a, b = torch.load(tmp_path / "sp.pt"), _single_process(tmp_path, 2)
     for x, y in zip(a["hist"], b["hist"]):
         assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
@@ -151,11 +161,9 @@ def test_context_parallel_trainer_matches_single_process(tmp_path):
     """mesh {dp: 1, cp: 2}: both ranks read the same rows, keep two zigzag chunks of every sequence, rotate by the
     chunks' global positions and run attention as a ring; each divides its summed loss by half of the global target
     count and the gradients are averaged over dp x cp.  Loss and gradient norm must follow the single-process run."""
-    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
-    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
     cp_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "cp": 2})
     run_distributed(_run_hist_only, 2, cp_cfg, str(tmp_path), str(tmp_path / "cp.pt"), timeout_s=240)
-    a, b = torch.load(tmp_path / "cp.pt"), torch.load(tmp_path / "one.pt")
+    a, b = torch.load(tmp_path / "cp.pt"), _single_process(tmp_path, 2)
     d = cp_cfg["data"]
     assert a["input_shapes"] == [(d["micro_batch_size"], d["seq_len"] // 2)], a["input_shapes"]   # half of every row
     for x, y in zip(a["hist"], b["hist"]):
@@ -166,12 +174,10 @@ def test_context_parallel_trainer_matches_single_process(tmp_path):
 def test_ulysses_trainer_matches_single_process(tmp_path):
     """mesh {dp: 1, cp: 2} with `cp.kind: "ulysses"`: contiguous halves of every sequence, all heads of the half
     exchanged for half of the heads of the whole sequence around attention."""
-    one_cfg = parity_config(world=1, steps=STEPS, accumulation=2)
-    run_distributed(_run_hist_only, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), timeout_s=240)
     u_cfg = parity_config(world=1, steps=STEPS, accumulation=2, mesh={"dp": 1, "cp": 2})
     u_cfg["cp"] = {"kind": "ulysses"}
     run_distributed(_run_hist_only, 2, u_cfg, str(tmp_path), str(tmp_path / "u.pt"), timeout_s=240)
-    a, b = torch.load(tmp_path / "u.pt"), torch.load(tmp_path / "one.pt")
+    a, b = torch.load(tmp_path / "u.pt"), _single_process(tmp_path, 2)
     d = u_cfg["data"]
     assert a["input_shapes"] == [(d["micro_batch_size"], d["seq_len"] // 2)], a["input_shapes"]
     for x, y in zip(a["hist"], b["hist"]):
@@ -194,12 +200,10 @@ def test_pipeline_trainer_matches_single_process(tmp_path, schedule="1f1b"):
     """mesh {dp: 1, pp: 2}: two stages of two blocks, the tied embedding / head held by both (gradients summed,
     values equal), four micro-batches per step through the schedule, the clip norm taken over both stages.  Loss,
     gradient norm and the final weights of BOTH stages must follow the single-process run."""
-    one_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
-    run_distributed(_run, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), 0, timeout_s=240)
     pp_cfg = parity_config(world=1, steps=STEPS, accumulation=4, mesh={"dp": 1, "pp": 2})
     pp_cfg["pp"] = {"schedule": schedule}
     run_distributed(_run_pp, 2, pp_cfg, str(tmp_path), str(tmp_path / "pp.pt"), 0, timeout_s=240)
-    one = torch.load(tmp_path / "one.pt")
+    one = _single_process(tmp_path, 4, 0)
     parts = [torch.load(f"{tmp_path}/pp.pt.{r}") for r in range(2)]
     assert "token_emb.weight" in parts[0]["params"] and "lm_head.weight" in parts[1]["params"]
     assert "blocks.0.norm1.weight" in parts[0]["params"] and "blocks.3.norm1.weight" in parts[1]["params"]
@@ -214,12 +218,10 @@ def test_pipeline_trainer_matches_single_process(tmp_path, schedule="1f1b"):
 
 def test_pipeline_with_data_parallel_replicas(tmp_path):
     """mesh {dp: 2, pp: 2} on four ranks (GPipe order) against one process fed the rows of both replicas."""
-    one_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
-    run_distributed(_run, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=240)
     pp_cfg = parity_config(world=2, steps=STEPS, accumulation=2, mesh={"dp": 2, "pp": 2})
     pp_cfg["pp"] = {"schedule": "gpipe"}
     run_distributed(_run_pp, 4, pp_cfg, str(tmp_path), str(tmp_path / "pp.pt"), 0, timeout_s=300)
-    one = torch.load(tmp_path / "one.pt")
+    one = _single_process(tmp_path, 4, 2)
     parts = [torch.load(f"{tmp_path}/pp.pt.{r}") for r in range(4)]    # ranks 0 / 1: stages 0 / 1 of replica 0
     merged = {**parts[0]["params"], **parts[1]["params"]}
     merged.pop("lm_head.weight")
@@ -292,8 +294,7 @@ def test_ddp_world2_matches_single_process(tmp_path):
     one_cfg = parity_config(world=1, steps=STEPS, accumulation=4)
     assert ddp_cfg["data"]["global_batch_size"] == one_cfg["data"]["global_batch_size"] == 8
     run_distributed(_run, 2, ddp_cfg, str(tmp_path), str(tmp_path / "ddp.pt"), 0, timeout_s=240)
-    run_distributed(_run, 1, one_cfg, str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=240)
-    _compare(torch.load(tmp_path / "ddp.pt"), torch.load(tmp_path / "one.pt"))  # Adam amplifies summation-order noise
+    _compare(torch.load(tmp_path / "ddp.pt"), _single_process(tmp_path, 4, 2))  # Adam amplifies summation-order noise
 
 
 def _run_resume(rank, world, home, out):

@@ -58,6 +58,11 @@ def validate_config(cfg: dict, world_size: int | None = None) -> dict:
     unknown = [a for a in mesh if a not in MESH_AXES]
     if unknown:
         raise ConfigError(f"unknown mesh axes {unknown}; known: {list(MESH_AXES)}")
+    if mesh.get("ep", 1) > 1:
+        raise ConfigError('expert parallelism is a library module (parallel/expert_parallel.py): no model of the registry '
+                          'has experts, so "ep" cannot be larger than 1')
+    if mesh.get("tp", 1) > 1 and ("dp_shard" in mesh or "dp_replicate" in mesh):
+        raise ConfigError('"tp" combines with "dp" only (not with "dp_shard" / "dp_replicate")')
     data_axes = [a for a in mesh if a in DATA_AXES]
     if not data_axes:
         raise ConfigError('mesh must define a data axis: "dp", or "dp_shard" (optionally after "dp_replicate")')
