@@ -118,6 +118,24 @@ def test_config_errors_are_loud():
         validate_config(bad, 2)
 
 
+def test_shipped_configs_validate():
+    """Every file under configs/ (the reference-schema ones and the synthetic ones per strategy) passes validation for
+    the world size its mesh spans."""
+    import glob
+    import json
+    import math
+    import os
+
+    from torchure_b200.config import validate_config
+
+    files = sorted(glob.glob(os.path.join(os.path.dirname(os.path.dirname(__file__)), "configs", "*.json")))
+    assert len(files) >= 12
+    for f in files:
+        with open(f) as fh:
+            cfg = json.load(fh)
+        validate_config(cfg, math.prod(cfg["mesh"].values()))
+
+
 @pytest.mark.gpu
 def test_device_wait_expires_with_status_and_context_survives():
     """A barrier that expects a peer that does not exist: nothing ever sets the flag, the bounded wait runs out after
