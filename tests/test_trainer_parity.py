@@ -185,6 +185,75 @@ def test_ulysses_trainer_matches_single_process(tmp_path):
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
 
 
+def _moe_config(world, accumulation, mesh=None, **kw):
+    cfg = parity_config(world=world, steps=STEPS, accumulation=accumulation, mesh=mesh, **kw)
+    cfg["model"] = {"name": "qwen3_moe", "config": dict(cfg["model"]["config"], num_experts=4, top_k=2,
+                                                        moe_ffn_dim=256, capacity_factor=8.0)}
+    return cfg
+
+
+def _run_moe(rank, world, cfg, home, out, emulate_world):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    tr = Trainer(cfg, rank, rank, world, benchmark=True, device="cpu")
+    if emulate_world:
+        tr.prefetcher = _Interleaved(cfg, emulate_world)
+    hist = tr.train_n_step_test(STEPS)
+    torch.save({"hist": hist, "params": _weights(tr)}, f"{out}.{rank}")
+
+
+def test_expert_parallel_trainer_matches_single_process(tmp_path):
+    """mesh {dp: 1, ep: 2} on the mixture-of-experts model: each rank keeps two of the four experts of every layer
+    and reads its own rows; tokens travel to their experts and back.  One process that holds all experts and is fed
+    both ranks' rows must see the same loss and gradient norm and end with the same weights (shared tensors on every
+    rank, each rank's experts equal to the matching slice)."""
+    run_distributed(_run_moe, 1, _moe_config(1, 2), str(tmp_path), str(tmp_path / "one.pt"), 2, timeout_s=240)
+    run_distributed(_run_moe, 2, _moe_config(2, 1, mesh={"dp": 1, "ep": 2}), str(tmp_path), str(tmp_path / "ep.pt"), 0,
+                    timeout_s=240)
+    one = torch.load(f"{tmp_path}/one.pt.0")
+    parts = [torch.load(f"{tmp_path}/ep.pt.{r}") for r in range(2)]
+    for x, y in zip(parts[0]["hist"], one["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
+    for r, part in enumerate(parts):
+        for n, v in part["params"].items():
+            want = one["params"][n]
+            if v.shape != want.shape:               # stacked expert weights: this rank's half
+                assert n.split(".")[-1] in ("w_gate", "w_up", "w_down"), n
+                want = want[r * v.shape[0]:(r + 1) * v.shape[0]]
+            assert (v - want).abs().max().item() < 5 * 3e-4, (n, (v - want).abs().max().item())
+            assert ((v - want).abs() > 1e-5 + 1e-4 * want.abs()).float().mean().item() < 1e-4, n
+
+
+def _run_moe_resume(rank, world, home, out):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    mesh = {"dp": 1, "ep": 2}
+    straight = Trainer(_moe_config(2, 1, mesh=mesh, run_name="ep_straight"), rank, rank, world, device="cpu")
+    straight.train()
+    first = Trainer(_moe_config(2, 1, mesh=mesh, run_name="ep_resumed", save_steps=3), rank, rank, world, device="cpu")
+    first.num_train_steps = 3
+    first.train()
+    second = Trainer(_moe_config(2, 1, mesh=mesh, run_name="ep_resumed", resume="auto", save_steps=1000), rank, rank,
+                     world, device="cpu")
+    assert second.start_step == 3
+    second.train()
+    torch.save({"a": _weights(straight), "b": _weights(second)}, f"{out}.{rank}")
+
+
+def test_expert_parallel_resume_is_exact(tmp_path):
+    run_distributed(_run_moe_resume, 2, str(tmp_path), str(tmp_path / "r.pt"), timeout_s=240)
+    for r in range(2):
+        got = torch.load(f"{tmp_path}/r.pt.{r}")
+        for n in got["a"]:
+            assert torch.equal(got["a"][n], got["b"][n]), n
+    files = sorted(os.listdir(tmp_path / "checkpoints" / "ep_resumed" / "3"))
+    assert "model_shard0.pt" in files and "model_shard1.pt" in files and "optimizer_shard1.pt" in files, files
+    assert "dataloader_rank0.pt" in " ".join(files) or any(f.startswith("dataloader") for f in files), files
+
+
 def _run_pp(rank, world, cfg, home, out, emulate_world):
     os.environ["TORCHURE_B200_HOME"] = home
     from torchure_b200.train.trainer import Trainer

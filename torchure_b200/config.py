@@ -6,9 +6,10 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
     model         {name, config{num_layers, num_heads, num_kv_heads, emb_dim, head_dim, vocab_size,
                    [ffn_dim], [norm_eps], [rope_theta], [impl]}}
     mesh          {axis: size, ...}   product == WORLD_SIZE.  Data axes: "dp" (DDP), or "dp_shard" (FSDP2) with an
-                  optional "dp_replicate" in front of it (HSDP); "tp" shards every block (Megatron column/row split);
-                  "cp" (after "dp") splits every sequence into zigzag chunks and runs attention as a ring.  At least one
-                  data axis is required.
+                  optional "dp_replicate" in front of it (HSDP); at least one is required.  After "dp", one of:
+                  "tp" shards every block (Megatron column / row split); "cp" splits every sequence into zigzag
+                  chunks and runs attention as a ring; "pp" cuts the blocks into pipeline stages; "ep" (model
+                  "qwen3_moe") spreads the experts of every layer and is a data axis as well.
     optimizer     {name, config{lr, weight_decay, betas, fused}, [max_norm],
                    scheduler{type, warmup_ratio, decay_ratio, total_steps}}
     objective     {name, config{ignore_index, fused_linear_ce, ce_chunk_size}}
@@ -59,8 +60,11 @@ def validate_config(cfg: dict, world_size: int | None = None) -> dict:
     if unknown:
         raise ConfigError(f"unknown mesh axes {unknown}; known: {list(MESH_AXES)}")
     if mesh.get("ep", 1) > 1:
-        raise ConfigError('expert parallelism is a library module (parallel/expert_parallel.py): no model of the registry '
-                          'has experts, so "ep" cannot be larger than 1')
+        if list(mesh)[: 2] != ["dp", "ep"] or len(mesh) != 2:
+            raise ConfigError('expert parallelism is selected by mesh {"dp": D, "ep": E} (in this order, no other axis)')
+        experts = cfg["model"]["config"].get("num_experts", 0) if cfg["model"].get("name") == "qwen3_moe" else 0
+        if experts == 0 or experts % mesh["ep"] != 0:
+            raise ConfigError('"ep" needs the mixture-of-experts model ("qwen3_moe") with num_experts divisible by ep')
     if mesh.get("tp", 1) > 1 and ("dp_shard" in mesh or "dp_replicate" in mesh):
         raise ConfigError('"tp" combines with "dp" only (not with "dp_shard" / "dp_replicate")')
     data_axes = [a for a in mesh if a in DATA_AXES]
@@ -103,7 +107,7 @@ def validate_config(cfg: dict, world_size: int | None = None) -> dict:
     for key in ("global_batch_size", "micro_batch_size", "seq_len"):
         if key not in data:
             raise ConfigError(f"data.{key} is required")
-    dp = math.prod(mesh[a] for a in data_axes)
+    dp = math.prod(mesh[a] for a in data_axes) * mesh.get("ep", 1)      # the ranks of an ep group read different rows
     per_backward = data["micro_batch_size"] * dp
     if data["global_batch_size"] % per_backward != 0:
         raise ConfigError(

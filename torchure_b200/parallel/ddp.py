@@ -139,7 +139,7 @@ class TorchReducer:
 class DDP:
     def __init__(self, model: nn.Module, mesh: MeshLike, dim: str = "dp", bucket_mb: float = 25,
                  fused: bool | None = None, merge_small: bool = True, comm_sms: int = 16, sm_reserve: int = 0,
-                 embed_tokens: int = 0):
+                 embed_tokens: int = 0, params: list | None = None):
         """`embed_tokens` (tokens per micro-batch, fused reducer with a tied embedding only): size of the symmetric
         buffer through which the ranks exchange embedding-row gradients, which lets the tied embedding / head bucket
         be reduced as soon as the loss head has produced its weight gradient instead of after the last kernel of
@@ -149,7 +149,10 @@ class DDP:
         self.requires_sync = True
         self._works: list = []
         self._accum_launches = 0
-        params = [p for p in model.parameters() if p.requires_grad]
+        # `params` restricts the wrapper to a subset of the model's parameters (expert parallelism reduces expert and
+        # shared parameters over different axes, with one wrapper each)
+        self._subset = params is not None
+        params = [p for p in (params if params is not None else model.parameters()) if p.requires_grad]
         on_gpu = bool(params) and params[0].is_cuda
         if fused is None:
             fused = False
@@ -161,6 +164,7 @@ class DDP:
         self.active = self.group_size > 1 or self.fused
         if not self.active:
             return
+        self._subset_params = list(params)
         if self.group_size > 1:
             self._replicate(model)
         params.reverse()
@@ -187,7 +191,8 @@ class DDP:
             p.register_post_accumulate_grad_hook(self._on_grad_ready)
 
     def _replicate(self, model: nn.Module) -> None:
-        for t in [*model.parameters(), *model.buffers()]:
+        tensors = self._subset_params if self._subset else [*model.parameters(), *model.buffers()]
+        for t in tensors:
             broadcast(t.detach(), self.mesh, self.dim, src=0)
 
     def _on_grad_ready(self, param: nn.Parameter) -> None:

@@ -48,6 +48,18 @@ class MoELayer(nn.Module):
         for w in (self.w_gate, self.w_up, self.w_down):
             nn.init.normal_(w, std=0.02)
 
+    def shard_(self, mesh, dim: str = "ep") -> None:
+        """Turn a layer that holds all experts into rank r's part of an expert-parallel one: experts
+        [r E / n, (r + 1) E / n) are kept (as new, smaller parameters), the router stays whole."""
+        assert self.n == 1, "already sharded"
+        n, r = mesh.size(dim), mesh.coordinate(dim)
+        assert self.E % n == 0, "experts must divide evenly over the ep axis"
+        local = self.E // n
+        for name in ("w_gate", "w_up", "w_down"):
+            full = getattr(self, name)
+            setattr(self, name, nn.Parameter(full.detach()[r * local:(r + 1) * local].clone()))
+        self.mesh, self.dim, self.n, self.r, self.local_E = mesh, dim, n, r, local
+
     def load_full_experts(self, w_gate, w_up, w_down) -> None:
         """Take this rank's slice of unsharded (E, ...) expert weights."""
         lo = self.r * self.local_E

@@ -72,6 +72,14 @@ class Trainer:
         # under context parallelism, the ranks that hold the other chunks of the same sequences
         self.cp_size = self.mesh.size("cp") if "cp" in self.mesh.axes() else 1
         self.pp_size = self.mesh.size("pp") if "pp" in self.mesh.axes() else 1
+        self.ep_size = self.mesh.size("ep") if "ep" in self.mesh.axes() else 1
+        if self.ep_size > 1:
+            # the ranks of an expert-parallel group read different rows: the axis is a data axis as well, and the
+            # shared (non-expert) parameters are averaged over dp x ep
+            assert data_axes == ("dp",) and len(self.mesh.axes()) == 2, "ep combines with plain dp only"
+            self.mesh.flatten(("dp", "ep"), "dp_ep")
+            self.data_axis = self.grad_axis = "dp_ep"
+            self.dp_size = self.mesh.size("dp_ep")
         self.grad_axis = self.data_axis
         if self.cp_size > 1:
             assert data_axes == ("dp",) and "tp" not in self.mesh.axes(), "cp combines with plain dp only"
@@ -117,7 +125,7 @@ class Trainer:
         self._wire_engine()
         # the ring exchange of context parallelism goes through library p2p calls on a side stream: not captured
         self.use_cuda_graph = (bool(self.config.get("cuda_graph", False)) and self.on_gpu and self.cp_size == 1
-                               and self.pp_size == 1)
+                               and self.pp_size == 1 and not hasattr(self.model, "expert_params"))
         self._graph = None
         self._graph_eager_left = int(self.config.get("cuda_graph_warmup", 3))
 
@@ -172,6 +180,25 @@ class Trainer:
         self._opt_params = None
         self.sharded = "dp_shard" in axes
         self.tp_size = self.mesh.size("tp") if "tp" in axes else 1
+        self.ddp_experts = None
+        if hasattr(model, "expert_params"):
+            # mixture-of-experts model: PyTorch blocks.  With an "ep" axis every rank keeps its slice of each layer's
+            # experts; expert gradients are reduced over "dp" only (the other ranks of the ep group hold other
+            # experts), everything else over dp x ep
+            assert not self.sharded and self.tp_size == 1 and self.cp_size == 1 and self.pp_size == 1, \
+                "the mixture-of-experts model combines with dp and ep only"
+            ddp_cfg = self.config.get("ddp", {})
+            kw = dict(bucket_mb=ddp_cfg.get("bucket_mb", 25), fused=False, merge_small=ddp_cfg.get("merge_small", True))
+            if self.ep_size > 1:
+                model.shard_experts(self.mesh, "ep")
+                experts = model.expert_params()
+                mine = {id(p) for p in experts}
+                shared = [p for p in model.parameters() if id(p) not in mine]
+                self.ddp = DDP(model, self.mesh, dim=self.grad_axis, params=shared, **kw)
+                self.ddp_experts = DDP(model, self.mesh, dim="dp", params=experts, **kw)
+            else:
+                self.ddp = DDP(model, self.mesh, dim=self.grad_axis, **kw)
+            return model
         if self.pp_size > 1:
             # every rank built the whole model from the same seed and keeps its stage: contiguous blocks, the first
             # stage also the embedding, the last the final norm and the head.  Stages run the PyTorch blocks; their
@@ -299,12 +326,12 @@ class Trainer:
             del full
             if "dp_replicate" not in self.mesh.axes() or self.mesh.coordinate("dp_replicate") == 0:
                 self.checkpointer.save_optimizer(self.optimizer, step, shard=self.mesh.coordinate("dp_shard"))
-        elif self.tp_size > 1 or self.pp_size > 1:
+        elif self.tp_size > 1 or self.pp_size > 1 or self.ep_size > 1:
             # every tensor-parallel coordinate holds different rows / columns, every pipeline stage different blocks
-            # (under the keys of the whole model): one file pair per coordinate, written by the first data-parallel
-            # replica
-            if self.mesh.coordinate(self.data_axis) == 0:
-                shard = self.mesh.coordinate("tp" if self.tp_size > 1 else "pp")
+            # (under the keys of the whole model), every expert-parallel coordinate different experts: one file pair
+            # per coordinate, written by the first data-parallel replica
+            if self.mesh.coordinate("dp") == 0:
+                shard = self.mesh.coordinate(self._split_axis())
                 self.checkpointer.save_model(self.model, step, shard=shard)
                 self.checkpointer.save_optimizer(self.optimizer, step, shard=shard)
         elif self.rank == 0:
@@ -327,6 +354,10 @@ class Trainer:
         if self.rank == 0:
             self.checkpointer.mark_complete(step)
 
+    def _split_axis(self) -> str:
+        """The axis whose coordinates hold different tensors (one checkpoint shard each)."""
+        return "tp" if self.tp_size > 1 else ("pp" if self.pp_size > 1 else "ep")
+
     def _resume(self) -> int:
         if self.resume is None:
             return 0
@@ -345,8 +376,8 @@ class Trainer:
         if self.sharded:
             self.ddp.load_full_state_dict(self.checkpointer._read(step, "model.pt"))
             self.checkpointer.load_optimizer(self.optimizer, step, shard=self.mesh.coordinate("dp_shard"))
-        elif self.tp_size > 1 or self.pp_size > 1:
-            shard = self.mesh.coordinate("tp" if self.tp_size > 1 else "pp")
+        elif self.tp_size > 1 or self.pp_size > 1 or self.ep_size > 1:
+            shard = self.mesh.coordinate(self._split_axis())
             self.checkpointer.load_model(self.model, step, shard=shard)
             self.checkpointer.load_optimizer(self.optimizer, step, shard=shard)
         else:
@@ -381,6 +412,8 @@ class Trainer:
         AdamW.  `batches` (one dict per micro-batch) are used instead of the prefetcher when given."""
         if self.pp_size > 1:
             return self._pipeline_step(batches)
+        if self.ddp_experts is not None:
+            return self._expert_step(batches)
         K = self.microbatches_per_step
         slot = self.ddp.loss_slot() if hasattr(self.ddp, "loss_slot") else None
         if slot is not None:
@@ -464,6 +497,40 @@ class Trainer:
         grad_norm = _total_norm(_collect(stage.norm_params()), self.mesh, ("pp",))
         if self.max_norm is not None:
             torch._foreach_mul_(grads, torch.clamp(self.max_norm / (grad_norm + 1e-6), max=1.0))
+        self.optimizer.step()
+        self.optimizer.zero_grad()
+        self._loss_averaged = False
+        return loss, grad_norm
+
+    def _expert_step(self, batches=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """One optimizer step under expert parallelism.  An expert's gradient collects the tokens of every rank of its
+        ep group, each differentiated against that rank's own mean loss: averaging over "dp" and dividing by the size
+        of the ep group makes it the gradient of the mean over all ranks, which is what the shared parameters get
+        from their average over dp x ep.  The clip norm counts shared tensors once and sums the experts over "ep"."""
+        from torchure_b200.core.grad_helper import _collect, _local_sq_norm
+
+        K = self.microbatches_per_step
+        wrappers = (self.ddp, self.ddp_experts)
+        loss = torch.zeros((), device=self.device)
+        for w in wrappers:
+            w.requires_sync = False
+        for i in range(K - 1):
+            loss += self.micro_train_step(batches[i] if batches else None)
+        for w in wrappers:
+            w.requires_sync = True
+        loss += self.micro_train_step(batches[K - 1] if batches else None)
+        for w in wrappers:
+            w.sync()
+        experts = self.model.expert_params()
+        mine = {id(p) for p in experts}
+        expert_grads = _collect(experts)
+        torch._foreach_mul_(expert_grads, 1.0 / self.ep_size)
+        shared_grads = _collect([p for p in self.model.parameters() if p.requires_grad and id(p) not in mine])
+        sq = _local_sq_norm(expert_grads).reshape(1).clone()
+        all_reduce(sq, self.mesh, "ep", "sum")
+        grad_norm = (sq + _local_sq_norm(shared_grads).reshape(1)).sqrt().reshape(())
+        if self.max_norm is not None:
+            torch._foreach_mul_(expert_grads + shared_grads, torch.clamp(self.max_norm / (grad_norm + 1e-6), max=1.0))
         self.optimizer.step()
         self.optimizer.zero_grad()
         self._loss_averaged = False
