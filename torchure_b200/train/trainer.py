@@ -4,8 +4,11 @@ Lifecycle (reference ``torchure/train/trainer.py:61-146``): mesh -> model -> ini
 parallelize -> objective -> optimizer -> scheduler -> data -> resume -> prefetcher.
 The mesh of the config selects the strategy: ``dp`` builds DDP; ``dp_shard`` (optionally after
 ``dp_replicate``) builds FSDP2 / HSDP (``parallel/fsdp_engine.py`` on the sm_100a engine,
-``parallel/fsdp.py`` hooks on the PyTorch path); a ``tp`` axis shards every block first
-(``parallel/tensor_parallel.py``).
+``parallel/fsdp.py`` hooks on the PyTorch path); after ``dp``, one more axis selects a model-parallel
+family: ``tp`` shards every block (``parallel/tensor_parallel.py``; ``tp.sequence_parallel``,
+``tp.loss_parallel``), ``cp`` splits every sequence (ring attention inside the engine, or Ulysses with
+``cp.kind``), ``pp`` cuts the blocks into pipeline stages (``_pipeline_step``), ``ep`` spreads the experts of the
+mixture-of-experts model (``_expert_step``).
 One optimizer step (reference ``trainer.py:371-402``): K micro-batches of forward+backward
 with ``requires_sync`` only on the last, ``ddp.sync()``, global grad-norm clip, optimizer,
 ``zero_grad``, scheduler, loss averaged over dp.
