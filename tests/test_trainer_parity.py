@@ -328,6 +328,39 @@ def test_pipeline_resume_is_exact(tmp_path):
     assert "model_shard0.pt" in files and "model_shard1.pt" in files and "optimizer_shard1.pt" in files, files
 
 
+def _run_and_save(rank, world, cfg, home):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    Trainer(cfg, rank, rank, world, device="cpu").train()
+
+
+def test_sharded_checkpoints_merge_into_the_unsharded_layout(tmp_path):
+    """Tensor-parallel, pipeline and expert-parallel runs write one model file per coordinate; merged, they must load
+    (strictly) into the whole model and, for the dense model, equal what a single process trained on the same rows."""
+    from torchure_b200.ckpt.merge import merge_model_shards
+    from torchure_b200.models import build_model
+
+    one = _single_process(tmp_path, 4, 0)
+    for name, mesh in (("tp", {"dp": 1, "tp": 2}), ("pp", {"dp": 1, "pp": 2})):
+        cfg = parity_config(world=1, steps=STEPS, accumulation=4, mesh=mesh, run_name=f"merge_{name}", save_steps=STEPS)
+        run_distributed(_run_and_save, 2, cfg, str(tmp_path), timeout_s=240)
+        root = str(tmp_path / "checkpoints" / f"merge_{name}")
+        merged = merge_model_shards(root, STEPS)
+        model = build_model(cfg["model"]["name"], cfg["model"]["config"])
+        model.load_state_dict(merged)          # strict: every key, every shape
+        got = {n: p.detach() for n, p in model.named_parameters()}
+        _compare({"hist": one["hist"], "params": got}, one)
+    cfg = _moe_config(2, 1, mesh={"dp": 1, "ep": 2}, run_name="merge_ep", save_steps=STEPS)
+    run_distributed(_run_and_save, 2, cfg, str(tmp_path), timeout_s=240)
+    merged = merge_model_shards(str(tmp_path / "checkpoints" / "merge_ep"), STEPS)
+    model = build_model(cfg["model"]["name"], cfg["model"]["config"])
+    model.load_state_dict(merged)
+    assert merged["blocks.0.ffn.w_gate"].shape[0] == 4
+    ids = torch.randint(0, 4096, (1, 32), generator=torch.Generator().manual_seed(0))
+    assert torch.isfinite(model(ids)).all()
+
+
 def _run_fsdp_resume(rank, world, home, out):
     os.environ["TORCHURE_B200_HOME"] = home
     from torchure_b200.train.trainer import Trainer
