@@ -335,6 +335,24 @@ def _run_and_save(rank, world, cfg, home):
     Trainer(cfg, rank, rank, world, device="cpu").train()
 
 
+def _check_warm_start(rank, world, cfg, home, merged_path):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    tr = Trainer(cfg, rank, rank, world, device="cpu")
+    merged = torch.load(merged_path)
+    sd = tr.model.state_dict()
+    q = merged["blocks.1.gqa.q_proj.weight"]
+    per = q.shape[0] // world
+    assert torch.equal(sd["blocks.1.gqa.q_proj.weight"], q[rank * per:(rank + 1) * per])
+    d = merged["blocks.2.ffn.down_proj.weight"]
+    perc = d.shape[1] // world
+    assert torch.equal(sd["blocks.2.ffn.down_proj.weight"], d[:, rank * perc:(rank + 1) * perc])
+    assert torch.equal(sd["token_emb.weight"], merged["token_emb.weight"])
+    assert torch.equal(sd["norm.weight"], merged["norm.weight"])
+    tr.train_n_step_test(1)
+
+
 def test_sharded_checkpoints_merge_into_the_unsharded_layout(tmp_path):
     """Tensor-parallel, pipeline and expert-parallel runs write one model file per coordinate; merged, they must load
     (strictly) into the whole model and, for the dense model, equal what a single process trained on the same rows."""
@@ -351,6 +369,13 @@ def test_sharded_checkpoints_merge_into_the_unsharded_layout(tmp_path):
         model.load_state_dict(merged)          # strict: every key, every shape
         got = {n: p.detach() for n, p in model.named_parameters()}
         _compare({"hist": one["hist"], "params": got}, one)
+    # ... and the merged file of the pipeline run starts a tensor-parallel run (`init_from`): the ranks' slices must be
+    # the slices of the merged tensors
+    out = str(tmp_path / "merged_pp.pt")
+    torch.save(merged, out)
+    warm = parity_config(world=1, steps=STEPS, accumulation=4, mesh={"dp": 1, "tp": 2}, run_name="warm_tp")
+    warm["init_from"] = out
+    run_distributed(_check_warm_start, 2, warm, str(tmp_path), out, timeout_s=240)
     cfg = _moe_config(2, 1, mesh={"dp": 1, "ep": 2}, run_name="merge_ep", save_steps=STEPS)
     run_distributed(_run_and_save, 2, cfg, str(tmp_path), timeout_s=240)
     merged = merge_model_shards(str(tmp_path / "checkpoints" / "merge_ep"), STEPS)

@@ -118,6 +118,12 @@ class Trainer:
 
         self.model = self._build_model()
         self._init_weights(self.model)
+        if self.config.get("init_from"):
+            # warm start: an unsharded model state dict (a `model.pt` of any run, or the output of `ckpt.merge` for
+            # runs that wrote shard files) replaces the initialisation BEFORE the strategy slices, stages or shards
+            # the model, so the weights of a run on one mesh can start a run on another.  Optimizer state starts fresh
+            state = torch.load(self.config["init_from"], map_location="cpu", weights_only=True)
+            self.model.load_state_dict(state)
         self.model = self._parallelize(self.model)
         self.objective = build_objective(self.config["objective"]["name"], self.config["objective"]["config"])
         opt_cfg = self.config["optimizer"]
