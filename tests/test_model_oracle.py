@@ -181,6 +181,28 @@ def test_models_match_the_hugging_face_implementations(kind):
                                rtol=1e-3, atol=1e-6)
 
 
+@pytest.mark.parametrize("kind", ["llama3", "qwen3"])
+def test_hugging_face_round_trip(kind, tmp_path):
+    """A Hugging Face directory (random init, written locally) imported into this layout gives the same logits;
+    exported again it loads into the Hugging Face class with identical tensors."""
+    transformers = pytest.importorskip("transformers")
+    from torchure_b200.models import build_model
+    from torchure_b200.models.hf import export_hf, import_hf
+
+    _, hf = _hf_pair(kind)
+    hf.save_pretrained(tmp_path / "hf_in")
+    section = import_hf(str(tmp_path / "hf_in"), str(tmp_path / "model.pt"))
+    assert section["name"] == ("llama3_2" if kind == "llama3" else "qwen3_dense")
+    ours = build_model(section["name"], section["config"])
+    ours.load_state_dict(torch.load(tmp_path / "model.pt"))
+    ids = torch.randint(0, 97, (2, 24), generator=torch.Generator().manual_seed(2))
+    torch.testing.assert_close(ours.eval()(ids), hf(input_ids=ids).logits, rtol=1e-4, atol=1e-5)
+    export_hf(str(tmp_path / "model.pt"), section, str(tmp_path / "hf_out"))
+    back = transformers.AutoModelForCausalLM.from_pretrained(tmp_path / "hf_out")
+    for (n, a), (_, b) in zip(hf.state_dict().items(), back.state_dict().items()):
+        assert torch.equal(a, b), n
+
+
 def test_llama3_registry_and_defaults():
     from torchure_b200.models import build_model
 
