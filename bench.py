@@ -263,6 +263,10 @@ def run_ours(args) -> None:
     from torchure_b200.train.train import init_distributed
     from torchure_b200.train.trainer import Trainer
 
+    if not torch.cuda.is_available():
+        # the benchmark is a GPU measurement: without a device say so instead of grinding through the model on CPU
+        print(json.dumps({"impl": "ours", "unavailable": "no CUDA device"}))
+        return
     rank, local_rank, world = init_distributed()
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     cfg = bench_config(args.model, world, args.steps * 2 + args.warmup + 8, args.micro_batch, args.ce_chunk,
