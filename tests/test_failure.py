@@ -75,6 +75,38 @@ def test_torn_checkpoint_is_not_resumed(tmp_path):
     assert ck.latest() == 5 and ck.valid_step(9) is None
 
 
+def _resume_faults(rank, world, home):
+    import os
+
+    os.environ["TORCHURE_B200_HOME"] = home
+    from tests.tiny import parity_config
+    from torchure_b200.train.trainer import Trainer
+
+    first = Trainer(parity_config(2, steps=4, run_name="faults", accumulation=1, save_steps=2), rank, rank, world,
+                    device="cpu")
+    first.num_train_steps = 2
+    first.train()
+    # a relaunch on another mesh must refuse the checkpoint instead of loading tensors of the wrong shape
+    other = parity_config(1, steps=4, run_name="faults", accumulation=2, resume="auto", mesh={"dp": 1, "tp": 2})
+    with pytest.raises(AssertionError, match="mesh change"):
+        Trainer(other, rank, rank, world, device="cpu")
+    # a checkpoint that lost this rank's dataloader position must not silently restart the data from the beginning
+    torch.distributed.barrier()
+    if rank == 1:
+        os.remove(os.path.join(home, "checkpoints", "faults", "2", "dataloader_dp1.pt"))
+    torch.distributed.barrier()
+    same = parity_config(2, steps=4, run_name="faults", accumulation=1, resume="auto")
+    if rank == 1:
+        with pytest.raises(FileNotFoundError):
+            Trainer(same, rank, rank, world, device="cpu")
+    else:
+        assert Trainer(same, rank, rank, world, device="cpu").start_step == 2
+
+
+def test_resume_refuses_another_mesh_and_a_missing_dataloader_file(tmp_path):
+    run_distributed(_resume_faults, 2, str(tmp_path), timeout_s=120)
+
+
 def test_config_errors_are_loud():
     from torchure_b200.config import ConfigError, validate_config
     from tests.tiny import parity_config
