@@ -226,6 +226,27 @@ def test_expert_parallel_trainer_matches_single_process(tmp_path):
             assert ((v - want).abs() > 1e-5 + 1e-4 * want.abs()).float().mean().item() < 1e-4, n
 
 
+def test_expert_parallel_with_data_parallel_replicas(tmp_path):
+    """mesh {dp: 2, ep: 2} on four ranks: the experts' gradients are averaged over the two replicas that hold the same
+    experts (and divided by the ep size), the shared parameters over all four ranks.  One process with all experts,
+    fed the four ranks' rows, must give the same losses and norms; replicas must stay identical."""
+    run_distributed(_run_moe, 1, _moe_config(1, 4), str(tmp_path), str(tmp_path / "one.pt"), 4, timeout_s=240)
+    run_distributed(_run_moe, 4, _moe_config(4, 1, mesh={"dp": 2, "ep": 2}), str(tmp_path), str(tmp_path / "ep.pt"), 0,
+                    timeout_s=300)
+    one = torch.load(f"{tmp_path}/one.pt.0")
+    parts = [torch.load(f"{tmp_path}/ep.pt.{r}") for r in range(4)]      # rank = dp * 2 + ep
+    for x, y in zip(parts[0]["hist"], one["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
+    for ep in range(2):
+        for n, v in parts[ep]["params"].items():
+            assert torch.equal(v, parts[2 + ep]["params"][n]), n         # same ep coordinate, other replica
+            want = one["params"][n]
+            if v.shape != want.shape:
+                want = want[ep * v.shape[0]:(ep + 1) * v.shape[0]]
+            assert (v - want).abs().max().item() < 5 * 3e-4, (n, (v - want).abs().max().item())
+
+
 def _run_moe_resume(rank, world, home, out):
     os.environ["TORCHURE_B200_HOME"] = home
     from torchure_b200.train.trainer import Trainer
