@@ -11,6 +11,7 @@
 
 import os
 
+import pytest
 import torch
 
 from tests.dist_utils import run_distributed
@@ -166,6 +167,21 @@ def test_context_parallel_trainer_matches_single_process(tmp_path):
     a, b = torch.load(tmp_path / "cp.pt"), _single_process(tmp_path, 2)
     d = cp_cfg["data"]
     assert a["input_shapes"] == [(d["micro_batch_size"], d["seq_len"] // 2)], a["input_shapes"]   # half of every row
+    for x, y in zip(a["hist"], b["hist"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
+
+
+@pytest.mark.parametrize("mesh,extra", [({"dp": 2, "cp": 2}, {}),
+                                        ({"dp": 2, "tp": 2}, {"tp": {"loss_parallel": True}})])
+def test_model_parallel_axes_with_data_parallel_replicas(tmp_path, mesh, extra):
+    """Four ranks: two data-parallel replicas of a context-parallel (or tensor-parallel, loss-parallel) pair, against
+    one process fed both replicas' rows.  Pins the flattened gradient axis, the per-replica loss divisor and the
+    gather of the head-gradient rows when the axes combine."""
+    cfg = parity_config(world=2, steps=STEPS, accumulation=2, mesh=mesh)
+    cfg.update(extra)
+    run_distributed(_run_hist_only, 4, cfg, str(tmp_path), str(tmp_path / "four.pt"), timeout_s=300)
+    a, b = torch.load(tmp_path / "four.pt"), _single_process(tmp_path, 4, 2)
     for x, y in zip(a["hist"], b["hist"]):
         assert abs(x["loss"] - y["loss"]) < 1e-4 * max(1.0, abs(y["loss"])), (x, y)
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-3 * max(1.0, abs(y["grad_norm"])), (x, y)
