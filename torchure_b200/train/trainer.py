@@ -114,7 +114,9 @@ class Trainer:
         if not is_synthetic(self.config["data"]):
             from tokenizers import Tokenizer
 
-            self.tokenizer = Tokenizer.from_pretrained(self.config["data"]["tokenizer"])
+            name = self.config["data"]["tokenizer"]
+            # a hub id as in the reference's configs, or the path of a local tokenizer.json (no network needed)
+            self.tokenizer = Tokenizer.from_file(name) if os.path.isfile(name) else Tokenizer.from_pretrained(name)
 
         self.model = self._build_model()
         self._init_weights(self.model)
