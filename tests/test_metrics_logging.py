@@ -1,0 +1,70 @@
+"""Metrics sinks of the Trainer (reference ``torchure/train/trainer.py:404-441``): the wandb run (a stand-in object
+here: init arguments, one log call per step, finish, run id kept in the checkpoint and passed back on resume) and the
+JSONL sink."""
+
+import json
+import os
+
+import torch
+
+from tests.dist_utils import run_distributed
+from tests.tiny import parity_config
+
+
+class _FakeRun:
+    def __init__(self, calls, run_id):
+        self.calls, self.id = calls, run_id
+
+    def log(self, payload, step=None):
+        self.calls.append(("log", step, sorted(payload)))
+
+    def finish(self):
+        self.calls.append(("finish",))
+
+
+class _FakeWandb:
+    def __init__(self):
+        self.calls = []
+
+    def init(self, **kw):
+        self.calls.append(("init", {k: kw[k] for k in ("project", "entity", "id", "resume")}, "config" in kw))
+        return _FakeRun(self.calls, kw.get("id") or "run-abc")
+
+
+def _run(rank, world, home, out):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train import trainer as T
+
+    fake = _FakeWandb()
+    T.wandb, T.HAS_WANDB = fake, True
+
+    def cfg(**kw):
+        c = parity_config(1, steps=4, run_name="logged", accumulation=1, **kw)
+        c["wandb"] = {"enabled": True, "project": "proj", "entity": "me"}
+        c["logging"] = {"jsonl": os.path.join(home, "metrics", "log.jsonl")}
+        return c
+
+    first = T.Trainer(cfg(save_steps=2), rank, rank, world, device="cpu")
+    first.num_train_steps = 2
+    first.train()
+    second = T.Trainer(cfg(resume="auto", save_steps=1000), rank, rank, world, device="cpu")
+    second.train()
+    torch.save(fake.calls, out)
+
+
+def test_wandb_run_and_jsonl_sink(tmp_path):
+    run_distributed(_run, 1, str(tmp_path), str(tmp_path / "calls.pt"), timeout_s=240)
+    calls = torch.load(tmp_path / "calls.pt", weights_only=False)
+    inits = [c for c in calls if c[0] == "init"]
+    assert inits[0][1] == {"project": "proj", "entity": "me", "id": None, "resume": None} and inits[0][2]
+    # the resumed run continues the SAME wandb run: the id travelled through trainer.pt
+    assert inits[1][1] == {"project": "proj", "entity": "me", "id": "run-abc", "resume": "must"}
+    logs = [c for c in calls if c[0] == "log"]
+    assert [c[1] for c in logs] == [1, 2, 3, 4]
+    assert {"train/loss", "train/grad_norm", "train/lr", "train/tokens", "perf/tps", "perf/step_time"} <= set(logs[0][2])
+    assert sum(1 for c in calls if c[0] == "finish") == 2
+    with open(tmp_path / "metrics" / "log.jsonl") as f:
+        recs = [json.loads(line) for line in f]
+    assert [r["step"] for r in recs] == [1, 2, 3, 4]
+    assert all(r["loss"] > 0 and r["tps"] > 0 and r["lr"] >= 0 for r in recs)
+    assert recs[-1]["tokens"] == 4 * 256 * 2       # steps x seq_len x global batch
