@@ -1,6 +1,6 @@
-"""Metrics sinks of the Trainer (reference ``torchure/train/trainer.py:404-441``): the wandb run (a stand-in object
-here: init arguments, one log call per step, finish, run id kept in the checkpoint and passed back on resume) and the
-JSONL sink."""
+"""Optional parts of the Trainer.  Metrics sinks (reference ``torchure/train/trainer.py:404-441``): the wandb run (a
+stand-in object here: init arguments, one log call per step, finish, run id kept in the checkpoint and passed back on
+resume) and the JSONL sink.  Per-block ``torch.compile`` of the PyTorch path (reference ``trainer.py:223-244``)."""
 
 import json
 import os
@@ -68,3 +68,35 @@ def test_wandb_run_and_jsonl_sink(tmp_path):
     assert [r["step"] for r in recs] == [1, 2, 3, 4]
     assert all(r["loss"] > 0 and r["tps"] > 0 and r["lr"] >= 0 for r in recs)
     assert recs[-1]["tokens"] == 4 * 256 * 2       # steps x seq_len x global batch
+
+
+def _per_block_compile(rank, world, home, out):
+    os.environ["TORCHURE_B200_HOME"] = home
+    import torch._dynamo
+
+    from torchure_b200.train.trainer import Trainer
+
+    def cfg(name, **kw):
+        c = parity_config(1, steps=3, run_name=name, accumulation=1)
+        c["compile"] = False            # the PyTorch path
+        c.update(kw)
+        return c
+
+    compiled = Trainer(cfg("pbc", torch_compile=True, compile_backend="aot_eager"), rank, rank, world, benchmark=True,
+                       device="cpu")
+    # one compiled region per transformer block plus the final norm, as the reference compiles (not the whole model)
+    assert all(b._compiled_call_impl is not None for b in compiled.model.blocks)
+    assert compiled.model.norm._compiled_call_impl is not None and compiled.model._compiled_call_impl is None
+    a = compiled.train_n_step_test(3)
+    b = Trainer(cfg("pbe"), rank, rank, world, benchmark=True, device="cpu").train_n_step_test(3)
+    torch.save({"compiled": a, "eager": b}, out)
+
+
+def test_per_block_compile_of_the_pytorch_path(tmp_path):
+    """`torch_compile: true` (with `compile: false`): every block and the final norm become compiled regions; the run
+    follows the eager one.  `compile_backend: "aot_eager"` keeps the test independent of a host C++ toolchain."""
+    run_distributed(_per_block_compile, 1, str(tmp_path), str(tmp_path / "c.pt"), timeout_s=240)
+    got = torch.load(tmp_path / "c.pt")
+    for x, y in zip(got["compiled"], got["eager"]):
+        assert abs(x["loss"] - y["loss"]) < 1e-5 * max(1.0, abs(y["loss"])), (x, y)
+        assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-4 * max(1.0, abs(y["grad_norm"])), (x, y)

@@ -28,7 +28,8 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
     [init_from]   str    path of an unsharded model state dict to start from (any mesh; optimizer state starts fresh)
     [wandb]       {enabled, project, entity}
     [compile]     bool   per-block fused execution (hand-written kernels) on/off
-    [torch_compile] bool, [compile_mode] str   with compile=false: torch.compile every block of the PyTorch path
+    [torch_compile] bool, [compile_mode] str, [compile_backend] str
+                  with compile=false: torch.compile every block of the PyTorch path
     [log_every]   int
 """
 

@@ -164,16 +164,20 @@ class Trainer:
     def _build_model(self):
         """``compile: false`` selects the PyTorch path (the oracle) instead of the sm_100a engine.  On that path
         ``torch_compile: true`` compiles every transformer block and the final norm in place, one region per block as
-        the reference does (``torchure/train/trainer.py:223-244``), with the reference's ``compile_mode`` key."""
+        the reference does (``torchure/train/trainer.py:223-244``), with the reference's ``compile_mode`` key (and
+        ``compile_backend`` for a Dynamo backend other than Inductor)."""
         mc = dict(self.config["model"]["config"])
         if not self.config.get("compile", True):
             mc["impl"] = "torch"
         model = build_model(self.config["model"]["name"], mc)
         if self.config.get("torch_compile", False) and mc.get("impl") == "torch":
-            mode = self.config.get("compile_mode", "default")
+            # `compile_mode` is the reference's key (an Inductor mode); `compile_backend` selects another Dynamo backend
+            # (e.g. "aot_eager", which needs no host compiler)
+            backend = self.config.get("compile_backend", "inductor")
+            kw = {"mode": self.config.get("compile_mode", "default")} if backend == "inductor" else {"backend": backend}
             for block in model.blocks:
-                block.compile(mode=mode)
-            model.norm.compile(mode=mode)
+                block.compile(**kw)
+            model.norm.compile(**kw)
         return model
 
     def _init_weights(self, model) -> None:
