@@ -100,3 +100,26 @@ def test_per_block_compile_of_the_pytorch_path(tmp_path):
     for x, y in zip(got["compiled"], got["eager"]):
         assert abs(x["loss"] - y["loss"]) < 1e-5 * max(1.0, abs(y["loss"])), (x, y)
         assert abs(x["grad_norm"] - y["grad_norm"]) < 1e-4 * max(1.0, abs(y["grad_norm"])), (x, y)
+
+
+def test_command_line_entrypoint_under_torchrun(tmp_path):
+    """`python -m torch.distributed.run ... -m torchure_b200.train.train --config C --steps N` (the reference's
+    interface, ``torchure/train/train.py:45-87``): two CPU ranks over gloo, benchmark mode, rank 0 prints one line per
+    step, both ranks exit 0 after destroying the process group."""
+    import subprocess
+    import sys
+
+    from tests.dist_utils import free_port
+
+    cfg = parity_config(2, steps=3, run_name="cli", accumulation=1)
+    path = tmp_path / "cli.json"
+    path.write_text(json.dumps(cfg))
+    env = dict(os.environ, TORCHURE_B200_HOME=str(tmp_path), OMP_NUM_THREADS="2")
+    out = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+         "127.0.0.1", "--master-port", str(free_port()), "-m", "torchure_b200.train.train", "--config", str(path),
+         "--steps", "3"],
+        capture_output=True, text=True, timeout=240, env=env, cwd=os.path.dirname(os.path.dirname(__file__)))
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("step=")]
+    assert len(lines) == 3 and "loss=" in lines[0] and "tps=" in lines[0], out.stdout[-1000:]
