@@ -41,7 +41,10 @@ def _entry(rank, world, port, fn, args, errq, timeout_s):
 
 
 def run_distributed(fn, world_size: int, *args, timeout_s: int = 60, join_s: int | None = None):
-    ctx = mp.get_context("spawn")
+    # a fork server that has torch imported already: every rank starts as a fork of that single-threaded server
+    # instead of a fresh interpreter that imports torch again (seconds per rank, dozens of ranks per session)
+    ctx = mp.get_context("forkserver")
+    ctx.set_forkserver_preload(["torch", "torch.distributed", "torch.multiprocessing"])
     errq = ctx.Queue()
     port = free_port()
     procs = [ctx.Process(target=_entry, args=(r, world_size, port, fn, args, errq, timeout_s))
