@@ -240,6 +240,30 @@ def test_expert_parallel_moe():
     run_distributed(_moe, 2, timeout_s=120)
 
 
+def _moe_autocast(rank, world):
+    """The dtype flow of a mixed-precision step (bf16 expert GEMMs and token exchange inside an fp32 residual stream),
+    exercised with CPU autocast: the layer must run, return the stream's dtype and stay close to its fp32 result."""
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.parallel.expert_parallel import MoELayer
+
+    mesh = Mesh({"ep": world})
+    torch.manual_seed(0)
+    layer = MoELayer(16, 32, num_experts=4, top_k=2, capacity_factor=8.0)
+    layer.shard_(mesh, "ep")
+    x = torch.randn(2, 6, 16, generator=torch.Generator().manual_seed(rank)).requires_grad_()
+    want = layer(x)
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        got = layer(x)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got, want, rtol=5e-2, atol=5e-3)
+    got.sum().backward()
+    assert x.grad is not None and torch.isfinite(x.grad).all()
+
+
+def test_expert_parallel_moe_mixed_precision():
+    run_distributed(_moe_autocast, 2, timeout_s=120)
+
+
 def _pp(rank, world, schedule):
     from torchure_b200.core.mesh import Mesh
     from torchure_b200.parallel.pipeline import PipelineStage, run_schedule, split_layers

@@ -102,6 +102,6 @@ class MoELayer(nn.Module):
         else:
             y = y.reshape(self.E * C, self.hidden)
         out = x.new_zeros(T, self.hidden)
-        contrib = y[slot[keep]] * gate.reshape(-1)[keep][:, None].to(y.dtype)
-        out = out.index_add(0, token[keep], contrib)
+        contrib = y[slot[keep]].to(out.dtype) * gate.reshape(-1)[keep][:, None].to(out.dtype)
+        out = out.index_add(0, token[keep], contrib)      # (under autocast y is bf16 while the residual stream is fp32)
         return out.view(shape)
