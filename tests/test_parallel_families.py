@@ -240,6 +240,37 @@ def test_expert_parallel_moe():
     run_distributed(_moe, 2, timeout_s=120)
 
 
+def _cp_autocast(rank, world):
+    """Context parallelism on the module path with mixed precision (CPU autocast stands in for the GPU's): bf16
+    q / k / v through the PyTorch ring and through Ulysses, loss (averaged over the axis) against the fp32
+    single-process value."""
+    from torchure_b200.core.mesh import Mesh
+    from torchure_b200.models import Qwen3
+    from torchure_b200.objectives import ARObjective
+
+    mesh = Mesh({"cp": world})
+    torch.manual_seed(0)
+    m = Qwen3(**dict(CFG, num_layers=2), impl="torch")
+    m.init_weights()
+    ids = torch.randint(0, CFG["vocab_size"], (2, 64), generator=torch.Generator().manual_seed(1))
+    obj = ARObjective(fused_linear_ce=True, ce_chunk_size=32)
+    want = obj.compute_loss(m, {"input_ids": ids, "labels": ids}).item()
+    for kind in ("ring", "ulysses"):
+        m.cp, m.cp_kind = (mesh, "cp"), kind
+        with torch.autocast("cpu", dtype=torch.bfloat16):
+            loss = obj.compute_loss(m, {"input_ids": ids, "labels": ids})
+        loss.backward()
+        total = loss.detach().clone()
+        torch.distributed.all_reduce(total)
+        assert abs(total.item() / world - want) < 5e-3 * abs(want), (kind, total.item() / world, want)
+        assert all(torch.isfinite(p.grad).all() for p in m.parameters())
+        m.zero_grad()
+
+
+def test_context_parallel_module_path_mixed_precision():
+    run_distributed(_cp_autocast, 2, timeout_s=120)
+
+
 def _moe_autocast(rank, world):
     """The dtype flow of a mixed-precision step (bf16 expert GEMMs and token exchange inside an fp32 residual stream),
     exercised with CPU autocast: the layer must run, return the stream's dtype and stay close to its fp32 result."""
