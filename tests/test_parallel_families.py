@@ -271,6 +271,40 @@ def test_context_parallel_module_path_mixed_precision():
     run_distributed(_cp_autocast, 2, timeout_s=120)
 
 
+def test_moe_load_balancing_term():
+    """E * sum_e share_e * mean-probability_e: exactly 1 for a router that is indifferent, larger for one that
+    over-subscribes an expert, differentiable through the router's probabilities; the model averages it over its
+    layers and the objective adds `aux_loss_coef` times it."""
+    from torchure_b200.models import build_model
+    from torchure_b200.objectives import ARObjective
+    from torchure_b200.parallel.expert_parallel import MoELayer
+
+    torch.manual_seed(0)
+    layer = MoELayer(16, 32, num_experts=4, top_k=2)
+    x = torch.randn(64, 16)
+    with torch.no_grad():
+        layer.router.weight.zero_()
+    layer(x)
+    torch.testing.assert_close(layer.aux_loss, torch.tensor(1.0))
+    with torch.no_grad():
+        layer.router.weight[0] = 0.5 * x.mean(0).sign()      # favours expert 0 for most tokens
+        layer.router.weight[0] += 0.3
+    layer(x + 1.0)
+    assert layer.aux_loss.item() > 1.05
+    layer.aux_loss.backward()
+    assert layer.router.weight.grad.abs().sum() > 0
+    cfg = dict(CFG, num_layers=2, num_experts=4, top_k=2, moe_ffn_dim=32, aux_loss_coef=0.5)
+    model = build_model("qwen3_moe", cfg)
+    model.init_weights()
+    ids = torch.randint(0, CFG["vocab_size"], (2, 16), generator=torch.Generator().manual_seed(0))
+    obj = ARObjective(fused_linear_ce=True, ce_chunk_size=16)
+    with_aux = obj.compute_loss(model, {"input_ids": ids, "labels": ids})
+    aux = model.aux_loss().detach()
+    model.aux_loss_coef = 0.0
+    plain = obj.compute_loss(model, {"input_ids": ids, "labels": ids})
+    torch.testing.assert_close(with_aux.detach(), plain.detach() + 0.5 * aux, rtol=1e-5, atol=1e-6)
+
+
 def _moe_autocast(rank, world):
     """The dtype flow of a mixed-precision step (bf16 expert GEMMs and token exchange inside an fp32 residual stream),
     exercised with CPU autocast: the layer must run, return the stream's dtype and stay close to its fp32 result."""

@@ -22,14 +22,17 @@ from torchure_b200.parallel.expert_parallel import MoELayer
 class Qwen3MoE(Qwen3):
     def __init__(self, num_layers: int, num_heads: int, num_kv_heads: int, emb_dim: int, head_dim: int | None,
                  vocab_size: int, num_experts: int, top_k: int = 2, moe_ffn_dim: int | None = None,
-                 capacity_factor: float = 2.0, ffn_dim: int | None = None, norm_eps: float = 1e-6,
+                 capacity_factor: float = 2.0, aux_loss_coef: float = 0.01, ffn_dim: int | None = None,
+                 norm_eps: float = 1e-6,
                  rope_theta: float = 1_000_000.0, qk_norm: bool = True, tie_embeddings: bool = True,
                  impl: str = "torch"):
         super().__init__(num_layers=num_layers, num_heads=num_heads, num_kv_heads=num_kv_heads, emb_dim=emb_dim,
                          head_dim=head_dim, vocab_size=vocab_size, ffn_dim=ffn_dim, norm_eps=norm_eps,
                          rope_theta=rope_theta, qk_norm=qk_norm, tie_embeddings=tie_embeddings, impl="torch")
         width = moe_ffn_dim if moe_ffn_dim is not None else self.cfg["ffn_dim"]
-        self.cfg.update(num_experts=num_experts, top_k=top_k, moe_ffn_dim=width, capacity_factor=capacity_factor)
+        self.cfg.update(num_experts=num_experts, top_k=top_k, moe_ffn_dim=width, capacity_factor=capacity_factor,
+                        aux_loss_coef=aux_loss_coef)
+        self.aux_loss_coef = aux_loss_coef
         for block in self.blocks:
             block.ffn = MoELayer(emb_dim, width, num_experts, top_k, capacity_factor)
 
@@ -49,6 +52,12 @@ class Qwen3MoE(Qwen3):
         for b in self.blocks:
             b.gqa.o_proj.weight.mul_(scale)
             b.ffn.w_down.mul_(scale)
+
+    def aux_loss(self) -> torch.Tensor:
+        """Mean over the layers of the routers' load-balancing terms of the LAST forward pass; the objective adds
+        ``aux_loss_coef`` times this to the language-model loss."""
+        terms = [b.ffn.aux_loss for b in self.blocks]
+        return torch.stack(terms).mean()
 
     def fused_param_groups(self):
         return [(b.gqa.q_proj.weight, b.gqa.k_proj.weight, b.gqa.v_proj.weight) for b in self.blocks]

@@ -19,6 +19,12 @@ class ARObjective:
         cp = getattr(model, "cp", None)
         if cp is not None:
             return self._compute_loss_cp(model, batch, loss_scale, *cp)
+        coef = getattr(model, "aux_loss_coef", 0.0)
+        if coef:      # mixture-of-experts model: add the routers' load-balancing term of this forward pass
+            return self._lm_loss(model, batch, loss_scale) + (coef * loss_scale) * model.aux_loss()
+        return self._lm_loss(model, batch, loss_scale)
+
+    def _lm_loss(self, model, batch, loss_scale: float) -> torch.Tensor:
         if self.fused_linear_ce:
             hidden = model(batch["input_ids"], return_final_hidden=True)
             labels = shift_labels(batch["labels"], self.ignore_index)

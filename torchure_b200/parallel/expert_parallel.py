@@ -42,6 +42,7 @@ class MoELayer(nn.Module):
         assert num_experts % self.n == 0, "experts must divide evenly over the ep axis"
         self.local_E = num_experts // self.n
         self.router = nn.Linear(hidden, num_experts, bias=False)
+        self.aux_loss = None
         self.w_gate = nn.Parameter(torch.empty(self.local_E, ffn, hidden))
         self.w_up = nn.Parameter(torch.empty(self.local_E, ffn, hidden))
         self.w_down = nn.Parameter(torch.empty(self.local_E, hidden, ffn))
@@ -79,6 +80,11 @@ class MoELayer(nn.Module):
         probs = F.softmax(self.router(x).float(), dim=-1)
         gate, expert = probs.topk(self.k, dim=-1)                 # (T, k)
         gate = gate / gate.sum(-1, keepdim=True)
+        # load-balancing term (Switch Transformer): E * sum_e (share of the assignments that went to e) * (mean router
+        # probability of e); 1 when routing is uniform, larger when experts are over-subscribed.  Over this rank's
+        # tokens; the owner of the loss reads `aux_loss` after the forward pass
+        share = F.one_hot(expert, self.E).sum(dim=(0, 1)).float() / (T * self.k)
+        self.aux_loss = self.E * (share * probs.mean(0)).sum()
         # slot of every (token, choice) inside its expert's buffer; choices beyond the capacity are dropped
         flat_e = expert.reshape(-1)
         onehot = F.one_hot(flat_e, self.E)
