@@ -123,3 +123,46 @@ def test_command_line_entrypoint_under_torchrun(tmp_path):
     assert out.returncode == 0, out.stderr[-2000:]
     lines = [ln for ln in out.stdout.splitlines() if ln.startswith("step=")]
     assert len(lines) == 3 and "loss=" in lines[0] and "tps=" in lines[0], out.stdout[-1000:]
+
+
+def _with_eval(rank, world, home, out):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    def cfg(name, mesh, **kw):
+        c = parity_config(world, steps=4, run_name=name, accumulation=1, mesh=mesh)
+        c["logging"] = {"jsonl": os.path.join(home, f"{name}.jsonl")}
+        c.update(kw)
+        return c
+
+    def weights(tr):
+        if getattr(tr, "sharded", False):
+            return {n: v.detach().clone() for n, v in tr.ddp.full_state_dict().items()}
+        return {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+
+    result = {}
+    for name, mesh in (("ddp", {"dp": world}), ("fsdp", {"dp_shard": world})):
+        plain = Trainer(cfg(f"{name}_plain", mesh), rank, rank, world, device="cpu")
+        plain.train()
+        evald = Trainer(cfg(f"{name}_eval", mesh, eval={"every": 2, "batches": 3}), rank, rank, world, device="cpu")
+        first = evald.evaluate().item()
+        assert evald.evaluate().item() == first           # the held-out stream restarts at every call
+        evald.train()
+        last = evald.evaluate().item()
+        a, b = weights(plain), weights(evald)
+        assert all(torch.equal(a[n], b[n]) for n in a), f"{name}: evaluating changed the training trajectory"
+        result[name] = (first, last)
+    if rank == 0:
+        torch.save(result, out)
+
+
+def test_held_out_evaluation(tmp_path):
+    """`eval: {every, batches}`: the loss on a held-out synthetic stream is logged at the cadence, is the same on
+    repeated calls, and leaves training untouched (bitwise the weights of a run without it), for DDP and FSDP."""
+    run_distributed(_with_eval, 2, str(tmp_path), str(tmp_path / "e.pt"), timeout_s=300)
+    got = torch.load(tmp_path / "e.pt")
+    assert abs(got["ddp"][0] - got["fsdp"][0]) < 1e-4 and got["ddp"][0] > 8.0      # ~ln(4096) at initialisation
+    with open(tmp_path / "ddp_eval.jsonl") as f:
+        recs = [json.loads(line) for line in f]
+    assert [("eval_loss" in r) for r in recs] == [False, True, False, True]
+    assert all(r["eval_loss"] > 0 for r in recs if "eval_loss" in r)

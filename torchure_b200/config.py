@@ -25,6 +25,8 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
     [comm]        {backend: "sm100" | "torch", [max_bytes]}
     checkpointing {save_steps, resume: null|"auto"|int, [resume_scheduler]}
     run_name      str
+    [eval]        {every: steps between held-out evaluations (0 = never), [batches]: micro-batches per rank,
+                   [data]: overrides of the data section for the held-out stream}
     [init_from]   str    path of an unsharded model state dict to start from (any mesh; optimizer state starts fresh)
     [wandb]       {enabled, project, entity}
     [compile]     bool   per-block fused execution (hand-written kernels) on/off

@@ -24,6 +24,13 @@ class ARObjective:
             return self._lm_loss(model, batch, loss_scale) + (coef * loss_scale) * model.aux_loss()
         return self._lm_loss(model, batch, loss_scale)
 
+    def eval_loss(self, model, batch: dict[str, torch.Tensor]) -> torch.Tensor:
+        """The language-model loss alone (no auxiliary terms), for held-out evaluation."""
+        cp = getattr(model, "cp", None)
+        if cp is not None:
+            return self._compute_loss_cp(model, batch, 1.0, *cp)
+        return self._lm_loss(model, batch, 1.0)
+
     def _lm_loss(self, model, batch, loss_scale: float) -> torch.Tensor:
         if self.fused_linear_ce:
             hidden = model(batch["input_ids"], return_final_hidden=True)

@@ -299,6 +299,38 @@ class Trainer:
         return build_dataloader(data_cfg, self.tokenizer, self.ignore_index,
                                 self.mesh.coordinate(self.data_axis), self.mesh.size(self.data_axis))
 
+    # -- held-out loss ---------------------------------------------------------------------------
+    @torch.no_grad()
+    def evaluate(self) -> torch.Tensor:
+        """Mean next-token loss over ``eval.batches`` micro-batches per data-parallel rank of a held-out stream: the
+        ``data`` section with the overrides of ``eval.data`` (for the synthetic source the seed defaults to the
+        training seed + 1).  The stream starts from its beginning at every call, so successive values are comparable;
+        training state (loader position, RNG, optimizer) is untouched.  Not in the reference, whose notes quote a
+        held-out perplexity without shipping the loop."""
+        ecfg = self.config.get("eval", {})
+        assert self.pp_size == 1, "evaluation under pipeline parallelism is not implemented"
+        data_cfg = dict(self.config["data"])
+        data_cfg.setdefault("vocab_size", self.config["model"]["config"]["vocab_size"])
+        data_cfg["seed"] = data_cfg.get("seed", 0) + 1
+        data_cfg.update(ecfg.get("data", {}))
+        loader = iter(build_dataloader(data_cfg, self.tokenizer, self.ignore_index,
+                                       self.mesh.coordinate(self.data_axis), self.mesh.size(self.data_axis)))
+        if hasattr(self.ddp, "begin_step"):
+            self.ddp.begin_step()      # sharded weights: gather what the last optimizer step changed (idempotent)
+        total = torch.zeros((), device=self.device)
+        n = int(ecfg.get("batches", 8))
+        for _ in range(n):
+            batch = {k: v.to(self.device, non_blocking=True) for k, v in next(loader).items()}
+            if self.on_gpu:
+                with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+                    total += self.objective.eval_loss(self.model, batch).float()
+            else:
+                total += self.objective.eval_loss(self.model, batch).float()
+        total /= n
+        if self.mesh.size(self.grad_axis) > 1:
+            all_reduce(total, self.mesh, self.grad_axis, "avg")
+        return total
+
     def _setup_wandb(self) -> None:
         self.wandb_run = None
         wcfg = self.config.get("wandb", {})
@@ -663,11 +695,15 @@ class Trainer:
             rec = {"step": step, "loss": metrics["loss"].item(), "grad_norm": metrics["grad_norm"].item(),
                    "lr": self.scheduler.get_last_lr()[0], "tokens": step * tokens_per_step,
                    "tps": tokens_per_step / seconds, "step_time": seconds, "mfu": self._mfu(tokens_per_step, seconds)}
+            if "eval_loss" in metrics:
+                rec["eval_loss"] = metrics["eval_loss"].item()
             os.makedirs(os.path.dirname(os.path.abspath(jsonl)), exist_ok=True)
             with open(jsonl, "a") as f:
                 f.write(json.dumps(rec) + "\n")
         if self.wandb_run is None:
             return
+        if "eval_loss" in metrics:
+            self.wandb_run.log({"eval/loss": metrics["eval_loss"].item()}, step=step)
         self.wandb_run.log({
             "train/loss": metrics["loss"].item(), "train/grad_norm": metrics["grad_norm"].item(),
             "train/lr": self.scheduler.get_last_lr()[0], "train/tokens": step * tokens_per_step,
@@ -685,10 +721,15 @@ class Trainer:
                     self.checkpoint(done)
                 if done % self.log_every == 0 or done == self.num_train_steps:
                     self.check_device_errors()   # every rank, at the cadence at which rank 0 reads the loss anyway
+                every = int(self.config.get("eval", {}).get("every", 0))
+                if every and (done % every == 0 or done == self.num_train_steps):
+                    metrics["eval_loss"] = self.evaluate()        # a collective: every rank takes part
                 if self.rank == 0:
                     self._log_metrics(metrics, done, tokens_per_step, seconds)
                     if done % self.log_every == 0 or done == self.num_train_steps:
                         print(self._line(step, metrics, seconds, tokens_per_step), flush=True)
+                    if "eval_loss" in metrics:
+                        print(f"step={step} || eval_loss={metrics['eval_loss'].item():.4f}", flush=True)
             if self.rank == 0 and self.on_gpu:
                 print(f"peak cuda mem: {torch.cuda.max_memory_allocated() / 2**30:.2f} GiB")
         finally:
