@@ -108,3 +108,18 @@ def test_prefetcher_position_is_exact(tmp_path):
     dl2.load_state_dict(state)
     pf2 = CUDAPrefetcher(dl2, torch.device("cpu"))
     assert torch.equal(next(pf2)["input_ids"], want)
+
+
+def test_prune_keeps_the_newest_complete_steps(tmp_path):
+    from torchure_b200.ckpt import Checkpointer
+
+    ck = Checkpointer(str(tmp_path))
+    for step in (2, 4, 6, 8):
+        ck.save_trainer({"step": step}, step)
+        ck.mark_complete(step)
+    ck.save_trainer({"step": 5}, 5)          # a writer died here before the marker
+    ck.save_trainer({"step": 10}, 10)        # ... and one is being written right now
+    assert ck.prune(2) == [2, 4, 5]
+    assert sorted(p.name for p in tmp_path.iterdir()) == ["10", "6", "8"]
+    assert ck.latest() == 8 and ck.valid_step(6) == 6 and ck.valid_step(4) is None
+    assert ck.prune(2) == []

@@ -166,3 +166,18 @@ def test_held_out_evaluation(tmp_path):
         recs = [json.loads(line) for line in f]
     assert [("eval_loss" in r) for r in recs] == [False, True, False, True]
     assert all(r["eval_loss"] > 0 for r in recs if "eval_loss" in r)
+
+
+def _keep_last(rank, world, home):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    cfg = parity_config(1, steps=5, run_name="pruned", accumulation=1, save_steps=1)
+    cfg["checkpointing"]["keep_last"] = 2
+    Trainer(cfg, rank, rank, world, device="cpu").train()
+
+
+def test_keep_last_bounds_the_checkpoints_on_disk(tmp_path):
+    run_distributed(_keep_last, 1, str(tmp_path), timeout_s=240)
+    assert sorted(os.listdir(tmp_path / "checkpoints" / "pruned")) == ["4", "5"]
+    assert (tmp_path / "checkpoints" / "pruned" / "5" / ".complete").exists()

@@ -12,7 +12,7 @@ Layout (reference ``torchure/checkpoint/checkpointer.py:18-102`` and ``trainer.p
 Files are written to a temporary name and renamed, so a crash leaves either the old file
 or the new one.  ``latest()`` / ``valid_step()`` only see completed steps.  Sharded
 strategies store per-shard files (``model_shard{r}.pt``, ``optimizer_shard{r}.pt``) in the
-same directory.
+same directory.  ``prune(keep_last)`` (config ``checkpointing.keep_last``) bounds the disk a long run uses.
 """
 
 from __future__ import annotations
@@ -56,6 +56,28 @@ class Checkpointer:
 
     def is_complete(self, step: int) -> bool:
         return (self.step_dir(step) / MARKER).exists()
+
+    def prune(self, keep_last: int) -> list[int]:
+        """Delete all but the newest `keep_last` COMPLETE steps (one caller per run: rank 0, after the newest step was
+        marked).  A step loses its marker first, so an interrupted deletion leaves a directory that does not count
+        as a checkpoint.  Incomplete directories older than the newest complete step are leftovers of a crashed
+        writer and go as well.  Returns the steps removed."""
+        import shutil
+
+        assert keep_last >= 1
+        steps = sorted(self._steps())
+        doomed = steps[:-keep_last]
+        newest = steps[-1] if steps else None
+        for child in self.root.iterdir():
+            if child.name.isdigit() and not (child / MARKER).exists() and newest is not None and int(child.name) < newest:
+                doomed.append(int(child.name))
+        for step in doomed:
+            d = self.step_dir(step)
+            marker = d / MARKER
+            if marker.exists():
+                marker.unlink()
+            shutil.rmtree(d, ignore_errors=True)
+        return sorted(doomed)
 
     # -- raw io ----------------------------------------------------------------------------
     def _write(self, payload, step: int, name: str) -> None:

@@ -400,6 +400,9 @@ class Trainer:
         barrier()
         if self.rank == 0:
             self.checkpointer.mark_complete(step)
+            keep = self.config["checkpointing"].get("keep_last")
+            if keep:
+                self.checkpointer.prune(int(keep))
 
     def _split_axis(self) -> str:
         """The axis whose coordinates hold different tensors (one checkpoint shard each)."""
