@@ -181,3 +181,47 @@ def test_keep_last_bounds_the_checkpoints_on_disk(tmp_path):
     run_distributed(_keep_last, 1, str(tmp_path), timeout_s=240)
     assert sorted(os.listdir(tmp_path / "checkpoints" / "pruned")) == ["4", "5"]
     assert (tmp_path / "checkpoints" / "pruned" / "5" / ".complete").exists()
+
+
+def _preempted(rank, world, home, out):
+    import signal
+
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    def cfg(name, **kw):
+        c = parity_config(2, steps=5, run_name=name, accumulation=1, **kw)
+        c["checkpointing"]["on_signal"] = True
+        return c
+
+    def weights(tr):
+        return {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+
+    straight = Trainer(cfg("pre_straight"), rank, rank, world, device="cpu")
+    straight.train()
+    first = Trainer(cfg("pre_resumed"), rank, rank, world, device="cpu")
+    calls = []
+
+    def in_second_step(mod, args):      # ONE rank is told to stop, in the middle of its second step
+        calls.append(1)
+        if rank == 1 and len(calls) == 2:
+            os.kill(os.getpid(), signal.SIGTERM)
+
+    first.model.register_forward_pre_hook(in_second_step)
+    first.train()
+    assert len(calls) == 2, "both ranks must leave after the step in which the signal arrived"
+    second = Trainer(cfg("pre_resumed", resume="auto"), rank, rank, world, device="cpu")
+    assert second.start_step == 2
+    second.train()
+    if rank == 0:
+        torch.save({"a": weights(straight), "b": weights(second)}, out)
+
+
+def test_signal_checkpoints_and_leaves_at_a_step_boundary(tmp_path):
+    """`checkpointing.on_signal`: SIGTERM on one rank during a step; every rank finishes the step, all write a
+    checkpoint of it and leave; the resumed run ends, bit for bit, where an undisturbed run does."""
+    run_distributed(_preempted, 2, str(tmp_path), str(tmp_path / "p.pt"), timeout_s=240)
+    got = torch.load(tmp_path / "p.pt")
+    for n in got["a"]:
+        assert torch.equal(got["a"][n], got["b"][n]), n
+    assert sorted(os.listdir(tmp_path / "checkpoints" / "pre_resumed")) == ["2", "5"]

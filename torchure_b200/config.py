@@ -23,7 +23,8 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
                   sequence all-to-alls around whole-sequence attention
     [pp]          {[schedule]: "1f1b" | "gpipe"}   with mesh {"dp": D, "pp": P}: contiguous stages of blocks
     [comm]        {backend: "sm100" | "torch", [max_bytes]}
-    checkpointing {save_steps, resume: null|"auto"|int, [resume_scheduler], [keep_last]: complete steps kept on disk}
+    checkpointing {save_steps, resume: null|"auto"|int, [resume_scheduler], [keep_last]: complete steps kept on disk,
+                   [on_signal]: checkpoint and leave at the next log cadence after SIGTERM / SIGUSR1}
     run_name      str
     [eval]        {every: steps between held-out evaluations (0 = never), [batches]: micro-batches per rank,
                    [data]: overrides of the data section for the held-out stream}

@@ -714,15 +714,44 @@ class Trainer:
             "perf/peak_mem_gib": torch.cuda.max_memory_allocated() / 2**30 if self.on_gpu else 0.0,
         }, step=step)
 
+    # -- preemption ------------------------------------------------------------------------------
+    def _watch_signals(self) -> None:
+        """``checkpointing.on_signal: true``: SIGTERM / SIGUSR1 (what a scheduler sends before it takes the machines
+        away) only set a flag; at the next log cadence the ranks agree on it (one max-reduce of a flag, where every
+        rank synchronises anyway), write a checkpoint of the step just completed and leave the loop, so that
+        ``resume: "auto"`` continues from there.  A rank is never stopped in the middle of a step or a collective."""
+        import signal
+
+        self._stop_requested = False
+        if not self.config["checkpointing"].get("on_signal", False):
+            return
+
+        def note(signum, frame):
+            self._stop_requested = True
+
+        for sig in (signal.SIGTERM, signal.SIGUSR1):
+            signal.signal(sig, note)
+
+    def _stop_agreed(self) -> bool:
+        if not self.config["checkpointing"].get("on_signal", False):
+            return False
+        flag = torch.tensor([1.0 if self._stop_requested else 0.0], device=self.device)
+        if self.world_size > 1:
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MAX)
+        return bool(flag.item() > 0)
+
     def train(self) -> None:
         tokens_per_step = self.config["data"]["seq_len"] * self.global_batch_size
+        self._watch_signals()
         try:
             for step in range(self.start_step, self.num_train_steps):
                 metrics, seconds = self.train_step()
                 done = step + 1
-                if (done % self.save_steps == 0 and step != 0) or done == self.num_train_steps:
+                at_cadence = done % self.log_every == 0 or done == self.num_train_steps
+                stop = at_cadence and done != self.num_train_steps and self._stop_agreed()
+                if (done % self.save_steps == 0 and step != 0) or done == self.num_train_steps or stop:
                     self.checkpoint(done)
-                if done % self.log_every == 0 or done == self.num_train_steps:
+                if at_cadence:
                     self.check_device_errors()   # every rank, at the cadence at which rank 0 reads the loss anyway
                 every = int(self.config.get("eval", {}).get("every", 0))
                 if every and (done % every == 0 or done == self.num_train_steps):
@@ -733,6 +762,10 @@ class Trainer:
                         print(self._line(step, metrics, seconds, tokens_per_step), flush=True)
                     if "eval_loss" in metrics:
                         print(f"step={step} || eval_loss={metrics['eval_loss'].item():.4f}", flush=True)
+                if stop:
+                    if self.rank == 0:
+                        print(f"stop requested by a signal: checkpoint written after step {done}, leaving", flush=True)
+                    break
             if self.rank == 0 and self.on_gpu:
                 print(f"peak cuda mem: {torch.cuda.max_memory_allocated() / 2**30:.2f} GiB")
         finally:
