@@ -225,3 +225,51 @@ def test_signal_checkpoints_and_leaves_at_a_step_boundary(tmp_path):
     for n in got["a"]:
         assert torch.equal(got["a"][n], got["b"][n]), n
     assert sorted(os.listdir(tmp_path / "checkpoints" / "pre_resumed")) == ["2", "5"]
+
+
+def _async_ckpt(rank, world, home, out):
+    os.environ["TORCHURE_B200_HOME"] = home
+    from torchure_b200.train.trainer import Trainer
+
+    def cfg(name, **kw):
+        c = parity_config(2, steps=5, run_name=name, accumulation=1, **kw)
+        c["checkpointing"]["async"] = True
+        return c
+
+    def weights(tr):
+        return {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+
+    # the files hold the state at the moment of checkpoint(), whatever training does while they are written, and the
+    # step exists only after finish_checkpoint()
+    probe = Trainer(cfg("async_probe"), rank, rank, world, device="cpu")
+    probe.train_step()
+    probe.train_step()
+    at_two = weights(probe)
+    probe.checkpoint(2)
+    assert not probe.checkpointer.is_complete(2)
+    probe.train_step()
+    probe.finish_checkpoint()
+    torch.distributed.barrier()          # rank 0 writes the marker after every rank's files are on disk
+    assert probe.checkpointer.is_complete(2)
+    saved = probe.checkpointer._read(2, "model.pt")
+    assert all(torch.equal(saved[n], at_two[n]) for n in at_two)
+    assert not torch.equal(saved["norm.weight"], weights(probe)["norm.weight"])
+    # and a run interrupted after step 3 resumes exactly
+    straight = Trainer(cfg("async_straight"), rank, rank, world, device="cpu")
+    straight.train()
+    first = Trainer(cfg("async_resumed", save_steps=3), rank, rank, world, device="cpu")
+    first.num_train_steps = 3
+    first.train()
+    second = Trainer(cfg("async_resumed", resume="auto", save_steps=1000), rank, rank, world, device="cpu")
+    assert second.start_step == 3
+    second.train()
+    if rank == 0:
+        torch.save({"a": weights(straight), "b": weights(second)}, out)
+
+
+def test_asynchronous_checkpoints(tmp_path):
+    run_distributed(_async_ckpt, 2, str(tmp_path), str(tmp_path / "a.pt"), timeout_s=240)
+    got = torch.load(tmp_path / "a.pt")
+    for n in got["a"]:
+        assert torch.equal(got["a"][n], got["b"][n]), n
+    assert sorted(os.listdir(tmp_path / "checkpoints" / "async_resumed")) == ["3", "5"]

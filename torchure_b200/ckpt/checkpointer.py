@@ -12,7 +12,9 @@ Layout (reference ``torchure/checkpoint/checkpointer.py:18-102`` and ``trainer.p
 Files are written to a temporary name and renamed, so a crash leaves either the old file
 or the new one.  ``latest()`` / ``valid_step()`` only see completed steps.  Sharded
 strategies store per-shard files (``model_shard{r}.pt``, ``optimizer_shard{r}.pt``) in the
-same directory.  ``prune(keep_last)`` (config ``checkpointing.keep_last``) bounds the disk a long run uses.
+same directory.  With ``background=True`` (config ``checkpointing.async``) the files are written by a worker thread from
+host snapshots while training goes on; the marker is only written once every rank's files are on disk.
+``prune(keep_last)`` (config ``checkpointing.keep_last``) bounds the disk a long run uses.
 """
 
 from __future__ import annotations
@@ -25,10 +27,63 @@ import torch
 MARKER = ".complete"
 
 
+def _host_snapshot(obj):
+    """A copy of `obj` that later training steps cannot change: tensors copied to host memory, containers rebuilt,
+    everything else deep-copied."""
+    import copy
+
+    if isinstance(obj, torch.Tensor):
+        return obj.detach().to("cpu", copy=True)
+    if isinstance(obj, dict):
+        return type(obj)((k, _host_snapshot(v)) for k, v in obj.items())
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_host_snapshot(v) for v in obj)
+    return copy.deepcopy(obj)
+
+
 class Checkpointer:
-    def __init__(self, root: str):
+    def __init__(self, root: str, background: bool = False):
+        """`background`: ``_write`` takes a host snapshot of its payload and returns; one worker thread serialises and
+        renames the files in order.  ``wait()`` blocks until everything queued is on disk (and re-raises a failed
+        write); the owner calls it before it marks a step complete."""
         self.root = Path(root)
         self.root.mkdir(parents=True, exist_ok=True)
+        self.background = background
+        self._queue = None
+        self._worker = None
+        self._failure: BaseException | None = None
+
+    # -- background writer -------------------------------------------------------------------
+    def _ensure_worker(self) -> None:
+        import queue
+        import threading
+
+        if self._worker is not None:
+            return
+        self._queue = queue.Queue()
+
+        def run():
+            while True:
+                job = self._queue.get()
+                try:
+                    if job is None:
+                        return
+                    if self._failure is None:
+                        self._write_now(*job)
+                except BaseException as e:      # reported by wait()
+                    self._failure = e
+                finally:
+                    self._queue.task_done()
+
+        self._worker = threading.Thread(target=run, name="checkpoint-writer", daemon=True)
+        self._worker.start()
+
+    def wait(self) -> None:
+        if self._queue is not None:
+            self._queue.join()
+        if self._failure is not None:
+            failure, self._failure = self._failure, None
+            raise RuntimeError("a background checkpoint write failed") from failure
 
     # -- discovery -------------------------------------------------------------------------
     def _steps(self) -> list[int]:
@@ -81,6 +136,13 @@ class Checkpointer:
 
     # -- raw io ----------------------------------------------------------------------------
     def _write(self, payload, step: int, name: str) -> None:
+        if self.background:
+            self._ensure_worker()
+            self._queue.put((_host_snapshot(payload), step, name))
+        else:
+            self._write_now(payload, step, name)
+
+    def _write_now(self, payload, step: int, name: str) -> None:
         final = self.step_dir(step, create=True) / name
         tmp = final.with_name(final.name + ".tmp")
         torch.save(payload, tmp)

@@ -24,6 +24,7 @@ Schema (superset of the reference's seven ``configs/*.json``; reference readers:
     [pp]          {[schedule]: "1f1b" | "gpipe"}   with mesh {"dp": D, "pp": P}: contiguous stages of blocks
     [comm]        {backend: "sm100" | "torch", [max_bytes]}
     checkpointing {save_steps, resume: null|"auto"|int, [resume_scheduler], [keep_last]: complete steps kept on disk,
+                   [async]: files written by a background thread from host snapshots,
                    [on_signal]: checkpoint and leave at the next log cadence after SIGTERM / SIGUSR1}
     run_name      str
     [eval]        {every: steps between held-out evaluations (0 = never), [batches]: micro-batches per rank,

@@ -151,7 +151,9 @@ class Trainer:
         self.run_name = f"{self.config['run_name']}_{stamp}"
         # keyed on the config's run_name alone so a relaunch finds its own checkpoints
         self.checkpointer_path = os.path.join(get_project_dir(), "checkpoints", self.config["run_name"])
-        self.checkpointer = Checkpointer(self.checkpointer_path)
+        self.checkpointer = Checkpointer(self.checkpointer_path,
+                                         background=bool(self.config["checkpointing"].get("async", False)))
+        self._unmarked_step: int | None = None
         ck = self.config["checkpointing"]
         self.resume, self.save_steps = ck["resume"], ck["save_steps"]
         self.resume_scheduler = ck.get("resume_scheduler", True)
@@ -364,6 +366,7 @@ class Trainer:
     def checkpoint(self, step: int) -> None:
         """Write the state after `step` completed steps; rank 0 writes replicas, every dp rank its loader."""
         self.check_device_errors()   # never persist the result of a step whose kernels gave up
+        self.finish_checkpoint()     # asynchronous writes: the previous step's files first
         if self.sharded:
             # model.pt keeps the reference's unsharded keys (gathered; collective), optimizer state stays sharded:
             # one file per shard coordinate, written by the first replica of that shard
@@ -397,6 +400,19 @@ class Trainer:
         if all(self.mesh.coordinate(a) == 0 for a in ("cp", "pp") if a in self.mesh.axes()):
             # (the ranks of a cp group, and the stages of a pipeline, read the same rows)
             self.checkpointer.save_dataloader(self.prefetcher, step, self.mesh.coordinate(self.data_axis))
+        self._unmarked_step = step
+        if not self.checkpointer.background:
+            self.finish_checkpoint()
+
+    def finish_checkpoint(self) -> None:
+        """Mark the last written step complete once EVERY rank's files are on disk.  Synchronous writes: right after
+        them.  ``checkpointing.async``: the files are written by a worker thread from host snapshots taken inside
+        ``checkpoint()`` while training continues, and this runs before the next checkpoint and when training ends;
+        a run that dies in between leaves a step without a marker, which does not exist for ``resume``."""
+        if self._unmarked_step is None:
+            return
+        step, self._unmarked_step = self._unmarked_step, None
+        self.checkpointer.wait()
         barrier()
         if self.rank == 0:
             self.checkpointer.mark_complete(step)
@@ -768,6 +784,7 @@ class Trainer:
                     break
             if self.rank == 0 and self.on_gpu:
                 print(f"peak cuda mem: {torch.cuda.max_memory_allocated() / 2**30:.2f} GiB")
+            self.finish_checkpoint()
         finally:
             if self.wandb_run is not None:
                 self.wandb_run.finish()
